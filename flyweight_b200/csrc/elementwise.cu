@@ -1,0 +1,151 @@
+// Embedding gather, RMSNorm (with the residual sum folded in), SiLU-gate product
+// and dtype casts.  All arithmetic is fp32; T only names the storage type.
+#include "common.cuh"
+
+using namespace fwb;
+
+// ------------------------------------------------------------------ embedding
+// out[t][:] = table[ids[t]][:] widened to fp32.  An id outside [0, V) writes
+// zeros and raises *bad (the host refuses such ids before upload; this is the
+// second fence).
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int T, int H, int V, int* bad) {
+    const int t = blockIdx.y;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0 && blockIdx.x == 0 && bad) atomicExch(bad, 1);
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < H; c += gridDim.x * blockDim.x)
+        out[(size_t)t * H + c] = ok ? to_f32<TW>(table[(size_t)id * H + c]) : 0.0f;
+}
+
+FWB_API int fwb_embed(const void* table, int table_bf16, const int* ids, float* out, int T, int H,
+                      int V, int* bad, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!table || !ids || !out || H <= 0 || V <= 0 || T > 65535) return FWB_BAD_ARGUMENT;
+    dim3 grid((H + 255) / 256 > 64 ? 64 : (H + 255) / 256, T);
+    if (table_bf16)
+        embed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+            (const __nv_bfloat16*)table, ids, out, T, H, V, bad);
+    else
+        embed_kernel<float><<<grid, 256, 0, stream>>>((const float*)table, ids, out, T, H, V, bad);
+    return fwb_launch_status();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// For output row r (source row s = rows ? rows[r] : r):
+//   v = x[s] + delta[s]     (the residual sum, fp32; without `rows` it is stored back to x)
+//   out[r] = (v * rsqrt(mean(v^2) + eps)) * w
+// With `rows` the launch gathers: x is left as it is (a row may be asked for twice).
+// One block per row; the sum of squares is reduced in an order fixed by the block
+// size, so a row's result does not depend on which other rows are in the batch.
+template <typename TO>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                               const float* __restrict__ w, TO* __restrict__ out,
+                               const int* __restrict__ rows, int H, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + s * H;
+    const float* dr = delta ? delta + s * H : nullptr;
+    const bool store = dr && !rows;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (dr) v += dr[c];
+        if (store) xr[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)r * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (dr && !store) v += dr[c];
+        orow[c] = from_f32<TO>((v * inv) * w[c]);
+    }
+}
+
+FWB_API int fwb_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_bf16,
+                        const int* rows, int R, int H, float eps, cudaStream_t stream) {
+    if (R <= 0) return FWB_OK;
+    if (!x || !w || !out || H <= 0) return FWB_BAD_ARGUMENT;
+    const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+    if (out_bf16)
+        rmsnorm_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>(x, delta, w, (__nv_bfloat16*)out,
+                                                                rows, H, eps);
+    else
+        rmsnorm_kernel<float><<<R, threads, 0, stream>>>(x, delta, w, (float*)out, rows, H, eps);
+    return fwb_launch_status();
+}
+
+// x += delta (fp32), for a residual that no norm follows.
+__global__ void add_kernel(float* __restrict__ x, const float* __restrict__ delta, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        x[i] += delta[i];
+}
+
+FWB_API int fwb_add(float* x, const float* delta, long long n, cudaStream_t stream) {
+    if (n <= 0) return FWB_OK;
+    if (!x || !delta) return FWB_BAD_ARGUMENT;
+    const int blocks = (int)((n + 255) / 256 > 4096 ? 4096 : (n + 255) / 256);
+    add_kernel<<<blocks, 256, 0, stream>>>(x, delta, (size_t)n);
+    return fwb_launch_status();
+}
+
+// ------------------------------------------------------------------ SiLU gate
+// gu is [T][2F] with the gate in columns [0,F) and the up projection in [F,2F);
+// out[t][f] = silu(gate) * up.
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int F) {
+    const size_t n = (size_t)T * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / F, f = i - t * F;
+        const float g = to_f32<TI>(gu[t * 2 * F + f]);
+        const float u = to_f32<TI>(gu[t * 2 * F + F + f]);
+        out[i] = from_f32<TO>(silu_f32(g) * u);
+    }
+}
+
+FWB_API int fwb_silu_mul(const void* gu, int in_bf16, void* out, int out_bf16, int T, int F,
+                         cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!gu || !out || F <= 0) return FWB_BAD_ARGUMENT;
+    const size_t n = (size_t)T * F;
+    const int blocks = (int)((n + 255) / 256 > 8192 ? 8192 : (n + 255) / 256);
+    if (in_bf16 && out_bf16)
+        silu_mul_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F);
+    else if (!in_bf16 && out_bf16)
+        silu_mul_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            (const float*)gu, (__nv_bfloat16*)out, T, F);
+    else if (!in_bf16 && !out_bf16)
+        silu_mul_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, T, F);
+    else
+        return FWB_UNSUPPORTED;
+    return fwb_launch_status();
+}
+
+// ------------------------------------------------------------------ casts
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(to_f32<TI>(in[i]));
+}
+
+FWB_API int fwb_cast(const void* in, int in_bf16, void* out, int out_bf16, long long n,
+                     cudaStream_t stream) {
+    if (n <= 0) return FWB_OK;
+    if (!in || !out || in_bf16 == out_bf16) return FWB_BAD_ARGUMENT;
+    const int blocks = (int)((n + 255) / 256 > 8192 ? 8192 : (n + 255) / 256);
+    if (in_bf16)
+        cast_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in,
+                                                                       (float*)out, (size_t)n);
+    else
+        cast_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)in,
+                                                                       (__nv_bfloat16*)out, (size_t)n);
+    return fwb_launch_status();
+}

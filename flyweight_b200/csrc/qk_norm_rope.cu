@@ -1,0 +1,124 @@
+// Per-head RMSNorm of q and k, rotary position encoding from a table, and the write
+// of k and v into the paged cache, in one pass over the fused q|k|v projection.
+//
+//   qkv[t] = [ q: nh*hd | k: nkv*hd | v: nkv*hd ]
+//   q^ = rope(rmsnorm_hd(q_head) * wq),  k^ = rope(rmsnorm_hd(k_head) * wk),  v unchanged
+//   rope (half-split over the first `rot` channels of a head): pair (i, i+rot/2),
+//       out[i] = a*cos - b*sin,  out[i+rot/2] = b*cos + a*sin,  (cos,sin) = table[pos][i]
+//   K[page][kvh][off][:] = k^,  V[page][kvh][off][:] = v   with page = block_table[seg][pos/P],
+//                                                          off = pos % P
+// Norm, angle lookup and rotation are fp32; only the stores round to the cache type.
+// With nkv_in == 0 the launch handles queries only (a layer that reads another
+// layer's cache writes none of its own).
+#include "common.cuh"
+
+using namespace fwb;
+
+namespace {
+
+constexpr int MAX_HD = 512;
+constexpr int WARPS = 4;
+
+template <typename TI, typename TQ, typename TC>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
+                    const float* __restrict__ wk, const float2* __restrict__ table,
+                    const int* __restrict__ positions, const int* __restrict__ tok_seg,
+                    const int* __restrict__ block_table, int max_pages, int page_size,
+                    TQ* __restrict__ q_out, TC* __restrict__ k_pool, TC* __restrict__ v_pool, int nh,
+                    int nkv, int hd, int rot, float eps, int use_norm) {
+    extern __shared__ float smem[];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* buf = smem + warp * hd;
+    const int pos = positions[t];
+    const int row_width = (nh + 2 * nkv) * hd;
+    const TI* row = qkv + (size_t)t * row_width;
+    const float2* cs = table + (size_t)pos * (rot / 2);
+    size_t cache_base = 0;
+    if (nkv > 0) {
+        const int page = block_table[(size_t)tok_seg[t] * max_pages + pos / page_size];
+        cache_base = ((size_t)page * nkv) * page_size * hd + (size_t)(pos % page_size) * hd;
+    }
+    const int heads = nh + 2 * nkv;
+    for (int h = warp; h < heads; h += WARPS) {
+        const TI* src = row + (size_t)h * hd;
+        if (h >= nh + nkv) {  // v: copy
+            const int kvh = h - nh - nkv;
+            TC* dst = v_pool + cache_base + (size_t)kvh * page_size * hd;
+            for (int i = lane; i < hd; i += 32) dst[i] = from_f32<TC>(to_f32<TI>(src[i]));
+            continue;
+        }
+        const bool is_q = h < nh;
+        const float* w = is_q ? wq : wk;
+        float ss = 0.0f;
+        for (int i = lane; i < hd; i += 32) {
+            const float v = to_f32<TI>(src[i]);
+            buf[i] = v;
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        const float inv = use_norm ? rsqrtf(ss / (float)hd + eps) : 1.0f;
+        __syncwarp();
+        const int half = rot / 2;
+        if (is_q) {
+            TQ* dst = q_out + ((size_t)t * nh + h) * hd;
+            for (int i = lane; i < half; i += 32) {
+                const float a = use_norm ? (buf[i] * inv) * w[i] : buf[i];
+                const float b = use_norm ? (buf[i + half] * inv) * w[i + half] : buf[i + half];
+                const float2 c = cs[i];
+                dst[i] = from_f32<TQ>(a * c.x - b * c.y);
+                dst[i + half] = from_f32<TQ>(b * c.x + a * c.y);
+            }
+            for (int i = rot + lane; i < hd; i += 32)
+                dst[i] = from_f32<TQ>(use_norm ? (buf[i] * inv) * w[i] : buf[i]);
+        } else {
+            TC* dst = k_pool + cache_base + (size_t)(h - nh) * page_size * hd;
+            for (int i = lane; i < half; i += 32) {
+                const float a = use_norm ? (buf[i] * inv) * w[i] : buf[i];
+                const float b = use_norm ? (buf[i + half] * inv) * w[i + half] : buf[i + half];
+                const float2 c = cs[i];
+                dst[i] = from_f32<TC>(a * c.x - b * c.y);
+                dst[i + half] = from_f32<TC>(b * c.x + a * c.y);
+            }
+            for (int i = rot + lane; i < hd; i += 32)
+                dst[i] = from_f32<TC>(use_norm ? (buf[i] * inv) * w[i] : buf[i]);
+        }
+        __syncwarp();
+    }
+}
+
+}  // namespace
+
+// qkv: [T][(nh+2*nkv)*hd] fp32 or bf16.  wq, wk: [hd] fp32 (ignored when use_norm == 0).
+// table: [max_pos][rot/2] float2 (cos, sin).  positions, tok_seg: [T].
+// block_table: [S][max_pages] page ids.  q_out: [T][nh*hd].  k_pool, v_pool:
+// [pages][nkv][page_size][hd].  Dtype flags: 0 fp32, 1 bf16.
+FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, const float* wk,
+                             const void* table, const int* positions, const int* tok_seg,
+                             const int* block_table, int max_pages, int page_size, void* q_out,
+                             int q_bf16, void* k_pool, void* v_pool, int cache_bf16, int T, int nh,
+                             int nkv, int hd, int rot, float eps, int use_norm,
+                             cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!qkv || !table || !positions || !q_out || nh <= 0 || nkv < 0) return FWB_BAD_ARGUMENT;
+    if (nkv > 0 && (!tok_seg || !block_table || !k_pool || !v_pool || page_size <= 0 || max_pages <= 0))
+        return FWB_BAD_ARGUMENT;
+    if (use_norm && (!wq || (nkv > 0 && !wk))) return FWB_BAD_ARGUMENT;
+    if (hd <= 0 || hd > MAX_HD || (hd & 1) || rot < 0 || rot > hd || (rot & 1)) return FWB_UNSUPPORTED;
+    const size_t smem = (size_t)WARPS * hd * sizeof(float);
+    using bf = __nv_bfloat16;
+#define FWB_QK(TI, TQ, TC)                                                                        \
+    qk_norm_rope_kernel<TI, TQ, TC><<<T, WARPS * 32, smem, stream>>>(                             \
+        (const TI*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table, max_pages, \
+        page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm)
+    const int key = (in_bf16 ? 4 : 0) | (q_bf16 ? 2 : 0) | (cache_bf16 ? 1 : 0);
+    switch (key) {
+        case 0: FWB_QK(float, float, float); break;
+        case 3: FWB_QK(float, bf, bf); break;
+        case 7: FWB_QK(bf, bf, bf); break;
+        default: return FWB_UNSUPPORTED;
+    }
+#undef FWB_QK
+    return fwb_launch_status();
+}

@@ -1,0 +1,103 @@
+// Gated short convolution over a ragged batch of segments, with the per-request
+// rolling state read and advanced in the same launch.
+//
+//   p[t] = [ B | C | x ]  (3*H columns, produced by in_proj)
+//   u    = B * x                                  (per token, per channel)
+//   y[c] = bias[c] + sum_{k<L} taps[c][k] * u[j-(L-1)+k]     (j = index inside the segment;
+//                                                  u at negative j comes from the state)
+//   z    = C * y
+//   state[slot][c][0..L-2] <- the last L-1 values of (state ++ u[0..n-1]), oldest first
+//
+// The filter is a FIR, so tokens are independent once the first L-1 of a segment have
+// the state.  The launch has two kinds of blocks: "body" threads own one (token,
+// channel) with j >= L-1 and never touch the state; "head" threads own one (segment,
+// channel): they read the old state once, produce the first min(n, L-1) outputs and
+// write the new state.  Nothing else reads or writes that state entry, so there is no
+// ordering problem inside the launch, however the batch was cut.
+#include "common.cuh"
+
+using namespace fwb;
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+
+template <typename TP, typename TZ>
+__global__ void shortconv_kernel(const TP* __restrict__ p, const float* __restrict__ taps,
+                                 const float* __restrict__ bias, float* __restrict__ state,
+                                 const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                                 const int* __restrict__ tok_seg, TZ* __restrict__ z, int T, int S,
+                                 int H, int L, int body_blocks) {
+    const int ld = 3 * H;
+    if ((int)blockIdx.x < body_blocks) {
+        const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+        if (idx >= (size_t)T * H) return;
+        const int t = (int)(idx / H), c = (int)(idx - (size_t)t * H);
+        const int j = t - seg_start[tok_seg[t]];
+        if (j < L - 1) return;  // a head thread produces this one
+        float y = bias ? bias[c] : 0.0f;
+        for (int k = 0; k < L; ++k) {
+            const TP* row = p + (size_t)(t - (L - 1) + k) * ld;
+            y = fmaf(taps[c * L + k], to_f32<TP>(row[c]) * to_f32<TP>(row[2 * H + c]), y);
+        }
+        z[idx] = from_f32<TZ>(to_f32<TP>(p[(size_t)t * ld + H + c]) * y);
+        return;
+    }
+    const size_t idx = (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)S * H) return;
+    const int s = (int)(idx / H), c = (int)(idx - (size_t)s * H);
+    const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
+    float* st = state + ((size_t)seg_slot[s] * H + c) * (L - 1);
+    // hist[0..L-2] = state (oldest first), hist[L-1..] = u of the first tokens.
+    float hist[2 * MAX_TAPS];
+    float w[MAX_TAPS];
+    for (int k = 0; k < L; ++k) w[k] = taps[c * L + k];
+    for (int k = 0; k < L - 1; ++k) hist[k] = st[k];
+    const int first = n < L - 1 ? n : L - 1;
+    for (int j = 0; j < first; ++j) {
+        const TP* row = p + (size_t)(t0 + j) * ld;
+        hist[L - 1 + j] = to_f32<TP>(row[c]) * to_f32<TP>(row[2 * H + c]);
+        float y = bias ? bias[c] : 0.0f;
+        for (int k = 0; k < L; ++k) y = fmaf(w[k], hist[j + k], y);
+        z[(size_t)(t0 + j) * H + c] = from_f32<TZ>(to_f32<TP>(row[H + c]) * y);
+    }
+    if (n >= L - 1) {
+        for (int k = 0; k < L - 1; ++k) {
+            const TP* row = p + (size_t)(t0 + n - (L - 1) + k) * ld;
+            st[k] = to_f32<TP>(row[c]) * to_f32<TP>(row[2 * H + c]);
+        }
+    } else {
+        // shorter than the state: shift by n, the new values are hist[L-1 .. L-1+n)
+        for (int k = 0; k < L - 1; ++k) st[k] = hist[k + n];
+    }
+}
+
+}  // namespace
+
+// p: [T][3H] (fp32 or bf16); taps: [H][L] fp32; bias: [H] fp32 or null;
+// state: [num_slots][H][L-1] fp32; seg_start: [S+1]; seg_slot: [S]; tok_seg: [T];
+// z: [T][H] (fp32 or bf16).
+FWB_API int fwb_shortconv(const void* p, int p_bf16, const float* taps, const float* bias,
+                          float* state, const int* seg_start, const int* seg_slot,
+                          const int* tok_seg, void* z, int z_bf16, int T, int S, int H, int L,
+                          cudaStream_t stream) {
+    if (T <= 0 || S <= 0) return FWB_OK;
+    if (!p || !taps || !state || !seg_start || !seg_slot || !tok_seg || !z || H <= 0)
+        return FWB_BAD_ARGUMENT;
+    if (L < 2 || L > MAX_TAPS) return FWB_UNSUPPORTED;
+    const int threads = 128;
+    const int body_blocks = (int)(((size_t)T * H + threads - 1) / threads);
+    const int head_blocks = (int)(((size_t)S * H + threads - 1) / threads);
+    const int blocks = body_blocks + head_blocks;
+    using bf = __nv_bfloat16;
+#define FWB_CONV(TP, TZ)                                                                          \
+    shortconv_kernel<TP, TZ><<<blocks, threads, 0, stream>>>(                                     \
+        (const TP*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (TZ*)z, T, S, H, L,        \
+        body_blocks)
+    if (p_bf16 && z_bf16) FWB_CONV(bf, bf);
+    else if (!p_bf16 && z_bf16) FWB_CONV(float, bf);
+    else if (!p_bf16 && !z_bf16) FWB_CONV(float, float);
+    else return FWB_UNSUPPORTED;
+#undef FWB_CONV
+    return fwb_launch_status();
+}

@@ -1,0 +1,128 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step`` takes entries ``(request, tokens, want)``: a request's next tokens
+(a portion of its prompt, cut anywhere, or one decoded token) and the places among them
+whose logits are wanted.  It runs only those tokens, as one batch, from the cache that
+earlier steps left, writes their keys, values and state into the cache, and returns the
+logits at the wanted places, ``[wanted][vocab]`` fp32, in the order of the entries.
+
+flyweight has two forwards instead, one token of one sequence
+(native/src/v2_runtime.cpp:27525) or a chunk of one sequence
+(native/src/v2_mtp_verifier.inc:296), and interleaves requests between forwards
+(native/src/v2_runtime.cpp:33695-33972); here requests share every kernel launch.
+"""
+from __future__ import annotations
+
+from typing import Hashable, List, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import PAGE_SIZE, CacheManager, OutOfPages
+from ..kernels.lib import require_cuda
+from .batch import Segment, StepBatch, StepContext
+
+Entry = Tuple[Hashable, Sequence[int], Sequence[int]]
+
+
+class StepError(ValueError):
+    """An entry the step function refuses (bad token id, empty portion, over-long request)."""
+
+
+class ModelRunner:
+    def __init__(self, model, num_pages: int, num_slots: int, max_model_len: int,
+                 max_batched_tokens: int = 8192):
+        require_cuda()
+        self.model = model
+        self.precision = model.precision
+        self.device = model.device
+        self.max_model_len = int(max_model_len)
+        self.max_batched_tokens = int(max_batched_tokens)
+        if self.max_model_len > model.spec.max_positions:
+            raise StepError(f"max_model_len {self.max_model_len} exceeds the model's "
+                            f"{model.spec.max_positions} positions")
+        model.prepare(self.max_model_len)
+        self.cache = CacheManager(model.state_specs(), num_pages, num_slots,
+                                  cache_dtype=self.precision.cache_dtype, device=self.device)
+        self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.steps = 0
+        self.tokens_run = 0
+        self.h2d_bytes = 0
+
+    # ------------------------------------------------------------------ checks
+    def _check_entries(self, entries: Sequence[Entry]) -> None:
+        vocab = self.model.spec.vocab_size
+        seen = set()
+        total = 0
+        for request, tokens, want in entries:
+            if request in seen:
+                raise StepError(f"request {request!r} appears twice in one step")
+            seen.add(request)
+            if len(tokens) == 0:
+                raise StepError(f"request {request!r} brings no tokens")
+            for token in tokens:
+                if not 0 <= int(token) < vocab:       # native/src/v2_runtime.cpp:27530
+                    raise StepError(f"token id {token} of request {request!r} is outside "
+                                    f"[0, {vocab})")
+            for place in want:
+                if not 0 <= int(place) < len(tokens):
+                    raise StepError(f"request {request!r} wants logits at place {place} of "
+                                    f"{len(tokens)} tokens")
+            have = self.cache.length(request) if self.cache.has(request) else 0
+            if have + len(tokens) > self.max_model_len:
+                raise StepError(f"request {request!r} would reach {have + len(tokens)} tokens, "
+                                f"beyond max_model_len {self.max_model_len}")
+            total += len(tokens)
+        if total > self.max_batched_tokens:
+            raise StepError(f"step of {total} tokens exceeds max_batched_tokens "
+                            f"{self.max_batched_tokens}")
+
+    def pages_short(self, entries: Sequence[Entry]) -> int:
+        """Pages lacking for this step over all groups (0: it fits).  Pages that a window
+        has passed are given back first."""
+        cache = self.cache
+        needs = [0] * len(cache.groups)
+        for request, tokens, _ in entries:
+            have = 0
+            if cache.has(request):
+                cache.release_passed(request)
+                have = cache.length(request)
+            for g, need in enumerate(cache.pages_needed(request, have + len(tokens))):
+                needs[g] += need
+        return sum(max(0, need - group.pool.n_free) for need, group in zip(needs, cache.groups))
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+        entries = [(r, [int(t) for t in toks], [int(w) for w in want]) for r, toks, want in entries]
+        vocab = self.model.spec.vocab_size
+        if not entries:
+            return torch.empty((0, vocab), dtype=torch.float32, device=self.device)
+        self._check_entries(entries)
+        new = [r for r, _, _ in entries if not self.cache.has(r)]
+        if len(new) > self.cache.free_slots:
+            from ..cache.manager import OutOfSlots
+            raise OutOfSlots(f"{len(new)} new requests but {self.cache.free_slots} free state slots")
+        short = self.pages_short(entries)
+        if short:
+            raise OutOfPages(f"this step needs {short} more cache pages than are free")
+        segments: List[Segment] = []
+        for request, tokens, want in entries:
+            if not self.cache.has(request):
+                self.cache.admit(request)
+            pos0 = self.cache.length(request)
+            self.cache.extend(request, pos0 + len(tokens))
+            segments.append(Segment(request, self.cache.slot(request), pos0, tokens, want))
+        requests = [seg.request for seg in segments]
+        width = self.cache.max_table_len(requests)
+        tables = [self.cache.block_table(g, requests, width) for g in range(len(self.cache.groups))]
+        batch = StepBatch(segments, tables, self.device)
+        ctx = StepContext(batch, self.precision, self.device, self.bad_token_flag)
+        logits = self.model.forward(ctx, self.cache.layer_caches)
+        self.steps += 1
+        self.tokens_run += batch.n_tokens
+        self.h2d_bytes += batch.h2d_bytes
+        return logits
+
+    def finish(self, request: Hashable) -> None:
+        """The request is over: its pages and its state slot go back to the pools."""
+        if self.cache.has(request):
+            self.cache.release(request)

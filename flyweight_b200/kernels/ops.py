@@ -1,0 +1,217 @@
+"""Python faces of the CUDA kernels: argument checks, output allocation, launch.
+
+Each function is one kernel (or one dispatch between kernels of the same operation).
+Shapes are checked here on the host before anything is launched.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import lib
+from .lib import KernelError, c_float, c_longlong, check_tensor, is_bf16, ptr, stream
+
+
+def _i32(name: str, tensor: torch.Tensor, count: Optional[int] = None) -> None:
+    check_tensor(name, tensor, torch.int32)
+    if count is not None and tensor.numel() < count:
+        raise KernelError(f"{name} holds {tensor.numel()} entries, {count} are needed")
+
+
+# ------------------------------------------------------------------ embedding
+def embed(table: torch.Tensor, ids: torch.Tensor, bad_flag: Optional[torch.Tensor] = None
+          ) -> torch.Tensor:
+    """Rows ``ids`` of ``table`` ([V][H], fp32 or bf16) widened to fp32: [T][H]."""
+    check_tensor("embedding table", table)
+    _i32("token ids", ids)
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    lib.call("fwb_embed", ptr(table), is_bf16(table), ptr(ids), ptr(out), T, H, V, ptr(bad_flag),
+             stream())
+    return out
+
+
+# ------------------------------------------------------------------ norms
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None
+            ) -> torch.Tensor:
+    """``(x * rsqrt(mean(x^2) + eps)) * weight`` per row of the fp32 residual ``x``.
+
+    With ``delta`` the residual sum ``x += delta`` happens first, in place and in fp32.
+    With ``rows`` (int32 indices) only those rows are normalised, into a compact output.
+    """
+    check_tensor("residual", x, torch.float32)
+    H = x.shape[-1]
+    check_tensor("norm weight", weight, torch.float32, (H,))
+    if delta is not None:
+        check_tensor("delta", delta, torch.float32, x.shape)
+    if rows is not None:
+        _i32("row indices", rows)
+        R = rows.numel()
+    else:
+        R = x.numel() // H
+    out = torch.empty((R, H), dtype=out_dtype, device=x.device)
+    lib.call("fwb_rmsnorm", ptr(x), ptr(delta), ptr(weight), ptr(out), is_bf16(out), ptr(rows), R, H,
+             c_float(eps), stream())
+    return out
+
+
+def add_(x: torch.Tensor, delta: torch.Tensor) -> None:
+    check_tensor("residual", x, torch.float32)
+    check_tensor("delta", delta, torch.float32, x.shape)
+    lib.call("fwb_add", ptr(x), ptr(delta), c_longlong(x.numel()), stream())
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    check_tensor("cast input", x)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    lib.call("fwb_cast", ptr(x), is_bf16(x), ptr(out), is_bf16(out), c_longlong(x.numel()), stream())
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+              addend: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None
+              ) -> torch.Tensor:
+    """``x @ w.T`` with fp32 FMA accumulation (no tensor cores).  x: [M][K], w: [N][K]."""
+    check_tensor("gemm input", x)
+    check_tensor("gemm weight", w)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: input has {K} columns, weight has {K2}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    else:
+        check_tensor("gemm output", out, out_dtype, (M, N))
+    if addend is not None:
+        check_tensor("gemm addend", addend, torch.float32, (M, N))
+    lib.call("fwb_gemm_simt", ptr(x), is_bf16(x), ptr(w), is_bf16(w), ptr(out), is_bf16(out),
+             ptr(addend), M, N, K, K, N, stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+           addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The matrix product the model uses: picks the kernel for the dtypes and sizes.
+
+    float32 weights always take the SIMT kernel (true 32-bit).  bfloat16 weights take
+    the tensor-core kernel when it accepts the shape, else the SIMT kernel.
+    """
+    if w.dtype == torch.float32:
+        if x.dtype != torch.float32:
+            x = cast(x, torch.float32)
+        return gemm_simt(x, w, out_dtype, addend)
+    if x.dtype != torch.bfloat16:
+        x = cast(x, torch.bfloat16)
+    from . import tensorcore
+    if tensorcore.accepts(x, w, out_dtype, addend):
+        return tensorcore.gemm(x, w, out_dtype, addend)
+    return gemm_simt(x, w, out_dtype, addend)
+
+
+def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up`` = [T][gate(F) | up(F)]."""
+    check_tensor("gate|up", gate_up)
+    T, F2 = gate_up.shape
+    if F2 % 2:
+        raise KernelError("gate|up needs an even number of columns")
+    out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
+    lib.call("fwb_silu_mul", ptr(gate_up), is_bf16(gate_up), ptr(out), is_bf16(out), T, F2 // 2,
+             stream())
+    return out
+
+
+# ------------------------------------------------------------------ gated short convolution
+def shortconv(p: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor],
+              state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor,
+              tok_seg: torch.Tensor, n_segments: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """p: [T][B|C|x]; taps: [H][L] fp32; state: [slots][H][L-1] fp32 (read and advanced)."""
+    check_tensor("conv input", p)
+    T, H3 = p.shape
+    H = H3 // 3
+    if H * 3 != H3:
+        raise KernelError("conv input needs 3*H columns")
+    L = taps.shape[1]
+    check_tensor("conv taps", taps, torch.float32, (H, L))
+    if bias is not None:
+        check_tensor("conv bias", bias, torch.float32, (H,))
+    check_tensor("conv state", state, torch.float32)
+    if tuple(state.shape[1:]) != (H, L - 1):
+        raise KernelError(f"conv state must be [slots][{H}][{L - 1}], got {tuple(state.shape)}")
+    _i32("seg_start", seg_start, n_segments + 1)
+    _i32("seg_slot", seg_slot, n_segments)
+    _i32("tok_seg", tok_seg, T)
+    out = torch.empty((T, H), dtype=out_dtype, device=p.device)
+    lib.call("fwb_shortconv", ptr(p), is_bf16(p), ptr(taps), ptr(bias), ptr(state), ptr(seg_start),
+             ptr(seg_slot), ptr(tok_seg), ptr(out), is_bf16(out), T, n_segments, H, L, stream())
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def qk_norm_rope(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+                 table: torch.Tensor, positions: torch.Tensor, tok_seg: torch.Tensor,
+                 block_table: Optional[torch.Tensor], k_pool: Optional[torch.Tensor],
+                 v_pool: Optional[torch.Tensor], n_heads: int, n_kv_in: int, head_dim: int,
+                 rotary_dim: int, eps: float, q_dtype: torch.dtype) -> torch.Tensor:
+    """Per-head RMSNorm + RoPE of q and k, k/v written to their pages; returns q [T][nh*hd].
+
+    ``n_kv_in`` is the number of KV heads present in ``qkv`` (0: queries only).
+    ``table`` is [max_pos][rotary_dim/2][2] fp32 (cos, sin)."""
+    check_tensor("qkv", qkv)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_in) * head_dim:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected "
+                          f"{(n_heads + 2 * n_kv_in) * head_dim}")
+    check_tensor("rope table", table, torch.float32)
+    if table.dim() != 3 or table.shape[1] != rotary_dim // 2 or table.shape[2] != 2:
+        raise KernelError("rope table must be [positions][rotary_dim/2][2]")
+    use_norm = 1 if q_norm is not None else 0
+    if use_norm:
+        check_tensor("q norm weight", q_norm, torch.float32, (head_dim,))
+        if n_kv_in:
+            check_tensor("k norm weight", k_norm, torch.float32, (head_dim,))
+    _i32("positions", positions, T)
+    _i32("tok_seg", tok_seg, T)
+    max_pages = page_size = 0
+    cache_bf16 = is_bf16(qkv) if n_kv_in == 0 else 0
+    if n_kv_in:
+        _i32("block table", block_table)
+        check_tensor("k pool", k_pool)
+        check_tensor("v pool", v_pool, k_pool.dtype, k_pool.shape)
+        if k_pool.dim() != 4 or k_pool.shape[1] != n_kv_in or k_pool.shape[3] != head_dim:
+            raise KernelError("cache pools must be [pages][kv_heads][page_size][head_dim]")
+        max_pages, page_size = block_table.shape[1], k_pool.shape[2]
+        cache_bf16 = is_bf16(k_pool)
+    q_out = torch.empty((T, n_heads * head_dim), dtype=q_dtype, device=qkv.device)
+    if n_kv_in == 0:
+        cache_bf16 = is_bf16(q_out)
+    lib.call("fwb_qk_norm_rope", ptr(qkv), is_bf16(qkv), ptr(q_norm), ptr(k_norm), ptr(table),
+             ptr(positions), ptr(tok_seg), ptr(block_table), max_pages, page_size, ptr(q_out),
+             is_bf16(q_out), ptr(k_pool), ptr(v_pool), cache_bf16, T, n_heads, n_kv_in, head_dim,
+             rotary_dim, c_float(eps), use_norm, stream())
+    return q_out
+
+
+def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   positions: torch.Tensor, tok_seg: torch.Tensor, block_table: torch.Tensor,
+                   n_heads: int, window: int, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """Causal GQA over the paged cache, SIMT fp32 arithmetic.  q: [T][nh*hd]."""
+    check_tensor("q", q)
+    check_tensor("k pool", k_pool)
+    check_tensor("v pool", v_pool, k_pool.dtype, k_pool.shape)
+    T = q.shape[0]
+    _, n_kv, page_size, head_dim = k_pool.shape
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError(f"q has {q.shape[1]} columns, expected {n_heads * head_dim}")
+    _i32("positions", positions, T)
+    _i32("tok_seg", tok_seg, T)
+    _i32("block table", block_table)
+    out = torch.empty((T, n_heads * head_dim), dtype=out_dtype, device=q.device)
+    lib.call("fwb_attention_simt", ptr(q), is_bf16(q), ptr(k_pool), ptr(v_pool), is_bf16(k_pool),
+             ptr(positions), ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size,
+             ptr(out), is_bf16(out), T, n_heads, n_kv, head_dim, window, c_float(scale), stream())
+    return out

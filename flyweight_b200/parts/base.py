@@ -1,0 +1,205 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part is built from a ``PartSpec`` alone: its sizes and constants are parameters,
+its tensors are named by the spec, and it never learns which model it is in.  There
+is one registry per kind of part; an architecture (or a test) adds an implementation
+with the matching ``register_*`` decorator and names it in its ``PartSpec.kind``.
+
+Interfaces
+----------
+``Norm.forward(ctx, x, delta=None, rows=None)``
+    x: fp32 residual [T][H].  Adds ``delta`` into x first when given (the residual
+    sum, fp32), returns the normalised rows in ``ctx.precision.act_dtype``.
+``Mixer.state_spec()`` -> ``PagedKV`` | ``FixedState`` | ``None``
+    what the cache manager must keep for one execution of this mixer.
+``Mixer.forward(ctx, h, cache)`` -> fp32 [T][H]
+    h: normalised input; cache: the ``LayerCache`` the manager made for this
+    execution (or for the execution it shares with).  Returns the residual delta.
+``FeedForward.forward(ctx, h)`` -> fp32 [T][H]
+``PositionEncoding.table(n_positions, device)`` -> what its kernel reads.
+``Arrangement.forward(ctx, x, pending, cache)`` -> (x, pending)
+    wires norms, mixer and feed-forward around the residual stream; ``pending`` is
+    a delta not yet added to x, handed to the next norm so that the sum and the
+    norm are one kernel.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
+
+import torch
+
+from ..config.spec import LayerSpec, PartSpec
+from ..weights.loader import TensorDecl
+
+
+# ------------------------------------------------------------------ precision
+@dataclass(frozen=True)
+class Precision:
+    """``float32``: everything in true 32-bit.  ``bfloat16``: the serving precision --
+    bfloat16 matrices, activations and cache, with the residual stream, norms,
+    softmax, rotation and conv state in fp32."""
+    name: str
+
+    def __post_init__(self):
+        if self.name not in ("float32", "bfloat16"):
+            raise ValueError(f"dtype must be float32 or bfloat16, got {self.name!r}")
+
+    @property
+    def act_dtype(self) -> torch.dtype:
+        return torch.float32 if self.name == "float32" else torch.bfloat16
+
+    @property
+    def cache_dtype(self) -> torch.dtype:
+        return self.act_dtype
+
+    def matrix(self, tensor: torch.Tensor, device) -> torch.Tensor:
+        """A weight matrix on the device.  float32 mode widens (exactly); bfloat16 mode
+        keeps the stored dtype (a matrix stored in 32-bit stays so and runs the 32-bit
+        product)."""
+        tensor = tensor.to(device)
+        if self.name == "float32" and tensor.dtype != torch.float32:
+            tensor = tensor.to(torch.float32)
+        return tensor.contiguous()
+
+    @staticmethod
+    def vector(tensor: torch.Tensor, device) -> torch.Tensor:
+        """Norm weights, conv taps, biases: kernels read them as fp32 (exact widening)."""
+        return tensor.to(device=device, dtype=torch.float32).contiguous()
+
+
+# ------------------------------------------------------------------ cache needs
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values that grow with the sequence.  ``window`` > 0: only the last
+    ``window`` positions are ever read again, older pages may be given back."""
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class FixedState:
+    """Per-request state of fixed size (fp32), zero when a request starts."""
+    shape: Tuple[int, ...]
+
+
+# ------------------------------------------------------------------ part interfaces
+class Part:
+    kind: str = ""
+
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+        self.params = dict(spec.params)
+        self.names = dict(spec.tensors)
+
+    def declare(self) -> Dict[str, TensorDecl]:
+        """Full tensor name -> declaration, for every tensor this part binds."""
+        return {}
+
+    def bind(self, get: Callable[[str], torch.Tensor], precision: Precision, device) -> None:
+        """Fetch the declared tensors (``get(full_name)`` returns the stored tensor)."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of device weights a step reads (for roofline accounting)."""
+        return 0
+
+
+class Norm(Part):
+    def forward(self, ctx, x, delta=None, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def table(self, n_positions: int, device):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def state_spec(self):
+        return None
+
+    def prepare(self, max_positions: int, device) -> None:
+        """Build position tables and the like once the engine's limits are known."""
+
+    def forward(self, ctx, h, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, h):
+        raise NotImplementedError
+
+
+class Arrangement:
+    def __init__(self, layer: LayerSpec):
+        self.layer = layer
+        self.mixer_norm = build_norm(layer.mixer_norm)
+        self.mixer = build_mixer(layer.mixer)
+        self.ffn_norm = build_norm(layer.ffn_norm)
+        self.feed_forward = build_feed_forward(layer.feed_forward)
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+
+    def forward(self, ctx, x, pending, cache):
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------ registries
+_NORMS: Dict[str, type] = {}
+_MIXERS: Dict[str, type] = {}
+_FEED_FORWARDS: Dict[str, type] = {}
+_POSITIONS: Dict[str, type] = {}
+_ARRANGEMENTS: Dict[str, type] = {}
+
+
+def _register(table: Dict[str, type], what: str):
+    def decorator_for(kind: str):
+        def decorator(cls):
+            cls.kind = kind
+            table[kind] = cls
+            return cls
+        return decorator
+    return decorator_for
+
+
+register_norm = _register(_NORMS, "norm")
+register_mixer = _register(_MIXERS, "mixer")
+register_feed_forward = _register(_FEED_FORWARDS, "feed-forward")
+register_position = _register(_POSITIONS, "position encoding")
+register_arrangement = _register(_ARRANGEMENTS, "arrangement")
+
+
+def _build(table: Dict[str, type], what: str, spec: PartSpec):
+    try:
+        cls = table[spec.kind]
+    except KeyError:
+        raise KeyError(f"no {what} registered under {spec.kind!r}; known: "
+                       + ", ".join(sorted(table))) from None
+    return cls(spec)
+
+
+def build_norm(spec: PartSpec) -> Norm:
+    return _build(_NORMS, "norm", spec)
+
+
+def build_mixer(spec: PartSpec) -> Mixer:
+    return _build(_MIXERS, "mixer", spec)
+
+
+def build_feed_forward(spec: PartSpec) -> FeedForward:
+    return _build(_FEED_FORWARDS, "feed-forward", spec)
+
+
+def build_position(spec: PartSpec) -> PositionEncoding:
+    return _build(_POSITIONS, "position encoding", spec)
+
+
+def build_arrangement(layer: LayerSpec) -> Arrangement:
+    try:
+        cls = _ARRANGEMENTS[layer.arrangement]
+    except KeyError:
+        raise KeyError(f"no arrangement registered under {layer.arrangement!r}; known: "
+                       + ", ".join(sorted(_ARRANGEMENTS))) from None
+    return cls(layer)

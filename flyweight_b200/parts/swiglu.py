@@ -1,0 +1,45 @@
+"""Dense SwiGLU feed-forward: down( silu(gate h) * (up h) ), no bias
+(native/src/v2_runtime.cpp:28797-28805; silu with a sign-split sigmoid,
+native/include/flyweight_v2_qwen_kernels.hpp:1217-1222)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import FeedForward, Precision, register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU(FeedForward):
+    """params: hidden_size, ffn_dim.  tensors: gate [F][H], up [F][H], down [H][F]."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.params["hidden_size"])
+        self.ffn_dim = int(self.params["ffn_dim"])
+        self.w_gate_up = self.w_down = None
+
+    def declare(self):
+        n, H, F = self.names, self.hidden, self.ffn_dim
+        return {n["gate"]: TensorDecl((F, H)), n["up"]: TensorDecl((F, H)),
+                n["down"]: TensorDecl((H, F))}
+
+    def bind(self, get, precision: Precision, device):
+        n = self.names
+        gate, up = get(n["gate"]), get(n["up"])
+        if gate.dtype != up.dtype:
+            gate, up = gate.to(torch.float32), up.to(torch.float32)
+        # gate and up as one projection: gate rows first, then up rows
+        self.w_gate_up = precision.matrix(torch.cat([gate, up], dim=0), device)
+        self.w_down = precision.matrix(get(n["down"]), device)
+
+    def weight_bytes(self):
+        return (self.w_gate_up.numel() * self.w_gate_up.element_size()
+                + self.w_down.numel() * self.w_down.element_size())
+
+    def forward(self, ctx, h):
+        act = ctx.precision.act_dtype
+        gate_up = ops.linear(h, self.w_gate_up, act)
+        a = ops.silu_mul(gate_up, act)
+        return ops.linear(a, self.w_down, torch.float32)
