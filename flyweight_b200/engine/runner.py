@@ -17,7 +17,7 @@ from typing import Hashable, List, Sequence, Tuple
 
 import torch
 
-from ..cache.manager import PAGE_SIZE, CacheManager, OutOfPages
+from ..cache.manager import PAGE_SIZE, CacheManager, OutOfPages, OutOfSlots
 from ..kernels.lib import require_cuda
 from .batch import Segment, StepBatch, StepContext
 
@@ -28,29 +28,20 @@ class StepError(ValueError):
     """An entry the step function refuses (bad token id, empty portion, over-long request)."""
 
 
-class ModelRunner:
-    def __init__(self, model, num_pages: int, num_slots: int, max_model_len: int,
-                 max_batched_tokens: int = 8192):
-        require_cuda()
-        self.model = model
-        self.precision = model.precision
-        self.device = model.device
+class StepPlanner:
+    """The host side of a step: checks, admission to the cache, page mapping.  It needs
+    no device, so schedulers and cache logic can be tested against it on the CPU."""
+
+    def __init__(self, cache: CacheManager, vocab_size: int, max_model_len: int,
+                 max_batched_tokens: int):
+        self.cache = cache
+        self.vocab_size = int(vocab_size)
         self.max_model_len = int(max_model_len)
         self.max_batched_tokens = int(max_batched_tokens)
-        if self.max_model_len > model.spec.max_positions:
-            raise StepError(f"max_model_len {self.max_model_len} exceeds the model's "
-                            f"{model.spec.max_positions} positions")
-        model.prepare(self.max_model_len)
-        self.cache = CacheManager(model.state_specs(), num_pages, num_slots,
-                                  cache_dtype=self.precision.cache_dtype, device=self.device)
-        self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.steps = 0
-        self.tokens_run = 0
-        self.h2d_bytes = 0
 
     # ------------------------------------------------------------------ checks
     def _check_entries(self, entries: Sequence[Entry]) -> None:
-        vocab = self.model.spec.vocab_size
+        vocab = self.vocab_size
         seen = set()
         total = 0
         for request, tokens, want in entries:
@@ -90,16 +81,14 @@ class ModelRunner:
                 needs[g] += need
         return sum(max(0, need - group.pool.n_free) for need, group in zip(needs, cache.groups))
 
-    # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+    # ------------------------------------------------------------------ planning
+    def plan(self, entries: Sequence[Entry]) -> List[Segment]:
+        """Check the entries, admit new requests, map their pages; all or nothing: if a
+        slot or a page is lacking, nothing has changed when the error is raised."""
         entries = [(r, [int(t) for t in toks], [int(w) for w in want]) for r, toks, want in entries]
-        vocab = self.model.spec.vocab_size
-        if not entries:
-            return torch.empty((0, vocab), dtype=torch.float32, device=self.device)
         self._check_entries(entries)
         new = [r for r, _, _ in entries if not self.cache.has(r)]
         if len(new) > self.cache.free_slots:
-            from ..cache.manager import OutOfSlots
             raise OutOfSlots(f"{len(new)} new requests but {self.cache.free_slots} free state slots")
         short = self.pages_short(entries)
         if short:
@@ -111,6 +100,37 @@ class ModelRunner:
             pos0 = self.cache.length(request)
             self.cache.extend(request, pos0 + len(tokens))
             segments.append(Segment(request, self.cache.slot(request), pos0, tokens, want))
+        return segments
+
+    def finish(self, request: Hashable) -> None:
+        """The request is over: its pages and its state slot go back to the pools."""
+        if self.cache.has(request):
+            self.cache.release(request)
+
+
+class ModelRunner(StepPlanner):
+    def __init__(self, model, num_pages: int, num_slots: int, max_model_len: int,
+                 max_batched_tokens: int = 8192):
+        require_cuda()
+        self.model = model
+        self.precision = model.precision
+        self.device = model.device
+        if int(max_model_len) > model.spec.max_positions:
+            raise StepError(f"max_model_len {max_model_len} exceeds the model's "
+                            f"{model.spec.max_positions} positions")
+        model.prepare(int(max_model_len))
+        cache = CacheManager(model.state_specs(), num_pages, num_slots,
+                             cache_dtype=self.precision.cache_dtype, device=self.device)
+        super().__init__(cache, model.spec.vocab_size, max_model_len, max_batched_tokens)
+        self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.steps = 0
+        self.tokens_run = 0
+        self.h2d_bytes = 0
+
+    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        segments = self.plan(entries)
         requests = [seg.request for seg in segments]
         width = self.cache.max_table_len(requests)
         tables = [self.cache.block_table(g, requests, width) for g in range(len(self.cache.groups))]
@@ -121,8 +141,3 @@ class ModelRunner:
         self.tokens_run += batch.n_tokens
         self.h2d_bytes += batch.h2d_bytes
         return logits
-
-    def finish(self, request: Hashable) -> None:
-        """The request is over: its pages and its state slot go back to the pools."""
-        if self.cache.has(request):
-            self.cache.release(request)

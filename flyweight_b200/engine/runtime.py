@@ -1,0 +1,223 @@
+"""The Python entry point, in flyweight's manner (src/flyweight/v2.py: ``V2Model`` :2188,
+``V2QwenRuntime`` :3297): open a model folder, ask it for a runtime, then either call the
+blocking ``generate`` or queue tasks and pump ``engine_step``.
+
+    model = Model("path/to/folder", dtype="bfloat16")
+    with model.native_runtime(context_limit=4096, parallel_sequences=8) as runtime:
+        runtime.generate([1, 2, 3], 16, print)                     # greedy, blocking
+        tid = runtime.task_submit([1, 2, 3], 16, stop_tokens=(7,), temperature=0.8, seed=1)
+        while runtime.has_work():
+            for task_id, token, kind in runtime.engine_step():     # 0 token, 1 finished,
+                ...                                                # 2 error, 3 progress
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import PAGE_SIZE
+from ..config.registry import load_config
+from ..sampling import sampler as device_sampler
+from ..sampling.config import GREEDY, SamplingConfig
+from .loading import load_model, parse_dtype, random_model
+from .runner import ModelRunner
+from .scheduler import (EVENT_ERROR, EVENT_FINISHED, EVENT_PROGRESS, EVENT_TOKEN, Scheduler, Task)
+
+
+@dataclass(frozen=True)
+class GenerationResult:
+    """As src/flyweight/generation.py:9-24, without the text fields (token ids in, out)."""
+    prompt_ids: Tuple[int, ...]
+    generated_ids: Tuple[int, ...]
+    finish_reason: str
+    stopped_on_eos: bool
+    preemptions: int = 0
+
+
+class Model:
+    """A model folder (``config.json`` + ``model.safetensors``) opened on one GPU, or a
+    configuration with seeded random weights (``Model.random``)."""
+
+    def __init__(self, path=None, dtype="bfloat16", device="cuda:0", *, _model=None):
+        if _model is None:
+            _model = load_model(path, dtype, device)
+        self.path = path
+        self.module = _model
+        self.config = getattr(_model, "config", None)
+        self.precision = _model.precision
+
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0",
+               preset: str = "baseline") -> "Model":
+        return cls(_model=random_model(config, seed, dtype, device, preset))
+
+    def native_runtime(self, context_limit: int = 4096, parallel_sequences: int = 1,
+                       cache_tokens: Optional[int] = None, max_batched_tokens: int = 2048,
+                       ) -> "Runtime":
+        """``context_limit``: most tokens (prompt + output) of one request;
+        ``parallel_sequences``: most requests live at a time (flyweight's ``--parallel``);
+        ``cache_tokens``: size of the KV pool in tokens (default: every live request at
+        the context limit); ``max_batched_tokens``: token budget of one step."""
+        return Runtime(self, context_limit, parallel_sequences, cache_tokens, max_batched_tokens)
+
+
+class Runtime:
+    def __init__(self, model: Model, context_limit: int, parallel_sequences: int,
+                 cache_tokens: Optional[int], max_batched_tokens: int):
+        self.model = model
+        self.context_limit = int(context_limit)
+        self.parallel_sequences = max(1, int(parallel_sequences))
+        if cache_tokens is None:
+            cache_tokens = self.parallel_sequences * (-(-self.context_limit // PAGE_SIZE)) * PAGE_SIZE
+        self.cache_tokens = int(cache_tokens)
+        self.max_batched_tokens = int(max_batched_tokens)
+        self.runner: Optional[ModelRunner] = None
+        self.scheduler: Optional[Scheduler] = None
+        self._counters = {"engine_steps": 0, "step_seconds": 0.0, "sampling_seconds": 0.0,
+                          "d2h_bytes": 0}
+        self.prepare()
+
+    # ------------------------------------------------------------------ life cycle
+    def prepare(self) -> None:
+        if self.runner is not None:
+            return
+        self.runner = ModelRunner(self.model.module, num_pages=max(1, self.cache_tokens // PAGE_SIZE),
+                                  num_slots=self.parallel_sequences,
+                                  max_model_len=self.context_limit,
+                                  max_batched_tokens=self.max_batched_tokens)
+        self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
+
+    def reset(self) -> None:
+        """Forget every request and give back everything the cache holds."""
+        self.runner.cache.reset()
+        self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
+
+    def close(self) -> None:
+        self.runner = None
+        self.scheduler = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+    # ------------------------------------------------------------------ tasks
+    def task_submit(self, prompt_tokens: Sequence[int], max_tokens: int,
+                    stop_tokens: Sequence[int] = (), *, temperature: float = 0.0, top_k: int = 20,
+                    top_p: float = 0.95, min_p: float = 0.0, repetition_penalty: float = 1.0,
+                    presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
+                    penalty_window: int = 64, seed: Optional[int] = None) -> int:
+        """Queue a request; returns its task id (names and defaults of
+        src/flyweight/v2.py:3878-3896)."""
+        sampling = SamplingConfig(temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p,
+                                  seed=seed, repetition_penalty=repetition_penalty,
+                                  presence_penalty=presence_penalty,
+                                  frequency_penalty=frequency_penalty,
+                                  penalty_window=penalty_window)
+        return self.scheduler.submit(prompt_tokens, max_tokens, stop_tokens, sampling)
+
+    def task_cancel(self, task_id: int) -> None:
+        self.scheduler.cancel(task_id)
+
+    def task(self, task_id: int) -> Task:
+        return self.scheduler.tasks[task_id]
+
+    def task_error(self, task_id: int) -> Optional[str]:
+        return self.scheduler.tasks[task_id].error
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def engine_step(self) -> List[Tuple[int, int, int]]:
+        """One scheduling cycle: one batched model step and one token for every request
+        that was due.  Returns events ``(task id, token or count, kind)``."""
+        scheduler, runner = self.scheduler, self.runner
+        started = time.perf_counter()
+        step = scheduler.schedule()
+        events = list(step.events)
+        if not step.entries:
+            return events
+        logits = runner.step(step.entries)
+        need = scheduler.advance(step)
+        for task in step.tasks:
+            if task not in need:
+                events.append((task.id, task.computed, EVENT_PROGRESS))
+        if need:
+            sampled = time.perf_counter()
+            if all(task.sampling.greedy for task in need):
+                tokens = device_sampler.argmax(logits)
+            else:
+                uniforms = [0.0 if task.sampling.greedy else task.rng.uniform() for task in need]
+                tokens = device_sampler.sample(logits, [task.sampling for task in need], uniforms,
+                                               [task.generated for task in need])
+            host = tokens.to("cpu").tolist()          # the step's only device->host read
+            self._counters["d2h_bytes"] += 4 * len(host)
+            self._counters["sampling_seconds"] += time.perf_counter() - sampled
+            for task, token in zip(need, host):
+                events.extend(scheduler.accept(task, token))
+        self._counters["engine_steps"] += 1
+        self._counters["step_seconds"] += time.perf_counter() - started
+        return events
+
+    # ------------------------------------------------------------------ blocking calls
+    def generate(self, prompt_tokens: Sequence[int], max_tokens: int,
+                 callback: Optional[Callable[[int], object]] = None) -> List[int]:
+        """Greedy decode of one prompt to ``max_tokens`` (no stop set); ``callback(token)``
+        returning False stops it (src/flyweight/v2.py:3837-3849).  Returns the tokens."""
+        if not prompt_tokens:
+            raise ValueError("prompt_tokens must not be empty")
+        if max_tokens <= 0:
+            raise ValueError("max_tokens must be positive")
+        task_id = self.scheduler.submit(prompt_tokens, max_tokens, (), GREEDY)
+        out: List[int] = []
+        while self.scheduler.tasks[task_id].state != "finished":
+            for tid, token, kind in self.engine_step():
+                if tid != task_id:
+                    continue
+                if kind == EVENT_TOKEN:
+                    out.append(token)
+                    if callback is not None and callback(token) is False:
+                        self.scheduler.cancel(task_id)
+                elif kind == EVENT_ERROR:
+                    raise RuntimeError(self.scheduler.tasks[task_id].error or "generation failed")
+        return out
+
+    def generate_batch(self, prompts: Sequence[Sequence[int]], max_tokens: int,
+                       sampling: Optional[SamplingConfig] = None,
+                       stop_tokens: Sequence[int] = (), seeds: Optional[Sequence[int]] = None
+                       ) -> List[GenerationResult]:
+        """Run several requests to the end through the scheduler; results in input order."""
+        sampling = sampling or GREEDY
+        ids = []
+        for index, prompt in enumerate(prompts):
+            cfg = sampling
+            if seeds is not None:
+                cfg = SamplingConfig(**{**sampling.__dict__, "seed": seeds[index]})
+            ids.append(self.scheduler.submit(prompt, max_tokens, stop_tokens, cfg))
+        while any(self.scheduler.tasks[i].state != "finished" for i in ids):
+            self.engine_step()
+        results = []
+        for i in ids:
+            task = self.scheduler.tasks[i]
+            if task.error:
+                raise RuntimeError(f"task {i}: {task.error}")
+            results.append(GenerationResult(tuple(task.prompt), tuple(task.generated),
+                                            task.finish_reason or "", task.finish_reason == "stop",
+                                            task.preemptions))
+        return results
+
+    # ------------------------------------------------------------------ counters
+    @property
+    def info(self) -> Dict[str, object]:
+        out: Dict[str, object] = dict(self._counters)
+        out.update(self.scheduler.stats)
+        out["cache"] = self.runner.cache.stats()
+        out["model_steps"] = self.runner.steps
+        out["tokens_run"] = self.runner.tokens_run
+        out["h2d_bytes"] = self.runner.h2d_bytes
+        return out

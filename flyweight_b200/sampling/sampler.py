@@ -1,0 +1,77 @@
+"""Turning rows of logits into token ids on the device.
+
+One launch for a batch of greedy rows (argmax, ties to the lowest id -- the order
+flyweight's fused argmax gives, native/include/flyweight_v2_qwen_kernels.hpp:2392-2398);
+one launch for rows that sample (top-k, penalties, temperature, top-p, min-p, draw: the
+order of native/src/v2_runtime.cpp:29331-29744), plus a second one only if some row keeps
+more than 1024 candidates.
+"""
+from __future__ import annotations
+
+import struct
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..kernels import lib
+from ..kernels.lib import KernelError, check_tensor, ptr, stream
+from .config import SamplingConfig
+
+SMALL_K = 1024
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """int32 [R]: index of the largest logit of each row, the lowest id among equals."""
+    check_tensor("logits", logits, torch.float32)
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    lib.call("fwb_argmax", ptr(logits), R, V, ptr(out), stream())
+    return out
+
+
+def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Sequence[float],
+           recents: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+    """int32 [R]: one token per row.  ``uniforms[r]`` is the number in [0, 1) row r draws
+    with; ``recents[r]`` the request's recent generated tokens (for the penalties)."""
+    check_tensor("logits", logits, torch.float32)
+    R, V = logits.shape
+    if len(configs) != R or len(uniforms) != R:
+        raise KernelError("one sampling config and one uniform number per row are needed")
+    stride = 0
+    rows: List[List[int]] = []
+    for r, cfg in enumerate(configs):
+        recent = list(recents[r])[-cfg.penalty_window:] if (recents and cfg.penalizes) else []
+        rows.append(recent)
+        stride = max(stride, len(recent))
+    need_large = False
+    blob = bytearray()
+    for cfg, recent in zip(configs, rows):
+        k = min(cfg.top_k, V) if cfg.top_k > 0 else V
+        sampled = (cfg.temperature > 0.0 or bool(recent)) and k > 1
+        if sampled and k > SMALL_K:
+            if recent:
+                raise KernelError("penalties need 0 < top_k <= 1024 (they act on the candidates)")
+            need_large = True
+        blob += struct.pack("<fifffffi", cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p,
+                            cfg.repetition_penalty, cfg.presence_penalty, cfg.frequency_penalty,
+                            len(recent))
+    device = logits.device
+    params = torch.frombuffer(blob, dtype=torch.uint8).to(device)
+    uni = torch.tensor(list(uniforms), dtype=torch.float64).to(device)
+    recent_dev = None
+    if stride:
+        padded = [row + [-1] * (stride - len(row)) for row in rows]
+        recent_dev = torch.tensor(padded, dtype=torch.int32).to(device)
+    out = torch.empty((R,), dtype=torch.int32, device=device)
+    keys = probs = None
+    vpad = 0
+    if need_large:
+        vpad = 1
+        while vpad < V:
+            vpad <<= 1
+        keys = torch.empty((R, vpad), dtype=torch.int64, device=device)
+        probs = torch.empty((R, vpad), dtype=torch.float64, device=device)
+    lib.call("fwb_sample", ptr(logits), R, V, ptr(params), ptr(uni), ptr(recent_dev), stride,
+             ptr(out), ptr(keys), ptr(probs), vpad, 1 if need_large else 0, stream(),
+             launches=2 if need_large else 1)
+    return out

@@ -23,10 +23,18 @@ import torch
 from .loader import TensorDecl
 from .safetensors_io import save_file
 
+_MASK = (1 << 64) - 1
+
 
 def _generator(seed: int, name: str, device) -> torch.Generator:
+    # splitmix64 of (seed, name): every bit of the result depends on both, because some
+    # generators use only the low 32 bits of the value they are seeded with
+    value = ((int(seed) & _MASK) * 0x9E3779B97F4A7C15 + zlib.crc32(name.encode())) & _MASK
+    value = ((value ^ (value >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    value = ((value ^ (value >> 27)) * 0x94D049BB133111EB) & _MASK
+    value ^= value >> 31
     gen = torch.Generator(device=device)
-    gen.manual_seed(((int(seed) & 0xFFFFFFFF) << 32) | zlib.crc32(name.encode()))
+    gen.manual_seed(value & 0x7FFFFFFFFFFFFFFF)
     return gen
 
 
