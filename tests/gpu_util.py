@@ -1,0 +1,160 @@
+"""Helpers shared by the GPU tests: model folders, the plain oracle, tolerances, traces."""
+from __future__ import annotations
+
+import functools
+import random
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import torch
+
+import plain_lfm2 as P
+from tiny_configs import TINY, make_model_dir
+
+DTYPES = ("float32", "bfloat16")
+STORED = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+# Tolerances, fixed before the first run and never widened.  They bound max|delta| relative to
+# scale = max(1, max|logit|).  float32: the acceptance bound of the 32-bit path.  bfloat16:
+# ten unit roundoffs (2^-9 each) of the logit scale against the float64 oracle on the same
+# bfloat16 weights; one unit roundoff between two ways of cutting the same work.
+TOL_ORACLE = {"float32": 1e-4, "bfloat16": 10 * 2.0 ** -9}
+TOL_CUTS = {"float32": 1e-5, "bfloat16": 2.0 ** -9}
+
+_TMP = tempfile.TemporaryDirectory(prefix="fwb200-tests-")
+
+
+@functools.lru_cache(maxsize=None)
+def model_dir(name: str, dtype: str, seed: int = 3) -> Path:
+    """A folder with the tiny configuration ``name`` stored in ``dtype`` (made once)."""
+    path = Path(_TMP.name) / f"{name}-{dtype}-{seed}"
+    make_model_dir(path, TINY[name], seed=seed, preset="unit", dtype=STORED[dtype])
+    return path
+
+
+@functools.lru_cache(maxsize=None)
+def plain_model(name: str, dtype: str, seed: int = 3):
+    return P.load_model_dir(model_dir(name, dtype, seed))
+
+
+@functools.lru_cache(maxsize=None)
+def _plain_logits_cached(name, dtype, seed, tokens):
+    cfg, w = plain_model(name, dtype, seed)
+    return P.forward(cfg, w, list(tokens))
+
+
+def plain_logits(name: str, dtype: str, tokens, seed: int = 3) -> np.ndarray:
+    return _plain_logits_cached(name, dtype, seed, tuple(int(t) for t in tokens))
+
+
+def random_tokens(name: str, length: int, seed: int) -> list:
+    rng = np.random.default_rng(seed)
+    return [int(t) for t in rng.integers(0, TINY[name]["vocab_size"], size=length)]
+
+
+@functools.lru_cache(maxsize=None)
+def engine_model(name: str, dtype: str, seed: int = 3):
+    from flyweight_b200.engine import load_model
+    return load_model(model_dir(name, dtype, seed), dtype)
+
+
+def new_runner(name: str, dtype: str, num_pages: int = 16, num_slots: int = 4,
+               max_model_len: int = 1024, seed: int = 3):
+    from flyweight_b200.engine import ModelRunner
+    return ModelRunner(engine_model(name, dtype, seed), num_pages=num_pages, num_slots=num_slots,
+                       max_model_len=max_model_len, max_batched_tokens=4096)
+
+
+def assert_close(got: np.ndarray, want: np.ndarray, rel: float, what: str = "") -> None:
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
+    assert np.isfinite(got).all(), f"{what}: non-finite values"
+    scale = max(1.0, float(np.abs(want).max()))
+    err = np.abs(got - want)
+    worst = float(err.max()) if err.size else 0.0
+    if worst > rel * scale:
+        row = int(np.unravel_index(err.argmax(), err.shape)[0])
+        first_bad = int(np.argmax(err.max(axis=-1) > rel * scale)) if err.ndim > 1 else row
+        raise AssertionError(f"{what}: max|delta| {worst:.3e} > {rel:.1e} * {scale:.3g} "
+                             f"(worst row {row}, first row over the bound {first_bad})")
+
+
+def run_whole(runner, rid, tokens) -> np.ndarray:
+    out = runner.step([(rid, tokens, list(range(len(tokens))))])
+    runner.finish(rid)
+    return out.cpu().numpy()
+
+
+def run_portions(runner, rid, tokens, sizes) -> np.ndarray:
+    """Feed ``tokens`` in portions of the given sizes (cycled), all logits wanted."""
+    outs, pos, i = [], 0, 0
+    while pos < len(tokens):
+        n = min(sizes[i % len(sizes)], len(tokens) - pos)
+        outs.append(runner.step([(rid, tokens[pos:pos + n], list(range(n)))]).cpu().numpy())
+        pos += n
+        i += 1
+    runner.finish(rid)
+    return np.concatenate(outs)
+
+
+def mixed_trace(lengths, vocab, num_pages, max_live=4, seed=0, tail=32, name_prefix="r"):
+    """A trace of steps over several requests: up to ``max_live`` live at a time, portions of
+    changing size for the body of each request and its last ``tail`` tokens one by one,
+    requests starting as soon as the pool has pages for their whole length (so pages and
+    slots of finished requests are used again).  Returns (steps, tokens by request); a step is
+    a dict like a trace_run line, with every position wanted."""
+    rng = random.Random(seed)
+    nprng = np.random.default_rng(seed)
+    tokens = {f"{name_prefix}{i}": [int(t) for t in nprng.integers(0, vocab, size=n)]
+              for i, n in enumerate(lengths)}
+    pages_of = {k: -(-len(v) // 64) for k, v in tokens.items()}
+    waiting = list(tokens)
+    live, done_pos = [], {}
+    free = num_pages
+    steps = []
+    sizes = [1, 2, 3, 7, 16, 33, 64, 2, 5]
+    while waiting or live:
+        while waiting and len(live) < max_live and pages_of[waiting[0]] <= free:
+            rid = waiting.pop(0)
+            free -= pages_of[rid]
+            live.append(rid)
+            done_pos[rid] = 0
+        assert live, "the pool is too small for the next request"
+        entries, ended = [], []
+        for rid in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                  # left out of this step, goes on later
+            total = len(tokens[rid])
+            pos = done_pos[rid]
+            body = max(0, total - tail)
+            n = min(rng.choice(sizes), body - pos) if pos < body else 1
+            entries.append({"id": rid, "tokens": tokens[rid][pos:pos + n],
+                            "want": list(range(n))})
+            done_pos[rid] = pos + n
+            if done_pos[rid] == total:
+                ended.append(rid)
+        if not entries:
+            continue
+        for rid in ended:
+            live.remove(rid)
+            free += pages_of[rid]
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps, tokens
+
+
+def replay_in_process(runner, steps):
+    """Run a trace through ``runner``; returns logits by request, in position order."""
+    out = {}
+    for step in steps:
+        logits = runner.step([(e["id"], e["tokens"], e["want"]) for e in step["entries"]])
+        logits = logits.cpu().numpy()
+        row = 0
+        for e in step["entries"]:
+            out.setdefault(e["id"], []).append(logits[row:row + len(e["want"])])
+            row += len(e["want"])
+        for rid in step["end"]:
+            runner.finish(rid)
+        runner.cache.check()
+    return {rid: np.concatenate(parts) for rid, parts in out.items()}
