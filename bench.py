@@ -1,0 +1,342 @@
+#!/usr/bin/env python3
+"""Headline benchmark: LFM2-1.2B with random bfloat16 weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 requests at a 4,096-token context.  The
+one JSON line it prints carries the decode rate timed on the device (``value``), the same
+through the Python entry point with host tokens in and out (``e2e``), a 2,048-token
+prefill (``prefill``), the decode step against the HBM roofline (``roofline``) and
+decode at batch 1 and 64 (``points``).  Inputs are synthetic: uniform-random token ids
+and seeded random weights (there are no published LFM2 numbers to compare with, so
+``vs_baseline`` is null).  For N > 1 it prints one line that says so and exits with 2:
+the engine is single-GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# The layer sizes of LFM2-1.2B (the benchmark configuration).
+LFM2_1P2B = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "num_hidden_layers": 16, "full_attn_idxs": [2, 5, 8, 10, 12, 14],
+    "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "intermediate_size": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+    "conv_L_cache": 3, "conv_bias": False, "vocab_size": 65536, "rope_theta": 1000000.0,
+    "norm_eps": 1e-5, "max_position_embeddings": 128000, "tie_embedding": True,
+}
+CONTEXT = 4096
+BATCH = 8
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def read_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as handle:
+            raw = json.load(handle)
+        peaks = {"hbm_gbs": float(raw["hbm_gbs"]),
+                 "bf16_tflops": float(raw.get("bf16_tflops_sustained") or raw["bf16_tflops"]),
+                 "bf16_tflops_burst": float(raw["bf16_tflops"]), "source": "measured"}
+        return peaks
+    except (OSError, KeyError, ValueError, TypeError):
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons while a region is timed."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[3:7]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def model_flops_per_token(model) -> float:
+    """2 x (weights of every matrix product a token passes through), head excluded."""
+    spec = model.spec
+    total = 0
+    for entry in spec.schedule:
+        layer = model.layers[entry.layer]
+        for part in (layer.mixer, layer.feed_forward):
+            for name in ("w_qkv", "w_o", "w_in", "w_out", "w_gate_up", "w_down"):
+                weight = getattr(part, name, None)
+                if weight is not None:
+                    total += weight.numel()
+    return 2.0 * total
+
+
+def attention_flops(model, n_tokens: int) -> float:
+    """Causal attention of one n-token prompt: QK^T and PV, 2 * n^2 * heads * head_dim a layer
+    (4 flops per query-key pair and channel, half of the pairs masked)."""
+    total = 0.0
+    for entry in model.spec.schedule:
+        mixer = model.layers[entry.layer].mixer
+        if hasattr(mixer, "n_heads"):
+            total += 2.0 * n_tokens * n_tokens * mixer.n_heads * mixer.head_dim
+    return total
+
+
+def kv_bytes_per_token(model) -> int:
+    total = 0
+    for entry in model.spec.schedule:
+        spec = model.layers[entry.layer].mixer.state_spec() if entry.cache_of is None else None
+        if spec is not None and hasattr(spec, "n_kv_heads"):
+            total += 2 * spec.n_kv_heads * spec.head_dim * model.precision.cache_dtype.itemsize
+    return total
+
+
+def fill_context(runner, requests, context, vocab, rng, chunk=2048):
+    """Put ``context`` random tokens of every request into the cache (untimed set-up)."""
+    import torch
+    prompts = {r: torch.randint(0, vocab, (context,), generator=rng).tolist() for r in requests}
+    for rid in requests:
+        for start in range(0, context, chunk):
+            runner.step([(rid, prompts[rid][start:start + chunk], [])])
+    return prompts
+
+
+def time_decode(model, batch, context, steps, warmup, vocab, seed=0):
+    """K decode steps of ``batch`` requests at ``context`` cached tokens each, timed with CUDA
+    events on the launching stream: model step + greedy sampling, tokens given by the host."""
+    import torch
+    from flyweight_b200.engine import ModelRunner
+    from flyweight_b200.kernels import launch_count
+    from flyweight_b200.sampling import sampler
+    total = context + warmup + steps + 2
+    pages = batch * (-(-total // 64))
+    runner = ModelRunner(model, num_pages=pages, num_slots=batch, max_model_len=total,
+                         max_batched_tokens=max(2048, batch))
+    rng = torch.Generator().manual_seed(seed)
+    requests = [f"b{i}" for i in range(batch)]
+    fill_context(runner, requests, context, vocab, rng)
+    tokens = torch.randint(0, vocab, (warmup + steps, batch), generator=rng).tolist()
+    for i in range(warmup):
+        sampler.argmax(runner.step([(r, [tokens[i][j]], [0]) for j, r in enumerate(requests)]))
+    torch.cuda.synchronize()
+    launches = launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(warmup, warmup + steps):
+        sampler.argmax(runner.step([(r, [tokens[i][j]], [0]) for j, r in enumerate(requests)]))
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    launches = launch_count() - launches
+    for r in requests:
+        runner.finish(r)
+    del runner
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3),
+            "launches": launches}
+
+
+def time_e2e(model, batch, context, steps, warmup, vocab, seed=1):
+    """The same through the public entry point: tasks queued on a Runtime, ``engine_step``
+    pumped; every step uploads its batch from pinned host memory and reads its tokens back."""
+    import torch
+    from flyweight_b200.engine.runtime import Model
+    rng = torch.Generator().manual_seed(seed)
+    # requests admitted first decode while the later ones still read their prompts, so every
+    # request gets room for those extra tokens and none finishes inside the timed region
+    slack = 2 * batch * (-(-context // 2048)) + 8
+    total = context + warmup + steps + slack
+    runtime = Model(_model=model).native_runtime(context_limit=total, parallel_sequences=batch,
+                                                max_batched_tokens=2048)
+    for _ in range(batch):
+        prompt = torch.randint(0, vocab, (context,), generator=rng).tolist()
+        runtime.task_submit(prompt, warmup + steps + slack - 2, temperature=0.0)
+    while runtime.scheduler.waiting or any(t.pending > 1 for t in runtime.scheduler.running):
+        runtime.engine_step()                     # prompts in (untimed)
+    for _ in range(warmup):
+        runtime.engine_step()
+    torch.cuda.synchronize()
+    h2d0, d2h0 = runtime.runner.h2d_bytes, runtime.info["d2h_bytes"]
+    begin = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += sum(1 for _, _, kind in runtime.engine_step() if kind == 0)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - begin
+    h2d = (runtime.runner.h2d_bytes - h2d0) / steps
+    d2h = (runtime.info["d2h_bytes"] - d2h0) / steps
+    runtime.close()
+    torch.cuda.empty_cache()
+    return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": seconds * 1e3 / steps}
+
+
+def time_prefill(model, n_tokens, vocab, repeats=5, warmup=3, seed=2):
+    import torch
+    from flyweight_b200.engine import ModelRunner
+    runner = ModelRunner(model, num_pages=-(-n_tokens // 64) + 1, num_slots=1,
+                         max_model_len=n_tokens + 64, max_batched_tokens=n_tokens)
+    rng = torch.Generator().manual_seed(seed)
+    prompt = torch.randint(0, vocab, (n_tokens,), generator=rng).tolist()
+    times = []
+    for i in range(warmup + repeats):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([("p", prompt, [n_tokens - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.finish("p")
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+    del runner
+    torch.cuda.empty_cache()
+    return statistics.median(times)
+
+
+def run_ours(args) -> int:
+    import torch
+    from flyweight_b200.engine.runtime import Model
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: flyweight_b200 has no CPU path"}))
+        return 1
+    peaks = read_peaks()
+    config = dict(LFM2_1P2B)
+    full_layers = config["num_hidden_layers"]
+    if args.layers and args.layers < full_layers:
+        config["num_hidden_layers"] = args.layers
+        config["full_attn_idxs"] = [i for i in config["full_attn_idxs"] if i < args.layers]
+    model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
+    vocab = config["vocab_size"]
+    params = model.parameter_count()
+
+    sampler_clock = ClockSampler(0)
+    sampler_clock.start()
+    main = time_decode(model, BATCH, CONTEXT, args.steps, args.warmup, vocab)
+    clocks = sampler_clock.stop()
+    e2e = time_e2e(model, BATCH, CONTEXT, args.steps, args.warmup, vocab)
+    points = {}
+    for batch in (1, 64):
+        steps = max(8, args.steps // (4 if batch == 64 else 1))
+        points[f"decode_b{batch}"] = time_decode(model, batch, CONTEXT, steps, args.warmup,
+                                                 vocab)["tokens_per_s"]
+    prefill_ms = time_prefill(model, PREFILL_TOKENS, vocab)
+    flops = (model_flops_per_token(model) * PREFILL_TOKENS + attention_flops(model, PREFILL_TOKENS)
+             + 2.0 * model.head.numel())
+    step_bytes = model.weight_bytes(with_embedding_rows=BATCH) + BATCH * CONTEXT * kv_bytes_per_token(model)
+    achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tokens/s, LFM2-1.2B bf16, batch 8, context 4096",
+        "value": main["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: uniform-random token ids, seeded random weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "LFM2-1.2B", "layers": config["num_hidden_layers"], "layers_full": full_layers,
+            "attention_layers": len(config["full_attn_idxs"]), "hidden": config["hidden_size"],
+            "heads": config["num_attention_heads"], "kv_heads": config["num_key_value_heads"],
+            "head_dim": model.config.head_dim, "ffn_dim": model.config.ffn_dim,
+            "conv_L_cache": config["conv_L_cache"], "vocab": vocab, "parameters": params,
+            "global_batch": BATCH, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single GPU", "page_size": 64,
+            "l2": "inputs larger than L2 (2.3 GB of weights read per step), no flush",
+            "peaks": peaks["source"],
+        },
+        "e2e": e2e,
+        "gpu_launches": main["launches"],
+        "clocks": clocks,
+        "prefill": {"value": PREFILL_TOKENS / (prefill_ms / 1e3), "tokens": PREFILL_TOKENS,
+                    "ms": prefill_ms, "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
+                    "flops": flops, "peak_tflops": peaks["bf16_tflops"]},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "bytes_per_step": step_bytes,
+                     "of": peaks["source"]},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(args) -> int:
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        from reference_arm import run as run_reference_arm
+    except Exception as error:                                     # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable":
+                          f"reference arm not set up: {type(error).__name__}: {error}"}))
+        return 0
+    return run_reference_arm(args, LFM2_1P2B, BATCH, CONTEXT)
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--layers", type=int, default=0,
+                        help="run fewer layers than the configuration has (both counts are reported)")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (N=1 only)")
+        return 2
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
