@@ -1,0 +1,448 @@
+"""Each kernel alone against a plain PyTorch reference of the same operation (fp64 on the
+host), at sizes other than the engine's: widths and vocabularies that are no power of two,
+head sizes in steps of 16, odd head and group counts."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def dev(t, dtype=None):
+    return t.to(device=DEV, dtype=dtype or t.dtype).contiguous()
+
+
+def close(got, want, rel, what=""):
+    got = got.detach().double().cpu()
+    want = want.detach().double().cpu()
+    assert got.shape == want.shape, f"{what}: {got.shape} vs {want.shape}"
+    scale = max(1.0, want.abs().max().item())
+    err = (got - want).abs().max().item()
+    assert math.isfinite(err) and err <= rel * scale, f"{what}: max|delta| {err:.3e} > {rel:.1e}*{scale:.3g}"
+
+
+def bf16_round(t):
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("V,H,T", [(300, 100, 7), (1000, 72, 1), (17, 2048, 33)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(V, H, T, dtype):
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    out = ops.embed(dev(table), dev(ids))
+    assert out.dtype == torch.float32
+    assert torch.equal(out.cpu(), table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("H", [64, 100, 1000, 2048, 4100])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_with_and_without_the_residual_sum(H, out_dtype):
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(H)
+    x = torch.randn(9, H, generator=g) * 3
+    d = torch.randn(9, H, generator=g)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    eps = 1e-5
+    tol = 1e-5 if out_dtype == torch.float32 else 2.0 ** -8
+
+    def ref(v):
+        v = v.double()
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w.double()
+
+    xd = dev(x)
+    close(ops.rmsnorm(xd, dev(w), eps, out_dtype), ref(x), tol, "norm")
+    assert torch.equal(xd.cpu(), x)
+    out = ops.rmsnorm(xd, dev(w), eps, out_dtype, delta=dev(d))
+    close(out, ref(x + d), tol, "sum + norm")
+    assert torch.equal(xd.cpu(), x + d)                       # the sum is stored, in fp32
+    rows = torch.tensor([5, 0, 5, 8], dtype=torch.int32)
+    xd = dev(x)
+    out = ops.rmsnorm(xd, dev(w), eps, out_dtype, delta=dev(d), rows=dev(rows))
+    close(out, ref(x + d)[rows.long()], tol, "gathered sum + norm")
+    assert torch.equal(xd.cpu(), x)                           # a gather leaves x alone
+
+
+@pytest.mark.parametrize("T,F", [(1, 192), (5, 320), (130, 1000)])
+def test_silu_mul(T, F):
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(1)
+    gu = torch.randn(T, 2 * F, generator=g) * 4
+    want = torch.from_numpy(P.silu(gu[:, :F].double().numpy())) * gu[:, F:].double()
+    close(ops.silu_mul(dev(gu), torch.float32), want, 1e-6, "silu fp32")
+    gb = gu.to(torch.bfloat16)
+    want = torch.from_numpy(P.silu(gb[:, :F].double().numpy())) * gb[:, F:].double()
+    close(ops.silu_mul(dev(gb), torch.bfloat16), want, 2.0 ** -8, "silu bf16")
+    big = torch.tensor([[100.0, -100.0, 1.0, 1.0]])
+    out = ops.silu_mul(dev(big), torch.float32).cpu()
+    assert torch.isfinite(out).all() and abs(out[0, 0].item() - 100.0) < 1e-4 and out[0, 1].abs() < 1e-30
+
+
+# ------------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 70, 50), (65, 129, 17), (130, 384, 96), (8, 100, 333)])
+def test_gemm_simt_fp32(M, N, K):
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(M * N + K)
+    x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    add = torch.randn(M, N, generator=g)
+    close(ops.gemm_simt(dev(x), dev(w), torch.float32), x.double() @ w.double().T, 1e-6, "gemm")
+    close(ops.gemm_simt(dev(x), dev(w), torch.float32, addend=dev(add)),
+          x.double() @ w.double().T + add.double(), 1e-6, "gemm + addend")
+
+
+def test_gemm_row_does_not_depend_on_the_batch():
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(5)
+    x, w = torch.randn(70, 200, generator=g), torch.randn(90, 200, generator=g)
+    whole = ops.gemm_simt(dev(x), dev(w), torch.float32)
+    single = ops.gemm_simt(dev(x[41:42]), dev(w), torch.float32)
+    assert torch.equal(whole[41:42], single)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (9, 200, 96), (200, 320, 96), (64, 2048, 512),
+                                   (300, 1000, 264), (128, 256, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_linear_bf16(M, N, K, out_dtype):
+    """The product the bfloat16 path uses, whichever kernel the dispatcher picks."""
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    tol = 1e-5 if out_dtype == torch.float32 else 2.0 ** -8
+    close(ops.linear(dev(x), dev(w), out_dtype), want, tol, f"linear {M}x{N}x{K}")
+    if out_dtype == torch.float32:
+        add = torch.randn(M, N, generator=g)
+        close(ops.linear(dev(x), dev(w), out_dtype, addend=dev(add)), want + add.double(), 1e-5,
+              "linear + addend")
+
+
+# ------------------------------------------------------------------ gated short convolution
+def conv_reference(p, taps, bias, state, segments):
+    """Token by token with a rolling state per slot (float64)."""
+    T, H3 = p.shape
+    H = H3 // 3
+    L = taps.shape[1]
+    z = torch.zeros(T, H, dtype=torch.float64)
+    state = state.clone().double()
+    t = 0
+    for slot, n in segments:
+        for _ in range(n):
+            b, c, x = p[t, :H].double(), p[t, H:2 * H].double(), p[t, 2 * H:].double()
+            window = torch.cat([state[slot], (b * x)[:, None]], dim=1)
+            state[slot] = window[:, 1:]
+            y = (window * taps.double()).sum(1)
+            if bias is not None:
+                y = y + bias.double()
+            z[t] = c * y
+            t += 1
+    return z, state
+
+
+@pytest.mark.parametrize("H,L,bias", [(64, 3, False), (96, 4, True), (100, 2, True), (40, 7, False)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_shortconv_over_ragged_segments(H, L, bias, dtype):
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(H + L)
+    segments = [(2, 1), (0, 5), (3, 1), (1, 2), (4, L - 1), (5, 40), (6, 1)]   # (slot, tokens)
+    T = sum(n for _, n in segments)
+    p = torch.randn(T, 3 * H, generator=g).to(dtype)
+    taps = torch.randn(H, L, generator=g)
+    b = torch.randn(H, generator=g) if bias else None
+    state = torch.randn(8, H, L - 1, generator=g)
+    seg_start = torch.tensor(np.cumsum([0] + [n for _, n in segments]), dtype=torch.int32)
+    seg_slot = torch.tensor([s for s, _ in segments], dtype=torch.int32)
+    tok_seg = torch.tensor([i for i, (_, n) in enumerate(segments) for _ in range(n)], dtype=torch.int32)
+    want_z, want_state = conv_reference(p, taps, b, state, segments)
+    sd = dev(state)
+    z = ops.shortconv(dev(p), dev(taps), None if b is None else dev(b), sd, dev(seg_start),
+                      dev(seg_slot), dev(tok_seg), len(segments), dtype)
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -7
+    close(z, want_z, tol, "conv output")
+    close(sd, want_state, 1e-6, "conv state")
+    assert torch.equal(sd[7].cpu(), state[7])                 # an unused slot is untouched
+
+
+def test_shortconv_cut_anywhere_gives_the_same_bits():
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(3)
+    H, L, T = 72, 4, 50
+    p = torch.randn(T, 3 * H, generator=g)
+    taps = torch.randn(H, L, generator=g)
+
+    def run(cuts):
+        state = torch.zeros(2, H, L - 1, device=DEV)
+        outs = []
+        pos = 0
+        for n in cuts:
+            outs.append(ops.shortconv(
+                dev(p[pos:pos + n]), dev(taps), None, state,
+                dev(torch.tensor([0, n], dtype=torch.int32)), dev(torch.tensor([1], dtype=torch.int32)),
+                dev(torch.zeros(n, dtype=torch.int32)), 1, torch.float32))
+            pos += n
+        return torch.cat(outs), state
+
+    whole, s0 = run([T])
+    for cuts in ([1] * T, [2, 1, 3, 44], [49, 1], [3, 3, 3, 41]):
+        got, s1 = run(cuts)
+        assert torch.equal(got, whole) and torch.equal(s0, s1), cuts
+
+
+# ------------------------------------------------------------------ q/k norm, rope, cache write
+def rope_table(theta, rot, n):
+    inv = theta ** (-torch.arange(rot // 2, dtype=torch.float64) * 2 / rot)
+    ang = torch.arange(n, dtype=torch.float64)[:, None] * inv[None]
+    return torch.stack([ang.cos(), ang.sin()], -1).float()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (3, 1, 32, 32), (5, 5, 48, 32), (2, 1, 80, 80),
+                                           (8, 2, 128, 64), (2, 2, 256, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_and_cache_write(nh, nkv, hd, rot, dtype):
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(nh * hd)
+    T, pages, P_ = 6, 5, 64
+    positions = torch.tensor([0, 1, 63, 64, 65, 130], dtype=torch.int32)
+    tok_seg = torch.tensor([0, 0, 1, 1, 1, 0], dtype=torch.int32)
+    table_rows = torch.tensor([[3, 1, 4], [0, 2, -1]], dtype=torch.int32)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g)
+    wq, wk = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
+    eps, theta = 1e-5, 1e4
+    table = rope_table(theta, rot, 200)
+    k_pool = torch.full((pages, nkv, P_, hd), 7.0).to(dtype)
+    v_pool = torch.full((pages, nkv, P_, hd), 7.0).to(dtype)
+    kd, vd = dev(k_pool), dev(v_pool)
+    q = ops.qk_norm_rope(dev(qkv), dev(wq), dev(wk), dev(table), dev(positions), dev(tok_seg),
+                         dev(table_rows), kd, vd, nh, nkv, hd, rot, eps, dtype)
+
+    def norm_rope(x, w, pos):                                 # x: [heads, hd] float64
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+        cs = table[pos].double()
+        a, b = x[:, :rot // 2], x[:, rot // 2:rot]
+        out = x.clone()
+        out[:, :rot // 2] = a * cs[:, 0] - b * cs[:, 1]
+        out[:, rot // 2:rot] = b * cs[:, 0] + a * cs[:, 1]
+        return out
+
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -7
+    want_k, want_v = k_pool.double().clone(), v_pool.double().clone()
+    for t in range(T):
+        pos = int(positions[t])
+        row = qkv[t].double()
+        qh = row[:nh * hd].reshape(nh, hd)
+        kh = row[nh * hd:(nh + nkv) * hd].reshape(nkv, hd)
+        vh = row[(nh + nkv) * hd:].reshape(nkv, hd)
+        close(q[t].reshape(nh, hd), norm_rope(qh, wq, pos), tol, f"q token {t}")
+        page = int(table_rows[int(tok_seg[t]), pos // P_])
+        want_k[page, :, pos % P_] = norm_rope(kh, wk, pos)
+        want_v[page, :, pos % P_] = vh
+    close(kd, want_k, tol, "k pool")                          # also: nothing else was written
+    close(vd, want_v, tol, "v pool")
+
+
+# ------------------------------------------------------------------ attention
+def attention_reference(q, k_seq, v_seq, pos, window, scale, group):
+    """One query token (heads x hd) over its sequence's keys [0..pos] (float64)."""
+    nh = q.shape[0]
+    lo = max(0, pos - window + 1) if window > 0 else 0
+    out = torch.zeros_like(q)
+    for h in range(nh):
+        kv = h // group
+        s = (k_seq[lo:pos + 1, kv] @ q[h]) * scale
+        p = torch.softmax(s, 0)
+        out[h] = p @ v_seq[lo:pos + 1, kv]
+    return out
+
+
+def build_paged(k_seqs, v_seqs, n_pages, dtype, shuffle_seed=0, fill=float("nan")):
+    """Scatter per-sequence K/V ([len][nkv][hd]) into pools through a shuffled block table;
+    everything that holds no token is filled with ``fill`` so that a read past a sequence's
+    end poisons the result."""
+    nkv, hd = k_seqs[0].shape[1:]
+    order = torch.randperm(n_pages, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+    k_pool = torch.full((n_pages, nkv, 64, hd), fill, dtype=torch.float64)
+    v_pool = torch.full((n_pages, nkv, 64, hd), fill, dtype=torch.float64)
+    width = max(-(-k.shape[0] // 64) for k in k_seqs)
+    table = torch.full((len(k_seqs), width), -1, dtype=torch.int32)
+    for s, (k, v) in enumerate(zip(k_seqs, v_seqs)):
+        for logical in range(-(-k.shape[0] // 64)):
+            page = order.pop()
+            table[s, logical] = page
+            n = min(64, k.shape[0] - logical * 64)
+            k_pool[page, :, :n] = k[logical * 64:logical * 64 + n].transpose(0, 1)
+            v_pool[page, :, :n] = v[logical * 64:logical * 64 + n].transpose(0, 1)
+    return k_pool.to(dtype), v_pool.to(dtype), table
+
+
+ATTN_SHAPES = [(4, 2, 16), (3, 1, 32), (6, 6, 48), (8, 1, 64), (32, 8, 64), (5, 5, 80), (16, 1, 128),
+               (2, 1, 256)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd", ATTN_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 70])
+def test_paged_attention_mixed_batch(nh, nkv, hd, dtype, window):
+    """A prompt portion with a cached prefix, a whole short prompt and two decode tokens in one
+    launch, over shuffled pages; rows past each sequence's end hold NaN."""
+    from flyweight_b200.kernels import ops, attention as attention_kernels
+    g = torch.Generator().manual_seed(nh + hd)
+    lens = [200, 37, 129, 64]                 # tokens in the cache after this step
+    new = [90, 37, 1, 1]                      # of which this step brings the last ...
+    k_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    v_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    k_pool, v_pool, table = build_paged(k_seqs, v_seqs, 12, dtype, shuffle_seed=hd)
+    qs, positions, tok_seg = [], [], []
+    for s, (n, m) in enumerate(zip(lens, new)):
+        for pos in range(n - m, n):
+            qs.append(bf16_round(torch.randn(nh, hd, generator=g).double()))
+            positions.append(pos)
+            tok_seg.append(s)
+    q = torch.stack(qs)
+    scale = 1.0 / math.sqrt(hd)
+    want = torch.stack([attention_reference(q[t], k_seqs[tok_seg[t]], v_seqs[tok_seg[t]], positions[t],
+                                            window, scale, nh // nkv) for t in range(len(qs))])
+
+    class Ctx:
+        pass
+    ctx, cache = Ctx(), Ctx()
+    ctx.batch = Ctx()
+    ctx.batch.positions = dev(torch.tensor(positions, dtype=torch.int32))
+    ctx.batch.tok_seg = dev(torch.tensor(tok_seg, dtype=torch.int32))
+    seg_start = np.cumsum([0] + new)
+    ctx.batch.seg_start = dev(torch.tensor(seg_start, dtype=torch.int32))
+    ctx.batch.seg_pos0 = dev(torch.tensor([n - m for n, m in zip(lens, new)], dtype=torch.int32))
+    ctx.batch.n_segments, ctx.batch.n_tokens = len(lens), len(qs)
+    ctx.batch.max_context, ctx.batch.max_segment = max(lens), max(new)
+    ctx.batch.segments = [type("S", (), {"pos0": n - m, "tokens": [0] * m})() for n, m in zip(lens, new)]
+    cache.k_pool, cache.v_pool = dev(k_pool), dev(v_pool)
+    qd = dev(q.reshape(len(qs), nh * hd).to(dtype))
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -7
+    got = ops.attention_simt(qd, cache.k_pool, cache.v_pool, ctx.batch.positions, ctx.batch.tok_seg,
+                             dev(table), nh, window, scale, dtype)
+    close(got.reshape(-1, nh, hd), want, tol, "SIMT attention")
+    got = attention_kernels.paged_attention(ctx, qd, cache, dev(table), nh, window, scale, dtype)
+    close(got.reshape(-1, nh, hd), want, tol, "dispatched attention")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_far_key_among_hundreds_and_the_edges_of_pages(dtype):
+    """Random keys hide a fault at one position; here one key per case is made to match the
+    query so strongly that the output must be (almost) that key's value: a far key (position 3
+    of 700), the last key of a page (63), the first of the next (64), and the query's own."""
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(9)
+    nh, nkv, hd, n = 4, 2, 64, 700
+    scale = 1.0 / math.sqrt(hd)
+    for target in (3, 63, 64, 639, 640, 699):
+        k = bf16_round(torch.randn(n, nkv, hd, generator=g).double() * 0.1)
+        v = bf16_round(torch.randn(n, nkv, hd, generator=g).double())
+        direction = torch.zeros(hd, dtype=torch.float64)
+        direction[target % hd] = 1.0
+        k[target, :, :] = direction * 16.0
+        q = (direction * 16.0).repeat(nh, 1)                  # score 256/8 = 32 above the rest
+        k_pool, v_pool, table = build_paged([k], [v], 12, dtype, shuffle_seed=target)
+        got = ops.attention_simt(dev(q.reshape(1, -1).to(dtype)), dev(k_pool), dev(v_pool),
+                                 dev(torch.tensor([n - 1], dtype=torch.int32)),
+                                 dev(torch.zeros(1, dtype=torch.int32)), dev(table), nh, 0, scale, dtype)
+        want = attention_reference(q, k, v, n - 1, 0, scale, nh // nkv)
+        close(got.reshape(nh, hd), want, 1e-5 if dtype == torch.float32 else 2.0 ** -7, f"target {target}")
+        close(got.reshape(nh, hd)[0], v[target, 0], 1e-3 if dtype == torch.float32 else 2.0 ** -6,
+              f"value of key {target}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_edge_of_a_window(dtype):
+    """The key just outside the window shouts, the key just inside whispers: a kernel that is
+    off by one at the window's edge returns the wrong value."""
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(4)
+    nh, nkv, hd, n, window = 2, 1, 32, 300, 100
+    scale = 1.0 / math.sqrt(hd)
+    pos = n - 1
+    k = bf16_round(torch.randn(n, nkv, hd, generator=g).double() * 0.1)
+    v = bf16_round(torch.randn(n, nkv, hd, generator=g).double())
+    direction = torch.zeros(hd, dtype=torch.float64)
+    direction[5] = 1.0
+    k[pos - window, 0] = direction * 16.0                     # just outside: must be ignored
+    k[pos - window + 1, 0] = direction * 8.0                  # just inside: must win
+    q = (direction * 16.0).repeat(nh, 1)
+    k_pool, v_pool, table = build_paged([k], [v], 6, dtype)
+    got = ops.attention_simt(dev(q.reshape(1, -1).to(dtype)), dev(k_pool), dev(v_pool),
+                             dev(torch.tensor([pos], dtype=torch.int32)), dev(torch.zeros(1, dtype=torch.int32)),
+                             dev(table), nh, window, scale, dtype)
+    want = attention_reference(q, k, v, pos, window, scale, nh)
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -7
+    close(got.reshape(nh, hd), want, tol, "window edge")
+    close(got.reshape(nh, hd)[0], v[pos - window + 1, 0], 1e-3 if dtype == torch.float32 else 2.0 ** -6,
+          "the key just inside the window")
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    from flyweight_b200.kernels import KernelError, ops
+    q = torch.zeros(1, 17 * 16, device=DEV)
+    pool = torch.zeros(2, 1, 64, 16, device=DEV)
+    i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="unsupported"):     # 17 query heads on one KV head
+        ops.attention_simt(q, pool, pool, i32(0), i32(0), i32(0).reshape(1, 1), 17, 0, 1.0, torch.float32)
+    with pytest.raises(KernelError, match="unsupported"):     # 17 taps
+        ops.shortconv(torch.zeros(1, 12, device=DEV), torch.zeros(4, 17, device=DEV), None,
+                      torch.zeros(1, 4, 16, device=DEV), i32(0, 1), i32(0), i32(0), 1, torch.float32)
+    with pytest.raises(KernelError, match="contiguous"):
+        ops.gemm_simt(torch.zeros(4, 8, device=DEV).t(), torch.zeros(3, 4, device=DEV), torch.float32)
+
+
+# ------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("V", [100, 384, 65536, 50001])
+def test_argmax_takes_the_lowest_id_among_equals(V):
+    from flyweight_b200.sampling import sampler
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(5, V, generator=g)
+    logits[1, [7, V - 1]] = 50.0
+    logits[2, :] = 0.0
+    logits[3, V - 1] = 99.0
+    want = [int(np.lexsort((np.arange(V), -row.numpy()))[0]) for row in logits]
+    assert sampler.argmax(dev(logits)).tolist() == want
+    assert want[1] == 7 and want[2] == 0 and want[3] == V - 1
+
+
+@pytest.mark.parametrize("V", [384, 5000, 65536])
+def test_sampling_equals_the_plain_sampler_draw_for_draw(V):
+    from flyweight_b200.sampling import SamplingConfig, sampler
+    g = torch.Generator().manual_seed(V + 1)
+    settings = [dict(temperature=0.8, top_k=40, top_p=0.95, min_p=0.05),
+                dict(temperature=1.5, top_k=5, top_p=1.0, min_p=0.0),
+                dict(temperature=0.3, top_k=1000, top_p=0.5, min_p=0.0),
+                dict(temperature=1.0, top_k=0, top_p=0.9, min_p=0.01),
+                dict(temperature=0.0, top_k=20, top_p=0.95, min_p=0.0),
+                dict(temperature=2.0, top_k=1, top_p=1.0, min_p=0.0),
+                dict(temperature=1.0, top_k=300, top_p=1.0, min_p=0.5)]
+    for trial in range(6):
+        logits = torch.randn(len(settings), V, generator=g) * 3
+        logits[:, 11] = logits[:, 13]                          # ties inside the candidates
+        rngs = [P.XorShift64Star(100 + trial * 10 + i) for i in range(len(settings))]
+        uniforms = [P.XorShift64Star(100 + trial * 10 + i).uniform() for i in range(len(settings))]
+        want = [P.sample(logits[i].numpy(), rng=rngs[i], **s) for i, s in enumerate(settings)]
+        got = sampler.sample(dev(logits), [SamplingConfig(**s) for s in settings], uniforms).tolist()
+        assert got == want, (trial, got, want)
+
+
+def test_penalties_act_on_the_candidates():
+    from flyweight_b200.sampling import SamplingConfig, sampler
+    logits = torch.zeros(2, 50)
+    logits[:, 4], logits[:, 9], logits[:, 2] = 5.0, 4.5, 4.0
+    greedy = SamplingConfig(temperature=0.0, top_k=20, top_p=1.0, min_p=0.0, repetition_penalty=1.5)
+    got = sampler.sample(dev(logits), [greedy, greedy], [0.0, 0.0], [[4, 4, 7], []]).tolist()
+    assert got == [9, 4]              # 5.0/1.5 < 4.5: the repeated token loses; no history: it wins
+    freq = SamplingConfig(temperature=0.0, top_k=20, top_p=1.0, min_p=0.0, frequency_penalty=0.3,
+                          presence_penalty=0.2)
+    got = sampler.sample(dev(logits), [freq, freq], [0.0, 0.0], [[4], [4, 4, 9, 9, 9]]).tolist()
+    assert got == [4, 4]              # 5-0.5=4.5 ties 4.5 -> lower id; 5-0.8=4.2 > 4.5-1.1
