@@ -1,0 +1,132 @@
+"""Generation through the Python entry point and the command line: greedy tokens against the
+plain implementation, seeded sampling against the plain sampler, preemption without a change
+of output."""
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as P
+from gpu_util import model_dir, plain_logits, plain_model, random_tokens
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def open_runtime(name, dtype, **kwargs):
+    from flyweight_b200 import Model
+    return Model(model_dir(name, dtype), dtype=dtype).native_runtime(**kwargs)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_equals_the_plain_implementation(name):
+    cfg, w = plain_model(name, "float32")
+    prompts = [random_tokens(name, n, seed=20 + n) for n in (5, 17, 33)]
+    with open_runtime(name, "float32", context_limit=128, parallel_sequences=3) as runtime:
+        seen = []
+        first = runtime.generate(prompts[0], 16, seen.append)
+        assert first == seen == P.greedy_generate(cfg, w, prompts[0], 16)
+        results = runtime.generate_batch(prompts, 16)
+        for prompt, result in zip(prompts, results):
+            assert list(result.generated_ids) == P.greedy_generate(cfg, w, prompt, 16)
+            assert result.finish_reason == "length"
+        info = runtime.info
+        assert info["cache"]["groups"][0]["pages_in_use"] == 0 and info["decode_tokens"] > 0
+
+
+def test_bfloat16_generation_follows_its_own_logits():
+    """bfloat16 may flip a near-tie against the oracle, so the check is on logits: at every
+    generated position the chosen token's oracle logit is within the bfloat16 bound of the
+    oracle's best."""
+    name, dtype = "B", "bfloat16"
+    prompt = random_tokens(name, 40, seed=3)
+    with open_runtime(name, dtype, context_limit=128, parallel_sequences=1) as runtime:
+        tokens = runtime.generate(prompt, 12)
+    logits = plain_logits(name, dtype, prompt + tokens)
+    scale = max(1.0, np.abs(logits).max())
+    for i, token in enumerate(tokens):
+        row = logits[len(prompt) - 1 + i]
+        assert row.max() - row[token] <= 2 * 10 * 2.0 ** -9 * scale
+
+
+def test_callback_returning_false_stops_and_stop_tokens_end_a_task():
+    cfg, w = plain_model("A", "float32")
+    prompt = random_tokens("A", 9, seed=1)
+    expected = P.greedy_generate(cfg, w, prompt, 8)
+    with open_runtime("A", "float32", context_limit=64, parallel_sequences=2) as runtime:
+        got = []
+        runtime.generate(prompt, 8, lambda t: (got.append(t), len(got) < 3)[1])
+        assert got == expected[:3]
+        tid = runtime.task_submit(prompt, 8, stop_tokens=(expected[4],))
+        events = []
+        while runtime.has_work():
+            events.extend(runtime.engine_step())
+        tokens = [t for i, t, kind in events if i == tid and kind == 0]
+        stop_at = expected.index(expected[4])
+        assert tokens == expected[:stop_at + 1] and runtime.task(tid).finish_reason == "stop"
+        assert (tid, 0, 1) in events
+
+
+def test_seeded_sampling_equals_the_plain_sampler_and_ignores_batching():
+    name = "B"
+    cfg, w = plain_model(name, "float32")
+    prompts = [random_tokens(name, n, seed=40 + n) for n in (1, 7, 64, 100, 129)]
+    settings = dict(temperature=0.8, top_k=40, top_p=0.95, min_p=0.05)
+
+    def plain_run(prompt, seed, count):
+        rng = P.XorShift64Star(seed)
+        text, out = list(prompt), []
+        for _ in range(count):
+            token = P.sample(P.forward(cfg, w, text)[-1].astype(np.float32), rng=rng, **settings)
+            out.append(token)
+            text.append(token)
+        return out
+
+    with open_runtime(name, "float32", context_limit=192, parallel_sequences=4,
+                      max_batched_tokens=16) as runtime:       # prompts enter in portions of <= 16
+        ids = [runtime.task_submit(p, 24, seed=7 + i, **settings) for i, p in enumerate(prompts)]
+        while runtime.has_work():
+            runtime.engine_step()
+        batched = [runtime.task(i).generated for i in ids]
+        solo = []
+        for i, p in enumerate(prompts[:2]):
+            tid = runtime.task_submit(p, 24, seed=7 + i, **settings)
+            while runtime.has_work():
+                runtime.engine_step()
+            solo.append(runtime.task(tid).generated)
+    assert batched[:2] == solo                                # same seed, same tokens, alone or not
+    # against the oracle: equal as long as no near-tie in float32 vs float64 decides a draw
+    for i in (0, 1, 2):
+        assert batched[i] == plain_run(prompts[i], 7 + i, 24)
+
+
+def test_preemption_does_not_change_the_output():
+    name = "A"
+    prompts = [random_tokens(name, n, seed=60 + n) for n in (50, 60, 70)]
+    with open_runtime(name, "float32", context_limit=256, parallel_sequences=3,
+                      cache_tokens=3 * 256) as runtime:
+        roomy = [list(r.generated_ids) for r in runtime.generate_batch(prompts, 120)]
+        assert runtime.info["preemptions"] == 0
+    with open_runtime(name, "float32", context_limit=256, parallel_sequences=3,
+                      cache_tokens=6 * 64) as runtime:         # 3 x 170..190 tokens need 9 pages
+        results = runtime.generate_batch(prompts, 120)
+        assert runtime.info["preemptions"] > 0
+        assert sum(r.preemptions for r in results) == runtime.info["preemptions"]
+    assert [list(r.generated_ids) for r in results] == roomy
+
+
+def test_command_line_generate_and_inspect():
+    cfg, w = plain_model("A", "float32")
+    prompt = random_tokens("A", 6, seed=2)
+    run = lambda *args: subprocess.run([sys.executable, "-m", "flyweight_b200", *args], cwd=ROOT,
+                                       capture_output=True, text=True, timeout=600)
+    proc = run("generate", str(model_dir("A", "float32")), "--prompt", ",".join(map(str, prompt)),
+               "--max-tokens", "5", "--temperature", "0", "--dtype", "float32")
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [int(t) for t in proc.stdout.split()] == P.greedy_generate(cfg, w, prompt, 5)
+    proc = run("inspect", str(model_dir("A", "float32")))
+    assert proc.returncode == 0 and '"ffn_dim": 192' in proc.stdout
