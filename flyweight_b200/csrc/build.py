@@ -141,7 +141,7 @@ def build(out: Path | None = None, digest: str | None = None, verbose_ptxas: boo
                 _log(f"  still compiling ({len(pending)} left, {time.time() - started:.0f} s) ...")
     tmp_lib = out / f".{LIB_NAME}.{os.getpid()}.tmp"
     link = [nvcc, "-shared", "-o", str(tmp_lib), *[str(o) for o in objects],
-            "-gencode", "arch=compute_100a,code=sm_100a", "-lcuda"]
+            "-gencode", "arch=compute_100a,code=sm_100a"]
     proc = subprocess.run(link, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"linking {LIB_NAME} failed:\n{proc.stdout}\n{proc.stderr}")

@@ -1,0 +1,475 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), sm_100a.
+//
+//   Y[t][f] = sum_k X[t][k] * W[f][k]        X: [M tokens][K], W: [N features][K], both K-major
+//
+// The weight matrix is the MMA's A operand and the activations its B operand ("swap-AB"):
+// a CTA owns 128 features x BN tokens, the accumulator D[128 x BN] lives in tensor memory
+// with one feature per TMEM lane and one token per column.  With BN = 16..64 the kernel is a
+// weight streamer for decode (every weight byte is read once, the few tokens ride along);
+// with BN = 256 it is the ordinary 128x256 tile for prefill.  One kernel, five BN.
+//
+// Roles inside a CTA (192 threads): warp 0 = TMA producer (one elected lane issues
+// cp.async.bulk.tensor loads of 128B-swizzled [rows x 64] boxes into a ring of stages),
+// warp 1 = TMEM allocator and MMA issuer (one elected lane issues tcgen05.mma, K = 16 per
+// instruction, four per stage, and commits stages back to the producer), warps 2..5 =
+// epilogue (tcgen05.ld of their lane quarter, then the fused epilogue and the store).
+//
+// Split-K without atomics or scratch in global memory: grid.z CTAs that share an output
+// tile form a thread-block cluster; each accumulates its slice of K in its own TMEM, parks
+// the partial tile in its own shared memory, and after a cluster barrier every CTA sums a
+// share of the columns over all peers through distributed shared memory, in rank order --
+// so the result does not depend on which CTA ran first.
+//
+// Epilogues: store fp32 / store bf16 / add an fp32 addend (the residual) and store fp32 /
+// SwiGLU: two accumulators (gate rows f, up rows F+f of the same matrix), silu(g)*u as bf16.
+//
+// Every wait on an mbarrier is bounded: after the limit the CTA raises the library's status
+// word, stops waiting everywhere, still meets its cluster barriers, frees its TMEM and
+// returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+using namespace fwb;
+
+namespace {
+
+constexpr int BM = 128;          // features per CTA (UMMA M)
+constexpr int BK = 64;           // K elements per stage: one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+enum Epilogue : int { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+
+__device__ int g_gemm_status = 0;   // 0 = fine; else the code of the first wait that gave up
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait.  Returns false if it gave up (or somebody else in the CTA did).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+    for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
+        if (mbar_test(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (spin > 2048) __nanosleep(64);
+    }
+    *abort_flag = code;
+    atomicCAS(&g_gemm_status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                            int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(holder)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return d;
+}
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+    return (1u << 4)                 // D: fp32
+           | (1u << 7) | (1u << 10)  // A, B: bf16
+           | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN, int NACC>
+struct Tile {
+    static constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB per accumulator
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = NACC * A_BYTES + B_BYTES;
+    static constexpr int RAW_STAGES = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = RAW_STAGES > 8 ? 8 : RAW_STAGES;
+    static constexpr int COLS = BN * NACC;                      // TMEM columns in use
+    static constexpr int TMEM_COLS = COLS <= 32 ? 32 : (COLS <= 64 ? 64 : (COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512)));
+    static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int PARTIAL_BYTES = COLS * BM * 4;         // fp32 partial tile for split-K
+    static constexpr int SMEM_BYTES = (PIPE_BYTES > PARTIAL_BYTES ? PIPE_BYTES : PARTIAL_BYTES) + 1024 + 256;
+};
+
+struct Params {
+    void* y;               // [M][ldy] fp32 or bf16
+    const float* addend;   // [M][ldy] fp32 or null
+    int M, N, K;           // tokens, features (of one accumulator), reduction
+    int ldy;
+    int up_row_offset;     // SwiGLU: rows of the up projection start here in W
+    int k_blocks_per_split;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const Params prm) {
+    constexpr int NACC = EPI == EPI_SWIGLU_BF16 ? 2 : 1;
+    using T = Tile<BN, NACC>;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + (T::PIPE_BYTES > T::PARTIAL_BYTES ? T::PIPE_BYTES : T::PARTIAL_BYTES));
+    uint64_t* empty_bar = full_bar + T::STAGES;
+    uint64_t* acc_bar = empty_bar + T::STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int feat0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
+    const int splits = gridDim.z;
+    const int total_kb = (prm.K + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * prm.k_blocks_per_split;
+    int kb_end = kb_begin + prm.k_blocks_per_split;
+    if (kb_end > total_kb) kb_end = total_kb;
+    const int n_kb = kb_end > kb_begin ? kb_end - kb_begin : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T::STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, T::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % T::STAGES;
+                const uint32_t round = i / T::STAGES;
+                if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, abort_flag, 1)) break;
+                uint8_t* stage = tiles + (size_t)s * T::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], T::STAGE_BYTES);
+                const int k = (kb_begin + i) * BK;
+                tma_load_2d(stage, &map_w, &full_bar[s], k, feat0);
+                if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[s], k, prm.up_row_offset + feat0);
+                tma_load_2d(stage + NACC * T::A_BYTES, &map_x, &full_bar[s], k, tok0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % T::STAGES;
+                const uint32_t round = i / T::STAGES;
+                ok = mbar_wait(&full_bar[s], round & 1, abort_flag, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t stage = smem_u32(tiles + (size_t)s * T::STAGE_BYTES);
+                const uint64_t b_desc = make_smem_desc(stage + NACC * T::A_BYTES);
+#pragma unroll
+                for (int a = 0; a < NACC; ++a) {
+                    const uint64_t a_desc = make_smem_desc(stage + a * T::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 elements = 32 bytes = 2 descriptor units along K inside the swizzle row
+                        umma_bf16(tmem_base + a * BN, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                  (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(&empty_bar[s]);       // the stage is free once these MMAs have read it
+            }
+            umma_commit(acc_bar);                 // arrives when every MMA above has completed
+        }
+    }
+    __syncwarp();
+
+    // ---------------------------------------------------------------- epilogue
+    const bool epi_warp = warp >= 2;
+    const int quarter = warp & 3;                  // the TMEM lanes this warp may read
+    const int row = quarter * 32 + lane;           // feature inside the tile
+    bool acc_ready = true;
+    if (epi_warp) {
+        if (n_kb > 0) acc_ready = mbar_wait(acc_bar, 0, abort_flag, 3);
+        acc_ready = acc_ready && !*abort_flag;
+        acc_ready = __all_sync(0xffffffffu, acc_ready);   // tcgen05.ld needs the whole warp
+        tc_fence_after();
+    }
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int f = feat0 + row;
+
+    auto finish = [&](int col, float g, float u) {
+        // col: token inside the tile; g: accumulator 0; u: accumulator 1 (SwiGLU only)
+        const int t = tok0 + col;
+        if (t >= prm.M || f >= prm.N) return;
+        const size_t at = (size_t)t * prm.ldy + f;
+        if (EPI == EPI_F32) reinterpret_cast<float*>(prm.y)[at] = g;
+        else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(prm.y)[at] = g + prm.addend[at];
+        else if (EPI == EPI_BF16) reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g);
+        else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(silu_f32(g) * u);
+    };
+
+    if (splits == 1) {
+        if (epi_warp && acc_ready) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float g[16], u[16];
+                if (n_kb > 0) {
+                    tmem_ld16(lane_addr + c0, g);
+                    if (NACC == 2) tmem_ld16(lane_addr + BN + c0, u);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) finish(c0 + j, g[j], NACC == 2 ? u[j] : 0.0f);
+            }
+        }
+    } else {
+        // park the partial tile in shared memory: partial[col][row], fp32 (the pipeline's
+        // stages are free: every MMA that read them has completed)
+        float* partial = reinterpret_cast<float*>(tiles);
+        if (epi_warp) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < T::COLS; c0 += 16) {
+                float v[16];
+                if (n_kb > 0 && acc_ready) tmem_ld16(lane_addr + c0, v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) partial[(c0 + j) * BM + row] = v[j];
+            }
+        }
+        tc_fence_before();
+        cluster_sync_all();
+        if (epi_warp) {
+            const uint32_t rank = cluster_rank();
+            const uint32_t base = smem_u32(partial);
+            for (int col = (int)rank; col < BN; col += splits) {
+                float g = 0.0f, u = 0.0f;
+                for (int r = 0; r < splits; ++r) {
+                    g += ld_dsmem_f32(base + (uint32_t)((col * BM + row) * 4), (uint32_t)r);
+                    if (NACC == 2) u += ld_dsmem_f32(base + (uint32_t)(((BN + col) * BM + row) * 4), (uint32_t)r);
+                }
+                if (!*abort_flag) finish(col, g, u);
+            }
+        }
+        cluster_sync_all();                        // nobody leaves while a peer still reads it
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, T::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// A [rows][K] bf16 row-major matrix seen as boxes of [box_rows][64] with 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int EPI>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& prm, int splits,
+           cudaStream_t stream) {
+    constexpr int NACC = EPI == EPI_SWIGLU_BF16 ? 2 : 1;
+    using T = Tile<BN, NACC>;
+    auto kernel = gemm_tcgen05_kernel<BN, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((prm.N + BM - 1) / BM, (prm.M + BN - 1) / BN, splits);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = T::SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_w, map_x, prm);
+    return e == cudaSuccess ? fwb_launch_status() : (int)e;
+}
+
+template <int BN>
+int launch_epi(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& prm, int splits,
+               cudaStream_t stream) {
+    switch (epi) {
+        case EPI_F32: return launch<BN, EPI_F32>(map_w, map_x, prm, splits, stream);
+        case EPI_BF16: return launch<BN, EPI_BF16>(map_w, map_x, prm, splits, stream);
+        case EPI_ADD_F32: return launch<BN, EPI_ADD_F32>(map_w, map_x, prm, splits, stream);
+        case EPI_SWIGLU_BF16: return launch<BN, EPI_SWIGLU_BF16>(map_w, map_x, prm, splits, stream);
+        default: return FWB_UNSUPPORTED;
+    }
+}
+
+}  // namespace
+
+// X: [M][K] bf16; W: [rows][K] bf16 (rows = N, or >= up_row_offset + N for SwiGLU);
+// Y: [M][ldy] (fp32 for epilogues 0 and 2, bf16 for 1 and 3).  `splits` (1..8) CTAs share the
+// K range of a tile as a cluster; with splits > 1 the token tile must be <= 64 wide.
+// K must be a multiple of 8 (TMA strides are multiples of 16 bytes) and both base
+// pointers 16-byte aligned; anything else is refused.
+FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float* addend, int M, int N,
+                             int K, int w_rows, int ldy, int epilogue, int up_row_offset, int splits,
+                             cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return FWB_OK;
+    if (!X || !W || !Y || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
+    if ((K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FWB_UNSUPPORTED;
+    if (epilogue == EPI_ADD_F32 && !addend) return FWB_BAD_ARGUMENT;
+    if (epilogue == EPI_SWIGLU_BF16 && (up_row_offset < N || w_rows < up_row_offset + N)) return FWB_BAD_ARGUMENT;
+    if (epilogue != EPI_SWIGLU_BF16 && w_rows < N) return FWB_BAD_ARGUMENT;
+    if (splits < 1 || splits > 8) return FWB_BAD_ARGUMENT;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+    const bool swiglu = epilogue == EPI_SWIGLU_BF16;
+    const int bn_eff = (swiglu && bn == 256) ? 128 : bn;     // two accumulators: 2 x 256 columns would fill TMEM
+    if (splits > 1 && bn_eff > 64) return FWB_UNSUPPORTED;
+    if ((M + bn_eff - 1) / bn_eff > 65535) return FWB_TOO_LARGE;
+    const int total_kb = (K + BK - 1) / BK;
+    if (splits > total_kb) splits = total_kb;
+    Params prm;
+    prm.y = Y;
+    prm.addend = addend;
+    prm.M = M;
+    prm.N = N;
+    prm.K = K;
+    prm.ldy = ldy;
+    prm.up_row_offset = up_row_offset;
+    prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
+    CUtensorMap map_w, map_x;
+    if (!make_map(&map_w, W, w_rows, K, BM)) return FWB_UNSUPPORTED;
+    if (!make_map(&map_x, X, M, K, bn_eff)) return FWB_UNSUPPORTED;
+    switch (bn_eff) {
+        case 16: return launch_epi<16>(epilogue, map_w, map_x, prm, splits, stream);
+        case 32: return launch_epi<32>(epilogue, map_w, map_x, prm, splits, stream);
+        case 64: return launch_epi<64>(epilogue, map_w, map_x, prm, splits, stream);
+        case 128: return launch_epi<128>(epilogue, map_w, map_x, prm, splits, stream);
+        default: return launch_epi<256>(epilogue, map_w, map_x, prm, splits, stream);
+    }
+}
+
+// Reads and clears the status word that a wait which gave up leaves behind (0 = none).
+// Synchronises the device.
+FWB_API int fwb_gemm_tcgen05_status() {
+    int value = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&value, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+    if (value) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+    return value;
+}

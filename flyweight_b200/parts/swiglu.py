@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import ops, tensorcore
 from ..weights.loader import TensorDecl
 from .base import FeedForward, Precision, register_feed_forward
 
@@ -40,6 +40,10 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, h):
         act = ctx.precision.act_dtype
-        gate_up = ops.linear(h, self.w_gate_up, act)
-        a = ops.silu_mul(gate_up, act)
+        if tensorcore.swiglu_accepts(h, self.w_gate_up):
+            # gate and up accumulate side by side in tensor memory; silu(g)*u is the epilogue
+            a = tensorcore.swiglu_gate_up(h, self.w_gate_up)
+        else:
+            gate_up = ops.linear(h, self.w_gate_up, act)
+            a = ops.silu_mul(gate_up, act)
         return ops.linear(a, self.w_down, torch.float32)

@@ -446,3 +446,62 @@ def test_penalties_act_on_the_candidates():
                           presence_penalty=0.2)
     got = sampler.sample(dev(logits), [freq, freq], [0.0, 0.0], [[4], [4, 4, 9, 9, 9]]).tolist()
     assert got == [4, 4]              # 5-0.5=4.5 ties 4.5 -> lower id; 5-0.8=4.2 > 4.5-1.1
+
+
+# ------------------------------------------------------------------ tcgen05 matrix products
+TC_SHAPES = [(1, 128, 64), (16, 128, 256), (8, 2048, 2048), (64, 6144, 2048), (100, 200, 96),
+             (17, 100, 72), (300, 1000, 264), (129, 384, 96), (2048, 2048, 512), (8, 512, 8192)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_tcgen05_gemm(M, N, K, out_dtype):
+    from flyweight_b200.kernels import tensorcore as tc
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    assert tc.accepts(dev(x), dev(w), out_dtype)
+    want = x.double() @ w.double().T
+    tol = 1e-5 if out_dtype == torch.float32 else 2.0 ** -8
+    close(tc.gemm(dev(x), dev(w), out_dtype), want, tol, "tcgen05")
+    assert tc.status() == 0
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("M", [1, 16, 40, 64])
+def test_tcgen05_split_k_over_a_cluster(splits, M):
+    from flyweight_b200.kernels import tensorcore as tc
+    g = torch.Generator().manual_seed(splits * 100 + M)
+    N, K = 384, 1096                                           # 17.1 k-blocks: ragged last split
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    add = torch.randn(M, N, generator=g)
+    want = x.double() @ w.double().T
+    first = tc.gemm(dev(x), dev(w), torch.float32, None, splits)
+    close(first, want, 1e-5, f"split {splits}")
+    assert torch.equal(first, tc.gemm(dev(x), dev(w), torch.float32, None, splits))   # deterministic
+    close(tc.gemm(dev(x), dev(w), torch.float32, dev(add), splits), want + add.double(), 1e-5, "addend")
+    assert tc.status() == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 128, 64), (8, 8192 // 8, 2048), (40, 192, 64), (64, 320, 96),
+                                   (200, 320, 96), (700, 1000, 264)])
+def test_tcgen05_swiglu_epilogue(M, F, K):
+    from flyweight_b200.kernels import tensorcore as tc
+    g = torch.Generator().manual_seed(M + F)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    gu = x.double() @ w.double().T
+    want = torch.from_numpy(P.silu(gu[:, :F].numpy())) * gu[:, F:]
+    close(tc.swiglu_gate_up(dev(x), dev(w)), want, 2.0 ** -8, "swiglu")
+    assert tc.status() == 0
+
+
+def test_tcgen05_refuses_what_tma_cannot_address():
+    from flyweight_b200.kernels import KernelError, tensorcore as tc
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K not a multiple of 8
+    w = torch.zeros(128, 100, dtype=torch.bfloat16, device=DEV)
+    assert not tc.accepts(x, w, torch.float32)
+    with pytest.raises(KernelError, match="unsupported"):
+        tc.gemm(x, w, torch.float32)
+    assert not tc.accepts(x.float(), w, torch.float32)

@@ -11,7 +11,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from gpu_util import (DTYPES, TOL_CUTS, TOL_ORACLE, assert_close, mixed_trace, model_dir,
+from gpu_util import (DTYPES, TOL_CUTS, TOL_CUTS_PINNED, TOL_ORACLE, assert_close, mixed_trace, model_dir,
                       new_runner, plain_logits, random_tokens, replay_in_process, run_portions,
                       run_whole)
 from tiny_configs import TINY
@@ -153,3 +153,27 @@ def test_a_step_that_wants_nothing_writes_nothing_and_refusals_are_clean(tmp_pat
     assert runner.cache.length("q") == 10 and not runner.cache.has("z")
     got = runner.step([("q", tokens[10:], [59])]).cpu().numpy()
     assert_close(got, plain_logits("A", "float32", tokens)[-1:], TOL_ORACLE["float32"], "after refusals")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_bfloat16_cuts_agree_to_one_roundoff_when_the_sums_keep_one_order(name):
+    """The bfloat16 kernels' own cache and batch logic, checked as sharply as in 32-bit: with
+    the split-K factor pinned, whole, decoded, portioned and mixed runs must agree to one
+    bfloat16 unit roundoff of the logit scale."""
+    from flyweight_b200.kernels import tensorcore
+    dtype = "bfloat16"
+    tensorcore.force_splits(1)
+    try:
+        runner = new_runner(name, dtype)
+        tokens = random_tokens(name, 200, seed=21)
+        whole = run_whole(runner, "whole", tokens)
+        for sizes in ([1], [2], [16, 2, 7, 64, 3, 2, 1, 30], [63, 1, 64, 2]):
+            got = run_portions(runner, "p", tokens, sizes)
+            assert_close(got, whole, TOL_CUTS_PINNED[dtype], f"{name} pinned portions {sizes}")
+        steps, toks = mixed_trace([150, 90, 200, 70], TINY[name]["vocab_size"], 9, seed=6)
+        got = replay_in_process(runner, steps)
+        for rid, seq in toks.items():
+            assert_close(got[rid], run_whole(runner, "w" + rid, seq), TOL_CUTS_PINNED[dtype],
+                         f"{name} pinned mixed {rid}")
+    finally:
+        tensorcore.force_splits(None)
