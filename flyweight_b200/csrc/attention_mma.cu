@@ -1,0 +1,533 @@
+// Causal grouped-query attention over the paged bfloat16 cache on tensor cores
+// (mma.sync m16n8k16, fp32 accumulation and fp32 softmax), for head sizes 16..128.
+//
+// The rows of a tile are (query token, query head of one KV head) pairs, so the query heads
+// that share a KV head also share every K/V tile that is loaded: a page of keys is read
+// once per group, not once per query head.
+//
+//   prefill kernel: one CTA = one tile of 64 rows (64/group tokens x group heads) of one
+//       segment and one KV head; 4 warps x 16 rows; walks the keys in 64-key tiles (one
+//       page tile each) with an online softmax, K and V staged in shared memory by cp.async,
+//       double buffered.
+//   decode kernel:  one CTA = one token, one KV head, one slice of the context ("split");
+//       the group's heads are the (padded) 16 rows, the 4 warps take 16 keys each of every
+//       64-key tile; warps and then splits are merged with the usual (max, sum, acc) rule --
+//       splits through a small fp32 scratch buffer and a second kernel.
+//
+// Key tiles start at multiples of 64 and are visited in ascending order, whatever the cut.
+#include "common.cuh"
+
+using namespace fwb;
+
+namespace {
+
+constexpr int KEYS = 64;            // keys per tile == page size
+constexpr int WARPS = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+struct Smem {
+    static constexpr int ROW = HD + 8;                     // bf16 elements; +16 bytes: no bank conflicts
+    static constexpr int TILE = KEYS * ROW;                // one K or V tile
+    static constexpr int BYTES = 2 * 2 * TILE * 2;         // 2 stages x (K, V) x bf16
+};
+
+// Copy one (page, kv head) tile of K and of V into shared memory (whole CTA).
+template <int HD>
+__device__ __forceinline__ void load_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
+                                          const __nv_bfloat16* __restrict__ k_pool,
+                                          const __nv_bfloat16* __restrict__ v_pool, size_t src) {
+    constexpr int CHUNKS = HD / 8;                         // 16-byte chunks per row
+    for (int i = threadIdx.x; i < KEYS * CHUNKS; i += WARPS * 32) {
+        const int r = i / CHUNKS, c = i - r * CHUNKS;
+        cp_async16(ks + r * Smem<HD>::ROW + c * 8, k_pool + src + (size_t)r * HD + c * 8);
+        cp_async16(vs + r * Smem<HD>::ROW + c * 8, v_pool + src + (size_t)r * HD + c * 8);
+    }
+}
+
+// Rows of a V tile past the last key anybody may see hold whatever the page held before
+// (or nothing yet); their probabilities are exactly 0, but 0 * garbage must stay 0, so the
+// rows are cleared.  Called by the whole CTA between two barriers.
+template <int HD>
+__device__ __forceinline__ void clear_v_rows(__nv_bfloat16* vs, int first_row) {
+    constexpr int CHUNKS = HD / 8;
+    for (int i = threadIdx.x; i < (KEYS - first_row) * CHUNKS; i += WARPS * 32) {
+        const int r = first_row + i / CHUNKS, c = i % CHUNKS;
+        *reinterpret_cast<uint4*>(vs + r * Smem<HD>::ROW + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+// One warp: S[16 x NK*8] += Q[16 x HD] * K[keys][HD]^T for the keys that start at `key0`.
+template <int HD, int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qf)[HD / 16][4],
+                                        const __nv_bfloat16* ks, int key0, int lane) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[n][j] = 0.0f;
+    // ldmatrix.x4: matrices (keys 0-7, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 0-7), (keys 8-15, d 8-15)
+    const int mat = lane >> 3, r = lane & 7;
+    const int key_off = (mat >> 1) * 8 + r, d_off = (mat & 1) * 8;
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+            uint32_t b[4];
+            ldmatrix_x4(b, ks + (key0 + n * 8 + key_off) * Smem<HD>::ROW + k * 16 + d_off);
+            mma_bf16(s[n], qf[k], b[0], b[1]);
+            mma_bf16(s[n + 1], qf[k], b[2], b[3]);
+        }
+    }
+}
+
+// One warp: O[16 x HD] += P[16 x NT*8] * V[keys][HD], P taken from the score registers.
+template <int HD, int NT>
+__device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&p)[NT][4],
+                                        const __nv_bfloat16* vs, int key0, int lane) {
+    // ldmatrix.x4.trans: matrices (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
+    const int mat = lane >> 3, r = lane & 7;
+    const int key_off = (mat & 1) * 8 + r, d_off = (mat >> 1) * 8;
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+        a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+        a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+        a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+#pragma unroll
+        for (int n = 0; n < HD / 8; n += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, vs + (key0 + kk * 16 + key_off) * Smem<HD>::ROW + n * 8 + d_off);
+            mma_bf16(o[n], a, b[0], b[1]);
+            mma_bf16(o[n + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Scale, mask and online-softmax one row pair (rows g and g+8 of the warp's 16) over NT*8 keys.
+// key index of s[n][j]: key_base + n*8 + 2*t + (j&1); row of s[n][j]: g + 8*(j>>1).
+template <int HD, int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD / 8][4], float (&m)[2],
+                                               float (&l)[2], int key_base, const int (&lo)[2],
+                                               const int (&hi)[2], float scale, int lane) {
+    const int t = lane & 3;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int key = key_base + n * 8 + 2 * t + (j & 1);
+            const int h = j >> 1;
+            const float v = (key >= lo[h] && key <= hi[h]) ? s[n][j] * scale : -INFINITY;
+            s[n][j] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    float corr[2], sum[2] = {0.0f, 0.0f}, base[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float m_new = fmaxf(m[h], mx[h]);
+        base[h] = m_new == -INFINITY ? 0.0f : m_new;       // a row that has seen no key yet
+        corr[h] = expf(m[h] - base[h]);                    // exp(-inf) = 0
+        m[h] = m_new;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int h = j >> 1;
+            const float p = expf(s[n][j] - base[h]);       // masked: exp(-inf) = 0
+            s[n][j] = p;
+            sum[h] += p;
+        }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+        l[h] = l[h] * corr[h] + sum[h];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        o[n][0] *= corr[0];
+        o[n][1] *= corr[0];
+        o[n][2] *= corr[1];
+        o[n][3] *= corr[1];
+    }
+}
+
+// Q fragments of 16 rows: row r of the warp reads HD bf16 at q_rows[r] (nullptr: a zero row).
+template <int HD>
+__device__ __forceinline__ void load_q(uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* row_lo,
+                                       const __nv_bfloat16* row_hi, int lane) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+        const int d = k * 16 + 2 * t;
+        qf[k][0] = row_lo ? *reinterpret_cast<const uint32_t*>(row_lo + d) : 0u;
+        qf[k][1] = row_hi ? *reinterpret_cast<const uint32_t*>(row_hi + d) : 0u;
+        qf[k][2] = row_lo ? *reinterpret_cast<const uint32_t*>(row_lo + d + 8) : 0u;
+        qf[k][3] = row_hi ? *reinterpret_cast<const uint32_t*>(row_hi + d + 8) : 0u;
+    }
+}
+
+// ------------------------------------------------------------------ prefill
+// tile_seg[b], tile_tok0[b]: segment and first token (global index) of row tile b.
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
+                         const int* __restrict__ seg_start, const int* __restrict__ tile_seg,
+                         const int* __restrict__ tile_tok0, const int* __restrict__ block_table,
+                         int max_pages, __nv_bfloat16* __restrict__ out, int nh, int nkv, int group,
+                         int tokens_per_tile, int window, float scale) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int seg = tile_seg[blockIdx.x], tok0 = tile_tok0[blockIdx.x], kvh = blockIdx.y;
+    const int seg_end = seg_start[seg + 1];
+    int n_tok = seg_end - tok0;
+    if (n_tok > tokens_per_tile) n_tok = tokens_per_tile;
+    const int rows = n_tok * group;                         // valid rows of this tile (<= 64)
+    const int* table = block_table + (size_t)seg * max_pages;
+
+    // the two rows this thread owns inside its warp's 16: r = warp*16 + g (+8)
+    int tok[2], head[2], lo[2], hi[2];
+    const __nv_bfloat16* qrow[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = warp * 16 + g + 8 * h;
+        const bool valid = r < rows;
+        tok[h] = tok0 + (valid ? r / group : 0);
+        head[h] = kvh * group + (valid ? r % group : 0);
+        const int pos = positions[tok[h]];
+        hi[h] = valid ? pos : -1;                           // an invalid row sees no key
+        lo[h] = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+        qrow[h] = valid ? q + ((size_t)tok[h] * nh + head[h]) * HD : nullptr;
+    }
+    uint32_t qf[HD / 16][4];
+    load_q<HD>(qf, qrow[0], qrow[1], lane);
+
+    // keys this CTA walks: from the lowest key any row may see to the position of its last token
+    const int pos_first = positions[tok0], pos_last = positions[tok0 + n_tok - 1];
+    const int lo_block = window > 0 ? (pos_first - window + 1 > 0 ? pos_first - window + 1 : 0) : 0;
+    const int tile_begin = lo_block / KEYS, tile_end = pos_last / KEYS + 1;
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[n][j] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+    auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
+    auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
+    auto issue = [&](int tile, int s) {
+        const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
+        load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
+        cp_async_commit();
+    };
+    issue(tile_begin, 0);
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+        const int s = (tile - tile_begin) & 1;
+        if (tile + 1 < tile_end) {
+            issue(tile + 1, s ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (pos_last - tile * KEYS + 1 < KEYS) {
+            clear_v_rows<HD>(stage_v(s), pos_last - tile * KEYS + 1);
+            __syncthreads();
+        }
+        // a warp whose rows all lie before this tile's first key has nothing to do in it
+        const int warp_hi = __reduce_max_sync(0xffffffffu, hi[0] > hi[1] ? hi[0] : hi[1]);
+        if (warp_hi >= tile * KEYS) {
+            float sc[8][4];
+            qk_tile<HD, 8>(sc, qf, stage_k(s), 0, lane);
+            softmax_update<HD, 8>(sc, o, m, l, tile * KEYS, lo, hi, scale, lane);
+            pv_tile<HD, 8>(o, sc, stage_v(s), 0, lane);
+        }
+        __syncthreads();                                    // the stage may be overwritten next
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (hi[h] < 0) continue;
+        const float inv = 1.0f / l[h];
+        __nv_bfloat16* dst = out + ((size_t)tok[h] * nh + head[h]) * HD;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+            *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    }
+}
+
+// ------------------------------------------------------------------ decode
+// grid (splits, nkv, T).  A split covers `tiles_per_split` key tiles; with splits == 1 the
+// result goes straight to `out`, else (acc, max, sum) go to the scratch buffers:
+//   part_o[t][kvh][split][group][HD] fp32 (not normalised), part_ml[t][kvh][split][group][2].
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
+                        const int* __restrict__ tok_seg, const int* __restrict__ block_table,
+                        int max_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int nh, int nkv, int group, int tiles_per_split,
+                        int window, float scale) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __shared__ float merge_ml[WARPS][16][2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, tok = blockIdx.z;
+    const int pos = positions[tok];
+    const int lo_key = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+    const int* table = block_table + (size_t)tok_seg[tok] * max_pages;
+    const int first_tile = lo_key / KEYS, last_tile = pos / KEYS;
+    const int tile_begin = first_tile + split * tiles_per_split;
+    int tile_end = tile_begin + tiles_per_split;
+    if (tile_end > last_tile + 1) tile_end = last_tile + 1;
+
+    // rows 0..group-1 are the group's query heads; the rest are padding
+    const __nv_bfloat16* qrow0 = g < group ? q + ((size_t)tok * nh + kvh * group + g) * HD : nullptr;
+    const __nv_bfloat16* qrow1 = g + 8 < group ? q + ((size_t)tok * nh + kvh * group + g + 8) * HD : nullptr;
+    uint32_t qf[HD / 16][4];
+    load_q<HD>(qf, qrow0, qrow1, lane);
+    const int lo[2] = {lo_key, lo_key};
+    const int hi[2] = {g < group ? pos : -1, g + 8 < group ? pos : -1};
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[n][j] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+    auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
+    auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
+    auto issue = [&](int tile, int s) {
+        const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
+        load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
+        cp_async_commit();
+    };
+    if (tile_begin < tile_end) issue(tile_begin, 0);
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+        const int s = (tile - tile_begin) & 1;
+        if (tile + 1 < tile_end) {
+            issue(tile + 1, s ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (pos - tile * KEYS + 1 < KEYS) {
+            clear_v_rows<HD>(stage_v(s), pos - tile * KEYS + 1);
+            __syncthreads();
+        }
+        float sc[2][4];                                     // this warp's 16 keys of the tile
+        qk_tile<HD, 2>(sc, qf, stage_k(s), warp * 16, lane);
+        softmax_update<HD, 2>(sc, o, m, l, tile * KEYS + warp * 16, lo, hi, scale, lane);
+        pv_tile<HD, 2>(o, sc, stage_v(s), warp * 16, lane);
+        __syncthreads();
+    }
+
+    // ---- merge the four warps (each saw a quarter of the keys) through shared memory
+    float* merge_o = reinterpret_cast<float*>(smem_raw);    // [WARPS][16][HD] fp32, stages are free now
+    if (t == 0) {
+        merge_ml[warp][g][0] = m[0];
+        merge_ml[warp][g][1] = l[0];
+        merge_ml[warp][g + 8][0] = m[1];
+        merge_ml[warp][g + 8][1] = l[1];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        float* row0 = merge_o + ((size_t)warp * 16 + g) * HD + n * 8 + 2 * t;
+        float* row1 = merge_o + ((size_t)warp * 16 + g + 8) * HD + n * 8 + 2 * t;
+        row0[0] = o[n][0];
+        row0[1] = o[n][1];
+        row1[0] = o[n][2];
+        row1[1] = o[n][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * HD; i += WARPS * 32) {
+        const int r = i / HD, d = i - r * HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, merge_ml[w][r][0]);
+        const float base = mm == -INFINITY ? 0.0f : mm;
+        float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float c = expf(merge_ml[w][r][0] - base);
+            acc += c * merge_o[((size_t)w * 16 + r) * HD + d];
+            ll += c * merge_ml[w][r][1];
+        }
+        if (splits == 1) {
+            out[((size_t)tok * nh + kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / ll);
+        } else {
+            const size_t at = (((size_t)tok * nkv + kvh) * splits + split) * group + r;
+            part_o[at * HD + d] = acc;
+            if (d == 0) {
+                part_ml[at * 2] = mm;
+                part_ml[at * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+// grid (nkv, T), block 128: sum the splits in ascending order.
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       __nv_bfloat16* __restrict__ out, int nh, int nkv, int group, int hd,
+                                       int splits) {
+    const int kvh = blockIdx.x, tok = blockIdx.y;
+    const size_t base_at = ((size_t)tok * nkv + kvh) * splits;
+    for (int i = threadIdx.x; i < group * hd; i += blockDim.x) {
+        const int r = i / hd, d = i - r * hd;
+        float mm = -INFINITY;
+        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[((base_at + s) * group + r) * 2]);
+        float acc = 0.0f, ll = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const size_t at = (base_at + s) * group + r;
+            const float c = expf(part_ml[at * 2] - mm);     // a split without keys: exp(-inf) = 0
+            acc += c * part_o[at * hd + d];
+            ll += c * part_ml[at * 2 + 1];
+        }
+        out[((size_t)tok * nh + kvh * group + r) * hd + d] = __float2bfloat16_rn(acc / ll);
+    }
+}
+
+template <typename K>
+int opt_in_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return FWB_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    return e == cudaSuccess ? FWB_OK : (int)e;
+}
+
+template <int HD>
+int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const int* positions,
+                   const int* seg_start, const int* tile_seg, const int* tile_tok0, const int* block_table,
+                   int max_pages, void* out, int n_tiles, int nh, int nkv, int tokens_per_tile, int window,
+                   float scale, cudaStream_t stream) {
+    auto kernel = attention_prefill_kernel<HD>;
+    int st = opt_in_smem(kernel, Smem<HD>::BYTES);
+    if (st != FWB_OK) return st;
+    using bf = __nv_bfloat16;
+    kernel<<<dim3(n_tiles, nkv), WARPS * 32, Smem<HD>::BYTES, stream>>>(
+        (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, seg_start, tile_seg, tile_tok0,
+        block_table, max_pages, (bf*)out, nh, nkv, nh / nkv, tokens_per_tile, window, scale);
+    return fwb_launch_status();
+}
+
+template <int HD>
+int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* positions,
+                  const int* tok_seg, const int* block_table, int max_pages, void* out, float* part_o,
+                  float* part_ml, int T, int nh, int nkv, int splits, int tiles_per_split, int window,
+                  float scale, cudaStream_t stream) {
+    auto kernel = attention_decode_kernel<HD>;
+    constexpr size_t merge_bytes = (size_t)WARPS * 16 * HD * 4;
+    constexpr size_t bytes = Smem<HD>::BYTES > merge_bytes ? Smem<HD>::BYTES : merge_bytes;
+    int st = opt_in_smem(kernel, bytes);
+    if (st != FWB_OK) return st;
+    using bf = __nv_bfloat16;
+    kernel<<<dim3(splits, nkv, T), WARPS * 32, bytes, stream>>>(
+        (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
+        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale);
+    st = fwb_launch_status();
+    if (st != FWB_OK || splits == 1) return st;
+    attention_merge_kernel<<<dim3(nkv, T), 128, 0, stream>>>(part_o, part_ml, (bf*)out, nh, nkv, nh / nkv, HD,
+                                                             splits);
+    return fwb_launch_status();
+}
+
+bool shape_ok(int nh, int nkv, int hd, int page_size) {
+    return nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16 && hd >= 16 && hd <= 128 && hd % 16 == 0 &&
+           page_size == KEYS && nkv <= 65535;
+}
+
+}  // namespace
+
+#define FWB_HD_SWITCH(hd, CALL)                  \
+    switch (hd) {                                \
+        case 16: return CALL(16);                \
+        case 32: return CALL(32);                \
+        case 48: return CALL(48);                \
+        case 64: return CALL(64);                \
+        case 80: return CALL(80);                \
+        case 96: return CALL(96);                \
+        case 112: return CALL(112);              \
+        case 128: return CALL(128);              \
+        default: return FWB_UNSUPPORTED;         \
+    }
+
+// Prompt portions (and anything else): q, out [T][nh*hd] bf16; pools [pages][nkv][64][hd] bf16.
+// tile_seg, tile_tok0: [n_tiles], a tile holds up to `tokens_per_tile` = 64 / group consecutive
+// tokens of one segment.
+FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const void* v_pool,
+                                      const int* positions, const int* seg_start, const int* tile_seg,
+                                      const int* tile_tok0, const int* block_table, int max_pages,
+                                      int page_size, void* out, int n_tiles, int nh, int nkv, int hd,
+                                      int tokens_per_tile, int window, float scale, cudaStream_t stream) {
+    if (n_tiles <= 0) return FWB_OK;
+    if (!q || !k_pool || !v_pool || !positions || !seg_start || !tile_seg || !tile_tok0 || !block_table || !out)
+        return FWB_BAD_ARGUMENT;
+    if (!shape_ok(nh, nkv, hd, page_size)) return FWB_UNSUPPORTED;
+    if (tokens_per_tile < 1 || tokens_per_tile * (nh / nkv) > 64) return FWB_BAD_ARGUMENT;
+#define CALL(HD)                                                                                          \
+    launch_prefill<HD>(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, block_table, max_pages, \
+                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, stream)
+    FWB_HD_SWITCH(hd, CALL)
+#undef CALL
+}
+
+// Decode tokens: one query token each.  With splits > 1, part_o needs T*nkv*splits*group*hd
+// floats and part_ml T*nkv*splits*group*2 floats of scratch.
+FWB_API int fwb_attention_decode_mma(const void* q, const void* k_pool, const void* v_pool,
+                                     const int* positions, const int* tok_seg, const int* block_table,
+                                     int max_pages, int page_size, void* out, float* part_o, float* part_ml,
+                                     int T, int nh, int nkv, int hd, int splits, int tiles_per_split,
+                                     int window, float scale, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!q || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out) return FWB_BAD_ARGUMENT;
+    if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
+    if (splits < 1 || tiles_per_split < 1 || (splits > 1 && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
+#define CALL(HD)                                                                                          \
+    launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, out, part_o, part_ml, T, \
+                      nh, nkv, splits, tiles_per_split, window, scale, stream)
+    FWB_HD_SWITCH(hd, CALL)
+#undef CALL
+}

@@ -78,6 +78,31 @@ class StepBatch:
         self.block_tables = [dev[start:start + s * w].view(s, w) for start, s, w in table_slices]
         self.max_context = max((seg.pos0 + len(seg.tokens) for seg in self.segments), default=0)
         self.max_segment = max((len(seg.tokens) for seg in self.segments), default=0)
+        self._device = device
+        self._tiles = {}
+
+    def attention_tiles(self, tokens_per_tile: int):
+        """Row tiles for the tiled attention kernel: every segment cut into runs of at most
+        ``tokens_per_tile`` tokens.  Returns (tile_seg, tile_tok0, n_tiles), int32 on the
+        device; made once per step and tile size."""
+        cached = self._tiles.get(tokens_per_tile)
+        if cached is None:
+            seg_of, tok0 = [], []
+            base = 0
+            for index, seg in enumerate(self.segments):
+                for start in range(0, len(seg.tokens), tokens_per_tile):
+                    seg_of.append(index)
+                    tok0.append(base + start)
+                base += len(seg.tokens)
+            host = torch.tensor(seg_of + tok0, dtype=torch.int32)
+            self.h2d_bytes += host.numel() * 4
+            if self._device is not None and torch.device(self._device).type == "cuda":
+                dev = host.pin_memory().to(self._device, non_blocking=True)
+            else:
+                dev = host
+            n = len(seg_of)
+            cached = self._tiles[tokens_per_tile] = (dev[:n], dev[n:], n)
+        return cached
 
 
 @dataclass

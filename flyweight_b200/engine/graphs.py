@@ -1,0 +1,121 @@
+"""CUDA graphs for decode steps.
+
+A decode step (every request brings exactly one token and wants its logits) is the same
+sequence of ~100 small kernel launches every time; only the contents of the batch
+arrays change.  For each (batch size, block-table width) the runner captures that
+sequence once into a CUDA graph over *static* device buffers, and afterwards a step is
+one upload of the batch arrays and one graph launch.  (flyweight captures only the dense
+feed-forward, seven launches per layer: native/src/v2_runtime.cpp:28797-28830.)
+
+The batch arrays live in one int32 buffer with the same fields as ``StepBatch``.  The
+upload goes through a small ring of pinned host buffers guarded by events, because the
+host may run several steps ahead of the device.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from ..kernels.lib import add_launches, launch_count
+from .batch import Segment, StepContext
+
+RING = 4
+
+
+class DecodeBatch:
+    """The fields of ``StepBatch`` for B one-token segments, over static buffers."""
+
+    def __init__(self, batch_size: int, n_groups: int, width: int, device):
+        B = self.n_segments = self.n_tokens = self.n_logit_rows = batch_size
+        self.width = width
+        self.n_groups = n_groups
+        fields = (("token_ids", B), ("positions", B), ("tok_seg", B), ("seg_start", B + 1),
+                  ("seg_slot", B), ("seg_pos0", B), ("logit_rows", B))
+        self._offsets = {}
+        cursor = 0
+        for name, count in fields:
+            self._offsets[name] = (cursor, count)
+            cursor += count
+        self._table_offsets = []
+        for _ in range(n_groups):
+            self._table_offsets.append(cursor)
+            cursor += B * width
+        self.size = cursor
+        self._dev = torch.zeros(cursor, dtype=torch.int32, device=device)
+        self._hosts = [torch.zeros(cursor, dtype=torch.int32).pin_memory() for _ in range(RING)]
+        self._events = [None] * RING
+        self._turn = 0
+        for name, (start, count) in self._offsets.items():
+            setattr(self, name, self._dev[start:start + count])
+        self.block_tables = [self._dev[start:start + B * width].view(B, width)
+                             for start in self._table_offsets]
+        self.segments: List[Segment] = []
+        self.max_segment = 1
+        self.max_context = 0
+        self.h2d_bytes = cursor * 4
+        # the parts that never change
+        for host in self._hosts:
+            start, _ = self._offsets["tok_seg"]
+            host[start:start + B] = torch.arange(B, dtype=torch.int32)
+            start, _ = self._offsets["seg_start"]
+            host[start:start + B + 1] = torch.arange(B + 1, dtype=torch.int32)
+            start, _ = self._offsets["logit_rows"]
+            host[start:start + B] = torch.arange(B, dtype=torch.int32)
+
+    def upload(self, segments: Sequence[Segment], tables: Sequence[List[List[int]]]) -> None:
+        turn = self._turn
+        self._turn = (turn + 1) % RING
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()      # the copy that last used this buffer is done
+        host = self._hosts[turn]
+        B = self.n_segments
+        values = host.numpy()
+        start = self._offsets["token_ids"][0]
+        values[start:start + B] = [seg.tokens[0] for seg in segments]
+        start = self._offsets["positions"][0]
+        values[start:start + B] = [seg.pos0 for seg in segments]
+        start = self._offsets["seg_slot"][0]
+        values[start:start + B] = [seg.slot for seg in segments]
+        start = self._offsets["seg_pos0"][0]
+        values[start:start + B] = [seg.pos0 for seg in segments]
+        for offset, rows in zip(self._table_offsets, tables):
+            values[offset:offset + B * self.width].reshape(B, self.width)[:] = rows
+        self._dev.copy_(host, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._events[turn] = event
+        self.segments = list(segments)
+        self.max_context = max(seg.pos0 + 1 for seg in segments)
+
+
+class DecodeGraph:
+    def __init__(self, model, caches, precision, device, bad_token_flag, batch_size: int,
+                 n_groups: int, width: int):
+        self.model = model
+        self.caches = caches
+        self.batch = DecodeBatch(batch_size, n_groups, width, device)
+        self.ctx = StepContext(self.batch, precision, device, bad_token_flag)
+        self.graph = None
+        self.logits = None
+        self.kernels = 0
+
+    def run(self, segments, tables) -> torch.Tensor:
+        """The step for these segments.  The first call runs the kernels directly and then
+        records the graph; later calls replay it.  The returned logits are a static buffer:
+        they are overwritten by the next step of the same batch size."""
+        self.batch.upload(segments, tables)
+        if self.graph is None:
+            logits = self.model.forward(self.ctx, self.caches)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = launch_count()
+            with torch.cuda.graph(graph):
+                self.logits = self.model.forward(self.ctx, self.caches)
+            self.kernels = launch_count() - before     # recorded, not run
+            add_launches(-self.kernels)
+            self.graph = graph
+            return logits
+        self.graph.replay()
+        add_launches(self.kernels)
+        return self.logits

@@ -20,6 +20,7 @@ import torch
 from ..cache.manager import PAGE_SIZE, CacheManager, OutOfPages, OutOfSlots
 from ..kernels.lib import require_cuda
 from .batch import Segment, StepBatch, StepContext
+from .graphs import DecodeGraph
 
 Entry = Tuple[Hashable, Sequence[int], Sequence[int]]
 
@@ -110,7 +111,7 @@ class StepPlanner:
 
 class ModelRunner(StepPlanner):
     def __init__(self, model, num_pages: int, num_slots: int, max_model_len: int,
-                 max_batched_tokens: int = 8192):
+                 max_batched_tokens: int = 8192, use_graphs: bool = True):
         require_cuda()
         self.model = model
         self.precision = model.precision
@@ -123,6 +124,11 @@ class ModelRunner(StepPlanner):
                              cache_dtype=self.precision.cache_dtype, device=self.device)
         super().__init__(cache, model.spec.vocab_size, max_model_len, max_batched_tokens)
         self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # decode steps replay a CUDA graph per (batch size, block-table width)
+        self.use_graphs = bool(use_graphs) and model.graph_safe
+        self.max_graph_batch = 256
+        self._graphs = {}
+        self.graph_replays = 0
         self.steps = 0
         self.tokens_run = 0
         self.h2d_bytes = 0
@@ -133,7 +139,27 @@ class ModelRunner(StepPlanner):
         segments = self.plan(entries)
         requests = [seg.request for seg in segments]
         width = self.cache.max_table_len(requests)
-        tables = [self.cache.block_table(g, requests, width) for g in range(len(self.cache.groups))]
+        n_groups = len(self.cache.groups)
+        if (self.use_graphs and len(segments) <= self.max_graph_batch
+                and all(len(seg.tokens) == 1 and seg.want == [0] for seg in segments)):
+            bucket = 4
+            while bucket < width:
+                bucket *= 2
+            tables = [self.cache.block_table(g, requests, bucket) for g in range(n_groups)]
+            key = (len(segments), bucket)
+            graph = self._graphs.get(key)
+            if graph is None:
+                graph = self._graphs[key] = DecodeGraph(
+                    self.model, self.cache.layer_caches, self.precision, self.device,
+                    self.bad_token_flag, len(segments), n_groups, bucket)
+            else:
+                self.graph_replays += 1
+            logits = graph.run(segments, tables)
+            self.steps += 1
+            self.tokens_run += len(segments)
+            self.h2d_bytes += graph.batch.h2d_bytes
+            return logits
+        tables = [self.cache.block_table(g, requests, width) for g in range(n_groups)]
         batch = StepBatch(segments, tables, self.device)
         ctx = StepContext(batch, self.precision, self.device, self.bad_token_flag)
         logits = self.model.forward(ctx, self.cache.layer_caches)

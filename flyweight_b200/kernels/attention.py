@@ -1,11 +1,64 @@
-"""Dispatch between the attention kernels for one step's batch."""
+"""Dispatch between the attention kernels for one step's batch.
+
+bfloat16 cache and a shape the tensor-core kernels take: a step of single decode tokens runs
+the split-context decode kernel, anything else the tiled prefill kernel.  Everything else
+(the 32-bit path, head sizes above 128, more than 16 query heads per KV head) runs the SIMT
+kernel.
+"""
 from __future__ import annotations
 
+import torch
+
 from . import ops
+
+SM_COUNT = 148
+_use_mma = True
+
+
+def set_mma_enabled(flag: bool) -> None:
+    """Tests switch the tensor-core kernels off to compare them with the SIMT kernel."""
+    global _use_mma
+    _use_mma = bool(flag)
+
+
+_force_tiled = False
+
+
+def force_tiled(flag: bool) -> None:
+    """Send single decode tokens through the tiled kernel too.  A row of that kernel is summed
+    in one order whatever else is in the step, so tests can compare cuts bit by bit."""
+    global _force_tiled
+    _force_tiled = bool(flag)
+
+
+def decode_splits(n_tokens: int, n_kv: int, max_tiles: int):
+    """How many slices of the context run as separate CTAs: enough to put about two CTAs on
+    every SM, never more slices than 64-key tiles.  Depends only on static sizes of the step
+    (tokens, KV heads, block-table width), so a captured graph stays valid."""
+    ctas = max(1, n_tokens * n_kv)
+    splits = max(1, min(max_tiles, -(-2 * SM_COUNT // ctas)))
+    tiles_per_split = -(-max_tiles // splits)
+    splits = -(-max_tiles // tiles_per_split)
+    return splits, tiles_per_split
 
 
 def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype):
     """Causal GQA of every token of the step over its request's pages."""
     batch = ctx.batch
-    return ops.attention_simt(q, cache.k_pool, cache.v_pool, batch.positions, batch.tok_seg,
-                              block_table, n_heads, window, scale, out_dtype)
+    k_pool, v_pool = cache.k_pool, cache.v_pool
+    _, n_kv, page_size, head_dim = k_pool.shape
+    if (_use_mma and q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
+            and out_dtype == torch.bfloat16
+            and ops.attention_mma_shape_ok(n_heads, n_kv, head_dim, page_size)):
+        if batch.max_segment == 1 and not _force_tiled:
+            splits, tiles_per_split = decode_splits(batch.n_tokens, n_kv, block_table.shape[1])
+            return ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg,
+                                            block_table, n_heads, window, scale, splits,
+                                            tiles_per_split)
+        tokens_per_tile = max(1, 64 // (n_heads // n_kv))
+        tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile)
+        return ops.attention_prefill_mma(q, k_pool, v_pool, batch.positions, batch.seg_start,
+                                         tile_seg, tile_tok0, n_tiles, tokens_per_tile, block_table,
+                                         n_heads, window, scale)
+    return ops.attention_simt(q, k_pool, v_pool, batch.positions, batch.tok_seg, block_table,
+                              n_heads, window, scale, out_dtype)

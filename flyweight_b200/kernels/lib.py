@@ -45,6 +45,12 @@ def launch_count() -> int:
     return _launch_count
 
 
+def add_launches(count: int) -> None:
+    """Kernels launched by replaying a CUDA graph that was recorded through this module."""
+    global _launch_count
+    _launch_count += count
+
+
 def require_cuda() -> None:
     if not torch.cuda.is_available():
         raise KernelError("flyweight_b200 runs on a CUDA device (sm_100a) only; none is visible "

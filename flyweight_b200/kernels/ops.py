@@ -215,3 +215,59 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
              ptr(positions), ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size,
              ptr(out), is_bf16(out), T, n_heads, n_kv, head_dim, window, c_float(scale), stream())
     return out
+
+
+def attention_mma_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    """Shapes the tensor-core attention kernels take (the SIMT kernel takes the rest)."""
+    return (n_heads % n_kv == 0 and n_heads // n_kv <= 16 and 16 <= head_dim <= 128
+            and head_dim % 16 == 0 and page_size == 64)
+
+
+def attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
+                          tokens_per_tile, block_table, n_heads, window, scale) -> torch.Tensor:
+    """Causal GQA of prompt portions (any mix of segments) on tensor cores; all bf16."""
+    check_tensor("q", q, torch.bfloat16)
+    check_tensor("k pool", k_pool, torch.bfloat16)
+    check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
+    T = q.shape[0]
+    _, n_kv, page_size, head_dim = k_pool.shape
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError(f"q has {q.shape[1]} columns, expected {n_heads * head_dim}")
+    _i32("positions", positions, T)
+    _i32("seg_start", seg_start)
+    _i32("tile_seg", tile_seg, n_tiles)
+    _i32("tile_tok0", tile_tok0, n_tiles)
+    _i32("block table", block_table)
+    out = torch.empty_like(q)
+    lib.call("fwb_attention_prefill_mma", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
+             ptr(seg_start), ptr(tile_seg), ptr(tile_tok0), ptr(block_table), block_table.shape[1],
+             page_size, ptr(out), n_tiles, n_heads, n_kv, head_dim, tokens_per_tile, window,
+             c_float(scale), stream())
+    return out
+
+
+def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_heads, window, scale,
+                         splits: int, tiles_per_split: int) -> torch.Tensor:
+    """Causal GQA of single decode tokens on tensor cores, the context cut into ``splits``
+    slices of ``tiles_per_split`` 64-key tiles that run as separate CTAs and are merged."""
+    check_tensor("q", q, torch.bfloat16)
+    check_tensor("k pool", k_pool, torch.bfloat16)
+    check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
+    T = q.shape[0]
+    _, n_kv, page_size, head_dim = k_pool.shape
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError(f"q has {q.shape[1]} columns, expected {n_heads * head_dim}")
+    _i32("positions", positions, T)
+    _i32("tok_seg", tok_seg, T)
+    _i32("block table", block_table)
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if splits > 1:
+        group = n_heads // n_kv
+        part_o = torch.empty((T, n_kv, splits, group, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T, n_kv, splits, group, 2), dtype=torch.float32, device=q.device)
+    lib.call("fwb_attention_decode_mma", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
+             ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size, ptr(out), ptr(part_o),
+             ptr(part_ml), T, n_heads, n_kv, head_dim, splits, tiles_per_split, window,
+             c_float(scale), stream(), launches=2 if splits > 1 else 1)
+    return out

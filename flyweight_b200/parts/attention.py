@@ -23,6 +23,8 @@ class GQAttention(Mixer):
     q/k norm), position (PartSpec of a position encoding), window (0: all keys),
     shares_cache (True: reads the cache of another execution and projects q only).
     tensors: q, k, v, o, q_norm, k_norm."""
+    graph_safe = True
+
 
     def __init__(self, spec):
         super().__init__(spec)

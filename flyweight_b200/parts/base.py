@@ -87,6 +87,10 @@ class FixedState:
 # ------------------------------------------------------------------ part interfaces
 class Part:
     kind: str = ""
+    # True when forward() only launches kernels whose arguments are device buffers of the
+    # step's batch (nothing read on the host), so a decode step may be captured in a CUDA
+    # graph and replayed with new batch contents.  Parts defined elsewhere default to False.
+    graph_safe: bool = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

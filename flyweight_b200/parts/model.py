@@ -59,6 +59,12 @@ class DecoderModel:
             for part in layer.parts():
                 part.bind(get, precision, device)
 
+    @property
+    def graph_safe(self) -> bool:
+        """Every part only launches kernels over the step's device buffers."""
+        return all(part.graph_safe for layer in self.layers for part in layer.parts()) \
+            and self.final_norm.graph_safe
+
     def prepare(self, max_positions: int) -> None:
         for layer in self.layers:
             layer.mixer.prepare(max_positions, self.device)

@@ -14,6 +14,8 @@ from .base import Norm, Precision, register_norm
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
     """params: size, eps.  tensors: weight [size]."""
+    graph_safe = True
+
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -19,6 +19,8 @@ from .base import FixedState, Mixer, Precision, register_mixer
 class GatedShortConv(Mixer):
     """params: hidden_size, taps (L >= 2), bias (bool).
     tensors: in_proj [3H][H], taps [H][L] (also stored as [H][1][L]), out_proj [H][H], bias [H]."""
+    graph_safe = True
+
 
     def __init__(self, spec):
         super().__init__(spec)

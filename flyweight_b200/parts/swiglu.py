@@ -13,6 +13,8 @@ from .base import FeedForward, Precision, register_feed_forward
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     """params: hidden_size, ffn_dim.  tensors: gate [F][H], up [F][H], down [H][F]."""
+    graph_safe = True
+
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -283,6 +283,17 @@ def build_paged(k_seqs, v_seqs, n_pages, dtype, shuffle_seed=0, fill=float("nan"
     return k_pool.to(dtype), v_pool.to(dtype), table
 
 
+def make_ctx(lens, new, table, k_pool, v_pool):
+    """A step context over hand-made pools: segment s has lens[s] tokens cached after the step,
+    the last new[s] of them brought by it."""
+    from flyweight_b200.engine import Segment, StepBatch, StepContext
+    segments = [Segment(f"s{i}", i, n - m, [0] * m, []) for i, (n, m) in enumerate(zip(lens, new))]
+    batch = StepBatch(segments, [table.tolist()], DEV)
+    cache = type("Cache", (), {})()
+    cache.k_pool, cache.v_pool = dev(k_pool), dev(v_pool)
+    return StepContext(batch, None, DEV), cache, batch.block_tables[0]
+
+
 ATTN_SHAPES = [(4, 2, 16), (3, 1, 32), (6, 6, 48), (8, 1, 64), (32, 8, 64), (5, 5, 80), (16, 1, 128),
                (2, 1, 256)]
 
@@ -311,25 +322,13 @@ def test_paged_attention_mixed_batch(nh, nkv, hd, dtype, window):
     want = torch.stack([attention_reference(q[t], k_seqs[tok_seg[t]], v_seqs[tok_seg[t]], positions[t],
                                             window, scale, nh // nkv) for t in range(len(qs))])
 
-    class Ctx:
-        pass
-    ctx, cache = Ctx(), Ctx()
-    ctx.batch = Ctx()
-    ctx.batch.positions = dev(torch.tensor(positions, dtype=torch.int32))
-    ctx.batch.tok_seg = dev(torch.tensor(tok_seg, dtype=torch.int32))
-    seg_start = np.cumsum([0] + new)
-    ctx.batch.seg_start = dev(torch.tensor(seg_start, dtype=torch.int32))
-    ctx.batch.seg_pos0 = dev(torch.tensor([n - m for n, m in zip(lens, new)], dtype=torch.int32))
-    ctx.batch.n_segments, ctx.batch.n_tokens = len(lens), len(qs)
-    ctx.batch.max_context, ctx.batch.max_segment = max(lens), max(new)
-    ctx.batch.segments = [type("S", (), {"pos0": n - m, "tokens": [0] * m})() for n, m in zip(lens, new)]
-    cache.k_pool, cache.v_pool = dev(k_pool), dev(v_pool)
+    ctx, cache, table_dev = make_ctx(lens, new, table, k_pool, v_pool)
     qd = dev(q.reshape(len(qs), nh * hd).to(dtype))
     tol = 1e-5 if dtype == torch.float32 else 2.0 ** -7
     got = ops.attention_simt(qd, cache.k_pool, cache.v_pool, ctx.batch.positions, ctx.batch.tok_seg,
-                             dev(table), nh, window, scale, dtype)
+                             table_dev, nh, window, scale, dtype)
     close(got.reshape(-1, nh, hd), want, tol, "SIMT attention")
-    got = attention_kernels.paged_attention(ctx, qd, cache, dev(table), nh, window, scale, dtype)
+    got = attention_kernels.paged_attention(ctx, qd, cache, table_dev, nh, window, scale, dtype)
     close(got.reshape(-1, nh, hd), want, tol, "dispatched attention")
 
 
@@ -505,3 +504,55 @@ def test_tcgen05_refuses_what_tma_cannot_address():
     with pytest.raises(KernelError, match="unsupported"):
         tc.gemm(x, w, torch.float32)
     assert not tc.accepts(x.float(), w, torch.float32)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (32, 8, 64), (6, 2, 80), (16, 1, 128), (5, 5, 48)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_decode_attention_over_split_contexts(nh, nkv, hd, window):
+    """A step of single tokens at very different context lengths (1 .. 1500 keys): the
+    tensor-core decode kernel with the context cut into slices, merged, against fp64."""
+    from flyweight_b200.kernels import attention as attention_kernels, ops
+    g = torch.Generator().manual_seed(nh * 3 + hd)
+    lens = [1, 64, 65, 700, 1500, 257]
+    new = [1] * len(lens)
+    k_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    v_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    k_pool, v_pool, table = build_paged(k_seqs, v_seqs, 48, torch.bfloat16, shuffle_seed=hd + 1)
+    q = torch.stack([bf16_round(torch.randn(nh, hd, generator=g).double()) for _ in lens])
+    scale = 1.0 / math.sqrt(hd)
+    want = torch.stack([attention_reference(q[t], k_seqs[t], v_seqs[t], lens[t] - 1, window, scale, nh // nkv)
+                        for t in range(len(lens))])
+    ctx, cache, table_dev = make_ctx(lens, new, table, k_pool, v_pool)
+    qd = dev(q.reshape(len(lens), nh * hd).to(torch.bfloat16))
+    assert ctx.batch.max_segment == 1
+    got = attention_kernels.paged_attention(ctx, qd, cache, table_dev, nh, window, scale, torch.bfloat16)
+    close(got.reshape(-1, nh, hd), want, 2.0 ** -7, "decode attention")
+    for splits, per in ((1, 24), (2, 12), (5, 5), (24, 1)):
+        got = ops.attention_decode_mma(qd, cache.k_pool, cache.v_pool, ctx.batch.positions, ctx.batch.tok_seg,
+                                       table_dev, nh, window, scale, splits, per)
+        close(got.reshape(-1, nh, hd), want, 2.0 ** -7, f"{splits} splits")
+
+
+def test_tensor_core_attention_finds_a_far_key_and_the_window_edge():
+    from flyweight_b200.kernels import attention as attention_kernels
+    g = torch.Generator().manual_seed(12)
+    nh, nkv, hd, n = 4, 2, 64, 700
+    scale = 1.0 / math.sqrt(hd)
+    for target, window in ((3, 0), (63, 0), (64, 0), (639, 0), (640, 0), (699, 0), (600, 100), (599, 100)):
+        k = bf16_round(torch.randn(n, nkv, hd, generator=g).double() * 0.1)
+        v = bf16_round(torch.randn(n, nkv, hd, generator=g).double())
+        direction = torch.zeros(hd, dtype=torch.float64)
+        direction[target % hd] = 1.0
+        k[target, :, :] = direction * 16.0
+        q = (direction * 16.0).repeat(nh, 1)
+        k_pool, v_pool, table = build_paged([k], [v], 12, torch.bfloat16, shuffle_seed=target)
+        want = attention_reference(q, k, v, n - 1, window, scale, nh // nkv)
+        for new in (1, 5):                                   # decode kernel, then the tiled kernel
+            ctx, cache, table_dev = make_ctx([n], [new], table, k_pool, v_pool)
+            qd = dev(q.reshape(1, -1).to(torch.bfloat16).repeat(new, 1))
+            got = attention_kernels.paged_attention(ctx, qd, cache, table_dev, nh, window, scale, torch.bfloat16)
+            close(got[-1].reshape(nh, hd), want, 2.0 ** -7, f"target {target} window {window} new {new}")
+            if window == 0 or target > n - 1 - window:
+                close(got[-1].reshape(nh, hd)[0], v[target, 0], 2.0 ** -6, f"value of key {target}")
+            else:                                            # the shouting key is outside the window
+                assert (got[-1].reshape(nh, hd)[0].double().cpu() - v[target, 0]).abs().max() > 0.1
