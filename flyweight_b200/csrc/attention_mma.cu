@@ -215,6 +215,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ tile_tok0, const int* __restrict__ block_table,
                          int max_pages, __nv_bfloat16* __restrict__ out, int nh, int nkv, int group,
                          int tokens_per_tile, int window, float scale) {
+    fwb::pdl_entry();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,6 +310,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int max_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int group, int tiles_per_split,
                         int window, float scale) {
+    fwb::pdl_entry();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __shared__ float merge_ml[WARPS][16][2];
@@ -414,6 +416,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int group, int hd,
                                        int splits) {
+    fwb::pdl_entry();
     const int kvh = blockIdx.x, tok = blockIdx.y;
     const size_t base_at = ((size_t)tok * nkv + kvh) * splits;
     for (int i = threadIdx.x; i < group * hd; i += blockDim.x) {
@@ -447,7 +450,7 @@ int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const 
     int st = opt_in_smem(kernel, Smem<HD>::BYTES);
     if (st != FWB_OK) return st;
     using bf = __nv_bfloat16;
-    kernel<<<dim3(n_tiles, nkv), WARPS * 32, Smem<HD>::BYTES, stream>>>(
+    fwb::pdl(kernel, dim3(n_tiles, nkv), WARPS * 32, Smem<HD>::BYTES, stream)(
         (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, seg_start, tile_seg, tile_tok0,
         block_table, max_pages, (bf*)out, nh, nkv, nh / nkv, tokens_per_tile, window, scale);
     return fwb_launch_status();
@@ -464,12 +467,12 @@ int launch_decode(const void* q, const void* k_pool, const void* v_pool, const i
     int st = opt_in_smem(kernel, bytes);
     if (st != FWB_OK) return st;
     using bf = __nv_bfloat16;
-    kernel<<<dim3(splits, nkv, T), WARPS * 32, bytes, stream>>>(
+    fwb::pdl(kernel, dim3(splits, nkv, T), WARPS * 32, bytes, stream)(
         (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
         (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale);
     st = fwb_launch_status();
     if (st != FWB_OK || splits == 1) return st;
-    attention_merge_kernel<<<dim3(nkv, T), 128, 0, stream>>>(part_o, part_ml, (bf*)out, nh, nkv, nh / nkv, HD,
+    fwb::pdl(attention_merge_kernel, dim3(nkv, T), 128, 0, stream)(part_o, part_ml, (bf*)out, nh, nkv, nh / nkv, HD,
                                                              splits);
     return fwb_launch_status();
 }

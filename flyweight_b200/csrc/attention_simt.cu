@@ -29,6 +29,7 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pool,
                       const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                       int max_pages, int page_size, TO* __restrict__ out, int nh, int nkv, int hd,
                       int window, float scale) {
+    fwb::pdl_entry();
     extern __shared__ float smem[];
     const int group = nh / nkv;
     float* qs = smem;                         // [group][hd]
@@ -136,7 +137,7 @@ FWB_API int fwb_attention_simt(const void* q, int q_bf16, const void* k_pool, co
                                                  (int)smem);                                      \
             if (e != cudaSuccess) return (int)e;                                                  \
         }                                                                                         \
-        kernel<<<grid, WARPS * 32, smem, stream>>>((const TQ*)q, (const TC*)k_pool,               \
+        fwb::pdl(kernel, grid, WARPS * 32, smem, stream)((const TQ*)q, (const TC*)k_pool,               \
                                                    (const TC*)v_pool, positions, tok_seg,         \
                                                    block_table, max_pages, page_size, (TO*)out,   \
                                                    nh, nkv, hd, window, scale);                   \

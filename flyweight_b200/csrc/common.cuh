@@ -24,6 +24,52 @@ static inline int fwb_launch_status() {
 
 namespace fwb {
 
+// ---- programmatic dependent launch ------------------------------------------------
+// Every kernel of the library is launched with programmatic stream serialisation: the next
+// kernel in the stream may be scheduled while this one still runs, and does its set-up
+// (shared-memory barriers, tensor-memory allocation, weight prefetch) in that shadow.
+// pdl_wait() returns once the previous kernel has completed and its writes are visible; no
+// kernel reads or writes anything another kernel touches before it.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_entry() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+
+inline bool& pdl_enabled() {
+    static bool enabled = true;
+    return enabled;
+}
+
+template <typename Kernel>
+struct PdlLauncher {
+    Kernel kernel;
+    dim3 grid, block;
+    size_t smem;
+    cudaStream_t stream;
+    template <typename... Args>
+    void operator()(Args... args) const {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = grid;
+        config.blockDim = block;
+        config.dynamicSmemBytes = smem;
+        config.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attr;
+        config.numAttrs = pdl_enabled() ? 1 : 0;
+        cudaLaunchKernelEx(&config, kernel, args...);   // errors surface through fwb_launch_status()
+    }
+};
+template <typename Kernel>
+PdlLauncher<Kernel> pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    return PdlLauncher<Kernel>{kernel, grid, block, smem, stream};
+}
+
 // ---- element access: everything is computed in fp32, stored as T --------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

@@ -11,6 +11,7 @@ using namespace fwb;
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int T, int H, int V, int* bad) {
+    fwb::pdl_entry();
     const int t = blockIdx.y;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
@@ -25,10 +26,10 @@ FWB_API int fwb_embed(const void* table, int table_bf16, const int* ids, float* 
     if (!table || !ids || !out || H <= 0 || V <= 0 || T > 65535) return FWB_BAD_ARGUMENT;
     dim3 grid((H + 255) / 256 > 64 ? 64 : (H + 255) / 256, T);
     if (table_bf16)
-        embed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        fwb::pdl(embed_kernel<__nv_bfloat16>, grid, 256, 0, stream)(
             (const __nv_bfloat16*)table, ids, out, T, H, V, bad);
     else
-        embed_kernel<float><<<grid, 256, 0, stream>>>((const float*)table, ids, out, T, H, V, bad);
+        fwb::pdl(embed_kernel<float>, grid, 256, 0, stream)((const float*)table, ids, out, T, H, V, bad);
     return fwb_launch_status();
 }
 
@@ -43,6 +44,7 @@ template <typename TO>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                const float* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int H, float eps) {
+    fwb::pdl_entry();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
@@ -66,21 +68,96 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
 }
 
+// The same operation for rows that fit the registers of one block (H a multiple of 4, at most
+// VEC float4 per thread): every load of the row is in flight at once and the row is read once.
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w,
+                   TO* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    fwb::pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int n4 = H >> 2;
+    float4 wv[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {           // the weight is nobody's output: load it early
+        const int c = threadIdx.x + i * 256;
+        wv[i] = c < n4 ? reinterpret_cast<const float4*>(w)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    fwb::pdl_wait();
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    float4* xr = reinterpret_cast<float4*>(x + s * H);
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + s * H) : nullptr;
+    const bool store = dr && !rows;
+    float4 v[VEC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const int c = threadIdx.x + i * 256;
+        v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (dr) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const int c = threadIdx.x + i * 256;
+            if (c < n4) {
+                const float4 d = dr[c];
+                v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
+                if (store) xr[c] = v[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c >= n4) continue;
+        const float a = (v[i].x * inv) * wv[i].x, b = (v[i].y * inv) * wv[i].y;
+        const float cc = (v[i].z * inv) * wv[i].z, d = (v[i].w * inv) * wv[i].w;
+        if (sizeof(TO) == 4) {
+            reinterpret_cast<float4*>(orow)[c] = make_float4(a, b, cc, d);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(cc, d);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(orow)[c] = packed;
+        }
+    }
+}
+
 FWB_API int fwb_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_bf16,
                         const int* rows, int R, int H, float eps, cudaStream_t stream) {
     if (R <= 0) return FWB_OK;
     if (!x || !w || !out || H <= 0) return FWB_BAD_ARGUMENT;
+    const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                         (!delta || ((uintptr_t)delta & 15) == 0);
+    if ((H & 3) == 0 && H >= 512 && H <= 4 * 256 * 4 && aligned) {
+        using bf = __nv_bfloat16;
+        const int vec = (H / 4 + 255) / 256;
+#define FWB_NORM(V)                                                                                     \
+    if (out_bf16) fwb::pdl(rmsnorm_vec_kernel<bf, V>, R, 256, 0, stream)(x, delta, w, (bf*)out, rows, H, eps); \
+    else fwb::pdl(rmsnorm_vec_kernel<float, V>, R, 256, 0, stream)(x, delta, w, (float*)out, rows, H, eps)
+        if (vec == 1) { FWB_NORM(1); } else if (vec == 2) { FWB_NORM(2); } else if (vec == 3) { FWB_NORM(3); } else { FWB_NORM(4); }
+#undef FWB_NORM
+        return fwb_launch_status();
+    }
     const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
     if (out_bf16)
-        rmsnorm_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>(x, delta, w, (__nv_bfloat16*)out,
+        fwb::pdl(rmsnorm_kernel<__nv_bfloat16>, R, threads, 0, stream)(x, delta, w, (__nv_bfloat16*)out,
                                                                 rows, H, eps);
     else
-        rmsnorm_kernel<float><<<R, threads, 0, stream>>>(x, delta, w, (float*)out, rows, H, eps);
+        fwb::pdl(rmsnorm_kernel<float>, R, threads, 0, stream)(x, delta, w, (float*)out, rows, H, eps);
     return fwb_launch_status();
 }
 
 // x += delta (fp32), for a residual that no norm follows.
 __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ delta, size_t n) {
+    fwb::pdl_entry();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x)
         x[i] += delta[i];
@@ -90,7 +167,7 @@ FWB_API int fwb_add(float* x, const float* delta, long long n, cudaStream_t stre
     if (n <= 0) return FWB_OK;
     if (!x || !delta) return FWB_BAD_ARGUMENT;
     const int blocks = (int)((n + 255) / 256 > 4096 ? 4096 : (n + 255) / 256);
-    add_kernel<<<blocks, 256, 0, stream>>>(x, delta, (size_t)n);
+    fwb::pdl(add_kernel, blocks, 256, 0, stream)(x, delta, (size_t)n);
     return fwb_launch_status();
 }
 
@@ -99,6 +176,7 @@ FWB_API int fwb_add(float* x, const float* delta, long long n, cudaStream_t stre
 // out[t][f] = silu(gate) * up.
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int F) {
+    fwb::pdl_entry();
     const size_t n = (size_t)T * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x) {
@@ -116,13 +194,13 @@ FWB_API int fwb_silu_mul(const void* gu, int in_bf16, void* out, int out_bf16, i
     const size_t n = (size_t)T * F;
     const int blocks = (int)((n + 255) / 256 > 8192 ? 8192 : (n + 255) / 256);
     if (in_bf16 && out_bf16)
-        silu_mul_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        fwb::pdl(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream)(
             (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F);
     else if (!in_bf16 && out_bf16)
-        silu_mul_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        fwb::pdl(silu_mul_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream)(
             (const float*)gu, (__nv_bfloat16*)out, T, F);
     else if (!in_bf16 && !out_bf16)
-        silu_mul_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, T, F);
+        fwb::pdl(silu_mul_kernel<float, float>, blocks, 256, 0, stream)((const float*)gu, (float*)out, T, F);
     else
         return FWB_UNSUPPORTED;
     return fwb_launch_status();
@@ -131,6 +209,7 @@ FWB_API int fwb_silu_mul(const void* gu, int in_bf16, void* out, int out_bf16, i
 // ------------------------------------------------------------------ casts
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    fwb::pdl_entry();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x)
         out[i] = from_f32<TO>(to_f32<TI>(in[i]));
@@ -142,10 +221,10 @@ FWB_API int fwb_cast(const void* in, int in_bf16, void* out, int out_bf16, long 
     if (!in || !out || in_bf16 == out_bf16) return FWB_BAD_ARGUMENT;
     const int blocks = (int)((n + 255) / 256 > 8192 ? 8192 : (n + 255) / 256);
     if (in_bf16)
-        cast_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in,
+        fwb::pdl(cast_kernel<__nv_bfloat16, float>, blocks, 256, 0, stream)((const __nv_bfloat16*)in,
                                                                        (float*)out, (size_t)n);
     else
-        cast_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)in,
+        fwb::pdl(cast_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream)((const float*)in,
                                                                        (__nv_bfloat16*)out, (size_t)n);
     return fwb_launch_status();
 }

@@ -17,6 +17,7 @@ template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restrict__ Y,
                  const float* __restrict__ addend, int M, int N, int K, int ldx, int ldy) {
+    fwb::pdl_entry();
     __shared__ float xs[TK][TM + 4];
     __shared__ float ws[TK][TN + 4];
     const int tid = threadIdx.x;
@@ -72,7 +73,7 @@ int launch(const void* X, const void* W, void* Y, const float* addend, int M, in
            int ldy, cudaStream_t stream) {
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (grid.y > 65535) return FWB_TOO_LARGE;
-    gemm_simt_kernel<TX, TW, TY><<<grid, 256, 0, stream>>>((const TX*)X, (const TW*)W, (TY*)Y,
+    fwb::pdl(gemm_simt_kernel<TX, TW, TY>, grid, 256, 0, stream)((const TX*)X, (const TW*)W, (TY*)Y,
                                                            addend, M, N, K, ldx, ldy);
     return fwb_launch_status();
 }

@@ -23,6 +23,11 @@
 // Epilogues: store fp32 / store bf16 / add an fp32 addend (the residual) and store fp32 /
 // SwiGLU: two accumulators (gate rows f, up rows F+f of the same matrix), silu(g)*u as bf16.
 //
+// The kernel is launched with programmatic stream serialisation: it may start while the kernel
+// before it still runs, sets up its barriers and tensor memory and requests its first ring of
+// WEIGHT tiles (which nothing in the stream writes) in that shadow, and touches activations,
+// addend and output only after griddepcontrol.wait.
+//
 // Every wait on an mbarrier is bounded: after the limit the CTA raises the library's status
 // word, stops waiting everywhere, still meets its cluster barriers, frees its TMEM and
 // returns.
@@ -170,7 +175,7 @@ struct Tile {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = NACC * A_BYTES + B_BYTES;
     static constexpr int RAW_STAGES = SMEM_BUDGET / STAGE_BYTES;
-    static constexpr int STAGES = RAW_STAGES > 8 ? 8 : RAW_STAGES;
+    static constexpr int STAGES = RAW_STAGES > 6 ? 6 : RAW_STAGES;   // <= 110 KiB: two CTAs fit an SM
     static constexpr int COLS = BN * NACC;                      // TMEM columns in use
     static constexpr int TMEM_COLS = COLS <= 32 ? 32 : (COLS <= 64 ? 64 : (COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512)));
     static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
@@ -202,6 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
+    pdl_launch_dependents();     // the next kernel may set itself up in this one's shadow
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feat0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
     const int splits = gridDim.z;
@@ -228,10 +234,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            // Weights do not depend on the kernel before this one: the first ring of weight
+            // tiles is requested before waiting for it, the activations after.
+            const int ahead = n_kb < T::STAGES ? n_kb : T::STAGES;
+            for (int i = 0; i < ahead; ++i) {
+                uint8_t* stage = tiles + (size_t)i * T::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], T::STAGE_BYTES);
+                const int k = (kb_begin + i) * BK;
+                tma_load_2d(stage, &map_w, &full_bar[i], k, feat0);
+                if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[i], k, prm.up_row_offset + feat0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES + NACC * T::A_BYTES, &map_x, &full_bar[i],
+                            (kb_begin + i) * BK, tok0);
+            for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % T::STAGES;
                 const uint32_t round = i / T::STAGES;
-                if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, abort_flag, 1)) break;
+                if (!mbar_wait(&empty_bar[s], (round - 1) & 1, abort_flag, 1)) break;
                 uint8_t* stage = tiles + (size_t)s * T::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
@@ -275,6 +295,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int row = quarter * 32 + lane;           // feature inside the tile
     bool acc_ready = true;
     if (epi_warp) {
+        pdl_wait();              // the addend is read and Y written only after the previous kernel
+
         if (n_kb > 0) acc_ready = mbar_wait(acc_bar, 0, abort_flag, 3);
         acc_ready = acc_ready && !*abort_flag;
         acc_ready = __all_sync(0xffffffffu, acc_ready);   // tcgen05.ld needs the whole warp
@@ -397,13 +419,15 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& prm
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = T::SMEM_BYTES;
     config.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = 1;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_w, map_x, prm);
     return e == cudaSuccess ? fwb_launch_status() : (int)e;
 }
@@ -472,4 +496,10 @@ FWB_API int fwb_gemm_tcgen05_status() {
     if (cudaMemcpyFromSymbol(&value, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
     if (value) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
     return value;
+}
+
+// Programmatic dependent launch for every kernel of the library: 1 = on (default), 0 = off.
+FWB_API int fwb_set_pdl(int enabled) {
+    fwb::pdl_enabled() = enabled != 0;
+    return FWB_OK;
 }

@@ -27,6 +27,7 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
                     const int* __restrict__ block_table, int max_pages, int page_size,
                     TQ* __restrict__ q_out, TC* __restrict__ k_pool, TC* __restrict__ v_pool, int nh,
                     int nkv, int hd, int rot, float eps, int use_norm) {
+    fwb::pdl_entry();
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -41,7 +42,7 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
         cache_base = ((size_t)page * nkv) * page_size * hd + (size_t)(pos % page_size) * hd;
     }
     const int heads = nh + 2 * nkv;
-    for (int h = warp; h < heads; h += WARPS) {
+    for (int h = blockIdx.y * WARPS + warp; h < heads; h += gridDim.y * WARPS) {
         const TI* src = row + (size_t)h * hd;
         if (h >= nh + nkv) {  // v: copy
             const int kvh = h - nh - nkv;
@@ -107,9 +108,13 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
     if (use_norm && (!wq || (nkv > 0 && !wk))) return FWB_BAD_ARGUMENT;
     if (hd <= 0 || hd > MAX_HD || (hd & 1) || rot < 0 || rot > hd || (rot & 1)) return FWB_UNSUPPORTED;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
+    // one warp per head; few tokens (decode) spread their heads over several blocks
+    const int head_blocks = T >= 256 ? 1 : (nh + 2 * nkv + WARPS - 1) / WARPS;
+    if (T > 2147483647 / 1 || head_blocks > 65535) return FWB_TOO_LARGE;
+    const dim3 grid(T, head_blocks);
     using bf = __nv_bfloat16;
 #define FWB_QK(TI, TQ, TC)                                                                        \
-    qk_norm_rope_kernel<TI, TQ, TC><<<T, WARPS * 32, smem, stream>>>(                             \
+    fwb::pdl(qk_norm_rope_kernel<TI, TQ, TC>, grid, WARPS * 32, smem, stream)(                             \
         (const TI*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table, max_pages, \
         page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm)
     const int key = (in_bf16 ? 4 : 0) | (q_bf16 ? 2 : 0) | (cache_bf16 ? 1 : 0);

@@ -69,6 +69,7 @@ __device__ unsigned long long block_max_key(unsigned long long v, unsigned long 
 // ------------------------------------------------------------------ greedy
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    fwb::pdl_entry();
     __shared__ unsigned long long scratch[33];
     const float* row = logits + (size_t)blockIdx.x * V;
     unsigned long long best = 0ull;
@@ -78,6 +79,46 @@ argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
     }
     best = block_max_key(best, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = key_id(best);
+}
+
+// The same over `chunks` blocks per row: every block writes the best key of its slice, and the
+// block that finds itself last for its row (a self-resetting counter) reduces the slices.  The
+// maximum of distinct keys does not depend on the order, so the result is the same every time.
+// partial: [R][chunks] keys; counters: [R] ints, zero before the first launch and left zero.
+__global__ void __launch_bounds__(256)
+argmax_split_kernel(const float* __restrict__ logits, int V, int* __restrict__ out,
+                    unsigned long long* __restrict__ partial, int* __restrict__ counters) {
+    fwb::pdl_entry();
+    __shared__ unsigned long long scratch[33];
+    __shared__ int last;
+    const int r = blockIdx.y, chunk = blockIdx.x, chunks = gridDim.x;
+    const float* row = logits + (size_t)r * V;
+    const int per = (V + chunks - 1) / chunks;
+    const int begin = chunk * per, end = begin + per < V ? begin + per : V;
+    unsigned long long best = 0ull;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const unsigned long long key = make_key(row[i], i);
+        best = key > best ? key : best;
+    }
+    best = block_max_key(best, scratch);
+    if (threadIdx.x == 0) {
+        partial[(size_t)r * chunks + chunk] = best;
+        __threadfence();
+        last = atomicAdd(&counters[r], 1) == chunks - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    best = 0ull;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+        const unsigned long long key = *(volatile unsigned long long*)&partial[(size_t)r * chunks + i];
+        best = key > best ? key : best;
+    }
+    best = block_max_key(best, scratch);
+    if (threadIdx.x == 0) {
+        out[r] = key_id(best);
+        counters[r] = 0;
+    }
 }
 
 // Descending bitonic sort of n (a power of two) keys by the whole block.
@@ -161,6 +202,7 @@ __global__ void __launch_bounds__(THREADS)
 sample_small_kernel(const float* __restrict__ logits, int V, const RowParams* __restrict__ params,
                     const double* __restrict__ uniform, const int* __restrict__ recent,
                     int recent_stride, int* __restrict__ out) {
+    fwb::pdl_entry();
     __shared__ unsigned long long keys[SMALL_K];
     __shared__ unsigned long long scratch[33];
     __shared__ double probs[SMALL_K];
@@ -259,6 +301,7 @@ sample_large_kernel(const float* __restrict__ logits, int V, int Vpad,
                     const RowParams* __restrict__ params, const double* __restrict__ uniform,
                     unsigned long long* __restrict__ keys_all, double* __restrict__ probs_all,
                     int* __restrict__ out) {
+    fwb::pdl_entry();
     const int r = blockIdx.x;
     if (out[r] != -1) return;
     const RowParams prm = params[r];
@@ -272,10 +315,18 @@ sample_large_kernel(const float* __restrict__ logits, int V, int Vpad,
 
 }  // namespace
 
-FWB_API int fwb_argmax(const float* logits, int R, int V, int* out, cudaStream_t stream) {
+// With scratch (partial: R*chunks keys of 8 bytes, counters: R zeroed ints) a row is cut into
+// `chunks` slices that run as separate blocks; without it one block scans a row.
+FWB_API int fwb_argmax(const float* logits, int R, int V, int* out, void* partial, int* counters,
+                       int chunks, cudaStream_t stream) {
     if (R <= 0) return FWB_OK;
     if (!logits || !out || V <= 0) return FWB_BAD_ARGUMENT;
-    argmax_kernel<<<R, THREADS, 0, stream>>>(logits, V, out);
+    if (partial && counters && chunks > 1 && R <= 65535) {
+        fwb::pdl(argmax_split_kernel, dim3(chunks, R), 256, 0, stream)(
+            logits, V, out, (unsigned long long*)partial, counters);
+        return fwb_launch_status();
+    }
+    fwb::pdl(argmax_kernel, R, THREADS, 0, stream)(logits, V, out);
     return fwb_launch_status();
 }
 
@@ -290,12 +341,12 @@ FWB_API int fwb_sample(const float* logits, int R, int V, const void* params, co
     if (R <= 0) return FWB_OK;
     if (!logits || !out || !params || !uniform || V <= 0) return FWB_BAD_ARGUMENT;
     if (recent_stride > MAX_RECENT || (recent_stride > 0 && !recent)) return FWB_BAD_ARGUMENT;
-    sample_small_kernel<<<R, THREADS, 0, stream>>>(logits, V, (const RowParams*)params, uniform,
+    fwb::pdl(sample_small_kernel, R, THREADS, 0, stream)(logits, V, (const RowParams*)params, uniform,
                                                    recent, recent_stride, out);
     int status = fwb_launch_status();
     if (status != FWB_OK || !need_large) return status;
     if (!keys_scratch || !probs_scratch || Vpad < V || (Vpad & (Vpad - 1))) return FWB_BAD_ARGUMENT;
-    sample_large_kernel<<<R, THREADS, 0, stream>>>(logits, V, Vpad, (const RowParams*)params, uniform,
+    fwb::pdl(sample_large_kernel, R, THREADS, 0, stream)(logits, V, Vpad, (const RowParams*)params, uniform,
                                                    (unsigned long long*)keys_scratch, probs_scratch,
                                                    out);
     return fwb_launch_status();

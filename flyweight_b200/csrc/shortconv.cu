@@ -28,6 +28,7 @@ __global__ void shortconv_kernel(const TP* __restrict__ p, const float* __restri
                                  const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                                  const int* __restrict__ tok_seg, TZ* __restrict__ z, int T, int S,
                                  int H, int L, int body_blocks) {
+    fwb::pdl_entry();
     const int ld = 3 * H;
     if ((int)blockIdx.x < body_blocks) {
         const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -91,7 +92,7 @@ FWB_API int fwb_shortconv(const void* p, int p_bf16, const float* taps, const fl
     const int blocks = body_blocks + head_blocks;
     using bf = __nv_bfloat16;
 #define FWB_CONV(TP, TZ)                                                                          \
-    shortconv_kernel<TP, TZ><<<blocks, threads, 0, stream>>>(                                     \
+    fwb::pdl(shortconv_kernel<TP, TZ>, blocks, threads, 0, stream)(                                     \
         (const TP*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (TZ*)z, T, S, H, L,        \
         body_blocks)
     if (p_bf16 && z_bf16) FWB_CONV(bf, bf);

@@ -142,9 +142,7 @@ class ModelRunner(StepPlanner):
         n_groups = len(self.cache.groups)
         if (self.use_graphs and len(segments) <= self.max_graph_batch
                 and all(len(seg.tokens) == 1 and seg.want == [0] for seg in segments)):
-            bucket = 4
-            while bucket < width:
-                bucket *= 2
+            bucket = 16 * (-(-width // 16))         # a new graph every 1,024 tokens of context
             tables = [self.cache.block_table(g, requests, bucket) for g in range(n_groups)]
             key = (len(segments), bucket)
             graph = self._graphs.get(key)

@@ -25,8 +25,25 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     check_tensor("logits", logits, torch.float32)
     R, V = logits.shape
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    lib.call("fwb_argmax", ptr(logits), R, V, ptr(out), stream())
+    chunks = max(1, min(64, V // 2048))
+    partial, counters = _argmax_scratch(logits.device, R * chunks, R)
+    lib.call("fwb_argmax", ptr(logits), R, V, ptr(out), ptr(partial), ptr(counters), chunks, stream())
     return out
+
+
+_scratch = {}
+
+
+def _argmax_scratch(device, n_partial: int, n_rows: int):
+    """Scratch of the split argmax: slice maxima and per-row arrival counters (kept zero by the
+    kernel itself).  One buffer per device, grown when a larger batch comes."""
+    key = str(device)
+    held = _scratch.get(key)
+    if held is None or held[0].numel() < n_partial or held[1].numel() < n_rows:
+        held = (torch.empty(max(n_partial, 4096), dtype=torch.int64, device=device),
+                torch.zeros(max(n_rows, 256), dtype=torch.int32, device=device))
+        _scratch[key] = held
+    return held
 
 
 def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Sequence[float],
