@@ -123,6 +123,8 @@ class CacheManager:
         self._slot_of: Dict[Hashable, int] = {}
         self._length: Dict[Hashable, int] = {}
         self._fixed_positions: List[int] = []
+        self._serial: Dict[Hashable, int] = {}
+        self._admissions = 0
         self.slots_high_water = 0
         by_window: Dict[int, int] = {}
         for position, spec in enumerate(state_specs):
@@ -159,6 +161,10 @@ class CacheManager:
     def slot(self, request: Hashable) -> int:
         return self._slot_of[request]
 
+    def serial(self, request: Hashable) -> int:
+        """A number that is new for every admission (a name may come back after a release)."""
+        return self._serial[request]
+
     @property
     def free_slots(self) -> int:
         return len(self._free_slots)
@@ -172,6 +178,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         self._slot_of[request] = slot
         self._length[request] = 0
+        self._admissions += 1
+        self._serial[request] = self._admissions
         self.slots_high_water = max(self.slots_high_water, len(self._slot_of))
         for group in self.groups:
             group.tables[request] = []
@@ -212,14 +220,16 @@ class CacheManager:
         return sum(max(0, need - group.pool.n_free)
                    for need, group in zip(self.pages_needed(request, new_length), self.groups))
 
-    def extend(self, request: Hashable, new_length: int) -> None:
+    def extend(self, request: Hashable, new_length: int, checked: bool = False) -> None:
         """Map pages so positions < ``new_length`` of ``request`` have a home.  Raises
-        ``OutOfPages`` and maps nothing if some group cannot."""
+        ``OutOfPages`` and maps nothing if some group cannot.  ``checked``: the caller has
+        already made sure that the pages are there (the step function checks a whole step)."""
         if new_length < self._length[request]:
             raise ValueError("a request's length never shrinks")
-        short = self.pages_short(request, new_length)
-        if short:
-            raise OutOfPages(f"request {request!r} needs {short} more pages than are free")
+        if not checked:
+            short = self.pages_short(request, new_length)
+            if short:
+                raise OutOfPages(f"request {request!r} needs {short} more pages than are free")
         for group in self.groups:
             table = group.tables[request]
             while len(table) * PAGE_SIZE < new_length:
@@ -230,6 +240,7 @@ class CacheManager:
         """Give back everything ``request`` holds."""
         slot = self._slot_of.pop(request)
         del self._length[request]
+        del self._serial[request]
         for group in self.groups:
             for page in group.tables.pop(request):
                 if page >= 0:

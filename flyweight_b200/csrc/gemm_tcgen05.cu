@@ -46,7 +46,13 @@ constexpr int THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
-enum Epilogue : int { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+// The WIDE forms give a CTA two adjacent 128-feature tiles (two accumulators over the same
+// token tile): per MMA the activations are read from L2 once for 256 features, which is what
+// keeps the tensor pipe fed at prefill sizes.
+enum Epilogue : int { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3,
+                      EPI_F32_WIDE = 4, EPI_BF16_WIDE = 5 };
+constexpr bool epi_wide(int epi) { return epi == EPI_F32_WIDE || epi == EPI_BF16_WIDE; }
+constexpr int epi_accumulators(int epi) { return (epi == EPI_SWIGLU_BF16 || epi_wide(epi)) ? 2 : 1; }
 
 __device__ int g_gemm_status = 0;   // 0 = fine; else the code of the first wait that gave up
 
@@ -153,6 +159,11 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank
     return v;
 }
 
+// silu for the bfloat16 epilogue: g / (1 + e^-g) with the hardware exponential and reciprocal.
+// The result is rounded to bfloat16 (8 bits) right away; their few-ulp fp32 error is far below
+// that.  For g << 0, e^-g overflows to +inf and the quotient is -0, the right limit.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
 // K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     uint64_t d = 0;
@@ -175,12 +186,17 @@ struct Tile {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = NACC * A_BYTES + B_BYTES;
     static constexpr int RAW_STAGES = SMEM_BUDGET / STAGE_BYTES;
-    static constexpr int STAGES = RAW_STAGES > 6 ? 6 : RAW_STAGES;   // <= 110 KiB: two CTAs fit an SM
+    static constexpr int MAX_STAGES = RAW_STAGES > 8 ? 8 : RAW_STAGES;
+    // the default ring keeps a CTA under ~110 KiB so that two fit an SM (the next kernel's CTAs
+    // can then be resident and prefetch weights while this kernel still runs)
+    static constexpr int DEFAULT_STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
     static constexpr int COLS = BN * NACC;                      // TMEM columns in use
     static constexpr int TMEM_COLS = COLS <= 32 ? 32 : (COLS <= 64 ? 64 : (COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512)));
-    static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int PARTIAL_BYTES = COLS * BM * 4;         // fp32 partial tile for split-K
-    static constexpr int SMEM_BYTES = (PIPE_BYTES > PARTIAL_BYTES ? PIPE_BYTES : PARTIAL_BYTES) + 1024 + 256;
+    static constexpr int PARTIAL_BYTES = BN <= 64 ? COLS * BM * 4 : 0;   // fp32 partial tile for split-K
+    static constexpr int data_bytes(int stages) {
+        return stages * STAGE_BYTES > PARTIAL_BYTES ? stages * STAGE_BYTES : PARTIAL_BYTES;
+    }
+    static constexpr int smem_bytes(int stages) { return data_bytes(stages) + 1024 + 256; }
 };
 
 struct Params {
@@ -190,26 +206,30 @@ struct Params {
     int ldy;
     int up_row_offset;     // SwiGLU: rows of the up projection start here in W
     int k_blocks_per_split;
+    int stages;            // depth of the shared-memory ring (<= Tile::MAX_STAGES)
 };
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const Params prm) {
-    constexpr int NACC = EPI == EPI_SWIGLU_BF16 ? 2 : 1;
+    constexpr int NACC = epi_accumulators(EPI);
+    constexpr bool WIDE = epi_wide(EPI);
     using T = Tile<BN, NACC>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + (T::PIPE_BYTES > T::PARTIAL_BYTES ? T::PIPE_BYTES : T::PARTIAL_BYTES));
-    uint64_t* empty_bar = full_bar + T::STAGES;
-    uint64_t* acc_bar = empty_bar + T::STAGES;
+    const int STAGES = prm.stages;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + T::data_bytes(STAGES));
+    uint64_t* empty_bar = full_bar + T::MAX_STAGES;
+    uint64_t* acc_bar = empty_bar + T::MAX_STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     pdl_launch_dependents();     // the next kernel may set itself up in this one's shadow
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int feat0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
+    const int feat0 = blockIdx.x * (WIDE ? 2 * BM : BM), tok0 = blockIdx.y * BN;
+    const int second_tile_row = WIDE ? feat0 + BM : prm.up_row_offset + feat0;   // accumulator 1's rows of W
     const int splits = gridDim.z;
     const int total_kb = (prm.K + BK - 1) / BK;
     const int kb_begin = blockIdx.z * prm.k_blocks_per_split;
@@ -218,7 +238,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int n_kb = kb_end > kb_begin ? kb_end - kb_begin : 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < T::STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
@@ -236,27 +256,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             // Weights do not depend on the kernel before this one: the first ring of weight
             // tiles is requested before waiting for it, the activations after.
-            const int ahead = n_kb < T::STAGES ? n_kb : T::STAGES;
+            const int ahead = n_kb < STAGES ? n_kb : STAGES;
             for (int i = 0; i < ahead; ++i) {
                 uint8_t* stage = tiles + (size_t)i * T::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[i], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 tma_load_2d(stage, &map_w, &full_bar[i], k, feat0);
-                if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[i], k, prm.up_row_offset + feat0);
+                if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[i], k, second_tile_row);
             }
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
                 tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES + NACC * T::A_BYTES, &map_x, &full_bar[i],
                             (kb_begin + i) * BK, tok0);
             for (int i = ahead; i < n_kb; ++i) {
-                const int s = i % T::STAGES;
-                const uint32_t round = i / T::STAGES;
+                const int s = i % STAGES;
+                const uint32_t round = i / STAGES;
                 if (!mbar_wait(&empty_bar[s], (round - 1) & 1, abort_flag, 1)) break;
                 uint8_t* stage = tiles + (size_t)s * T::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 tma_load_2d(stage, &map_w, &full_bar[s], k, feat0);
-                if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[s], k, prm.up_row_offset + feat0);
+                if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[s], k, second_tile_row);
                 tma_load_2d(stage + NACC * T::A_BYTES, &map_x, &full_bar[s], k, tok0);
             }
         }
@@ -265,8 +285,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             constexpr uint32_t idesc = make_idesc(BN);
             bool ok = true;
             for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % T::STAGES;
-                const uint32_t round = i / T::STAGES;
+                const int s = i % STAGES;
+                const uint32_t round = i / STAGES;
                 ok = mbar_wait(&full_bar[s], round & 1, abort_flag, 2);
                 if (!ok) break;
                 tc_fence_after();
@@ -311,9 +331,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (t >= prm.M || f >= prm.N) return;
         const size_t at = (size_t)t * prm.ldy + f;
         if (EPI == EPI_F32) reinterpret_cast<float*>(prm.y)[at] = g;
-        else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(prm.y)[at] = g + prm.addend[at];
+        else if (EPI == EPI_F32_WIDE) {
+            reinterpret_cast<float*>(prm.y)[at] = g;
+            if (f + BM < prm.N) reinterpret_cast<float*>(prm.y)[at + BM] = u;
+        } else if (EPI == EPI_BF16_WIDE) {
+            reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g);
+            if (f + BM < prm.N) reinterpret_cast<__nv_bfloat16*>(prm.y)[at + BM] = __float2bfloat16_rn(u);
+        } else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(prm.y)[at] = g + prm.addend[at];
         else if (EPI == EPI_BF16) reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g);
-        else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(silu_f32(g) * u);
+        else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(silu_fast(g) * u);
     };
 
     if (splits == 1) {
@@ -403,21 +429,26 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows)
 }
 
 template <int BN, int EPI>
-int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& prm, int splits,
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, Params prm, int splits,
            cudaStream_t stream) {
-    constexpr int NACC = EPI == EPI_SWIGLU_BF16 ? 2 : 1;
+    constexpr int NACC = epi_accumulators(EPI);
     using T = Tile<BN, NACC>;
     auto kernel = gemm_tcgen05_kernel<BN, EPI>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             T::smem_bytes(T::MAX_STAGES));
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    if (prm.stages <= 0) prm.stages = T::DEFAULT_STAGES;
+    if (prm.stages > T::MAX_STAGES) prm.stages = T::MAX_STAGES;
+    if (prm.stages < 2) prm.stages = 2;
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((prm.N + BM - 1) / BM, (prm.M + BN - 1) / BN, splits);
+    constexpr int FEATURES = epi_wide(EPI) ? 2 * BM : BM;
+    config.gridDim = dim3((prm.N + FEATURES - 1) / FEATURES, (prm.M + BN - 1) / BN, splits);
     config.blockDim = dim3(THREADS);
-    config.dynamicSmemBytes = T::SMEM_BYTES;
+    config.dynamicSmemBytes = T::smem_bytes(prm.stages);
     config.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -440,6 +471,8 @@ int launch_epi(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, cons
         case EPI_BF16: return launch<BN, EPI_BF16>(map_w, map_x, prm, splits, stream);
         case EPI_ADD_F32: return launch<BN, EPI_ADD_F32>(map_w, map_x, prm, splits, stream);
         case EPI_SWIGLU_BF16: return launch<BN, EPI_SWIGLU_BF16>(map_w, map_x, prm, splits, stream);
+        case EPI_F32_WIDE: return launch<BN, EPI_F32_WIDE>(map_w, map_x, prm, splits, stream);
+        case EPI_BF16_WIDE: return launch<BN, EPI_BF16_WIDE>(map_w, map_x, prm, splits, stream);
         default: return FWB_UNSUPPORTED;
     }
 }
@@ -449,11 +482,13 @@ int launch_epi(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, cons
 // X: [M][K] bf16; W: [rows][K] bf16 (rows = N, or >= up_row_offset + N for SwiGLU);
 // Y: [M][ldy] (fp32 for epilogues 0 and 2, bf16 for 1 and 3).  `splits` (1..8) CTAs share the
 // K range of a tile as a cluster; with splits > 1 the token tile must be <= 64 wide.
+// `stages` sets the depth of the shared-memory ring (0: the default).  `tile_tokens` (0: by M)
+// may ask for a 128-token tile where 256 would be picked; `wide` gives a CTA two feature tiles.
 // K must be a multiple of 8 (TMA strides are multiples of 16 bytes) and both base
 // pointers 16-byte aligned; anything else is refused.
 FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float* addend, int M, int N,
                              int K, int w_rows, int ldy, int epilogue, int up_row_offset, int splits,
-                             cudaStream_t stream) {
+                             int stages, int tile_tokens, int wide, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return FWB_OK;
     if (!X || !W || !Y || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
     if ((K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FWB_UNSUPPORTED;
@@ -461,9 +496,22 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     if (epilogue == EPI_SWIGLU_BF16 && (up_row_offset < N || w_rows < up_row_offset + N)) return FWB_BAD_ARGUMENT;
     if (epilogue != EPI_SWIGLU_BF16 && w_rows < N) return FWB_BAD_ARGUMENT;
     if (splits < 1 || splits > 8) return FWB_BAD_ARGUMENT;
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
-    const bool swiglu = epilogue == EPI_SWIGLU_BF16;
-    const int bn_eff = (swiglu && bn == 256) ? 128 : bn;     // two accumulators: 2 x 256 columns would fill TMEM
+    int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+    if (tile_tokens == 16 || tile_tokens == 32 || tile_tokens == 64 || tile_tokens == 128 || tile_tokens == 256) {
+        if (tile_tokens < bn && tile_tokens >= 128) bn = tile_tokens;      // a smaller tile: more CTAs
+    } else if (tile_tokens != 0) {
+        return FWB_BAD_ARGUMENT;
+    }
+    const int bn_eff = bn;
+    // a full token tile and enough features: two 128-feature tiles per CTA (all 512 TMEM columns)
+    // (`wide`: 1 = yes, 0 = no, -1 = when single tiles would not fit the GPU in one wave; measured
+    // at 2,048 tokens on B200: 2048-feature products are faster narrow, 3072 and up faster wide)
+    const long narrow_ctas = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+    const bool go_wide = wide == 1 || (wide < 0 && bn == 256 && narrow_ctas > 148);
+    if (go_wide && bn >= 128 && N >= 2 * BM && splits == 1) {
+        if (epilogue == EPI_F32) epilogue = EPI_F32_WIDE;
+        else if (epilogue == EPI_BF16) epilogue = EPI_BF16_WIDE;
+    }
     if (splits > 1 && bn_eff > 64) return FWB_UNSUPPORTED;
     if ((M + bn_eff - 1) / bn_eff > 65535) return FWB_TOO_LARGE;
     const int total_kb = (K + BK - 1) / BK;
@@ -477,6 +525,7 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     prm.ldy = ldy;
     prm.up_row_offset = up_row_offset;
     prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
+    prm.stages = stages;
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, W, w_rows, K, BM)) return FWB_UNSUPPORTED;
     if (!make_map(&map_x, X, M, K, bn_eff)) return FWB_UNSUPPORTED;

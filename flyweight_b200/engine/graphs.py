@@ -54,39 +54,60 @@ class DecodeBatch:
         self.max_segment = 1
         self.max_context = 0
         self.h2d_bytes = cursor * 4
-        # the parts that never change
-        for host in self._hosts:
-            start, _ = self._offsets["tok_seg"]
-            host[start:start + B] = torch.arange(B, dtype=torch.int32)
-            start, _ = self._offsets["seg_start"]
-            host[start:start + B + 1] = torch.arange(B + 1, dtype=torch.int32)
-            start, _ = self._offsets["logit_rows"]
-            host[start:start + B] = torch.arange(B, dtype=torch.int32)
+        # host mirror of the arrays; the parts that never change are written once
+        import numpy as np
+        self._current = np.zeros(cursor, dtype=np.int32)
+        for name, count in (("tok_seg", B), ("seg_start", B + 1), ("logit_rows", B)):
+            start = self._offsets[name][0]
+            self._current[start:start + count] = np.arange(count, dtype=np.int32)
+        self._views = tuple(self._current[self._offsets[name][0]:self._offsets[name][0] + B]
+                            for name in ("token_ids", "seg_slot", "seg_pos0"))
+        self._table_rows = [self._current[start:start + B * width].reshape(B, width)
+                            for start in self._table_offsets]
+        for rows in self._table_rows:
+            rows[:] = -1
+        self._stamps = [[None] * B for _ in range(n_groups)]
+        self._host_arrays = [host.numpy() for host in self._hosts]
 
-    def upload(self, segments: Sequence[Segment], tables: Sequence[List[List[int]]]) -> None:
+    def upload(self, segments: Sequence[Segment], cache) -> None:
+        """Refresh the batch arrays for these one-token segments and send them to the device.
+        Block-table rows are rewritten only for requests whose table changed since the last
+        step of this batch size (a row grows by one page every 64 tokens)."""
+        B = self.n_segments
+        values = self._current
+        tokens, slots, pos0 = self._views
+        for index, seg in enumerate(segments):
+            tokens[index] = seg.tokens[0]
+            slots[index] = seg.slot
+            pos0[index] = seg.pos0
+        start = self._offsets["positions"][0]
+        values[start:start + B] = pos0
+        for g, offset in enumerate(self._table_offsets):
+            group = cache.groups[g]
+            rows = self._table_rows[g]
+            stamps = self._stamps[g]
+            for index, seg in enumerate(segments):
+                table = group.tables[seg.request]
+                stamp = (cache.serial(seg.request), len(table),
+                         group.window and sum(1 for p in table if p < 0))
+                if stamps[index] != stamp:
+                    stamps[index] = stamp
+                    row = rows[index]
+                    row[:len(table)] = table
+                    row[len(table):] = -1
         turn = self._turn
         self._turn = (turn + 1) % RING
         if self._events[turn] is not None:
             self._events[turn].synchronize()      # the copy that last used this buffer is done
         host = self._hosts[turn]
-        B = self.n_segments
-        values = host.numpy()
-        start = self._offsets["token_ids"][0]
-        values[start:start + B] = [seg.tokens[0] for seg in segments]
-        start = self._offsets["positions"][0]
-        values[start:start + B] = [seg.pos0 for seg in segments]
-        start = self._offsets["seg_slot"][0]
-        values[start:start + B] = [seg.slot for seg in segments]
-        start = self._offsets["seg_pos0"][0]
-        values[start:start + B] = [seg.pos0 for seg in segments]
-        for offset, rows in zip(self._table_offsets, tables):
-            values[offset:offset + B * self.width].reshape(B, self.width)[:] = rows
+        self._host_arrays[turn][:] = values
         self._dev.copy_(host, non_blocking=True)
-        event = torch.cuda.Event()
+        event = self._events[turn]
+        if event is None:
+            event = self._events[turn] = torch.cuda.Event()
         event.record()
-        self._events[turn] = event
-        self.segments = list(segments)
-        self.max_context = max(seg.pos0 + 1 for seg in segments)
+        self.segments = segments
+        self.max_context = int(pos0.max()) + 1
 
 
 class DecodeGraph:
@@ -100,11 +121,11 @@ class DecodeGraph:
         self.logits = None
         self.kernels = 0
 
-    def run(self, segments, tables) -> torch.Tensor:
+    def run(self, segments, cache) -> torch.Tensor:
         """The step for these segments.  The first call runs the kernels directly and then
         records the graph; later calls replay it.  The returned logits are a static buffer:
         they are overwritten by the next step of the same batch size."""
-        self.batch.upload(segments, tables)
+        self.batch.upload(segments, cache)
         if self.graph is None:
             logits = self.model.forward(self.ctx, self.caches)
             torch.cuda.current_stream().synchronize()

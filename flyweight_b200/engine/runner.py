@@ -83,15 +83,17 @@ class StepPlanner:
         return sum(max(0, need - group.pool.n_free) for need, group in zip(needs, cache.groups))
 
     # ------------------------------------------------------------------ planning
-    def plan(self, entries: Sequence[Entry]) -> List[Segment]:
+    def plan(self, entries: Sequence[Entry], pages_checked: bool = False) -> List[Segment]:
         """Check the entries, admit new requests, map their pages; all or nothing: if a
-        slot or a page is lacking, nothing has changed when the error is raised."""
+        slot or a page is lacking, nothing has changed when the error is raised.
+        ``pages_checked``: the caller (the scheduler) has just asked ``pages_short`` for exactly
+        these entries and got 0."""
         entries = [(r, [int(t) for t in toks], [int(w) for w in want]) for r, toks, want in entries]
         self._check_entries(entries)
         new = [r for r, _, _ in entries if not self.cache.has(r)]
         if len(new) > self.cache.free_slots:
             raise OutOfSlots(f"{len(new)} new requests but {self.cache.free_slots} free state slots")
-        short = self.pages_short(entries)
+        short = 0 if pages_checked else self.pages_short(entries)
         if short:
             raise OutOfPages(f"this step needs {short} more cache pages than are free")
         segments: List[Segment] = []
@@ -99,7 +101,7 @@ class StepPlanner:
             if not self.cache.has(request):
                 self.cache.admit(request)
             pos0 = self.cache.length(request)
-            self.cache.extend(request, pos0 + len(tokens))
+            self.cache.extend(request, pos0 + len(tokens), checked=True)
             segments.append(Segment(request, self.cache.slot(request), pos0, tokens, want))
         return segments
 
@@ -133,17 +135,16 @@ class ModelRunner(StepPlanner):
         self.tokens_run = 0
         self.h2d_bytes = 0
 
-    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+    def step(self, entries: Sequence[Entry], pages_checked: bool = False) -> torch.Tensor:
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        segments = self.plan(entries)
+        segments = self.plan(entries, pages_checked)
         requests = [seg.request for seg in segments]
         width = self.cache.max_table_len(requests)
         n_groups = len(self.cache.groups)
         if (self.use_graphs and len(segments) <= self.max_graph_batch
                 and all(len(seg.tokens) == 1 and seg.want == [0] for seg in segments)):
             bucket = 16 * (-(-width // 16))         # a new graph every 1,024 tokens of context
-            tables = [self.cache.block_table(g, requests, bucket) for g in range(n_groups)]
             key = (len(segments), bucket)
             graph = self._graphs.get(key)
             if graph is None:
@@ -152,7 +153,7 @@ class ModelRunner(StepPlanner):
                     self.bad_token_flag, len(segments), n_groups, bucket)
             else:
                 self.graph_replays += 1
-            logits = graph.run(segments, tables)
+            logits = graph.run(segments, self.cache)
             self.steps += 1
             self.tokens_run += len(segments)
             self.h2d_bytes += graph.batch.h2d_bytes

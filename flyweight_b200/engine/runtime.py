@@ -76,6 +76,8 @@ class Runtime:
         self.max_batched_tokens = int(max_batched_tokens)
         self.runner: Optional[ModelRunner] = None
         self.scheduler: Optional[Scheduler] = None
+        self._token_buffer: Optional[torch.Tensor] = None
+        self._token_event = None
         self._counters = {"engine_steps": 0, "step_seconds": 0.0, "sampling_seconds": 0.0,
                           "d2h_bytes": 0}
         self.prepare()
@@ -142,7 +144,7 @@ class Runtime:
         events = list(step.events)
         if not step.entries:
             return events
-        logits = runner.step(step.entries)
+        logits = runner.step(step.entries, pages_checked=True)
         need = scheduler.advance(step)
         for task in step.tasks:
             if task not in need:
@@ -155,7 +157,7 @@ class Runtime:
                 uniforms = [0.0 if task.sampling.greedy else task.rng.uniform() for task in need]
                 tokens = device_sampler.sample(logits, [task.sampling for task in need], uniforms,
                                                [task.generated for task in need])
-            host = tokens.to("cpu").tolist()          # the step's only device->host read
+            host = self._read_tokens(tokens)          # the step's only device->host read
             self._counters["d2h_bytes"] += 4 * len(host)
             self._counters["sampling_seconds"] += time.perf_counter() - sampled
             for task, token in zip(need, host):
@@ -163,6 +165,18 @@ class Runtime:
         self._counters["engine_steps"] += 1
         self._counters["step_seconds"] += time.perf_counter() - started
         return events
+
+    def _read_tokens(self, tokens: torch.Tensor) -> List[int]:
+        """Sampled token ids to the host through a pinned buffer (no allocation per step)."""
+        count = tokens.numel()
+        if self._token_buffer is None or self._token_buffer.numel() < count:
+            self._token_buffer = torch.empty(max(count, 256), dtype=torch.int32).pin_memory()
+            self._token_event = torch.cuda.Event()
+        view = self._token_buffer[:count]
+        view.copy_(tokens, non_blocking=True)
+        self._token_event.record()
+        self._token_event.synchronize()
+        return view.tolist()
 
     # ------------------------------------------------------------------ blocking calls
     def generate(self, prompt_tokens: Sequence[int], max_tokens: int,

@@ -1,0 +1,141 @@
+"""Run one kernel of the library alone on synthetic inputs, timed with CUDA events.
+
+    python -m flyweight_b200.kernels.microbench gemm --tokens 8 --features 6144 --k 2048
+    python -m flyweight_b200.kernels.microbench gemm --tokens 2048 --features 8192 --k 2048 --swiglu
+    python -m flyweight_b200.kernels.microbench attention-decode --batch 8 --context 4096
+    python -m flyweight_b200.kernels.microbench attention-prefill --tokens 2048
+
+It is what the ncu summaries under ``profiles/`` were captured from (small cases of the same
+kernels the engine runs), and a quick way to see what a shape costs.  Weight matrices are
+rotated through enough copies to exceed the L2 cache, so the timed reads come from HBM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+
+def _time(fn, repeat: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(repeat):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / repeat          # microseconds
+
+
+def run_gemm(args) -> dict:
+    from . import tensorcore
+    M, N, K = args.tokens, args.features, args.k
+    rows = 2 * N if args.swiglu else N
+    copies = max(2, min(16, int(160e6 // (rows * K * 2)) + 1))
+    weights = [(torch.randn(rows, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+               for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    turn = [0]
+
+    def step():
+        turn[0] = (turn[0] + 1) % copies
+        w = weights[turn[0]]
+        if args.swiglu:
+            return tensorcore.swiglu_gate_up(x, w, args.splits or None, args.stages, args.tile_tokens)
+        return tensorcore.gemm(x, w, torch.float32 if args.fp32_out else torch.bfloat16, None,
+                               args.splits or None, args.stages, args.tile_tokens, args.wide)
+
+    us = _time(step, args.repeat)
+    flops = 2.0 * M * rows * K
+    return {"kernel": "gemm_tcgen05", "tokens": M, "features": N, "k": K, "swiglu": args.swiglu,
+            "us": us, "tflops": flops / us / 1e6, "weight_gb_s": rows * K * 2 / us / 1e3,
+            "status": tensorcore.status()}
+
+
+def _paged_inputs(batch, context, new, n_heads, n_kv, head_dim):
+    pages_per = -(-context // 64)
+    width = 16 * (-(-pages_per // 16))
+    k_pool = torch.randn(batch * pages_per, n_kv, 64, head_dim, device="cuda").to(torch.bfloat16)
+    v_pool = torch.randn(batch * pages_per, n_kv, 64, head_dim, device="cuda").to(torch.bfloat16)
+    table = torch.full((batch, width), -1, dtype=torch.int32)
+    for b in range(batch):
+        table[b, :pages_per] = torch.arange(b * pages_per, (b + 1) * pages_per)
+    q = torch.randn(batch * new, n_heads * head_dim, device="cuda").to(torch.bfloat16)
+    return q, k_pool, v_pool, table.cuda(), width
+
+
+def run_attention_decode(args) -> dict:
+    from . import attention, ops
+    B, ctx = args.batch, args.context
+    q, k_pool, v_pool, table, width = _paged_inputs(B, ctx, 1, args.heads, args.kv_heads, args.head_dim)
+    positions = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
+    tok_seg = torch.arange(B, dtype=torch.int32, device="cuda")
+    splits, per = attention.decode_splits(B, args.kv_heads, width)
+    if args.splits:
+        splits, per = args.splits, -(-width // args.splits)
+    scale = 1.0 / math.sqrt(args.head_dim)
+    us = _time(lambda: ops.attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, table,
+                                                args.heads, 0, scale, splits, per), args.repeat)
+    kv_bytes = B * ctx * args.kv_heads * args.head_dim * 2 * 2
+    return {"kernel": "attention_decode_mma", "batch": B, "context": ctx, "splits": splits,
+            "us": us, "kv_gb_s": kv_bytes / us / 1e3}
+
+
+def run_attention_prefill(args) -> dict:
+    from . import ops
+    T = args.tokens
+    group = args.heads // args.kv_heads
+    q, k_pool, v_pool, table, _ = _paged_inputs(1, T, T, args.heads, args.kv_heads, args.head_dim)
+    positions = torch.arange(T, dtype=torch.int32, device="cuda")
+    seg_start = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    per_tile = max(1, 64 // group)
+    n_tiles = -(-T // per_tile)
+    tile_seg = torch.zeros(n_tiles, dtype=torch.int32, device="cuda")
+    tile_tok0 = (torch.arange(n_tiles, dtype=torch.int32) * per_tile).cuda()
+    scale = 1.0 / math.sqrt(args.head_dim)
+    us = _time(lambda: ops.attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg,
+                                                 tile_tok0, n_tiles, per_tile, table, args.heads, 0,
+                                                 scale), args.repeat)
+    flops = 2.0 * T * T * args.heads * args.head_dim        # causal: half of 4*T*T*h*d
+    return {"kernel": "attention_prefill_mma", "tokens": T, "us": us, "tflops": flops / us / 1e6}
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="python -m flyweight_b200.kernels.microbench",
+                                     description=__doc__,
+                                     formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = parser.add_subparsers(dest="kernel", required=True)
+    gemm = sub.add_parser("gemm")
+    gemm.add_argument("--tokens", type=int, default=8)
+    gemm.add_argument("--features", type=int, default=2048)
+    gemm.add_argument("--k", type=int, default=2048)
+    gemm.add_argument("--swiglu", action="store_true", help="features = F; the weight is [2F][K]")
+    gemm.add_argument("--fp32-out", action="store_true")
+    gemm.add_argument("--splits", type=int, default=0)
+    gemm.add_argument("--stages", type=int, default=0)
+    gemm.add_argument("--tile-tokens", type=int, default=0, help="128 or 256 (0: by token count)")
+    gemm.add_argument("--wide", type=int, default=-1, help="two feature tiles per CTA: 1/0 (-1: auto)")
+    for name in ("attention-decode", "attention-prefill"):
+        p = sub.add_parser(name)
+        p.add_argument("--batch", type=int, default=8)
+        p.add_argument("--context", type=int, default=4096)
+        p.add_argument("--tokens", type=int, default=2048)
+        p.add_argument("--heads", type=int, default=32)
+        p.add_argument("--kv-heads", type=int, default=8)
+        p.add_argument("--head-dim", type=int, default=64)
+        p.add_argument("--splits", type=int, default=0)
+    for p in sub.choices.values():
+        p.add_argument("--repeat", type=int, default=20)
+    args = parser.parse_args(argv)
+    runner = {"gemm": run_gemm, "attention-decode": run_attention_decode,
+              "attention-prefill": run_attention_prefill}[args.kernel]
+    print(json.dumps(runner(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

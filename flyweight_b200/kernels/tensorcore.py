@@ -39,6 +39,9 @@ def accepts(x, w, out_dtype, addend=None) -> bool:
 
 
 _forced_splits = None
+# Per-shape overrides found by measurement: (features, K, accumulators) -> (splits, stages);
+# 0 keeps the rule's choice.  Only decode-sized token counts (<= 64) consult it.
+TUNED = {}
 
 
 def force_splits(splits) -> None:
@@ -59,22 +62,32 @@ def pick_splits(M: int, N: int, K: int) -> int:
     return _splits_for(M, N, K, 1)
 
 
+def _ring_depth(bn: int, accumulators: int) -> int:
+    """Stages of the shared-memory ring for decode-sized steps: shallow enough that several
+    CTAs (and the next kernel's, prefetching weights) fit an SM."""
+    if accumulators == 2:
+        return 3 if bn <= 32 else 4
+    return 4
+
+
 def _splits_for(M: int, N: int, K: int, accumulators: int) -> int:
-    """The largest power of two (<= 8) that still lets every CTA be resident at once:
-    measured on B200, a second wave costs more than the extra slices win."""
+    """The largest power of two (<= 8) that still lets every CTA be resident at once; measured
+    on B200 inside the decode step of LFM2-1.2B at batch 1, 8 and 64: a second wave costs more
+    than the extra slices win."""
     bn = 16 if M <= 16 else (32 if M <= 32 else 64)
+    if accumulators == 2 and bn == 64:
+        return 1
     stage = accumulators * 16384 + bn * 128
-    stages = min(6, (200 * 1024) // stage)
-    per_sm = max(1, (227 * 1024) // (stages * stage + 2048))
+    per_sm = max(1, (227 * 1024) // (_ring_depth(bn, accumulators) * stage + 2048))
     tiles = -(-N // 128)
     k_blocks = -(-K // 64)
     splits = 1
-    while splits < 8 and tiles * splits * 2 <= SM_COUNT * per_sm and k_blocks >= splits * 4:
+    while splits < 8 and tiles * splits * 2 <= 0.9 * SM_COUNT * per_sm and k_blocks >= splits * 8:
         splits *= 2
     return splits
 
 
-def gemm(x, w, out_dtype, addend=None, splits=None) -> torch.Tensor:
+def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wide=-1) -> torch.Tensor:
     """``x @ w.T``: x [M][K] bf16, w [N][K] bf16 -> [M][N] fp32 or bf16 (+ fp32 addend)."""
     check_tensor("gemm input", x, torch.bfloat16)
     check_tensor("gemm weight", w, torch.bfloat16)
@@ -88,10 +101,16 @@ def gemm(x, w, out_dtype, addend=None, splits=None) -> torch.Tensor:
         epilogue = EPI_ADD_F32
     else:
         epilogue = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
+    if M <= 64 and (N, K, 1) in TUNED and _forced_splits is None:
+        tuned = TUNED[(N, K, 1)]
+        splits = splits or tuned[0] or None
+        stages = stages or tuned[1]
     if splits is None:
         splits = pick_splits(M, N, K)
+    if not stages and M <= 64:
+        stages = _ring_depth(16 if M <= 16 else (32 if M <= 32 else 64), 1)
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w), ptr(out), ptr(addend), M, N, K, N, N, epilogue, 0,
-             splits, stream())
+             splits, stages, tile_tokens, wide, stream())
     return out
 
 
@@ -99,7 +118,7 @@ def swiglu_accepts(x, w_gate_up) -> bool:
     return accepts(x, w_gate_up, torch.bfloat16)
 
 
-def swiglu_gate_up(x, w_gate_up, splits=None) -> torch.Tensor:
+def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` as bf16, for ``w_gate_up`` = [gate rows | up rows]:
     both products accumulate side by side in tensor memory and never reach global memory."""
     check_tensor("swiglu input", x, torch.bfloat16)
@@ -110,10 +129,16 @@ def swiglu_gate_up(x, w_gate_up, splits=None) -> torch.Tensor:
     if w_gate_up.shape[1] != K or F * 2 != F2:
         raise KernelError("swiglu: weight must be [2F][K]")
     out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
+    if M <= 64 and (F, K, 2) in TUNED and _forced_splits is None:
+        tuned = TUNED[(F, K, 2)]
+        splits = splits or tuned[0] or None
+        stages = stages or tuned[1]
     if splits is None:
         splits = (_forced_splits if _forced_splits is not None else _splits_for(M, F, K, 2)) if M <= 64 else 1
+    if not stages and M <= 64:
+        stages = _ring_depth(16 if M <= 16 else (32 if M <= 32 else 64), 2)
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, F, K, F2, F,
-             EPI_SWIGLU_BF16, F, splits, stream())
+             EPI_SWIGLU_BF16, F, splits, stages, tile_tokens, -1, stream())
     return out
 
 

@@ -90,8 +90,8 @@ class GQAttention(Mixer):
 
     def forward(self, ctx, h, cache):
         act = ctx.precision.act_dtype
-        # q|k|v keeps fp32 out of the product: the head norm and the rotation read it
-        qkv = ops.linear(h, self.w_qkv, torch.float32)
+        # q|k|v in the activation dtype; the head norm and the rotation widen it to fp32
+        qkv = ops.linear(h, self.w_qkv, act)
         block_table = ctx.batch.block_tables[cache.group]
         q = ops.qk_norm_rope(
             qkv, self.q_norm, self.k_norm, self.rope_table, ctx.batch.positions,

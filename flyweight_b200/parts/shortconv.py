@@ -56,7 +56,8 @@ class GatedShortConv(Mixer):
 
     def forward(self, ctx, h, cache):
         batch = ctx.batch
-        p = ops.linear(h, self.w_in, torch.float32)
+        # B|C|x in the activation dtype: the conv kernel widens them and multiplies in fp32
+        p = ops.linear(h, self.w_in, ctx.precision.act_dtype)
         z = ops.shortconv(p, self.taps, self.bias, cache.state, batch.seg_start, batch.seg_slot,
                           batch.tok_seg, batch.n_segments, ctx.precision.act_dtype)
         return ops.linear(z, self.w_out, torch.float32)
