@@ -23,6 +23,10 @@ namespace {
 
 constexpr int KEYS = 64;            // keys per tile == page size
 constexpr int WARPS = 4;
+// Scores are kept in base 2: s * scale * log2(e), so the softmax exponentials are single ex2
+// operations (fp32, relative error 2^-22); running maxima and the partial results of context
+// slices live in the same domain.
+constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -149,7 +153,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
         for (int j = 0; j < 4; ++j) {
             const int key = key_base + n * 8 + 2 * t + (j & 1);
             const int h = j >> 1;
-            const float v = (key >= lo[h] && key <= hi[h]) ? s[n][j] * scale : -INFINITY;
+            const float v = (key >= lo[h] && key <= hi[h]) ? s[n][j] * scale : -INFINITY;   // scale has log2(e) folded in
             s[n][j] = v;
             mx[h] = fmaxf(mx[h], v);
         }
@@ -163,7 +167,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
     for (int h = 0; h < 2; ++h) {
         const float m_new = fmaxf(m[h], mx[h]);
         base[h] = m_new == -INFINITY ? 0.0f : m_new;       // a row that has seen no key yet
-        corr[h] = expf(m[h] - base[h]);                    // exp(-inf) = 0
+        corr[h] = exp2f(m[h] - base[h]);                   // 2^(-inf) = 0
         m[h] = m_new;
     }
 #pragma unroll
@@ -171,7 +175,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int h = j >> 1;
-            const float p = expf(s[n][j] - base[h]);       // masked: exp(-inf) = 0
+            const float p = exp2f(s[n][j] - base[h]);      // masked: 2^(-inf) = 0
             s[n][j] = p;
             sum[h] += p;
         }
@@ -208,7 +212,7 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[HD / 16][4], const __nv_bf
 // ------------------------------------------------------------------ prefill
 // tile_seg[b], tile_tok0[b]: segment and first token (global index) of row tile b.
 template <int HD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, HD <= 64 ? 4 : 2)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
                          const int* __restrict__ seg_start, const int* __restrict__ tile_seg,
@@ -395,7 +399,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         float acc = 0.0f, ll = 0.0f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const float c = expf(merge_ml[w][r][0] - base);
+            const float c = exp2f(merge_ml[w][r][0] - base);
             acc += c * merge_o[((size_t)w * 16 + r) * HD + d];
             ll += c * merge_ml[w][r][1];
         }
@@ -426,7 +430,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
         float acc = 0.0f, ll = 0.0f;
         for (int s = 0; s < splits; ++s) {
             const size_t at = (base_at + s) * group + r;
-            const float c = expf(part_ml[at * 2] - mm);     // a split without keys: exp(-inf) = 0
+            const float c = exp2f(part_ml[at * 2] - mm);    // a split without keys: 2^(-inf) = 0
             acc += c * part_o[at * hd + d];
             ll += c * part_ml[at * 2 + 1];
         }
@@ -436,6 +440,9 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 
 template <typename K>
 int opt_in_smem(K kernel, size_t bytes) {
+    // these kernels live on shared memory, not L1: ask for the largest carve-out so that as many
+    // CTAs as the registers allow are resident
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (bytes <= 48 * 1024) return FWB_OK;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     return e == cudaSuccess ? FWB_OK : (int)e;
@@ -452,7 +459,7 @@ int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const 
     using bf = __nv_bfloat16;
     fwb::pdl(kernel, dim3(n_tiles, nkv), WARPS * 32, Smem<HD>::BYTES, stream)(
         (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, seg_start, tile_seg, tile_tok0,
-        block_table, max_pages, (bf*)out, nh, nkv, nh / nkv, tokens_per_tile, window, scale);
+        block_table, max_pages, (bf*)out, nh, nkv, nh / nkv, tokens_per_tile, window, scale * LOG2E);
     return fwb_launch_status();
 }
 
@@ -469,7 +476,7 @@ int launch_decode(const void* q, const void* k_pool, const void* v_pool, const i
     using bf = __nv_bfloat16;
     fwb::pdl(kernel, dim3(splits, nkv, T), WARPS * 32, bytes, stream)(
         (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
-        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale);
+        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E);
     st = fwb_launch_status();
     if (st != FWB_OK || splits == 1) return st;
     fwb::pdl(attention_merge_kernel, dim3(nkv, T), 128, 0, stream)(part_o, part_ml, (bf*)out, nh, nkv, nh / nkv, HD,

@@ -73,6 +73,80 @@ __global__ void shortconv_kernel(const TP* __restrict__ p, const float* __restri
     }
 }
 
+// The bfloat16 form of the same launch with body threads that own 8 adjacent channels of one
+// token: every load is one 16-byte vector, the B*x products of a tap are formed once per
+// 8 outputs.  Head threads are the scalar ones above (there are S*H of them, few).
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__global__ void shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ taps,
+                                        const float* __restrict__ bias, float* __restrict__ state,
+                                        const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                                        const int* __restrict__ tok_seg, __nv_bfloat16* __restrict__ z,
+                                        int T, int S, int H, int L, int body_blocks) {
+    fwb::pdl_entry();
+    const int ld = 3 * H;
+    if ((int)blockIdx.x < body_blocks) {
+        const int groups = H >> 3;
+        const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+        if (idx >= (size_t)T * groups) return;
+        const int t = (int)(idx / groups), c = (int)(idx - (size_t)t * groups) * 8;
+        const int j = t - seg_start[tok_seg[t]];
+        if (j < L - 1) return;  // a head thread produces this one
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = bias ? bias[c + i] : 0.0f;
+        for (int k = 0; k < L; ++k) {
+            const __nv_bfloat16* row = p + (size_t)(t - (L - 1) + k) * ld;
+            float b[8], x[8];
+            unpack8(*reinterpret_cast<const uint4*>(row + c), b);
+            unpack8(*reinterpret_cast<const uint4*>(row + 2 * H + c), x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = fmaf(taps[(c + i) * L + k], b[i] * x[i], y[i]);
+        }
+        float g[8];
+        unpack8(*reinterpret_cast<const uint4*>(p + (size_t)t * ld + H + c), g);
+        uint4 out;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(g[2 * i] * y[2 * i], g[2 * i + 1] * y[2 * i + 1]);
+        *reinterpret_cast<uint4*>(z + (size_t)t * H + c) = out;
+        return;
+    }
+    const size_t idx = (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)S * H) return;
+    const int s = (int)(idx / H), c = (int)(idx - (size_t)s * H);
+    const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
+    float* st = state + ((size_t)seg_slot[s] * H + c) * (L - 1);
+    float hist[2 * MAX_TAPS];
+    float w[MAX_TAPS];
+    for (int k = 0; k < L; ++k) w[k] = taps[c * L + k];
+    for (int k = 0; k < L - 1; ++k) hist[k] = st[k];
+    const int first = n < L - 1 ? n : L - 1;
+    for (int j = 0; j < first; ++j) {
+        const __nv_bfloat16* row = p + (size_t)(t0 + j) * ld;
+        hist[L - 1 + j] = __bfloat162float(row[c]) * __bfloat162float(row[2 * H + c]);
+        float y = bias ? bias[c] : 0.0f;
+        for (int k = 0; k < L; ++k) y = fmaf(w[k], hist[j + k], y);
+        z[(size_t)(t0 + j) * H + c] = __float2bfloat16_rn(__bfloat162float(row[H + c]) * y);
+    }
+    if (n >= L - 1) {
+        for (int k = 0; k < L - 1; ++k) {
+            const __nv_bfloat16* row = p + (size_t)(t0 + n - (L - 1) + k) * ld;
+            st[k] = __bfloat162float(row[c]) * __bfloat162float(row[2 * H + c]);
+        }
+    } else {
+        for (int k = 0; k < L - 1; ++k) st[k] = hist[k + n];
+    }
+}
+
 }  // namespace
 
 // p: [T][3H] (fp32 or bf16); taps: [H][L] fp32; bias: [H] fp32 or null;
@@ -87,6 +161,14 @@ FWB_API int fwb_shortconv(const void* p, int p_bf16, const float* taps, const fl
         return FWB_BAD_ARGUMENT;
     if (L < 2 || L > MAX_TAPS) return FWB_UNSUPPORTED;
     const int threads = 128;
+    if (p_bf16 && z_bf16 && (H & 7) == 0 && ((uintptr_t)p & 15) == 0 && ((uintptr_t)z & 15) == 0) {
+        const int body = (int)(((size_t)T * (H >> 3) + threads - 1) / threads);
+        const int head = (int)(((size_t)S * H + threads - 1) / threads);
+        fwb::pdl(shortconv_bf16x8_kernel, body + head, threads, 0, stream)(
+            (const __nv_bfloat16*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (__nv_bfloat16*)z, T, S,
+            H, L, body);
+        return fwb_launch_status();
+    }
     const int body_blocks = (int)(((size_t)T * H + threads - 1) / threads);
     const int head_blocks = (int)(((size_t)S * H + threads - 1) / threads);
     const int blocks = body_blocks + head_blocks;
