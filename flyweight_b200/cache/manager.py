@@ -236,6 +236,13 @@ class CacheManager:
                 table.append(group.pool.allocate())
         self._length[request] = new_length
 
+    def bump(self, request: Hashable) -> None:
+        """One more token of ``request`` inside its last mapped page (the caller has checked)."""
+        length = self._length[request]
+        if length % PAGE_SIZE == 0:
+            raise OutOfPages(f"request {request!r} needs a new page for position {length}")
+        self._length[request] = length + 1
+
     def release(self, request: Hashable) -> None:
         """Give back everything ``request`` holds."""
         slot = self._slot_of.pop(request)

@@ -110,6 +110,31 @@ class DecodeBatch:
         self.max_context = int(pos0.max()) + 1
 
 
+    def upload_next(self, tokens: Sequence[int]) -> None:
+        """The same requests one position further (no page changes): only the token ids and the
+        positions move."""
+        B = self.n_segments
+        values = self._current
+        ids, _, pos0 = self._views
+        ids[:] = tokens
+        pos0 += 1
+        start = self._offsets["positions"][0]
+        values[start:start + B] = pos0
+        for seg in self.segments:
+            seg.pos0 += 1
+        turn = self._turn
+        self._turn = (turn + 1) % RING
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()
+        self._host_arrays[turn][:] = values
+        self._dev.copy_(self._hosts[turn], non_blocking=True)
+        event = self._events[turn]
+        if event is None:
+            event = self._events[turn] = torch.cuda.Event()
+        event.record()
+        self.max_context += 1
+
+
 class DecodeGraph:
     def __init__(self, model, caches, precision, device, bad_token_flag, batch_size: int,
                  n_groups: int, width: int):
@@ -137,6 +162,13 @@ class DecodeGraph:
             add_launches(-self.kernels)
             self.graph = graph
             return logits
+        self.graph.replay()
+        add_launches(self.kernels)
+        return self.logits
+
+    def run_next(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Replay for the same requests, each one token further."""
+        self.batch.upload_next(tokens)
         self.graph.replay()
         add_launches(self.kernels)
         return self.logits

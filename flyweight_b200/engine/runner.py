@@ -130,6 +130,7 @@ class ModelRunner(StepPlanner):
         self.use_graphs = bool(use_graphs) and model.graph_safe
         self.max_graph_batch = 256
         self._graphs = {}
+        self.last_decode_graph = None      # the graph the last step replayed (None: it ran eagerly)
         self.graph_replays = 0
         self.steps = 0
         self.tokens_run = 0
@@ -154,10 +155,12 @@ class ModelRunner(StepPlanner):
             else:
                 self.graph_replays += 1
             logits = graph.run(segments, self.cache)
+            self.last_decode_graph = graph
             self.steps += 1
             self.tokens_run += len(segments)
             self.h2d_bytes += graph.batch.h2d_bytes
             return logits
+        self.last_decode_graph = None
         tables = [self.cache.block_table(g, requests, width) for g in range(n_groups)]
         batch = StepBatch(segments, tables, self.device)
         ctx = StepContext(batch, self.precision, self.device, self.bad_token_flag)
@@ -165,4 +168,17 @@ class ModelRunner(StepPlanner):
         self.steps += 1
         self.tokens_run += batch.n_tokens
         self.h2d_bytes += batch.h2d_bytes
+        return logits
+
+    def step_same_requests(self, tokens: Sequence[int]) -> torch.Tensor:
+        """The decode step that follows the last one for exactly the same requests, none of
+        which needs a new page: lengths grow by one, the captured graph is replayed."""
+        graph = self.last_decode_graph
+        for seg in graph.batch.segments:
+            self.cache.bump(seg.request)
+        logits = graph.run_next(tokens)
+        self.graph_replays += 1
+        self.steps += 1
+        self.tokens_run += len(tokens)
+        self.h2d_bytes += graph.batch.h2d_bytes
         return logits

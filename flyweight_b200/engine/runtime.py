@@ -78,8 +78,9 @@ class Runtime:
         self.scheduler: Optional[Scheduler] = None
         self._token_buffer: Optional[torch.Tensor] = None
         self._token_event = None
-        self._counters = {"engine_steps": 0, "step_seconds": 0.0, "sampling_seconds": 0.0,
-                          "d2h_bytes": 0}
+        self._counters = {"engine_steps": 0, "steady_steps": 0, "step_seconds": 0.0,
+                          "sampling_seconds": 0.0, "d2h_bytes": 0}
+        self.steady_decode = True          # take the short way when a step repeats the last one
         self.prepare()
 
     # ------------------------------------------------------------------ life cycle
@@ -140,6 +141,17 @@ class Runtime:
         that was due.  Returns events ``(task id, token or count, kind)``."""
         scheduler, runner = self.scheduler, self.runner
         started = time.perf_counter()
+        need = self._same_requests_again() if self.steady_decode else None
+        if need is not None:
+            self._counters["steady_steps"] += 1
+            # steady decoding: nothing to schedule, no page to map; replay one position further
+            logits = runner.step_same_requests([task.generated[-1] for task in need])
+            scheduler.advance_decode(need)
+            events = []
+            self._sample_and_accept(need, logits, events)
+            self._counters["engine_steps"] += 1
+            self._counters["step_seconds"] += time.perf_counter() - started
+            return events
         step = scheduler.schedule()
         events = list(step.events)
         if not step.entries:
@@ -150,21 +162,47 @@ class Runtime:
             if task not in need:
                 events.append((task.id, task.computed, EVENT_PROGRESS))
         if need:
-            sampled = time.perf_counter()
-            if all(task.sampling.greedy for task in need):
-                tokens = device_sampler.argmax(logits)
-            else:
-                uniforms = [0.0 if task.sampling.greedy else task.rng.uniform() for task in need]
-                tokens = device_sampler.sample(logits, [task.sampling for task in need], uniforms,
-                                               [task.generated for task in need])
-            host = self._read_tokens(tokens)          # the step's only device->host read
-            self._counters["d2h_bytes"] += 4 * len(host)
-            self._counters["sampling_seconds"] += time.perf_counter() - sampled
-            for task, token in zip(need, host):
-                events.extend(scheduler.accept(task, token))
+            self._sample_and_accept(need, logits, events)
         self._counters["engine_steps"] += 1
         self._counters["step_seconds"] += time.perf_counter() - started
         return events
+
+    def _sample_and_accept(self, need, logits, events) -> None:
+        sampled = time.perf_counter()
+        if all(task.sampling.greedy for task in need):
+            tokens = device_sampler.argmax(logits)
+        else:
+            uniforms = [0.0 if task.sampling.greedy else task.rng.uniform() for task in need]
+            tokens = device_sampler.sample(logits, [task.sampling for task in need], uniforms,
+                                           [task.generated for task in need])
+        host = self._read_tokens(tokens)              # the step's only device->host read
+        self._counters["d2h_bytes"] += 4 * len(host)
+        self._counters["sampling_seconds"] += time.perf_counter() - sampled
+        for task, token in zip(need, host):
+            events.extend(self.scheduler.accept(task, token))
+
+    def _same_requests_again(self):
+        """The running tasks, if the next step is the last one moved on by one token: nobody
+        waits, everybody decodes, the last step replayed a graph for exactly these requests in
+        this order, and nobody needs a new page or reaches a limit.  Else None."""
+        scheduler, runner = self.scheduler, self.runner
+        graph = runner.last_decode_graph
+        tasks = scheduler.running
+        if graph is None or graph.graph is None or scheduler.waiting or not tasks:
+            return None
+        segments = graph.batch.segments
+        if len(segments) != len(tasks):
+            return None
+        cache = runner.cache
+        if any(group.window for group in cache.groups):
+            return None                      # a window may hand pages back between steps
+        for task, segment in zip(tasks, segments):
+            if segment.request != task.id or task.cancelled or task.pending != 1:
+                return None
+            length = cache.length(task.id)
+            if length % PAGE_SIZE == 0 or length + 1 > runner.max_model_len:
+                return None
+        return list(tasks)
 
     def _read_tokens(self, tokens: torch.Tensor) -> List[int]:
         """Sampled token ids to the host through a pinned buffer (no allocation per step)."""

@@ -234,6 +234,13 @@ class Scheduler:
         self.stats["steps"] += 1
         return need
 
+    def advance_decode(self, tasks: Sequence[Task]) -> None:
+        """``advance`` for a step in which every running task decoded one token."""
+        for task in tasks:
+            task.computed += 1
+        self.stats["decode_tokens"] += len(tasks)
+        self.stats["steps"] += 1
+
     def accept(self, task: Task, token: int) -> List[Tuple[int, int, int]]:
         """A sampled token for ``task``: emit it, then finish on a stop token, on
         ``max_tokens`` or at the context limit (emit-then-stop order of

@@ -130,3 +130,26 @@ def test_command_line_generate_and_inspect():
     assert [int(t) for t in proc.stdout.split()] == P.greedy_generate(cfg, w, prompt, 5)
     proc = run("inspect", str(model_dir("A", "float32")))
     assert proc.returncode == 0 and '"ffn_dim": 192' in proc.stdout
+
+
+def test_the_steady_decode_shortcut_changes_nothing():
+    """When a step has the same requests as the last one and nobody needs a page, the runtime
+    skips scheduling and replays the captured graph one position further.  Same tokens as the
+    long way, sampled or greedy, across page edges and with requests that end at different times."""
+    name = "B"
+    prompts = [random_tokens(name, n, seed=80 + n) for n in (30, 61, 64, 100)]
+    settings = dict(temperature=0.7, top_k=30, top_p=0.9, min_p=0.02)
+
+    def run(steady):
+        with open_runtime(name, "float32", context_limit=256, parallel_sequences=4) as runtime:
+            runtime.steady_decode = steady
+            ids = [runtime.task_submit(p, 40 + 17 * i, seed=3 + i, **(settings if i % 2 else {}))
+                   for i, p in enumerate(prompts)]
+            while runtime.has_work():
+                runtime.engine_step()
+            return [runtime.task(i).generated for i in ids], runtime.info["steady_steps"]
+
+    fast, steady_steps = run(True)
+    slow, none = run(False)
+    assert fast == slow
+    assert steady_steps > 40 and none == 0
