@@ -556,3 +556,18 @@ def test_tensor_core_attention_finds_a_far_key_and_the_window_edge():
                 close(got[-1].reshape(nh, hd)[0], v[target, 0], 2.0 ** -6, f"value of key {target}")
             else:                                            # the shouting key is outside the window
                 assert (got[-1].reshape(nh, hd)[0].double().cpu() - v[target, 0]).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("M,N,K", [(600, 1000, 264), (300, 256, 64), (257, 3072, 512), (1030, 700, 96)])
+@pytest.mark.parametrize("tile_tokens,wide", [(256, 1), (128, 1), (128, 0), (256, 0)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_tcgen05_tile_shapes_for_prompts(M, N, K, tile_tokens, wide, out_dtype):
+    """Token tiles of 128 and 256 and the two-feature-tile ("wide") form, on ragged edges."""
+    from flyweight_b200.kernels import tensorcore as tc
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    got = tc.gemm(dev(x), dev(w), out_dtype, None, None, 0, tile_tokens, wide)
+    close(got, want, 1e-5 if out_dtype == torch.float32 else 2.0 ** -8, "tile shape")
+    assert tc.status() == 0
