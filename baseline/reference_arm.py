@@ -1,5 +1,6 @@
 """The reference arm of bench.py: the UNMODIFIED yairpatch/flyweight, installed offline into
-``baseline/_ref`` (see DESIGN.md for the install command), driven through its own public Python
+``baseline/_ref`` (``pip install --no-index --no-build-isolation --no-deps --target baseline/_ref``
+on a copy of its tree, with ``CXX=/usr/bin/g++`` so that CMake finds OpenMP), driven through its own public Python
 API and stock code path for the same metric and configuration as the engine's own arm.
 
 flyweight loads LFM2 from GGUF only, so this file writes one: the LFM2-1.2B geometry with

@@ -483,7 +483,7 @@ int launch_epi(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, cons
 // Y: [M][ldy] (fp32 for epilogues 0 and 2, bf16 for 1 and 3).  `splits` (1..8) CTAs share the
 // K range of a tile as a cluster; with splits > 1 the token tile must be <= 64 wide.
 // `stages` sets the depth of the shared-memory ring (0: the default).  `tile_tokens` (0: by M)
-// may ask for a 128-token tile where 256 would be picked; `wide` gives a CTA two feature tiles.
+// may ask for a smaller token tile than M would pick (more CTAs); `wide` gives a CTA two feature tiles.
 // K must be a multiple of 8 (TMA strides are multiples of 16 bytes) and both base
 // pointers 16-byte aligned; anything else is refused.
 FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float* addend, int M, int N,
@@ -498,7 +498,7 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     if (splits < 1 || splits > 8) return FWB_BAD_ARGUMENT;
     int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
     if (tile_tokens == 16 || tile_tokens == 32 || tile_tokens == 64 || tile_tokens == 128 || tile_tokens == 256) {
-        if (tile_tokens < bn && tile_tokens >= 128) bn = tile_tokens;      // a smaller tile: more CTAs
+        if (tile_tokens < bn) bn = tile_tokens;                            // a smaller tile: more CTAs
     } else if (tile_tokens != 0) {
         return FWB_BAD_ARGUMENT;
     }

@@ -62,27 +62,42 @@ def pick_splits(M: int, N: int, K: int) -> int:
     return _splits_for(M, N, K, 1)
 
 
-def _ring_depth(bn: int, accumulators: int) -> int:
-    """Stages of the shared-memory ring for decode-sized steps: shallow enough that several
-    CTAs (and the next kernel's, prefetching weights) fit an SM."""
-    if accumulators == 2:
-        return 3 if bn <= 32 else 4
-    return 4
+def _decode_tile(M: int, N: int) -> int:
+    """Token tile of a decode-sized step.  33..64 tokens are cut into two tiles of 32 when the
+    product has too few feature tiles to occupy the GPU (measured at batch 64: 6 % off the
+    step); a product with many tiles keeps one token tile, so no weight is fetched twice."""
+    if M <= 16:
+        return 16
+    if M <= 32 or -(-N // 128) < SM_COUNT:
+        return 32
+    return 64
+
+
+def _ring_depth(M: int, N: int, splits: int, accumulators: int) -> int:
+    """Stages of the shared-memory ring for decode-sized steps: at most four, and few enough
+    that every CTA of the product is resident at once (measured: a product that needs a second
+    wave of CTAs loses far more than a shallower ring does)."""
+    bn = _decode_tile(M, N)
+    stage = accumulators * 16384 + bn * 128
+    ctas = -(-N // 128) * -(-M // bn) * splits
+    per_sm = max(1, -(-ctas // SM_COUNT))
+    fit = ((227 * 1024) // per_sm - 2048) // stage
+    return max(2, min(3 if (accumulators == 2 and bn <= 16) else 4, fit))
 
 
 def _splits_for(M: int, N: int, K: int, accumulators: int) -> int:
-    """The largest power of two (<= 8) that still lets every CTA be resident at once; measured
-    on B200 inside the decode step of LFM2-1.2B at batch 1, 8 and 64: a second wave costs more
-    than the extra slices win."""
-    bn = 16 if M <= 16 else (32 if M <= 32 else 64)
-    if accumulators == 2 and bn == 64:
-        return 1
-    stage = accumulators * 16384 + bn * 128
-    per_sm = max(1, (227 * 1024) // (_ring_depth(bn, accumulators) * stage + 2048))
-    tiles = -(-N // 128)
+    """Slices of K per output tile (a cluster, a power of two <= 8).  Measured inside the decode
+    step of LFM2-1.2B on B200 at batch 1, 8 and 64: the step is fastest with about 400 CTAs per
+    product (256 with two accumulators), as long as a slice keeps at least four 64-wide blocks."""
+    bn = _decode_tile(M, N)
+    tiles = -(-N // 128) * -(-M // bn)
     k_blocks = -(-K // 64)
+    budget = 256 if accumulators == 2 else 400
+    limit = 4 if accumulators == 2 else 8
+    if accumulators == 2 and M > 32:
+        return 1                    # two accumulators of two token tiles: the reduction costs more
     splits = 1
-    while splits < 8 and tiles * splits * 2 <= 0.9 * SM_COUNT * per_sm and k_blocks >= splits * 8:
+    while splits < limit and tiles * splits * 2 <= budget and k_blocks >= splits * 8:
         splits *= 2
     return splits
 
@@ -105,10 +120,13 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
         tuned = TUNED[(N, K, 1)]
         splits = splits or tuned[0] or None
         stages = stages or tuned[1]
+        if len(tuned) > 2:
+            tile_tokens = tile_tokens or tuned[2]
     if splits is None:
         splits = pick_splits(M, N, K)
-    if not stages and M <= 64:
-        stages = _ring_depth(16 if M <= 16 else (32 if M <= 32 else 64), 1)
+    if M <= 64:
+        stages = stages or _ring_depth(M, N, splits, 1)
+        tile_tokens = tile_tokens or _decode_tile(M, N)
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w), ptr(out), ptr(addend), M, N, K, N, N, epilogue, 0,
              splits, stages, tile_tokens, wide, stream())
     return out
@@ -133,10 +151,13 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
         tuned = TUNED[(F, K, 2)]
         splits = splits or tuned[0] or None
         stages = stages or tuned[1]
+        if len(tuned) > 2:
+            tile_tokens = tile_tokens or tuned[2]
     if splits is None:
         splits = (_forced_splits if _forced_splits is not None else _splits_for(M, F, K, 2)) if M <= 64 else 1
-    if not stages and M <= 64:
-        stages = _ring_depth(16 if M <= 16 else (32 if M <= 32 else 64), 2)
+    if M <= 64:
+        stages = stages or _ring_depth(M, F, splits, 2)
+        tile_tokens = tile_tokens or _decode_tile(M, F)
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, F, K, F2, F,
              EPI_SWIGLU_BF16, F, splits, stages, tile_tokens, -1, stream())
     return out

@@ -101,10 +101,12 @@ def main(reference_root: str) -> None:
         out[f"{name}.prompt"] = np.asarray(prompt, dtype=np.int32)
         out[f"{name}.tokens"] = np.asarray(tokens, dtype=np.int32)
         for k, v in hf.items():
-            out[f"{name}.w.{k}"] = v.astype(np.float16).astype(np.float32) if False else v
+            out[f"{name}.w.{k}"] = v
     np.savez_compressed(HERE / "lfm2_reference_greedy.npz", **out)
     print("wrote", HERE / "lfm2_reference_greedy.npz")
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/flyweight")
+    main(sys.argv[1])
