@@ -228,7 +228,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     pdl_launch_dependents();     // the next kernel may set itself up in this one's shadow
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int feat0 = blockIdx.x * (WIDE ? 2 * BM : BM), tok0 = blockIdx.y * BN;
+    // token tiles are the fast grid dimension: CTAs that run together share weight tiles, and
+    // a wave's weights plus all the activations fit the L2 cache
+    const int feat0 = blockIdx.y * (WIDE ? 2 * BM : BM), tok0 = blockIdx.x * BN;
     const int second_tile_row = WIDE ? feat0 + BM : prm.up_row_offset + feat0;   // accumulator 1's rows of W
     const int splits = gridDim.z;
     const int total_kb = (prm.K + BK - 1) / BK;
@@ -446,7 +448,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, Params prm, int s
     if (prm.stages < 2) prm.stages = 2;
     cudaLaunchConfig_t config = {};
     constexpr int FEATURES = epi_wide(EPI) ? 2 * BM : BM;
-    config.gridDim = dim3((prm.N + FEATURES - 1) / FEATURES, (prm.M + BN - 1) / BN, splits);
+    config.gridDim = dim3((prm.M + BN - 1) / BN, (prm.N + FEATURES - 1) / FEATURES, splits);
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = T::smem_bytes(prm.stages);
     config.stream = stream;
@@ -513,7 +515,7 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
         else if (epilogue == EPI_BF16) epilogue = EPI_BF16_WIDE;
     }
     if (splits > 1 && bn_eff > 64) return FWB_UNSUPPORTED;
-    if ((M + bn_eff - 1) / bn_eff > 65535) return FWB_TOO_LARGE;
+    if ((N + BM - 1) / BM > 65535) return FWB_TOO_LARGE;
     const int total_kb = (K + BK - 1) / BK;
     if (splits > total_kb) splits = total_kb;
     Params prm;
