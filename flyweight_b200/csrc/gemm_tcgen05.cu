@@ -8,10 +8,10 @@
 // weight streamer for decode (every weight byte is read once, the few tokens ride along);
 // with BN = 256 it is the ordinary 128x256 tile for prefill.  One kernel, five BN.
 //
-// Roles inside a CTA (192 threads): warp 0 = TMA producer (one elected lane issues
+// Roles inside a CTA (192 or 576 threads): warp 0 = TMA producer (one elected lane issues
 // cp.async.bulk.tensor loads of 128B-swizzled [rows x 64] boxes into a ring of stages),
 // warp 1 = TMEM allocator and MMA issuer (one elected lane issues tcgen05.mma, K = 16 per
-// instruction, four per stage, and commits stages back to the producer), warps 2..5 =
+// instruction, four per stage, and commits stages back to the producer), warps 2..5 or 2..17 =
 // epilogue (tcgen05.ld of their lane quarter, then the fused epilogue and the store).
 //
 // Split-K without atomics or scratch in global memory: grid.z CTAs that share an output
@@ -31,20 +31,36 @@
 // Every wait on an mbarrier is bounded: after the limit the CTA raises the library's status
 // word, stops waiting everywhere, still meets its cluster barriers, frees its TMEM and
 // returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 using namespace fwb;
+using namespace fwb::tc5;
+
+namespace {
+__device__ int g_gemm_status = 0;
+}
+
+namespace fwb {
+namespace tc5 {
+int* status_word() {
+    static int* address = nullptr;
+    if (!address) {
+        void* found = nullptr;
+        if (cudaGetSymbolAddress(&found, g_gemm_status) == cudaSuccess) address = static_cast<int*>(found);
+    }
+    return address;
+}
+}  // namespace tc5
+}  // namespace fwb
 
 namespace {
 
-constexpr int BM = 128;          // features per CTA (UMMA M)
-constexpr int BK = 64;           // K elements per stage: one 128-byte swizzle row of bf16
-constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+// Epilogue warps: four for decode-sized token tiles (little to store, and several CTAs share an
+// SM), sixteen -- four per quarter of the TMEM lanes -- for prompt-sized tiles, where the stores
+// of 128 x 256 (x2) values would otherwise leave the tensor pipe idle for a fifth of the time.
+constexpr int epi_warps(int bn) { return bn >= 128 ? 16 : 4; }
+constexpr int threads_for(int bn) { return 64 + 32 * epi_warps(bn); }   // + producer and MMA warps
 constexpr int SMEM_BUDGET = 200 * 1024;
-constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 // The WIDE forms give a CTA two adjacent 128-feature tiles (two accumulators over the same
 // token tile): per MMA the activations are read from L2 once for 256 features, which is what
@@ -54,131 +70,6 @@ enum Epilogue : int { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF1
 constexpr bool epi_wide(int epi) { return epi == EPI_F32_WIDE || epi == EPI_BF16_WIDE; }
 constexpr int epi_accumulators(int epi) { return (epi == EPI_SWIGLU_BF16 || epi_wide(epi)) ? 2 : 1; }
 
-__device__ int g_gemm_status = 0;   // 0 = fine; else the code of the first wait that gave up
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Bounded wait.  Returns false if it gave up (or somebody else in the CTA did).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int code) {
-    for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
-        if (mbar_test(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (spin > 2048) __nanosleep(64);
-    }
-    *abort_flag = code;
-    atomicCAS(&g_gemm_status, 0, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
-                                            int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(holder)),
-                 "r"(cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                     smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
-
-// silu for the bfloat16 epilogue: g / (1 + e^-g) with the hardware exponential and reciprocal.
-// The result is rounded to bfloat16 (8 bits) right away; their few-ulp fp32 error is far below
-// that.  For g << 0, e^-g overflows to +inf and the quotient is -0, the right limit.
-__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
-
-// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle): 1
-    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-    return d;
-}
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-    return (1u << 4)                 // D: fp32
-           | (1u << 7) | (1u << 10)  // A, B: bf16
-           | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
 
 template <int BN, int NACC>
 struct Tile {
@@ -207,10 +98,11 @@ struct Params {
     int up_row_offset;     // SwiGLU: rows of the up projection start here in W
     int k_blocks_per_split;
     int stages;            // depth of the shared-memory ring (<= Tile::MAX_STAGES)
+    int* status;           // the library's status word (see tc5::status_word)
 };
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(threads_for(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const Params prm) {
     constexpr int NACC = epi_accumulators(EPI);
@@ -273,7 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t round = i / STAGES;
-                if (!mbar_wait(&empty_bar[s], (round - 1) & 1, abort_flag, 1)) break;
+                if (!mbar_wait(&empty_bar[s], (round - 1) & 1, abort_flag, 1, prm.status)) break;
                 uint8_t* stage = tiles + (size_t)s * T::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
@@ -289,7 +181,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
                 const uint32_t round = i / STAGES;
-                ok = mbar_wait(&full_bar[s], round & 1, abort_flag, 2);
+                ok = mbar_wait(&full_bar[s], round & 1, abort_flag, 2, prm.status);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t stage = smem_u32(tiles + (size_t)s * T::STAGE_BYTES);
@@ -313,13 +205,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     // ---------------------------------------------------------------- epilogue
     const bool epi_warp = warp >= 2;
+    // sixteen epilogue warps: four per quarter of the TMEM lanes (a warp may only read the quarter
+    // its index selects); with one slice of K they split the token columns between them, which
+    // keeps several warps per scheduler busy during the stores instead of one
+    const int column_group = (warp - 2) >> 2;
+    const int column_half = column_group;          // 0 for the warps that do the split-K reduction
     const int quarter = warp & 3;                  // the TMEM lanes this warp may read
     const int row = quarter * 32 + lane;           // feature inside the tile
     bool acc_ready = true;
     if (epi_warp) {
         pdl_wait();              // the addend is read and Y written only after the previous kernel
 
-        if (n_kb > 0) acc_ready = mbar_wait(acc_bar, 0, abort_flag, 3);
+        if (n_kb > 0) acc_ready = mbar_wait(acc_bar, 0, abort_flag, 3, prm.status);
         acc_ready = acc_ready && !*abort_flag;
         acc_ready = __all_sync(0xffffffffu, acc_ready);   // tcgen05.ld needs the whole warp
         tc_fence_after();
@@ -346,8 +243,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (splits == 1) {
         if (epi_warp && acc_ready) {
+            constexpr int GROUPS = epi_warps(BN) / 4;
+            constexpr int PER_GROUP = BN / GROUPS >= 16 ? BN / GROUPS : 16;
+            const int c_begin = column_group * PER_GROUP;
+            const int c_end = c_begin + PER_GROUP < BN ? c_begin + PER_GROUP : BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = c_begin; c0 < c_end; c0 += 16) {
                 float g[16], u[16];
                 if (n_kb > 0) {
                     tmem_ld16(lane_addr + c0, g);
@@ -364,7 +265,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // park the partial tile in shared memory: partial[col][row], fp32 (the pipeline's
         // stages are free: every MMA that read them has completed)
         float* partial = reinterpret_cast<float*>(tiles);
-        if (epi_warp) {
+        if (epi_warp && column_half == 0) {
 #pragma unroll 1
             for (int c0 = 0; c0 < T::COLS; c0 += 16) {
                 float v[16];
@@ -379,7 +280,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         tc_fence_before();
         cluster_sync_all();
-        if (epi_warp) {
+        if (epi_warp && column_half == 0) {
             const uint32_t rank = cluster_rank();
             const uint32_t base = smem_u32(partial);
             for (int col = (int)rank; col < BN; col += splits) {
@@ -449,7 +350,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, Params prm, int s
     cudaLaunchConfig_t config = {};
     constexpr int FEATURES = epi_wide(EPI) ? 2 * BM : BM;
     config.gridDim = dim3((prm.M + BN - 1) / BN, (prm.N + FEATURES - 1) / FEATURES, splits);
-    config.blockDim = dim3(THREADS);
+    config.blockDim = dim3(threads_for(BN));
     config.dynamicSmemBytes = T::smem_bytes(prm.stages);
     config.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -528,6 +429,7 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     prm.up_row_offset = up_row_offset;
     prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
     prm.stages = stages;
+    prm.status = status_word();
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, W, w_rows, K, BM)) return FWB_UNSUPPORTED;
     if (!make_map(&map_x, X, M, K, bn_eff)) return FWB_UNSUPPORTED;

@@ -39,6 +39,14 @@ def accepts(x, w, out_dtype, addend=None) -> bool:
 
 
 _forced_splits = None
+_use_pairs = True
+
+
+def set_pairs_enabled(flag: bool) -> None:
+    """Prompt-sized products on CTA pairs (on by default); off: the single-CTA kernel."""
+    global _use_pairs
+    _use_pairs = bool(flag)
+
 # Per-shape overrides found by measurement: (features, K, accumulators) -> (splits, stages);
 # 0 keeps the rule's choice.  Only decode-sized token counts (<= 64) consult it.
 TUNED = {}
@@ -116,6 +124,12 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
         epilogue = EPI_ADD_F32
     else:
         epilogue = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
+    if (_use_pairs and M > 128 and addend is None and splits is None and not stages
+            and not tile_tokens and wide == -1 and N >= 256):
+        # prompt-sized: CTA pairs (cta_group::2); two feature blocks per pair when single blocks
+        # would make more CTAs than the GPU holds at once (measured at 2,048 tokens on B200)
+        pairs = -(-N // 256) * -(-M // 256)
+        return gemm_pair(x, w, out_dtype, wide=pairs > SM_COUNT // 2)
     if M <= 64 and (N, K, 1) in TUNED and _forced_splits is None:
         tuned = TUNED[(N, K, 1)]
         splits = splits or tuned[0] or None
@@ -167,3 +181,30 @@ def status() -> int:
     """0, or the code a wait that gave up inside the kernel left (reads and clears it;
     synchronises the device)."""
     return int(lib.library().fwb_gemm_tcgen05_status())
+
+
+def gemm_pair(x, w, out_dtype, wide=False) -> torch.Tensor:
+    """``x @ w.T`` on CTA pairs (tcgen05 cta_group::2): 256 features x 256 tokens per pair and
+    accumulator.  For prompt-sized steps; bf16 in, fp32 or bf16 out."""
+    check_tensor("gemm input", x, torch.bfloat16)
+    check_tensor("gemm weight", w, torch.bfloat16)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: input has {K} columns, weight has {w.shape[1]}")
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w), ptr(out), M, N, K, N, N,
+             EPI_F32 if out_dtype == torch.float32 else EPI_BF16, 0, 1 if wide else 0, stream())
+    return out
+
+
+def swiglu_gate_up_pair(x, w_gate_up) -> torch.Tensor:
+    """The fused gate/up product with the SwiGLU epilogue on CTA pairs."""
+    check_tensor("swiglu input", x, torch.bfloat16)
+    check_tensor("swiglu weight", w_gate_up, torch.bfloat16)
+    M, K = x.shape
+    F = w_gate_up.shape[0] // 2
+    out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
+    lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w_gate_up), ptr(out), M, F, K, 2 * F, F,
+             EPI_SWIGLU_BF16, F, 0, stream())
+    return out

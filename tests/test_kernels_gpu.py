@@ -571,3 +571,31 @@ def test_tcgen05_tile_shapes_for_prompts(M, N, K, tile_tokens, wide, out_dtype):
     got = tc.gemm(dev(x), dev(w), out_dtype, None, None, 0, tile_tokens, wide)
     close(got, want, 1e-5 if out_dtype == torch.float32 else 2.0 ** -8, "tile shape")
     assert tc.status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(129, 256, 64), (256, 256, 256), (300, 700, 264), (1030, 1000, 96),
+                                   (2048, 2048, 512), (513, 3072, 200)])
+@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_tcgen05_cta_pair_gemm(M, N, K, wide, out_dtype):
+    """The cta_group::2 kernel: 256 features x 256 tokens per CTA pair, ragged edges included."""
+    from flyweight_b200.kernels import tensorcore as tc
+    g = torch.Generator().manual_seed(M + 3 * N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    close(tc.gemm_pair(dev(x), dev(w), out_dtype, wide), want,
+          1e-5 if out_dtype == torch.float32 else 2.0 ** -8, "pair gemm")
+    assert tc.status() == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(200, 320, 96), (700, 1000, 264), (2048, 512, 128)])
+def test_tcgen05_cta_pair_swiglu(M, F, K):
+    from flyweight_b200.kernels import tensorcore as tc
+    g = torch.Generator().manual_seed(M + F)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    gu = x.double() @ w.double().T
+    want = torch.from_numpy(P.silu(gu[:, :F].numpy())) * gu[:, F:]
+    close(tc.swiglu_gate_up_pair(dev(x), dev(w)), want, 2.0 ** -8, "pair swiglu")
+    assert tc.status() == 0
