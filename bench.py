@@ -309,6 +309,46 @@ def run_ours(args) -> int:
     return 0
 
 
+def run_profile_step(args) -> int:
+    """One step (decode at batch 8 / context 4,096, or a 2,048-token prefill) between
+    cudaProfilerStart/Stop after warm-up, with CUDA graphs off so that every kernel is a launch
+    of its own: the target of ``ncu --profile-from-start off`` for a per-kernel launch list."""
+    import torch
+    from flyweight_b200.engine import ModelRunner
+    from flyweight_b200.engine.runtime import Model
+    from flyweight_b200.sampling import sampler
+    model = Model.random(dict(LFM2_1P2B), seed=0, dtype="bfloat16", device="cuda:0").module
+    vocab = LFM2_1P2B["vocab_size"]
+    rng = torch.Generator().manual_seed(0)
+    if args.profile == "decode":
+        total = CONTEXT + 16
+        runner = ModelRunner(model, num_pages=BATCH * (-(-total // 64)), num_slots=BATCH,
+                             max_model_len=total, max_batched_tokens=2048, use_graphs=False)
+        requests = [f"b{i}" for i in range(BATCH)]
+        fill_context(runner, requests, CONTEXT, vocab, rng)
+
+        def step():
+            sampler.argmax(runner.step([(r, [7], [0]) for r in requests]))
+    else:
+        runner = ModelRunner(model, num_pages=PREFILL_TOKENS // 64 + 2, num_slots=1,
+                             max_model_len=PREFILL_TOKENS + 64, max_batched_tokens=PREFILL_TOKENS,
+                             use_graphs=False)
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=rng).tolist()
+
+        def step():
+            runner.step([("p", prompt, [PREFILL_TOKENS - 1])])
+            runner.finish("p")
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(json.dumps({"profiled": args.profile, "launches_per_step": "see the profiler's list"}))
+    return 0
+
+
 def run_reference(args) -> int:
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     try:
@@ -328,11 +368,15 @@ def main() -> int:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--layers", type=int, default=0,
                         help="run fewer layers than the configuration has (both counts are reported)")
+    parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
+                        help="run one step inside cudaProfilerStart/Stop (for a profiler) and exit")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (N=1 only)")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.profile:
+        return run_profile_step(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
