@@ -224,7 +224,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int seg = tile_seg[blockIdx.x], tok0 = tile_tok0[blockIdx.x], kvh = blockIdx.y;
+    // the last tiles of a prompt walk the most keys: they go first, so that the launch does not
+    // end on a few long CTAs
+    const int tile_index = gridDim.x - 1 - blockIdx.x;
+    const int seg = tile_seg[tile_index], tok0 = tile_tok0[tile_index], kvh = blockIdx.y;
     const int seg_end = seg_start[seg + 1];
     int n_tok = seg_end - tok0;
     if (n_tok > tokens_per_tile) n_tok = tokens_per_tile;

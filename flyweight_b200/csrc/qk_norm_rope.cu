@@ -89,6 +89,98 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
     }
 }
 
+// All-bfloat16 form: hd/8 adjacent lanes own one head, 8 contiguous channels each (one 16-byte
+// load and store per lane), so a warp works on 32/(hd/8) heads at a time.  The sum of squares
+// goes over the lanes of a head in lane order; the rotation partner (i +- rot/2) sits
+// rot/16 lanes away and is fetched with shuffles.  Needs hd % 8 == 0, hd <= 256, rot % 16 == 0.
+__device__ __forceinline__ void load8(const __nv_bfloat16* src, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&f)[8]) {
+    uint4 out;
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(dst) = out;
+}
+
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ wq,
+                           const float* __restrict__ wk, const float2* __restrict__ table,
+                           const int* __restrict__ positions, const int* __restrict__ tok_seg,
+                           const int* __restrict__ block_table, int max_pages, int page_size,
+                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
+                           __nv_bfloat16* __restrict__ v_pool, int nh, int nkv, int hd, int rot, float eps,
+                           int use_norm) {
+    fwb::pdl_entry();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = hd >> 3, per_warp = 32 / G;
+    const int sub = lane / G, gl = lane - sub * G;
+    const int pos = positions[t];
+    const int heads = nh + 2 * nkv;
+    const __nv_bfloat16* row = qkv + (size_t)t * heads * hd;
+    const float2* cs = table + (size_t)pos * (rot / 2);
+    size_t cache_base = 0;
+    if (nkv > 0) {
+        const int page = block_table[(size_t)tok_seg[t] * max_pages + pos / page_size];
+        cache_base = ((size_t)page * nkv) * page_size * hd + (size_t)(pos % page_size) * hd;
+    }
+    const int half_lanes = rot >> 4, rot_lanes = rot >> 3;
+    const int partner = gl < half_lanes ? lane + half_lanes : (gl < rot_lanes ? lane - half_lanes : lane);
+    for (int h0 = (blockIdx.y * WARPS + warp) * per_warp; h0 < heads; h0 += gridDim.y * WARPS * per_warp) {
+        const int h = h0 + sub;
+        const bool valid = sub < per_warp && h < heads;
+        float v[8];
+        if (valid) {
+            load8(row + (size_t)h * hd + gl * 8, v);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        }
+        const bool is_v = h >= nh + nkv, is_q = h < nh;
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+        float total = 0.0f;
+        for (int j = 0; j < G; ++j) total += __shfl_sync(0xffffffffu, ss, (sub * G + j) & 31);
+        if (use_norm && !is_v) {
+            const float inv = rsqrtf(total / (float)hd + eps);
+            const float* w = (is_q ? wq : wk) + gl * 8;
+            if (valid) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (v[i] * inv) * w[i];
+            }
+        }
+        float other[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, v[i], partner);
+        if (!valid) continue;
+        if (!is_v && gl < rot_lanes) {
+            const bool low = gl < half_lanes;
+            const float2* c = cs + (low ? gl : gl - half_lanes) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 a = c[i];
+                v[i] = low ? v[i] * a.x - other[i] * a.y : v[i] * a.x + other[i] * a.y;
+            }
+        }
+        __nv_bfloat16* dst;
+        if (is_q) dst = q_out + ((size_t)t * nh + h) * hd;
+        else if (!is_v) dst = k_pool + cache_base + (size_t)(h - nh) * page_size * hd;
+        else dst = v_pool + cache_base + (size_t)(h - nh - nkv) * page_size * hd;
+        store8(dst + gl * 8, v);
+    }
+}
+
 }  // namespace
 
 // qkv: [T][(nh+2*nkv)*hd] fp32 or bf16.  wq, wk: [hd] fp32 (ignored when use_norm == 0).
@@ -118,6 +210,16 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
         (const TI*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table, max_pages, \
         page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm)
     const int key = (in_bf16 ? 4 : 0) | (q_bf16 ? 2 : 0) | (cache_bf16 ? 1 : 0);
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
+    if (key == 7 && (hd & 7) == 0 && hd <= 256 && (rot & 15) == 0 && aligned) {
+        const int per_block = WARPS * (32 / (hd >> 3));
+        const dim3 vgrid(T, T >= 256 ? 1 : (nh + 2 * nkv + per_block - 1) / per_block);
+        fwb::pdl(qk_norm_rope_bf16x8_kernel, vgrid, WARPS * 32, 0, stream)(
+            (const __nv_bfloat16*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table,
+            max_pages, page_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh,
+            nkv, hd, rot, eps, use_norm);
+        return fwb_launch_status();
+    }
     switch (key) {
         case 0: FWB_QK(float, float, float); break;
         case 3: FWB_QK(float, bf, bf); break;

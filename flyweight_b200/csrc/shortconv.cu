@@ -86,6 +86,39 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     }
 }
 
+// Head work of the bfloat16 launches: thread idx owns (segment, channel): the first L-1 outputs
+// of the segment and the state.
+__device__ __forceinline__ void conv_head_bf16(const __nv_bfloat16* __restrict__ p, const float* __restrict__ taps,
+                                               const float* __restrict__ bias, float* __restrict__ state,
+                                               const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                                               __nv_bfloat16* __restrict__ z, int S, int H, int L, size_t idx) {
+    const int ld = 3 * H;
+    if (idx >= (size_t)S * H) return;
+    const int s = (int)(idx / H), c = (int)(idx - (size_t)s * H);
+    const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
+    float* st = state + ((size_t)seg_slot[s] * H + c) * (L - 1);
+    float hist[2 * MAX_TAPS];
+    float w[MAX_TAPS];
+    for (int k = 0; k < L; ++k) w[k] = taps[c * L + k];
+    for (int k = 0; k < L - 1; ++k) hist[k] = st[k];
+    const int first = n < L - 1 ? n : L - 1;
+    for (int j = 0; j < first; ++j) {
+        const __nv_bfloat16* row = p + (size_t)(t0 + j) * ld;
+        hist[L - 1 + j] = __bfloat162float(row[c]) * __bfloat162float(row[2 * H + c]);
+        float y = bias ? bias[c] : 0.0f;
+        for (int k = 0; k < L; ++k) y = fmaf(w[k], hist[j + k], y);
+        z[(size_t)(t0 + j) * H + c] = __float2bfloat16_rn(__bfloat162float(row[H + c]) * y);
+    }
+    if (n >= L - 1) {
+        for (int k = 0; k < L - 1; ++k) {
+            const __nv_bfloat16* row = p + (size_t)(t0 + n - (L - 1) + k) * ld;
+            st[k] = __bfloat162float(row[c]) * __bfloat162float(row[2 * H + c]);
+        }
+    } else {
+        for (int k = 0; k < L - 1; ++k) st[k] = hist[k + n];
+    }
+}
+
 __global__ void shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ taps,
                                         const float* __restrict__ bias, float* __restrict__ state,
                                         const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
@@ -120,31 +153,90 @@ __global__ void shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, con
         *reinterpret_cast<uint4*>(z + (size_t)t * H + c) = out;
         return;
     }
-    const size_t idx = (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)S * H) return;
-    const int s = (int)(idx / H), c = (int)(idx - (size_t)s * H);
-    const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
-    float* st = state + ((size_t)seg_slot[s] * H + c) * (L - 1);
-    float hist[2 * MAX_TAPS];
-    float w[MAX_TAPS];
-    for (int k = 0; k < L; ++k) w[k] = taps[c * L + k];
-    for (int k = 0; k < L - 1; ++k) hist[k] = st[k];
-    const int first = n < L - 1 ? n : L - 1;
-    for (int j = 0; j < first; ++j) {
-        const __nv_bfloat16* row = p + (size_t)(t0 + j) * ld;
-        hist[L - 1 + j] = __bfloat162float(row[c]) * __bfloat162float(row[2 * H + c]);
-        float y = bias ? bias[c] : 0.0f;
-        for (int k = 0; k < L; ++k) y = fmaf(w[k], hist[j + k], y);
-        z[(size_t)(t0 + j) * H + c] = __float2bfloat16_rn(__bfloat162float(row[H + c]) * y);
-    }
-    if (n >= L - 1) {
-        for (int k = 0; k < L - 1; ++k) {
-            const __nv_bfloat16* row = p + (size_t)(t0 + n - (L - 1) + k) * ld;
-            st[k] = __bfloat162float(row[c]) * __bfloat162float(row[2 * H + c]);
+    conv_head_bf16(p, taps, bias, state, seg_start, seg_slot, z, S, H, L,
+                   (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x);
+}
+
+// Prompt-sized bfloat16 launches: a body thread owns 8 adjacent channels over a run of
+// consecutive tokens and slides the window of B*x products through registers, so each row of p
+// is loaded once per run instead of once per tap.  Products that precede the run are reloaded
+// at its start; a run that crosses into another segment carries products of the previous
+// segment only into outputs with j < L-1, which the head threads own.  The sum runs in the
+// same order as everywhere else: bias, then taps oldest first.
+template <int L>
+__global__ void __launch_bounds__(128)
+shortconv_bf16_run_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ taps,
+                          const float* __restrict__ bias, float* __restrict__ state,
+                          const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                          const int* __restrict__ tok_seg, __nv_bfloat16* __restrict__ z, int T, int S,
+                          int H, int body_blocks, int run) {
+    fwb::pdl_entry();
+    const int ld = 3 * H;
+    if ((int)blockIdx.x < body_blocks) {
+        const int groups = H >> 3;
+        const int runs = (T + run - 1) / run;
+        const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+        if (idx >= (size_t)runs * groups) return;
+        const int r = (int)(idx / groups), c = (int)(idx - (size_t)r * groups) * 8;
+        const int t0 = r * run, t1 = min(T, t0 + run);
+        float w[L][8], b0[8], hist[L - 1][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            b0[i] = bias ? bias[c + i] : 0.0f;
+#pragma unroll
+            for (int k = 0; k < L; ++k) w[k][i] = taps[(c + i) * L + k];
         }
-    } else {
-        for (int k = 0; k < L - 1; ++k) st[k] = hist[k + n];
+#pragma unroll
+        for (int k = 0; k < L - 1; ++k) {
+            const int t = t0 - (L - 1) + k;
+            if (t >= 0) {
+                const __nv_bfloat16* row = p + (size_t)t * ld;
+                float b[8], x[8];
+                unpack8(*reinterpret_cast<const uint4*>(row + c), b);
+                unpack8(*reinterpret_cast<const uint4*>(row + 2 * H + c), x);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) hist[k][i] = b[i] * x[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) hist[k][i] = 0.0f;
+            }
+        }
+        for (int t = t0; t < t1; ++t) {
+            const __nv_bfloat16* row = p + (size_t)t * ld;
+            float b[8], x[8], u[8];
+            unpack8(*reinterpret_cast<const uint4*>(row + c), b);
+            unpack8(*reinterpret_cast<const uint4*>(row + 2 * H + c), x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) u[i] = b[i] * x[i];
+            const int j = t - seg_start[tok_seg[t]];
+            if (j >= L - 1) {
+                float g[8], y[8];
+                unpack8(*reinterpret_cast<const uint4*>(row + H + c), g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    y[i] = b0[i];
+#pragma unroll
+                    for (int k = 0; k < L - 1; ++k) y[i] = fmaf(w[k][i], hist[k][i], y[i]);
+                    y[i] = fmaf(w[L - 1][i], u[i], y[i]);
+                }
+                uint4 out;
+                __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    o[i] = __floats2bfloat162_rn(g[2 * i] * y[2 * i], g[2 * i + 1] * y[2 * i + 1]);
+                *reinterpret_cast<uint4*>(z + (size_t)t * H + c) = out;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                for (int k = 0; k + 1 < L - 1; ++k) hist[k][i] = hist[k + 1][i];
+                hist[L - 2][i] = u[i];
+            }
+        }
+        return;
     }
+    conv_head_bf16(p, taps, bias, state, seg_start, seg_slot, z, S, H, L,
+                   (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x);
 }
 
 }  // namespace
@@ -162,8 +254,21 @@ FWB_API int fwb_shortconv(const void* p, int p_bf16, const float* taps, const fl
     if (L < 2 || L > MAX_TAPS) return FWB_UNSUPPORTED;
     const int threads = 128;
     if (p_bf16 && z_bf16 && (H & 7) == 0 && ((uintptr_t)p & 15) == 0 && ((uintptr_t)z & 15) == 0) {
-        const int body = (int)(((size_t)T * (H >> 3) + threads - 1) / threads);
         const int head = (int)(((size_t)S * H + threads - 1) / threads);
+        if (T >= 256 && L >= 2 && L <= 4) {
+            const int run = 4;
+            const int body = (int)(((size_t)((T + run - 1) / run) * (H >> 3) + threads - 1) / threads);
+#define FWB_CONV_RUN(LL)                                                                          \
+    fwb::pdl(shortconv_bf16_run_kernel<LL>, body + head, threads, 0, stream)(                     \
+        (const __nv_bfloat16*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (__nv_bfloat16*)z, T, S, \
+        H, body, run)
+            if (L == 2) FWB_CONV_RUN(2);
+            else if (L == 3) FWB_CONV_RUN(3);
+            else FWB_CONV_RUN(4);
+#undef FWB_CONV_RUN
+            return fwb_launch_status();
+        }
+        const int body = (int)(((size_t)T * (H >> 3) + threads - 1) / threads);
         fwb::pdl(shortconv_bf16x8_kernel, body + head, threads, 0, stream)(
             (const __nv_bfloat16*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (__nv_bfloat16*)z, T, S,
             H, L, body);

@@ -166,6 +166,51 @@ __host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n) {
 }
 __host__ __device__ constexpr uint32_t make_idesc(int n) { return make_idesc_mn(BM, n); }
 
+// The same for an operand whose MN dimension is the contiguous one (a [K rows][64 MN] tile of
+// 128-byte rows, as TMA leaves a row-major [keys][head_dim] box): 8-row groups along K are
+// 1024 bytes apart (stride offset), 64-element blocks along MN `mn_block_bytes` apart (leading
+// offset).  Goes with the MN-major bit of the instruction descriptor.
+__device__ __forceinline__ uint64_t make_smem_desc_mn_major(uint32_t saddr, uint32_t mn_block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+constexpr uint32_t IDESC_B_MN_MAJOR = 1u << 16;
+
+// ------------------------------------------------------------------ host: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// A [rows][K] bf16 row-major matrix seen as boxes of [box_rows][64] with 128-byte swizzle.
+inline bool make_map(CUtensorMap* map, const void* base, long rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 }  // namespace tc5
 }  // namespace fwb

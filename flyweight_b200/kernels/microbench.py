@@ -4,6 +4,8 @@
     python -m flyweight_b200.kernels.microbench gemm --tokens 2048 --features 8192 --k 2048 --swiglu
     python -m flyweight_b200.kernels.microbench attention-decode --batch 8 --context 4096
     python -m flyweight_b200.kernels.microbench attention-prefill --tokens 2048
+    python -m flyweight_b200.kernels.microbench shortconv --tokens 2048
+    python -m flyweight_b200.kernels.microbench qk-norm-rope --tokens 2048
 
 It is what the ncu summaries under ``profiles/`` were captured from (small cases of the same
 kernels the engine runs), and a quick way to see what a shape costs.  Weight matrices are
@@ -29,6 +31,20 @@ def _time(fn, repeat: int, warmup: int = 3) -> float:
     stop.record()
     torch.cuda.synchronize()
     return start.elapsed_time(stop) * 1e3 / repeat          # microseconds
+
+
+def _time_graph(fn, repeat: int) -> float:
+    """The same for kernels shorter than a Python call: ``repeat`` launches captured into one
+    CUDA graph, the replay timed."""
+    fn()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(repeat):
+                fn()
+    return _time(graph.replay, 5) / repeat
 
 
 def run_gemm(args) -> dict:
@@ -104,6 +120,41 @@ def run_attention_prefill(args) -> dict:
     return {"kernel": "attention_prefill_mma", "tokens": T, "us": us, "tflops": flops / us / 1e6}
 
 
+def run_shortconv(args) -> dict:
+    from . import ops
+    T, H, L = args.tokens, args.hidden, args.taps
+    p = torch.randn(T, 3 * H, device="cuda").to(torch.bfloat16)
+    taps = torch.randn(H, L, device="cuda")
+    state = torch.zeros(1, H, L - 1, device="cuda")
+    seg_start = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    seg_slot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tok_seg = torch.zeros(T, dtype=torch.int32, device="cuda")
+    us = _time_graph(lambda: ops.shortconv(p, taps, None, state, seg_start, seg_slot, tok_seg, 1,
+                                           torch.bfloat16), args.repeat)
+    return {"kernel": "shortconv", "tokens": T, "hidden": H, "taps": L, "us": us,
+            "gb_s": T * H * 2 * 4 / us / 1e3}
+
+
+def run_qk_norm_rope(args) -> dict:
+    from . import ops
+    T, nh, nkv, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
+    pages = -(-T // 64)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda").to(torch.bfloat16)
+    w = torch.ones(hd, device="cuda")
+    angles = torch.arange(T, dtype=torch.float64)[:, None] * (1e6 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
+    table = torch.stack([angles.cos(), angles.sin()], -1).float().cuda()
+    positions = torch.arange(T, dtype=torch.int32, device="cuda")
+    tok_seg = torch.zeros(T, dtype=torch.int32, device="cuda")
+    block_table = torch.arange(pages, dtype=torch.int32, device="cuda")[None]
+    k_pool = torch.zeros(pages, nkv, 64, hd, device="cuda", dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    us = _time_graph(lambda: ops.qk_norm_rope(qkv, w, w, table, positions, tok_seg, block_table,
+                                              k_pool, v_pool, nh, nkv, hd, hd, 1e-5, torch.bfloat16),
+                     args.repeat)
+    return {"kernel": "qk_norm_rope", "tokens": T, "us": us,
+            "gb_s": T * (nh + 2 * nkv) * hd * 2 * 2 / us / 1e3}
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m flyweight_b200.kernels.microbench",
                                      description=__doc__,
@@ -128,11 +179,21 @@ def main(argv=None) -> int:
         p.add_argument("--kv-heads", type=int, default=8)
         p.add_argument("--head-dim", type=int, default=64)
         p.add_argument("--splits", type=int, default=0)
+    conv = sub.add_parser("shortconv")
+    conv.add_argument("--tokens", type=int, default=2048)
+    conv.add_argument("--hidden", type=int, default=2048)
+    conv.add_argument("--taps", type=int, default=3)
+    rope = sub.add_parser("qk-norm-rope")
+    rope.add_argument("--tokens", type=int, default=2048)
+    rope.add_argument("--heads", type=int, default=32)
+    rope.add_argument("--kv-heads", type=int, default=8)
+    rope.add_argument("--head-dim", type=int, default=64)
     for p in sub.choices.values():
         p.add_argument("--repeat", type=int, default=20)
     args = parser.parse_args(argv)
     runner = {"gemm": run_gemm, "attention-decode": run_attention_decode,
-              "attention-prefill": run_attention_prefill}[args.kernel]
+              "attention-prefill": run_attention_prefill, "shortconv": run_shortconv,
+              "qk-norm-rope": run_qk_norm_rope}[args.kernel]
     print(json.dumps(runner(args)))
     return 0
 

@@ -172,6 +172,47 @@ def test_shortconv_over_ragged_segments(H, L, bias, dtype):
     assert torch.equal(sd[7].cpu(), state[7])                 # an unused slot is untouched
 
 
+@pytest.mark.parametrize("H,L,bias", [(64, 3, True), (104, 2, False), (72, 4, True), (40, 5, False)])
+def test_shortconv_prompt_sized_bfloat16(H, L, bias):
+    """Long segments take the kernel that slides a window over runs of tokens: segment edges
+    inside a run, a run that starts at a segment's first tokens, the tail of the batch."""
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(H * L)
+    segments = [(1, 130), (0, 1), (2, 2), (3, 301), (4, L - 1), (5, 67), (6, 3)]
+    T = sum(n for _, n in segments)
+    p = torch.randn(T, 3 * H, generator=g).to(torch.bfloat16)
+    taps = torch.randn(H, L, generator=g)
+    b = torch.randn(H, generator=g) if bias else None
+    state = torch.randn(8, H, L - 1, generator=g)
+    seg_start = torch.tensor(np.cumsum([0] + [n for _, n in segments]), dtype=torch.int32)
+    seg_slot = torch.tensor([s for s, _ in segments], dtype=torch.int32)
+    tok_seg = torch.tensor([i for i, (_, n) in enumerate(segments) for _ in range(n)], dtype=torch.int32)
+    want_z, want_state = conv_reference(p, taps, b, state, segments)
+    sd = dev(state)
+    z = ops.shortconv(dev(p), dev(taps), None if b is None else dev(b), sd, dev(seg_start),
+                      dev(seg_slot), dev(tok_seg), len(segments), torch.bfloat16)
+    close(z, want_z, 2.0 ** -7, "conv output")
+    close(sd, want_state, 1e-6, "conv state")
+    # and the same bits as the per-token kernel that short batches take
+    cut = 200
+    sd2 = dev(state)
+    parts = []
+    for lo, hi in ((0, cut), (cut, T)):
+        segs = []
+        t = 0
+        for slot, n in segments:
+            a, e = max(t, lo), min(t + n, hi)
+            if e > a:
+                segs.append((slot, e - a))
+            t += n
+        ss = torch.tensor(np.cumsum([0] + [n for _, n in segs]), dtype=torch.int32)
+        sl = torch.tensor([s_ for s_, _ in segs], dtype=torch.int32)
+        ts = torch.tensor([i for i, (_, n) in enumerate(segs) for _ in range(n)], dtype=torch.int32)
+        parts.append(ops.shortconv(dev(p[lo:hi]), dev(taps), None if b is None else dev(b), sd2,
+                                   dev(ss), dev(sl), dev(ts), len(segs), torch.bfloat16))
+    assert torch.equal(torch.cat(parts), z) and torch.equal(sd2, sd)
+
+
 def test_shortconv_cut_anywhere_gives_the_same_bits():
     from flyweight_b200.kernels import ops
     g = torch.Generator().manual_seed(3)
@@ -206,8 +247,9 @@ def rope_table(theta, rot, n):
 
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (3, 1, 32, 32), (5, 5, 48, 32), (2, 1, 80, 80),
                                            (8, 2, 128, 64), (2, 2, 256, 256)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_qk_norm_rope_and_cache_write(nh, nkv, hd, rot, dtype):
+@pytest.mark.parametrize("dtype,bf16_input", [(torch.float32, False), (torch.bfloat16, False),
+                                              (torch.bfloat16, True)])
+def test_qk_norm_rope_and_cache_write(nh, nkv, hd, rot, dtype, bf16_input):
     from flyweight_b200.kernels import ops
     g = torch.Generator().manual_seed(nh * hd)
     T, pages, P_ = 6, 5, 64
@@ -215,6 +257,8 @@ def test_qk_norm_rope_and_cache_write(nh, nkv, hd, rot, dtype):
     tok_seg = torch.tensor([0, 0, 1, 1, 1, 0], dtype=torch.int32)
     table_rows = torch.tensor([[3, 1, 4], [0, 2, -1]], dtype=torch.int32)
     qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g)
+    if bf16_input:                                            # the engine's bfloat16 path: 16-byte lanes
+        qkv = qkv.to(torch.bfloat16)
     wq, wk = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
     eps, theta = 1e-5, 1e4
     table = rope_table(theta, rot, 200)
