@@ -1,7 +1,8 @@
 """Dispatch between the attention kernels for one step's batch.
 
 bfloat16 cache and a shape the tensor-core kernels take: a step of single decode tokens runs
-the split-context decode kernel, anything else the tiled prefill kernel.  Everything else
+the split-context decode kernel; prompt portions that fill 128-row tiles run the tcgen05 kernel
+(head sizes 64 and 128); anything else the tiled mma.sync kernel.  Everything else
 (the 32-bit path, head sizes above 128, more than 16 query heads per KV head) runs the SIMT
 kernel.
 """
@@ -22,6 +23,14 @@ def set_mma_enabled(flag: bool) -> None:
 
 
 _force_tiled = False
+_use_tcgen05 = True
+
+
+def set_tcgen05_enabled(flag: bool) -> None:
+    """Prompt portions through the mma.sync kernel instead of the tcgen05 one (for comparisons)."""
+    global _use_tcgen05
+    _use_tcgen05 = bool(flag)
+
 
 
 def force_tiled(flag: bool) -> None:
@@ -55,7 +64,16 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
             return ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg,
                                             block_table, n_heads, window, scale, splits,
                                             tiles_per_split)
-        tokens_per_tile = max(1, 64 // (n_heads // n_kv))
+        group = n_heads // n_kv
+        if (_use_tcgen05 and not _force_tiled and ops.attention_tcgen05_shape_ok(n_heads, n_kv, head_dim, page_size)
+                and 2 * batch.max_segment * group >= 128):
+            # prompt portions that fill at least half of a 128-row tile: S and PV in tensor memory
+            tokens_per_tile = max(1, 128 // group)
+            tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile)
+            return ops.attention_prefill_tcgen05(q, k_pool, v_pool, batch.positions, batch.seg_start,
+                                                 tile_seg, tile_tok0, n_tiles, tokens_per_tile,
+                                                 block_table, n_heads, window, scale)
+        tokens_per_tile = max(1, 64 // group)
         tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile)
         return ops.attention_prefill_mma(q, k_pool, v_pool, batch.positions, batch.seg_start,
                                          tile_seg, tile_tok0, n_tiles, tokens_per_tile, block_table,

@@ -108,16 +108,18 @@ def run_attention_prefill(args) -> dict:
     q, k_pool, v_pool, table, _ = _paged_inputs(1, T, T, args.heads, args.kv_heads, args.head_dim)
     positions = torch.arange(T, dtype=torch.int32, device="cuda")
     seg_start = torch.tensor([0, T], dtype=torch.int32, device="cuda")
-    per_tile = max(1, 64 // group)
+    per_tile = max(1, (64 if args.mma_sync else 128) // group)
     n_tiles = -(-T // per_tile)
     tile_seg = torch.zeros(n_tiles, dtype=torch.int32, device="cuda")
     tile_tok0 = (torch.arange(n_tiles, dtype=torch.int32) * per_tile).cuda()
     scale = 1.0 / math.sqrt(args.head_dim)
-    us = _time(lambda: ops.attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg,
-                                                 tile_tok0, n_tiles, per_tile, table, args.heads, 0,
-                                                 scale), args.repeat)
+    kernel = ops.attention_prefill_mma if args.mma_sync else ops.attention_prefill_tcgen05
+    us = _time(lambda: kernel(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
+                              per_tile, table, args.heads, 0, scale), args.repeat)
     flops = 2.0 * T * T * args.heads * args.head_dim        # causal: half of 4*T*T*h*d
-    return {"kernel": "attention_prefill_mma", "tokens": T, "us": us, "tflops": flops / us / 1e6}
+    from . import tensorcore
+    return {"kernel": "attention_prefill_mma" if args.mma_sync else "attention_prefill_tcgen05",
+            "tokens": T, "us": us, "tflops": flops / us / 1e6, "status": tensorcore.status()}
 
 
 def run_shortconv(args) -> dict:
@@ -179,6 +181,7 @@ def main(argv=None) -> int:
         p.add_argument("--kv-heads", type=int, default=8)
         p.add_argument("--head-dim", type=int, default=64)
         p.add_argument("--splits", type=int, default=0)
+        p.add_argument("--mma-sync", action="store_true", help="the mma.sync prompt kernel")
     conv = sub.add_parser("shortconv")
     conv.add_argument("--tokens", type=int, default=2048)
     conv.add_argument("--hidden", type=int, default=2048)

@@ -246,6 +246,36 @@ def attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg, til
     return out
 
 
+def attention_tcgen05_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    """Shapes the tcgen05 prompt kernel takes: head sizes 64 and 128, up to 128 rows per KV head."""
+    return (head_dim in (64, 128) and page_size == 64 and n_kv > 0 and n_heads % n_kv == 0
+            and n_heads // n_kv <= 128)
+
+
+def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
+                              tokens_per_tile, block_table, n_heads, window, scale) -> torch.Tensor:
+    """The same operation on tcgen05 tensor cores: 128 query rows per CTA, S and PV in tensor
+    memory (head sizes 64 and 128); all bf16."""
+    check_tensor("q", q, torch.bfloat16)
+    check_tensor("k pool", k_pool, torch.bfloat16)
+    check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
+    T = q.shape[0]
+    num_pages, n_kv, page_size, head_dim = k_pool.shape
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError(f"q has {q.shape[1]} columns, expected {n_heads * head_dim}")
+    _i32("positions", positions, T)
+    _i32("seg_start", seg_start)
+    _i32("tile_seg", tile_seg, n_tiles)
+    _i32("tile_tok0", tile_tok0, n_tiles)
+    _i32("block table", block_table)
+    out = torch.empty_like(q)
+    lib.call("fwb_attention_prefill_tcgen05", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
+             ptr(seg_start), ptr(tile_seg), ptr(tile_tok0), ptr(block_table), block_table.shape[1],
+             page_size, num_pages, ptr(out), n_tiles, n_heads, n_kv, head_dim, tokens_per_tile, window,
+             c_float(scale), stream())
+    return out
+
+
 def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_heads, window, scale,
                          splits: int, tiles_per_split: int) -> torch.Tensor:
     """Causal GQA of single decode tokens on tensor cores, the context cut into ``splits``

@@ -591,7 +591,7 @@ def test_tensor_core_attention_finds_a_far_key_and_the_window_edge():
         q = (direction * 16.0).repeat(nh, 1)
         k_pool, v_pool, table = build_paged([k], [v], 12, torch.bfloat16, shuffle_seed=target)
         want = attention_reference(q, k, v, n - 1, window, scale, nh // nkv)
-        for new in (1, 5):                                   # decode kernel, then the tiled kernel
+        for new in (1, 5, 100):                              # decode, tiled mma.sync and tcgen05 kernels
             ctx, cache, table_dev = make_ctx([n], [new], table, k_pool, v_pool)
             qd = dev(q.reshape(1, -1).to(torch.bfloat16).repeat(new, 1))
             got = attention_kernels.paged_attention(ctx, qd, cache, table_dev, nh, window, scale, torch.bfloat16)
@@ -600,6 +600,41 @@ def test_tensor_core_attention_finds_a_far_key_and_the_window_edge():
                 close(got[-1].reshape(nh, hd)[0], v[target, 0], 2.0 ** -6, f"value of key {target}")
             else:                                            # the shouting key is outside the window
                 assert (got[-1].reshape(nh, hd)[0].double().cpu() - v[target, 0]).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 8, 64), (8, 1, 64), (3, 1, 64), (16, 2, 128), (2, 2, 128)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_tcgen05_prompt_attention(nh, nkv, hd, window):
+    """Prompt portions on the tcgen05 kernel: a whole prompt over several 128-row tiles, a
+    portion behind a cached prefix that starts inside a page, a prompt that ends on a page's
+    first key, a single token; shuffled pages, NaN wherever no key was written."""
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(nh * hd + window)
+    lens = [300, 200, 65, 129]
+    new = [300, 130, 65, 1]
+    k_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    v_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    k_pool, v_pool, table = build_paged(k_seqs, v_seqs, 16, torch.bfloat16, shuffle_seed=hd + nh)
+    qs, positions, tok_seg = [], [], []
+    for s_, (n, m) in enumerate(zip(lens, new)):
+        for pos in range(n - m, n):
+            qs.append(bf16_round(torch.randn(nh, hd, generator=g).double()))
+            positions.append(pos)
+            tok_seg.append(s_)
+    q = torch.stack(qs)
+    scale = 1.0 / math.sqrt(hd)
+    want = torch.stack([attention_reference(q[t], k_seqs[tok_seg[t]], v_seqs[tok_seg[t]], positions[t],
+                                            window, scale, nh // nkv) for t in range(len(qs))])
+    ctx, cache, table_dev = make_ctx(lens, new, table, k_pool, v_pool)
+    qd = dev(q.reshape(len(qs), nh * hd).to(torch.bfloat16))
+    per_tile = max(1, 128 // (nh // nkv))
+    tile_seg, tile_tok0, n_tiles = ctx.batch.attention_tiles(per_tile)
+    got = ops.attention_prefill_tcgen05(qd, cache.k_pool, cache.v_pool, ctx.batch.positions,
+                                        ctx.batch.seg_start, tile_seg, tile_tok0, n_tiles, per_tile,
+                                        table_dev, nh, window, scale)
+    from flyweight_b200.kernels import tensorcore
+    assert tensorcore.status() == 0
+    close(got.reshape(-1, nh, hd), want, 2.0 ** -7, "tcgen05 attention")
 
 
 @pytest.mark.parametrize("M,N,K", [(600, 1000, 264), (300, 256, 64), (257, 3072, 512), (1030, 700, 96)])
