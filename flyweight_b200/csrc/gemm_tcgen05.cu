@@ -28,6 +28,13 @@
 // WEIGHT tiles (which nothing in the stream writes) in that shadow, and touches activations,
 // addend and output only after griddepcontrol.wait.
 //
+// NORMED forms (token tiles <= 64): the activations are not a bf16 matrix but the fp32 residual
+// stream and an RMSNorm weight.  The four epilogue warps, idle until the accumulator is ready,
+// build the B tiles themselves: bf16(x * w) straight into the swizzled ring slot, and the sum of
+// squares of each token's row on the way.  The accumulator is multiplied by rsqrt(mean + eps) in the
+// epilogue -- (W (x*w)) * r = W (x*w*r) -- so the norm costs no kernel and no pass over memory.
+// With split K each CTA sums the squares of its slice and the cluster adds them in rank order.
+//
 // Every wait on an mbarrier is bounded: after the limit the CTA raises the library's status
 // word, stops waiting everywhere, still meets its cluster barriers, frees its TMEM and
 // returns.
@@ -87,7 +94,8 @@ struct Tile {
     static constexpr int data_bytes(int stages) {
         return stages * STAGE_BYTES > PARTIAL_BYTES ? stages * STAGE_BYTES : PARTIAL_BYTES;
     }
-    static constexpr int smem_bytes(int stages) { return data_bytes(stages) + 1024 + 256; }
+    // + alignment slack, barriers (256 bytes) and one float per token for the sums of squares
+    static constexpr int smem_bytes(int stages) { return data_bytes(stages) + 1024 + 512; }
 };
 
 struct Params {
@@ -99,9 +107,113 @@ struct Params {
     int k_blocks_per_split;
     int stages;            // depth of the shared-memory ring (<= Tile::MAX_STAGES)
     int* status;           // the library's status word (see tc5::status_word)
+    // NORMED forms: rows of the fp32 residual [.][K] (row t, or norm_rows[t]), the norm's weight [K], eps
+    const float* norm_x;
+    const float* norm_w;
+    const int* norm_rows;
+    float norm_eps;
 };
 
-template <int BN, int EPI>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// NORMED forms, run by the 128 threads of the four epilogue warps: for every 64-wide block of
+// this CTA's K slice, write bf16(x[t][k] * w[k]) for the tile's tokens into the ring slot's B
+// tile (128-byte rows, 16-byte chunks XOR-swizzled by row: what TMA would have left) and arrive
+// on the slot's barrier; add up x^2 per token.  A thread owns chunk c = thread & 7 of token
+// rows thread >> 3, + 16, ...; the sums of the eight chunk lanes of a row are added by shuffles,
+// so sum_sq[r] is this CTA's share for token r, summed in an order fixed by K and the split.
+// Loads of up to GROUP blocks are in flight together: a decode step's slice is one group.
+template <int BN, int NACC>
+__device__ __forceinline__ void produce_normed_tiles(const Params& prm, uint8_t* tiles, uint64_t* full_bar,
+                                                     uint64_t* empty_bar, volatile int* abort_flag,
+                                                     float* sum_sq, int STAGES, int kb_begin, int n_kb,
+                                                     int tok0) {
+    using T = Tile<BN, NACC>;
+    constexpr int PASSES = BN / 16;
+    constexpr int GROUP = BN == 16 ? 4 : (BN == 32 ? 2 : 1);
+    const int et = (int)threadIdx.x - 64, lane = et & 31;
+    const int c = et & 7, r0 = et >> 3;
+    const float* rows[PASSES];
+    float sq[PASSES];
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) {
+        const int t = tok0 + r0 + 16 * p;
+        rows[p] = t < prm.M ? prm.norm_x + (size_t)(prm.norm_rows ? prm.norm_rows[t] : t) * prm.K : nullptr;
+        sq[p] = 0.0f;
+    }
+    bool ok = true;
+    // tiles [announced, upto) are written: one fence for all of them, then their barriers
+    int announced = 0;
+    auto announce = [&](int upto) {
+        if (upto <= announced) return;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core
+        __syncwarp();
+        if (lane == 0)
+            for (int k = announced; k < upto; ++k) mbar_arrive(&full_bar[k % STAGES]);
+        announced = upto;
+    };
+    for (int i0 = 0; i0 < n_kb && ok; i0 += GROUP) {
+        float4 xv[GROUP][PASSES][2], wv[GROUP][2];
+#pragma unroll
+        for (int gi = 0; gi < GROUP; ++gi) {
+            const int k = (kb_begin + i0 + gi) * BK + c * 8;
+            const bool in = i0 + gi < n_kb && k < prm.K;           // K is a multiple of 8: a chunk is whole or absent
+            wv[gi][0] = in ? *reinterpret_cast<const float4*>(prm.norm_w + k) : make_float4(0, 0, 0, 0);
+            wv[gi][1] = in ? *reinterpret_cast<const float4*>(prm.norm_w + k + 4) : make_float4(0, 0, 0, 0);
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p) {
+                const bool on = in && rows[p];
+                xv[gi][p][0] = on ? *reinterpret_cast<const float4*>(rows[p] + k) : make_float4(0, 0, 0, 0);
+                xv[gi][p][1] = on ? *reinterpret_cast<const float4*>(rows[p] + k + 4) : make_float4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int gi = 0; gi < GROUP; ++gi) {
+            const int i = i0 + gi;
+            if (i >= n_kb) break;
+            const int s = i % STAGES;
+            if (i >= STAGES) {
+                // the slot comes free only after tiles already written here have been announced
+                announce(i);
+                ok = mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag, 4, prm.status);
+            }
+            if (!ok) break;
+            uint8_t* b_tile = tiles + (size_t)s * T::STAGE_BYTES + NACC * T::A_BYTES;
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p) {
+                const float4 a = xv[gi][p][0], b = xv[gi][p][1], wa = wv[gi][0], wb = wv[gi][1];
+                sq[p] = fmaf(a.x, a.x, sq[p]); sq[p] = fmaf(a.y, a.y, sq[p]);
+                sq[p] = fmaf(a.z, a.z, sq[p]); sq[p] = fmaf(a.w, a.w, sq[p]);
+                sq[p] = fmaf(b.x, b.x, sq[p]); sq[p] = fmaf(b.y, b.y, sq[p]);
+                sq[p] = fmaf(b.z, b.z, sq[p]); sq[p] = fmaf(b.w, b.w, sq[p]);
+                uint4 packed;
+                __nv_bfloat162 h;
+                h = __floats2bfloat162_rn(a.x * wa.x, a.y * wa.y); packed.x = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(a.z * wa.z, a.w * wa.w); packed.y = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(b.x * wb.x, b.y * wb.y); packed.z = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(b.z * wb.z, b.w * wb.w); packed.w = *reinterpret_cast<uint32_t*>(&h);
+                const int r = r0 + 16 * p;
+                *reinterpret_cast<uint4*>(b_tile + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
+            }
+        }
+        if (ok) announce(i0 + GROUP < n_kb ? i0 + GROUP : n_kb);
+    }
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) {
+        float v = sq[p];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        if (c == 0) sum_sq[r0 + 16 * p] = v;
+    }
+    // all four warps' sums are in place before anybody's epilogue reads them (and, with split K,
+    // before the cluster barrier that precedes the peers' reads)
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int BN, int EPI, bool NORMED>
 __global__ void __launch_bounds__(threads_for(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const Params prm) {
@@ -117,6 +229,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint64_t* acc_bar = empty_bar + T::MAX_STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    float* sum_sq = reinterpret_cast<float*>(tiles + T::data_bytes(STAGES) + 256);   // [BN], NORMED only
 
     pdl_launch_dependents();     // the next kernel may set itself up in this one's shadow
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,7 +246,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], NORMED ? 1 + epi_warps(BN) : 1);   // + the warps that write the B tile
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(acc_bar, 1);
@@ -153,25 +266,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int ahead = n_kb < STAGES ? n_kb : STAGES;
             for (int i = 0; i < ahead; ++i) {
                 uint8_t* stage = tiles + (size_t)i * T::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[i], T::STAGE_BYTES);
+                mbar_expect_tx(&full_bar[i], NORMED ? NACC * T::A_BYTES : T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 tma_load_2d(stage, &map_w, &full_bar[i], k, feat0);
                 if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[i], k, second_tile_row);
             }
             pdl_wait();
-            for (int i = 0; i < ahead; ++i)
-                tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES + NACC * T::A_BYTES, &map_x, &full_bar[i],
-                            (kb_begin + i) * BK, tok0);
+            if (!NORMED)
+                for (int i = 0; i < ahead; ++i)
+                    tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES + NACC * T::A_BYTES, &map_x, &full_bar[i],
+                                (kb_begin + i) * BK, tok0);
             for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t round = i / STAGES;
                 if (!mbar_wait(&empty_bar[s], (round - 1) & 1, abort_flag, 1, prm.status)) break;
                 uint8_t* stage = tiles + (size_t)s * T::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], T::STAGE_BYTES);
+                mbar_expect_tx(&full_bar[s], NORMED ? NACC * T::A_BYTES : T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 tma_load_2d(stage, &map_w, &full_bar[s], k, feat0);
                 if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[s], k, second_tile_row);
-                tma_load_2d(stage + NACC * T::A_BYTES, &map_x, &full_bar[s], k, tok0);
+                if (!NORMED) tma_load_2d(stage + NACC * T::A_BYTES, &map_x, &full_bar[s], k, tok0);
             }
         }
     } else if (warp == 1) {
@@ -215,7 +329,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     bool acc_ready = true;
     if (epi_warp) {
         pdl_wait();              // the addend is read and Y written only after the previous kernel
-
+        if constexpr (NORMED) produce_normed_tiles<BN, NACC>(prm, tiles, full_bar, empty_bar, abort_flag, sum_sq, STAGES,
+                                                   kb_begin, n_kb, tok0);
         if (n_kb > 0) acc_ready = mbar_wait(acc_bar, 0, abort_flag, 3, prm.status);
         acc_ready = acc_ready && !*abort_flag;
         acc_ready = __all_sync(0xffffffffu, acc_ready);   // tcgen05.ld needs the whole warp
@@ -224,10 +339,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int f = feat0 + row;
 
-    auto finish = [&](int col, float g, float u) {
-        // col: token inside the tile; g: accumulator 0; u: accumulator 1 (SwiGLU only)
+    auto finish = [&](int col, float g, float u, float r) {
+        // col: token inside the tile; g: accumulator 0; u: accumulator 1 (SwiGLU only);
+        // r: the token's rsqrt(mean square + eps) (NORMED only)
         const int t = tok0 + col;
         if (t >= prm.M || f >= prm.N) return;
+        if (NORMED) {
+            g *= r;
+            u *= r;
+        }
         const size_t at = (size_t)t * prm.ldy + f;
         if (EPI == EPI_F32) reinterpret_cast<float*>(prm.y)[at] = g;
         else if (EPI == EPI_F32_WIDE) {
@@ -236,7 +356,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         } else if (EPI == EPI_BF16_WIDE) {
             reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g);
             if (f + BM < prm.N) reinterpret_cast<__nv_bfloat16*>(prm.y)[at + BM] = __float2bfloat16_rn(u);
-        } else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(prm.y)[at] = g + prm.addend[at];
+        } else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(prm.y)[at] = g + (splits > 1 ? u : prm.addend[at]);
         else if (EPI == EPI_BF16) reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g);
         else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(silu_fast(g) * u);
     };
@@ -258,7 +378,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.0f;
                 }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) finish(c0 + j, g[j], NACC == 2 ? u[j] : 0.0f);
+                for (int j = 0; j < 16; ++j)
+                    finish(c0 + j, g[j], NACC == 2 ? u[j] : 0.0f,
+                           NORMED ? rsqrtf(sum_sq[c0 + j] / (float)prm.K + prm.norm_eps) : 1.0f);
             }
         }
     } else {
@@ -284,12 +406,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const uint32_t rank = cluster_rank();
             const uint32_t base = smem_u32(partial);
             for (int col = (int)rank; col < BN; col += splits) {
-                float g = 0.0f, u = 0.0f;
-                for (int r = 0; r < splits; ++r) {
-                    g += ld_dsmem_f32(base + (uint32_t)((col * BM + row) * 4), (uint32_t)r);
-                    if (NACC == 2) u += ld_dsmem_f32(base + (uint32_t)(((BN + col) * BM + row) * 4), (uint32_t)r);
+                // the addend's load is in flight while the partial tiles are fetched
+                float add = 0.0f;
+                if (EPI == EPI_ADD_F32 && tok0 + col < prm.M && f < prm.N)
+                    add = prm.addend[(size_t)(tok0 + col) * prm.ldy + f];
+                // all peers' values are requested before the first is used (one round trip through
+                // distributed shared memory, not one per peer), then summed in rank order
+                float pg[8], pu[8], ps[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const bool on = r < splits;
+                    pg[r] = on ? ld_dsmem_f32(base + (uint32_t)((col * BM + row) * 4), (uint32_t)r) : 0.0f;
+                    pu[r] = (on && NACC == 2) ? ld_dsmem_f32(base + (uint32_t)(((BN + col) * BM + row) * 4), (uint32_t)r) : 0.0f;
+                    ps[r] = (on && NORMED) ? ld_dsmem_f32(smem_u32(sum_sq) + (uint32_t)(col * 4), (uint32_t)r) : 0.0f;
                 }
-                if (!*abort_flag) finish(col, g, u);
+                float g = 0.0f, u = 0.0f, sq = 0.0f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    g += pg[r];                      // + 0 beyond the last rank: exact
+                    u += pu[r];
+                    sq += ps[r];
+                }
+                if (EPI == EPI_ADD_F32) u = add;
+                if (!*abort_flag)
+                    finish(col, g, u, NORMED ? rsqrtf(sq / (float)prm.K + prm.norm_eps) : 1.0f);
             }
         }
         cluster_sync_all();                        // nobody leaves while a peer still reads it
@@ -301,12 +441,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 // ------------------------------------------------------------------ host side
-template <int BN, int EPI>
+template <int BN, int EPI, bool NORMED = false>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, Params prm, int splits,
            cudaStream_t stream) {
     constexpr int NACC = epi_accumulators(EPI);
     using T = Tile<BN, NACC>;
-    auto kernel = gemm_tcgen05_kernel<BN, EPI>;
+    auto kernel = gemm_tcgen05_kernel<BN, EPI, NORMED>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -334,6 +474,17 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, Params prm, int s
     config.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_w, map_x, prm);
     return e == cudaSuccess ? fwb_launch_status() : (int)e;
+}
+
+// The NORMED forms exist for decode-sized token tiles and the epilogues that follow a norm.
+template <int BN>
+int launch_normed(int epi, const CUtensorMap& map_w, const Params& prm, int splits, cudaStream_t stream) {
+    switch (epi) {
+        case EPI_F32: return launch<BN, EPI_F32, true>(map_w, map_w, prm, splits, stream);
+        case EPI_BF16: return launch<BN, EPI_BF16, true>(map_w, map_w, prm, splits, stream);
+        case EPI_SWIGLU_BF16: return launch<BN, EPI_SWIGLU_BF16, true>(map_w, map_w, prm, splits, stream);
+        default: return FWB_UNSUPPORTED;
+    }
 }
 
 template <int BN>
@@ -400,6 +551,10 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
     prm.stages = stages;
     prm.status = status_word();
+    prm.norm_x = nullptr;
+    prm.norm_w = nullptr;
+    prm.norm_rows = nullptr;
+    prm.norm_eps = 0.0f;
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, W, w_rows, K, BM)) return FWB_UNSUPPORTED;
     if (!make_map(&map_x, X, M, K, bn_eff)) return FWB_UNSUPPORTED;
@@ -409,6 +564,54 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
         case 64: return launch_epi<64>(epilogue, map_w, map_x, prm, splits, stream);
         case 128: return launch_epi<128>(epilogue, map_w, map_x, prm, splits, stream);
         default: return launch_epi<256>(epilogue, map_w, map_x, prm, splits, stream);
+    }
+}
+
+// The same product with the RMSNorm that precedes it folded in: the activations are rows of the
+// fp32 residual `x_res` ([.][K]; row t of the product reads row `rows[t]`, or row t when `rows`
+// is null), normalised with weight `norm_w` [K] and `eps`:
+//     Y[t][f] = sum_k W[f][k] * bf16(x[t][k] * norm_w[k])  *  rsqrt(mean_k x[t][k]^2 + eps)
+// Token tiles of at most 64 (M <= 64 or tile_tokens <= 64); epilogues 0 (fp32), 1 (bf16), 3 (SwiGLU).
+FWB_API int fwb_gemm_tcgen05_normed(const float* x_res, const float* norm_w, const int* rows, float eps,
+                                    const void* W, void* Y, int M, int N, int K, int w_rows, int ldy,
+                                    int epilogue, int up_row_offset, int splits, int stages,
+                                    int tile_tokens, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return FWB_OK;
+    if (!x_res || !norm_w || !W || !Y || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
+    if ((K & 7) || ((uintptr_t)W & 15) || ((uintptr_t)x_res & 15) || ((uintptr_t)norm_w & 15)) return FWB_UNSUPPORTED;
+    if (epilogue == EPI_SWIGLU_BF16 && (up_row_offset < N || w_rows < up_row_offset + N)) return FWB_BAD_ARGUMENT;
+    if (epilogue != EPI_SWIGLU_BF16 && w_rows < N) return FWB_BAD_ARGUMENT;
+    if (splits < 1 || splits > 8) return FWB_BAD_ARGUMENT;
+    int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if (tile_tokens == 16 || tile_tokens == 32 || tile_tokens == 64) {
+        if (tile_tokens < bn) bn = tile_tokens;
+    } else if (tile_tokens != 0) {
+        return FWB_BAD_ARGUMENT;
+    }
+    if ((N + BM - 1) / BM > 65535) return FWB_TOO_LARGE;
+    const int total_kb = (K + BK - 1) / BK;
+    if (splits > total_kb) splits = total_kb;
+    Params prm;
+    prm.y = Y;
+    prm.addend = nullptr;
+    prm.M = M;
+    prm.N = N;
+    prm.K = K;
+    prm.ldy = ldy;
+    prm.up_row_offset = up_row_offset;
+    prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
+    prm.stages = stages;
+    prm.status = status_word();
+    prm.norm_x = x_res;
+    prm.norm_w = norm_w;
+    prm.norm_rows = rows;
+    prm.norm_eps = eps;
+    CUtensorMap map_w;
+    if (!make_map(&map_w, W, w_rows, K, BM)) return FWB_UNSUPPORTED;
+    switch (bn) {
+        case 16: return launch_normed<16>(epilogue, map_w, prm, splits, stream);
+        case 32: return launch_normed<32>(epilogue, map_w, prm, splits, stream);
+        default: return launch_normed<64>(epilogue, map_w, prm, splits, stream);
     }
 }
 

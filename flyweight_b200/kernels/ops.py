@@ -94,23 +94,41 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+def linear(x, w: torch.Tensor, out_dtype: torch.dtype,
            addend: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The matrix product the model uses: picks the kernel for the dtypes and sizes.
 
     float32 weights always take the SIMT kernel (true 32-bit).  bfloat16 weights take
-    the tensor-core kernel when it accepts the shape, else the SIMT kernel.
+    the tensor-core kernel when it accepts the shape, else the SIMT kernel.  ``x`` may be a
+    norm not yet applied (``parts.base.DeferredNorm``): an RMS norm in front of a decode-sized
+    bfloat16 product runs inside that product's kernel, otherwise its own kernel runs first.
     """
+    from . import tensorcore
+    if not isinstance(x, torch.Tensor):                       # a DeferredNorm
+        if (addend is None and x.kind == "rmsnorm"
+                and tensorcore.normed_accepts(x.n_rows, x.x.shape[-1], w, 1, w.shape[0])):
+            return tensorcore.gemm_normed(x.x, x.weight, x.eps, w, out_dtype, rows=x.rows, n_rows=x.n_rows)
+        x = x.materialize(torch.float32 if w.dtype == torch.float32 else torch.bfloat16)
     if w.dtype == torch.float32:
         if x.dtype != torch.float32:
             x = cast(x, torch.float32)
         return gemm_simt(x, w, out_dtype, addend)
     if x.dtype != torch.bfloat16:
         x = cast(x, torch.bfloat16)
-    from . import tensorcore
     if tensorcore.accepts(x, w, out_dtype, addend):
         return tensorcore.gemm(x, w, out_dtype, addend)
     return gemm_simt(x, w, out_dtype, addend)
+
+
+def linear_into_residual(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]):
+    """``residual += x @ w.T`` in the product's epilogue when the tensor-core kernel has that
+    form for the shape (returns None); otherwise the fp32 product, for the caller to hand on."""
+    from . import tensorcore
+    if (residual is not None and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+            and tensorcore.adds_in_place(x, w, residual)):
+        tensorcore.gemm(x, w, torch.float32, addend=residual, out=residual)
+        return None
+    return linear(x, w, torch.float32)
 
 
 def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

@@ -81,6 +81,9 @@ def _decode_tile(M: int, N: int) -> int:
     return 64
 
 
+_stage_cap = 8
+
+
 def _ring_depth(M: int, N: int, splits: int, accumulators: int) -> int:
     """Stages of the shared-memory ring for decode-sized steps: at most four, and few enough
     that every CTA of the product is resident at once (measured: a product that needs a second
@@ -90,7 +93,7 @@ def _ring_depth(M: int, N: int, splits: int, accumulators: int) -> int:
     ctas = -(-N // 128) * -(-M // bn) * splits
     per_sm = max(1, -(-ctas // SM_COUNT))
     fit = ((227 * 1024) // per_sm - 2048) // stage
-    return max(2, min(3 if (accumulators == 2 and bn <= 16) else 4, fit))
+    return max(2, min(3 if (accumulators == 2 and bn <= 16) else 4, fit, _stage_cap))
 
 
 def _splits_for(M: int, N: int, K: int, accumulators: int) -> int:
@@ -110,15 +113,29 @@ def _splits_for(M: int, N: int, K: int, accumulators: int) -> int:
     return splits
 
 
-def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wide=-1) -> torch.Tensor:
-    """``x @ w.T``: x [M][K] bf16, w [N][K] bf16 -> [M][N] fp32 or bf16 (+ fp32 addend)."""
+def adds_in_place(x, w, residual) -> bool:
+    """Whether ``gemm(x, w, fp32, addend=residual, out=residual)`` is available: the single-CTA
+    kernel has the epilogue (every element is read and written by the same thread), the
+    CTA-pair kernel of prompt-sized steps has not."""
+    return (_add_in_place and (x.shape[0] >= FUSE_FROM_TOKENS or _fuse_always)
+            and accepts(x, w, torch.float32, residual) and x.shape[0] <= 128
+            and residual.dtype == torch.float32 and residual.is_contiguous()
+            and tuple(residual.shape) == (x.shape[0], w.shape[0]))
+
+
+def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wide=-1, out=None) -> torch.Tensor:
+    """``x @ w.T``: x [M][K] bf16, w [N][K] bf16 -> [M][N] fp32 or bf16 (+ fp32 addend).
+    ``out`` may be the addend itself (the sum in place)."""
     check_tensor("gemm input", x, torch.bfloat16)
     check_tensor("gemm weight", w, torch.bfloat16)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm: input has {K} columns, weight has {w.shape[1]}")
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    else:
+        check_tensor("gemm output", out, out_dtype, (M, N))
     if addend is not None:
         check_tensor("gemm addend", addend, torch.float32, (M, N))
         epilogue = EPI_ADD_F32
@@ -174,6 +191,86 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
         tile_tokens = tile_tokens or _decode_tile(M, F)
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, F, K, F2, F,
              EPI_SWIGLU_BF16, F, splits, stages, tile_tokens, -1, stream())
+    return out
+
+
+_fuse_norm = True
+_add_in_place = True
+_fuse_always = False
+# Measured inside the decode step of LFM2-1.2B on B200: folding the norms into the products
+# (and the residual sums into the epilogues) takes 2-3 % off the step from 16 tokens on; below
+# that the separate norm kernel is faster, because the next product's first weight tiles are
+# fetched while it runs.
+FUSE_FROM_TOKENS = 16
+
+
+def fuse_always(flag: bool) -> None:
+    """Fold norms and residual sums at every decode-sized token count (tests of that path)."""
+    global _fuse_always
+    _fuse_always = bool(flag)
+
+
+
+def set_norm_fusion(flag: bool) -> None:
+    """Norms folded into the product that follows them (on by default).  Off: the norm kernel
+    writes bf16 rows first, as prompt-sized steps always do; tests that compare cuts bit by bit
+    switch it off so that every cut runs the same arithmetic."""
+    global _fuse_norm, _add_in_place
+    _fuse_norm = _add_in_place = bool(flag)
+
+
+def normed_accepts(M: int, K: int, w, accumulators: int, N: int) -> bool:
+    """Decode-sized token counts whose K slice per CTA is short enough that building the
+    activation tiles inside the kernel stays off the critical path."""
+    if not (_enabled and _fuse_norm) or w.dtype != torch.bfloat16 or M > 64 or K % 8 or not _aligned(w):
+        return False
+    if M < FUSE_FROM_TOKENS and not _fuse_always:
+        return False
+    splits = _forced_splits if _forced_splits is not None else _splits_for(M, N, K, accumulators)
+    return -(-K // 64) <= 8 * splits
+
+
+def gemm_normed(x_res, norm_weight, eps, w, out_dtype, rows=None, n_rows=None, splits=None, stages=0,
+                tile_tokens=0) -> torch.Tensor:
+    """``rmsnorm(x_res[rows]) @ w.T`` in one kernel: fp32 residual rows in, [M][N] fp32 or bf16 out."""
+    check_tensor("residual", x_res, torch.float32)
+    check_tensor("norm weight", norm_weight, torch.float32)
+    check_tensor("gemm weight", w, torch.bfloat16)
+    K = x_res.shape[-1]
+    M = x_res.numel() // K if rows is None else (rows.numel() if n_rows is None else n_rows)
+    N = w.shape[0]
+    if w.shape[1] != K or norm_weight.numel() != K:
+        raise KernelError(f"gemm: residual has {K} columns, weight has {w.shape[1]}, norm {norm_weight.numel()}")
+    out = torch.empty((M, N), dtype=out_dtype, device=x_res.device)
+    if splits is None:
+        splits = pick_splits(M, N, K)
+    stages = stages or _ring_depth(M, N, splits, 1)
+    tile_tokens = tile_tokens or _decode_tile(M, N)
+    lib.call("fwb_gemm_tcgen05_normed", ptr(x_res), ptr(norm_weight), ptr(rows), lib.c_float(eps), ptr(w),
+             ptr(out), M, N, K, N, N, EPI_F32 if out_dtype == torch.float32 else EPI_BF16, 0, splits,
+             stages, tile_tokens, stream())
+    return out
+
+
+def swiglu_gate_up_normed(x_res, norm_weight, eps, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.Tensor:
+    """``silu(n @ gate.T) * (n @ up.T)`` with n = rmsnorm(x_res), in one kernel."""
+    check_tensor("residual", x_res, torch.float32)
+    check_tensor("norm weight", norm_weight, torch.float32)
+    check_tensor("swiglu weight", w_gate_up, torch.bfloat16)
+    K = x_res.shape[-1]
+    M = x_res.numel() // K
+    F2 = w_gate_up.shape[0]
+    F = F2 // 2
+    if w_gate_up.shape[1] != K or F * 2 != F2 or norm_weight.numel() != K:
+        raise KernelError("swiglu: weight must be [2F][K] and the norm weight [K]")
+    out = torch.empty((M, F), dtype=torch.bfloat16, device=x_res.device)
+    if splits is None:
+        splits = _forced_splits if _forced_splits is not None else _splits_for(M, F, K, 2)
+    stages = stages or _ring_depth(M, F, splits, 2)
+    tile_tokens = tile_tokens or _decode_tile(M, F)
+    lib.call("fwb_gemm_tcgen05_normed", ptr(x_res), ptr(norm_weight), ptr(None), lib.c_float(eps),
+             ptr(w_gate_up), ptr(out), M, F, K, F2, F, EPI_SWIGLU_BF16, F, splits, stages, tile_tokens,
+             stream())
     return out
 
 

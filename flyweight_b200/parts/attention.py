@@ -24,7 +24,8 @@ class GQAttention(Mixer):
     shares_cache (True: reads the cache of another execution and projects q only).
     tensors: q, k, v, o, q_norm, k_norm."""
     graph_safe = True
-
+    takes_deferred_norm = True
+    adds_residual = True
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -88,7 +89,7 @@ class GQAttention(Mixer):
     def prepare(self, max_positions, device):
         self.rope_table = self.position.table(max_positions, device)
 
-    def forward(self, ctx, h, cache):
+    def forward(self, ctx, h, cache, residual=None):
         act = ctx.precision.act_dtype
         # q|k|v in the activation dtype; the head norm and the rotation widen it to fp32
         qkv = ops.linear(h, self.w_qkv, act)
@@ -102,4 +103,4 @@ class GQAttention(Mixer):
         from ..kernels import attention as attention_kernels
         out = attention_kernels.paged_attention(ctx, q, cache, block_table, self.n_heads,
                                                 self.window, self.scale, act)
-        return ops.linear(out, self.w_o, torch.float32)
+        return ops.linear_into_residual(out, self.w_o, residual)

@@ -10,12 +10,17 @@ Interfaces
 ``Norm.forward(ctx, x, delta=None, rows=None)``
     x: fp32 residual [T][H].  Adds ``delta`` into x first when given (the residual
     sum, fp32), returns the normalised rows in ``ctx.precision.act_dtype``.
+``Norm.defer(ctx, x, rows=None)`` -> ``DeferredNorm`` | ``None``  (optional)
+    the same rows as a recipe instead of a tensor, for a consumer with ``takes_deferred_norm``:
+    its first matrix product may then apply the norm itself (``ops.linear`` takes either).
 ``Mixer.state_spec()`` -> ``PagedKV`` | ``FixedState`` | ``None``
     what the cache manager must keep for one execution of this mixer.
 ``Mixer.forward(ctx, h, cache)`` -> fp32 [T][H]
     h: normalised input; cache: the ``LayerCache`` the manager made for this
     execution (or for the execution it shares with).  Returns the residual delta.
 ``FeedForward.forward(ctx, h)`` -> fp32 [T][H]
+    A mixer or feed-forward with ``adds_residual`` is called with ``residual=x`` as well and
+    may add its delta into x itself (its last product's epilogue); it then returns None.
 ``PositionEncoding.table(n_positions, device)`` -> what its kernel reads.
 ``Arrangement.forward(ctx, x, pending, cache)`` -> (x, pending)
     wires norms, mixer and feed-forward around the residual stream; ``pending`` is
@@ -84,6 +89,27 @@ class FixedState:
     shape: Tuple[int, ...]
 
 
+# ------------------------------------------------------------------ a norm not yet applied
+@dataclass
+class DeferredNorm:
+    """Rows of the fp32 residual together with the norm that is still to be applied to them.
+    ``materialize`` runs the norm's kernel; ``ops.linear`` and the fused feed-forward product
+    fold an RMS norm into their own kernel instead when the shape allows it."""
+    x: torch.Tensor                      # fp32 residual [T][H]
+    weight: torch.Tensor                 # fp32 [H]
+    eps: float
+    rows: Optional[torch.Tensor] = None  # int32 row indices (None: every row)
+    kind: str = "rmsnorm"
+
+    @property
+    def n_rows(self) -> int:
+        return self.rows.numel() if self.rows is not None else self.x.numel() // self.x.shape[-1]
+
+    def materialize(self, dtype: torch.dtype) -> torch.Tensor:
+        from ..kernels import ops
+        return ops.rmsnorm(self.x, self.weight, self.eps, dtype, rows=self.rows)
+
+
 # ------------------------------------------------------------------ part interfaces
 class Part:
     kind: str = ""
@@ -91,6 +117,10 @@ class Part:
     # step's batch (nothing read on the host), so a decode step may be captured in a CUDA
     # graph and replayed with new batch contents.  Parts defined elsewhere default to False.
     graph_safe: bool = False
+    # True when forward() accepts a ``DeferredNorm`` in place of the normalised input.
+    takes_deferred_norm: bool = False
+    # True when forward() takes ``residual=`` and may add its delta into it (returning None).
+    adds_residual: bool = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec
@@ -112,6 +142,11 @@ class Part:
 class Norm(Part):
     def forward(self, ctx, x, delta=None, rows=None):
         raise NotImplementedError
+
+    def defer(self, ctx, x, rows=None):
+        """The norm of ``x`` (no pending delta) as a ``DeferredNorm``, or None if this norm
+        has no such form."""
+        return None
 
 
 class PositionEncoding(Part):

@@ -99,5 +99,7 @@ class DecoderModel:
             x, pending = self.layers[entry.layer].forward(ctx, x, pending, caches[source])
         if batch.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
-        n = self.final_norm.forward(ctx, x, delta=pending, rows=batch.logit_rows)
+        n = self.final_norm.defer(ctx, x, rows=batch.logit_rows) if pending is None else None
+        if n is None:
+            n = self.final_norm.forward(ctx, x, delta=pending, rows=batch.logit_rows)
         return ops.linear(n, self.head, torch.float32)

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import Norm, Precision, register_norm
+from .base import DeferredNorm, Norm, Precision, register_norm
 
 
 @register_norm("rmsnorm")
@@ -34,3 +34,6 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, x, delta=None, rows=None):
         return ops.rmsnorm(x, self.weight, self.eps, ctx.precision.act_dtype, delta=delta, rows=rows)
+
+    def defer(self, ctx, x, rows=None):
+        return DeferredNorm(x, self.weight, self.eps, rows)

@@ -20,7 +20,8 @@ class GatedShortConv(Mixer):
     """params: hidden_size, taps (L >= 2), bias (bool).
     tensors: in_proj [3H][H], taps [H][L] (also stored as [H][1][L]), out_proj [H][H], bias [H]."""
     graph_safe = True
-
+    takes_deferred_norm = True
+    adds_residual = True
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -54,10 +55,10 @@ class GatedShortConv(Mixer):
     def state_spec(self):
         return FixedState((self.hidden, self.taps_len - 1))
 
-    def forward(self, ctx, h, cache):
+    def forward(self, ctx, h, cache, residual=None):
         batch = ctx.batch
         # B|C|x in the activation dtype: the conv kernel widens them and multiplies in fp32
         p = ops.linear(h, self.w_in, ctx.precision.act_dtype)
         z = ops.shortconv(p, self.taps, self.bias, cache.state, batch.seg_start, batch.seg_slot,
                           batch.tok_seg, batch.n_segments, ctx.precision.act_dtype)
-        return ops.linear(z, self.w_out, torch.float32)
+        return ops.linear_into_residual(z, self.w_out, residual)

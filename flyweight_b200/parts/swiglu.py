@@ -14,7 +14,8 @@ from .base import FeedForward, Precision, register_feed_forward
 class SwiGLU(FeedForward):
     """params: hidden_size, ffn_dim.  tensors: gate [F][H], up [F][H], down [H][F]."""
     graph_safe = True
-
+    takes_deferred_norm = True
+    adds_residual = True
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -40,12 +41,19 @@ class SwiGLU(FeedForward):
         return (self.w_gate_up.numel() * self.w_gate_up.element_size()
                 + self.w_down.numel() * self.w_down.element_size())
 
-    def forward(self, ctx, h):
+    def forward(self, ctx, h, residual=None):
         act = ctx.precision.act_dtype
+        if not isinstance(h, torch.Tensor):                   # a norm not yet applied
+            if h.kind == "rmsnorm" and tensorcore.normed_accepts(h.n_rows, self.hidden, self.w_gate_up, 2,
+                                                                  self.ffn_dim):
+                # the norm, both products and silu(g)*u in one kernel
+                a = tensorcore.swiglu_gate_up_normed(h.x, h.weight, h.eps, self.w_gate_up)
+                return ops.linear_into_residual(a, self.w_down, residual)
+            h = h.materialize(act)
         if tensorcore.swiglu_accepts(h, self.w_gate_up):
             # gate and up accumulate side by side in tensor memory; silu(g)*u is the epilogue
             a = tensorcore.swiglu_gate_up(h, self.w_gate_up)
         else:
             gate_up = ops.linear(h, self.w_gate_up, act)
             a = ops.silu_mul(gate_up, act)
-        return ops.linear(a, self.w_down, torch.float32)
+        return ops.linear_into_residual(a, self.w_down, residual)

@@ -540,6 +540,48 @@ def test_tcgen05_swiglu_epilogue(M, F, K):
     assert tc.status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 384, 2048), (16, 200, 96), (17, 256, 512), (40, 320, 264),
+                                   (64, 2048, 1024)])
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_tcgen05_gemm_with_the_norm_folded_in(M, N, K, splits):
+    """rmsnorm(x) @ W^T in one kernel: the kernel builds its activation tiles from the fp32
+    residual, sums the squares per slice of K and scales the accumulator at the end."""
+    from flyweight_b200.kernels import tensorcore
+    g = torch.Generator().manual_seed(M + N + K + splits)
+    x = torch.randn(M + 3, K, generator=g) * torch.linspace(0.1, 30.0, M + 3)[:, None]   # rows of very different size
+    nw = 1 + 0.2 * torch.randn(K, generator=g)
+    w = bf16_round(torch.randn(N, K, generator=g) / math.sqrt(K))
+    eps = 1e-5
+    rows = torch.randperm(M + 3, generator=g)[:M].to(torch.int32)
+    for use_rows in (False, True):
+        src = x[rows.long()] if use_rows else x[:M]
+        normed = src.double() * torch.rsqrt((src.double() ** 2).mean(-1, keepdim=True) + eps) * nw.double()
+        want = normed @ w.double().T
+        xin = dev(x) if use_rows else dev(x[:M].contiguous())
+        for out_dtype in (torch.float32, torch.bfloat16):
+            got = tensorcore.gemm_normed(xin, dev(nw), eps, dev(w, torch.bfloat16), out_dtype,
+                                         rows=dev(rows) if use_rows else None, splits=splits)
+            assert tensorcore.status() == 0
+            close(got, want, 2.0 ** -7, f"normed gemm rows={use_rows} {out_dtype}")
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 128, 64), (8, 1024, 2048), (40, 192, 128), (64, 320, 96)])
+def test_tcgen05_swiglu_with_the_norm_folded_in(M, F, K):
+    from flyweight_b200.kernels import tensorcore
+    g = torch.Generator().manual_seed(M + F + K)
+    x = torch.randn(M, K, generator=g) * 3.0
+    nw = 1 + 0.2 * torch.randn(K, generator=g)
+    w = bf16_round(torch.randn(2 * F, K, generator=g) / math.sqrt(K))
+    eps = 1e-6
+    normed = x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * nw.double()
+    gate, up = normed @ w[:F].double().T, normed @ w[F:].double().T
+    want = gate * torch.sigmoid(gate) * up
+    for splits in (1, 2, 4):
+        got = tensorcore.swiglu_gate_up_normed(dev(x), dev(nw), eps, dev(w, torch.bfloat16), splits=splits)
+        assert tensorcore.status() == 0
+        close(got, want, 2.0 ** -6, f"normed swiglu splits={splits}")
+
+
 def test_tcgen05_refuses_what_tma_cannot_address():
     from flyweight_b200.kernels import KernelError, tensorcore as tc
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K not a multiple of 8

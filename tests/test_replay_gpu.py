@@ -50,6 +50,32 @@ def test_one_long_step_then_the_last_32_one_by_one(name, dtype):
     assert_close(got, whole, TOL_CUTS[dtype], f"{name} {dtype} decode vs whole")
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_norms_and_residual_sums_folded_into_the_products_at_every_size(name):
+    """Below 16 tokens a step runs the norm kernels by default; here the folded forms (the norm
+    inside the next product, the residual sum in the epilogue) run for single tokens and small
+    portions too, through CUDA graphs and without."""
+    from flyweight_b200.kernels import tensorcore
+    tensorcore.fuse_always(True)
+    try:
+        for use_graphs in (True, False):
+            runner = new_runner(name, "bfloat16")
+            runner.use_graphs = use_graphs
+            tokens = random_tokens(name, 150, seed=14)
+            want = plain_logits(name, "bfloat16", tokens)
+            head = len(tokens) - 32
+            parts = [runner.step([("d", tokens[:head], list(range(head)))]).cpu().numpy()]
+            for token in tokens[head:]:
+                parts.append(runner.step([("d", [token], [0])]).cpu().numpy())
+            runner.finish("d")
+            assert_close(np.concatenate(parts), want, TOL_ORACLE["bfloat16"], f"{name} folded, decode of the last 32")
+            got = run_portions(runner, "p", tokens, [3, 2, 9, 40, 1, 14])
+            assert_close(got, want, TOL_ORACLE["bfloat16"], f"{name} folded, small portions")
+            runner.cache.check()
+    finally:
+        tensorcore.fuse_always(False)
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_portions_of_changing_size(name, dtype):
     runner = new_runner(name, dtype)
@@ -164,6 +190,7 @@ def test_bfloat16_cuts_agree_to_one_roundoff_when_the_sums_keep_one_order(name):
     from flyweight_b200.kernels import attention, tensorcore
     dtype = "bfloat16"
     tensorcore.force_splits(1)
+    tensorcore.set_norm_fusion(False)   # a norm folded into its product rounds bf16(x*w), the norm kernel bf16(x*r*w)
     attention.force_tiled(True)         # the decode kernel merges key slices in another order
     try:
         runner = new_runner(name, dtype)
@@ -180,4 +207,5 @@ def test_bfloat16_cuts_agree_to_one_roundoff_when_the_sums_keep_one_order(name):
                          f"{name} pinned mixed {rid}")
     finally:
         tensorcore.force_splits(None)
+        tensorcore.set_norm_fusion(True)
         attention.force_tiled(False)
