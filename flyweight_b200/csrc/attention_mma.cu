@@ -309,7 +309,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 // grid (splits, nkv, T).  A split covers `tiles_per_split` key tiles; with splits == 1 the
 // result goes straight to `out`, else (acc, max, sum) go to the scratch buffers:
 //   part_o[t][kvh][split][group][HD] fp32 (not normalised), part_ml[t][kvh][split][group][2].
-template <int HD>
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
@@ -377,6 +377,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 
     // ---- merge the four warps (each saw a quarter of the keys) through shared memory
     float* merge_o = reinterpret_cast<float*>(smem_raw);    // [WARPS][16][HD] fp32, stages are free now
+    float* cta_o = merge_o + WARPS * 16 * HD;               // [16][HD]: this CTA's result (CLUSTER)
+    float* cta_ml = cta_o + 16 * HD;                        // [16][2]
     if (t == 0) {
         merge_ml[warp][g][0] = m[0];
         merge_ml[warp][g][1] = l[0];
@@ -408,6 +410,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         }
         if (splits == 1) {
             out[((size_t)tok * nh + kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / ll);
+        } else if (CLUSTER) {
+            cta_o[r * HD + d] = acc;
+            if (d == 0) {
+                cta_ml[r * 2] = mm;
+                cta_ml[r * 2 + 1] = ll;
+            }
         } else {
             const size_t at = (((size_t)tok * nkv + kvh) * splits + split) * group + r;
             part_o[at * HD + d] = acc;
@@ -416,6 +424,46 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                 part_ml[at * 2 + 1] = ll;
             }
         }
+    }
+    if (CLUSTER && splits > 1) {
+        // The slices of one (token, KV head) form a thread-block cluster: every CTA left its
+        // (acc, max, sum) in its own shared memory; each then merges a share of the outputs over
+        // all slices, read through distributed shared memory in slice order.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const uint32_t o_base = static_cast<uint32_t>(__cvta_generic_to_shared(cta_o));
+        const uint32_t ml_base = static_cast<uint32_t>(__cvta_generic_to_shared(cta_ml));
+        auto peer = [](uint32_t local, uint32_t rank) {
+            uint32_t remote;
+            float v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+            return v;
+        };
+        for (int i = split * (WARPS * 32) + threadIdx.x; i < group * HD; i += splits * WARPS * 32) {
+            const int r = i / HD, d = i - r * HD;
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const bool on = s < splits;
+                ms[s] = on ? peer(ml_base + (uint32_t)(r * 2) * 4, s) : -INFINITY;
+                ls[s] = on ? peer(ml_base + (uint32_t)(r * 2 + 1) * 4, s) : 0.0f;
+                os[s] = on ? peer(o_base + (uint32_t)(r * HD + d) * 4, s) : 0.0f;
+            }
+            float mm = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) mm = fmaxf(mm, ms[s]);
+            float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const float c = exp2f(ms[s] - mm);          // a slice without keys: 2^(-inf) = 0
+                acc += c * os[s];
+                ll += c * ls[s];
+            }
+            out[((size_t)tok * nh + kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / ll);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // nobody leaves while a peer reads
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
 }
 
@@ -470,13 +518,38 @@ template <int HD>
 int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                   const int* tok_seg, const int* block_table, int max_pages, void* out, float* part_o,
                   float* part_ml, int T, int nh, int nkv, int splits, int tiles_per_split, int window,
-                  float scale, cudaStream_t stream) {
-    auto kernel = attention_decode_kernel<HD>;
-    constexpr size_t merge_bytes = (size_t)WARPS * 16 * HD * 4;
+                  float scale, bool in_cluster, cudaStream_t stream) {
+    constexpr size_t merge_bytes = (size_t)(WARPS + 1) * 16 * HD * 4 + 16 * 2 * 4;
     constexpr size_t bytes = Smem<HD>::BYTES > merge_bytes ? Smem<HD>::BYTES : merge_bytes;
+    using bf = __nv_bfloat16;
+    if (splits > 1 && in_cluster) {
+        // the slices of a (token, KV head) as a cluster: merged through distributed shared memory
+        auto kernel = attention_decode_kernel<HD, true>;
+        int st = opt_in_smem(kernel, bytes);
+        if (st != FWB_OK) return st;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(splits, nkv, T);
+        config.blockDim = dim3(WARPS * 32);
+        config.dynamicSmemBytes = bytes;
+        config.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attr;
+        config.numAttrs = pdl_enabled() ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&config, kernel, (const bf*)q, (const bf*)k_pool, (const bf*)v_pool,
+                                           positions, tok_seg, block_table, max_pages, (bf*)out,
+                                           (float*)nullptr, (float*)nullptr, nh, nkv, nh / nkv,
+                                           tiles_per_split, window, scale * LOG2E);
+        return e == cudaSuccess ? fwb_launch_status() : (int)e;
+    }
+    auto kernel = attention_decode_kernel<HD, false>;
     int st = opt_in_smem(kernel, bytes);
     if (st != FWB_OK) return st;
-    using bf = __nv_bfloat16;
     fwb::pdl(kernel, dim3(splits, nkv, T), WARPS * 32, bytes, stream)(
         (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
         (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E);
@@ -527,20 +600,23 @@ FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const v
 #undef CALL
 }
 
-// Decode tokens: one query token each.  With splits > 1, part_o needs T*nkv*splits*group*hd
-// floats and part_ml T*nkv*splits*group*2 floats of scratch.
+// Decode tokens: one query token each.  The slices of the context are merged either inside the
+// kernel (`merge_in_cluster` != 0, splits <= 8: the slices form a thread-block cluster; best
+// while the launch has few CTAs) or by a second kernel through scratch: part_o needs
+// T*nkv*splits*group*hd floats and part_ml T*nkv*splits*group*2 floats.
 FWB_API int fwb_attention_decode_mma(const void* q, const void* k_pool, const void* v_pool,
                                      const int* positions, const int* tok_seg, const int* block_table,
                                      int max_pages, int page_size, void* out, float* part_o, float* part_ml,
                                      int T, int nh, int nkv, int hd, int splits, int tiles_per_split,
-                                     int window, float scale, cudaStream_t stream) {
+                                     int window, float scale, int merge_in_cluster, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!q || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out) return FWB_BAD_ARGUMENT;
     if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
-    if (splits < 1 || tiles_per_split < 1 || (splits > 1 && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
+    const bool in_cluster = merge_in_cluster != 0 && splits <= 8;
+    if (splits < 1 || tiles_per_split < 1 || (splits > 1 && !in_cluster && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
 #define CALL(HD)                                                                                          \
     launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, out, part_o, part_ml, T, \
-                      nh, nkv, splits, tiles_per_split, window, scale, stream)
+                      nh, nkv, splits, tiles_per_split, window, scale, in_cluster, stream)
     FWB_HD_SWITCH(hd, CALL)
 #undef CALL
 }

@@ -13,6 +13,7 @@ import torch
 from . import ops
 
 SM_COUNT = 148
+CLUSTER_MERGE_CTAS = 1024
 _use_mma = True
 
 
@@ -44,11 +45,16 @@ def decode_splits(n_tokens: int, n_kv: int, max_tiles: int):
     """How many slices of the context run as separate CTAs.  Depends only on static sizes of the step
     (tokens, KV heads, block-table width), so a captured graph stays valid."""
     # measured on B200 (hd 64, 8 KV heads, batch 1..64, 4k..32k context): about eight 64-key tiles
-    # per slice, at most 16 slices
+    # per slice, at most 16 slices.  While the launch has few CTAs (small batches), up to 8 slices
+    # that merge inside the kernel as a cluster beat more slices with a merge kernel; with many
+    # CTAs the clusters' placement costs more than the second launch.
     splits = max(1, min(16, -(-max_tiles // 8)))
+    in_cluster = n_tokens * n_kv * min(splits, 8) <= CLUSTER_MERGE_CTAS
+    if in_cluster:
+        splits = min(8, splits)
     tiles_per_split = -(-max_tiles // splits)
     splits = -(-max_tiles // tiles_per_split)
-    return splits, tiles_per_split
+    return splits, tiles_per_split, in_cluster
 
 
 def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype):
@@ -60,10 +66,10 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
             and out_dtype == torch.bfloat16
             and ops.attention_mma_shape_ok(n_heads, n_kv, head_dim, page_size)):
         if batch.max_segment == 1 and not _force_tiled:
-            splits, tiles_per_split = decode_splits(batch.n_tokens, n_kv, block_table.shape[1])
+            splits, tiles_per_split, in_cluster = decode_splits(batch.n_tokens, n_kv, block_table.shape[1])
             return ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg,
                                             block_table, n_heads, window, scale, splits,
-                                            tiles_per_split)
+                                            tiles_per_split, in_cluster)
         group = n_heads // n_kv
         if (_use_tcgen05 and not _force_tiled and ops.attention_tcgen05_shape_ok(n_heads, n_kv, head_dim, page_size)
                 and 2 * batch.max_segment * group >= 128):

@@ -90,12 +90,12 @@ def run_attention_decode(args) -> dict:
     q, k_pool, v_pool, table, width = _paged_inputs(B, ctx, 1, args.heads, args.kv_heads, args.head_dim)
     positions = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
     tok_seg = torch.arange(B, dtype=torch.int32, device="cuda")
-    splits, per = attention.decode_splits(B, args.kv_heads, width)
+    splits, per, in_cluster = attention.decode_splits(B, args.kv_heads, width)
     if args.splits:
-        splits, per = args.splits, -(-width // args.splits)
+        splits, per, in_cluster = args.splits, -(-width // args.splits), args.cluster_merge
     scale = 1.0 / math.sqrt(args.head_dim)
     us = _time(lambda: ops.attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, table,
-                                                args.heads, 0, scale, splits, per), args.repeat)
+                                                args.heads, 0, scale, splits, per, in_cluster), args.repeat)
     kv_bytes = B * ctx * args.kv_heads * args.head_dim * 2 * 2
     return {"kernel": "attention_decode_mma", "batch": B, "context": ctx, "splits": splits,
             "us": us, "kv_gb_s": kv_bytes / us / 1e3}
@@ -182,6 +182,7 @@ def main(argv=None) -> int:
         p.add_argument("--head-dim", type=int, default=64)
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--mma-sync", action="store_true", help="the mma.sync prompt kernel")
+        p.add_argument("--cluster-merge", action="store_true", help="with --splits <= 8: merge inside the kernel")
     conv = sub.add_parser("shortconv")
     conv.add_argument("--tokens", type=int, default=2048)
     conv.add_argument("--hidden", type=int, default=2048)

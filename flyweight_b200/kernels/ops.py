@@ -295,9 +295,11 @@ def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg,
 
 
 def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_heads, window, scale,
-                         splits: int, tiles_per_split: int) -> torch.Tensor:
+                         splits: int, tiles_per_split: int, merge_in_cluster: bool = False) -> torch.Tensor:
     """Causal GQA of single decode tokens on tensor cores, the context cut into ``splits``
-    slices of ``tiles_per_split`` 64-key tiles that run as separate CTAs and are merged."""
+    slices of ``tiles_per_split`` 64-key tiles that run as separate CTAs and are merged: inside
+    the kernel (``merge_in_cluster``, up to 8 slices as a thread-block cluster) or through scratch
+    and a second kernel."""
     check_tensor("q", q, torch.bfloat16)
     check_tensor("k pool", k_pool, torch.bfloat16)
     check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
@@ -310,12 +312,14 @@ def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_h
     _i32("block table", block_table)
     out = torch.empty_like(q)
     part_o = part_ml = None
-    if splits > 1:
+    in_cluster = merge_in_cluster and 1 < splits <= 8
+    if splits > 1 and not in_cluster:
         group = n_heads // n_kv
         part_o = torch.empty((T, n_kv, splits, group, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((T, n_kv, splits, group, 2), dtype=torch.float32, device=q.device)
     lib.call("fwb_attention_decode_mma", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
              ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size, ptr(out), ptr(part_o),
              ptr(part_ml), T, n_heads, n_kv, head_dim, splits, tiles_per_split, window,
-             c_float(scale), stream(), launches=2 if splits > 1 else 1)
+             c_float(scale), 1 if in_cluster else 0, stream(),
+             launches=2 if (splits > 1 and not in_cluster) else 1)
     return out

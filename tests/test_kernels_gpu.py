@@ -617,6 +617,10 @@ def test_decode_attention_over_split_contexts(nh, nkv, hd, window):
         got = ops.attention_decode_mma(qd, cache.k_pool, cache.v_pool, ctx.batch.positions, ctx.batch.tok_seg,
                                        table_dev, nh, window, scale, splits, per)
         close(got.reshape(-1, nh, hd), want, 2.0 ** -7, f"{splits} splits")
+    for splits, per in ((2, 12), (3, 8), (5, 5), (8, 3)):        # the slices as a cluster, merged in the kernel
+        got = ops.attention_decode_mma(qd, cache.k_pool, cache.v_pool, ctx.batch.positions, ctx.batch.tok_seg,
+                                       table_dev, nh, window, scale, splits, per, merge_in_cluster=True)
+        close(got.reshape(-1, nh, hd), want, 2.0 ** -7, f"{splits} splits in a cluster")
 
 
 def test_tensor_core_attention_finds_a_far_key_and_the_window_edge():
