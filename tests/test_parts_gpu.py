@@ -309,3 +309,163 @@ def test_a_toy_architecture_defined_in_the_test(window, tmp_path):
         assert table[1] == -1 and runner.cache.groups[0].pool.n_used == 2
     runner.finish("b")
     assert runner.cache.groups[0].pool.n_used == 0
+
+
+# ------------------------------------------------------------------ a second toy: routing, positions
+def toy_routed_architecture():
+    """Another toy, again defined only here: a feed-forward that routes every token to one of
+    three small experts (router logits and softmax in fp32, top-1, the expert's output scaled
+    by its probability) and a position encoding of its own (rotary angles at pos / 4, full
+    head), in a model whose two layers differ (dense SwiGLU in one, routed experts in the other)."""
+    from flyweight_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from flyweight_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position
+    from flyweight_b200.parts.model import DecoderModel
+    from flyweight_b200.weights import TensorDecl
+
+    @register_position("toy_slow_rope")
+    class SlowRope(PositionEncoding):
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.rotary_dim = int(self.params["rotary_dim"])
+            self.slowdown = float(self.params["slowdown"])
+
+        def table(self, n_positions, device):
+            half = self.rotary_dim // 2
+            inv = 50.0 ** (-torch.arange(half, dtype=torch.float64) * 2 / self.rotary_dim)
+            angle = (torch.arange(n_positions, dtype=torch.float64) / self.slowdown)[:, None] * inv[None]
+            return torch.stack([angle.cos(), angle.sin()], -1).float().contiguous().to(device)
+
+    @register_feed_forward("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.hidden, self.width, self.n = (int(self.params[k]) for k in ("hidden_size", "width", "experts"))
+
+        def declare(self):
+            n = self.names
+            return {n["router"]: TensorDecl((self.n, self.hidden)),
+                    n["up"]: TensorDecl((self.n * self.width, self.hidden)),
+                    n["down"]: TensorDecl((self.n * self.hidden, self.width))}
+
+        def bind(self, get, precision, device):
+            f32 = lambda name: get(self.names[name]).to(device=device, dtype=torch.float32)
+            self.router = f32("router")
+            self.up = f32("up").reshape(self.n, self.width, self.hidden)
+            self.down = f32("down").reshape(self.n, self.hidden, self.width)
+
+        def forward(self, ctx, h):                 # test code: plain torch on the device
+            h = h.float()
+            prob = torch.softmax(h @ self.router.T, dim=-1)
+            weight, expert = prob.max(dim=-1)
+            hidden = torch.relu(torch.einsum("th,twh->tw", h, self.up[expert]))
+            return weight[:, None] * torch.einsum("tw,thw->th", hidden, self.down[expert])
+
+    class RoutedConfig:
+        architectures = ("ToyRoutedForCausalLM",)
+
+        def __init__(self, raw):
+            self.raw = dict(raw)
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw)
+
+        def to_dict(self):
+            return dict(self.raw)
+
+        def model_spec(self):
+            H, V = self.raw["hidden_size"], self.raw["vocab_size"]
+            norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-6}, {"weight": name})
+            attn = lambda i: PartSpec("gqa_attention", {
+                "hidden_size": H, "num_heads": 3, "num_kv_heads": 3, "head_dim": 16, "qk_norm_eps": None,
+                "position": PartSpec("toy_slow_rope", {"rotary_dim": 16, "slowdown": 4.0})},
+                {k: f"l{i}.attn.{k}" for k in ("q", "k", "v", "o")})
+            dense = PartSpec("swiglu", {"hidden_size": H, "ffn_dim": 80},
+                             {"gate": "l0.gate", "up": "l0.up", "down": "l0.down"})
+            routed = PartSpec("toy_top1_experts", {"hidden_size": H, "width": 24, "experts": 3},
+                              {"router": "l1.router", "up": "l1.experts.up", "down": "l1.experts.down"})
+            layers = (LayerSpec("prenorm_residual", norm("l0.n1"), attn(0), norm("l0.n2"), dense),
+                      LayerSpec("prenorm_residual", norm("l1.n1"), attn(1), norm("l1.n2"), routed))
+            return ModelSpec("ToyRoutedForCausalLM", H, V, 512, "embed", norm("final"), "head", layers,
+                             (ScheduleEntry(0), ScheduleEntry(1)))
+
+    class ToyRoutedForCausalLM(DecoderModel):
+        def __init__(self, config, precision, device):
+            self.config = config
+            super().__init__(config.model_spec(), precision, device)
+
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, ToyRoutedForCausalLM)
+    return {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 48, "vocab_size": 70}
+
+
+def toy_routed_reference(raw, w, tokens):
+    H, T, hd, nh = raw["hidden_size"], len(tokens), 16, 3
+    x = w["embed"][np.asarray(tokens)]
+    pos = np.arange(T)
+
+    def rope(v):                                   # [T][nh][hd], angles at pos / 4, base 50
+        half = hd // 2
+        inv = 50.0 ** (-np.arange(half) * 2.0 / hd)
+        ang = (pos / 4.0)[:, None] * inv[None]
+        cos, sin = np.cos(ang)[:, None], np.sin(ang)[:, None]
+        a, b = v[..., :half], v[..., half:]
+        return np.concatenate([a * cos - b * sin, b * cos + a * sin], -1)
+
+    def attend(h, i):
+        q = rope((h @ w[f"l{i}.attn.q"].T).reshape(T, nh, hd))
+        k = rope((h @ w[f"l{i}.attn.k"].T).reshape(T, nh, hd))
+        v = (h @ w[f"l{i}.attn.v"].T).reshape(T, nh, hd)
+        out = np.zeros((T, nh, hd))
+        ok = pos[None] <= pos[:, None]
+        for head in range(nh):
+            s = np.where(ok, q[:, head] @ k[:, head].T / math.sqrt(hd), -np.inf)
+            p = np.exp(s - s.max(-1, keepdims=True))
+            out[:, head] = (p / p.sum(-1, keepdims=True)) @ v[:, head]
+        return out.reshape(T, nh * hd) @ w[f"l{i}.attn.o"].T
+
+    def experts(h):
+        logits = h @ w["l1.router"].T
+        prob = np.exp(logits - logits.max(-1, keepdims=True))
+        prob /= prob.sum(-1, keepdims=True)
+        up = w["l1.experts.up"].reshape(3, 24, H)
+        down = w["l1.experts.down"].reshape(3, H, 24)
+        out = np.zeros_like(h)
+        for t in range(T):
+            e = int(prob[t].argmax())
+            out[t] = prob[t, e] * (down[e] @ np.maximum(up[e] @ h[t], 0.0))
+        return out
+
+    x = x + attend(P.rms_norm(x, w["l0.n1"], 1e-6), 0)
+    h = P.rms_norm(x, w["l0.n2"], 1e-6)
+    x = x + (P.silu(h @ w["l0.gate"].T) * (h @ w["l0.up"].T)) @ w["l0.down"].T
+    x = x + attend(P.rms_norm(x, w["l1.n1"], 1e-6), 1)
+    x = x + experts(P.rms_norm(x, w["l1.n2"], 1e-6))
+    return P.rms_norm(x, w["final"], 1e-6) @ w["head"].T
+
+
+def test_a_routed_feed_forward_and_another_position_encoding_defined_in_the_test(tmp_path):
+    """A feed-forward with routing and a position encoding of its own are registered here,
+    named by a toy configuration layer by layer (one dense, one routed), and the model is
+    built, loaded, stepped whole and in portions, and decoded through the framework."""
+    from flyweight_b200.engine import ModelRunner, load_model
+    from flyweight_b200.weights import load_model_tensors
+    from tiny_configs import make_model_dir
+    raw = toy_routed_architecture()
+    folder = make_model_dir(tmp_path / "routed", raw, seed=4, dtype=torch.float32)
+    model = load_model(folder, "float32")
+    assert not model.graph_safe                     # a part defined elsewhere: decode steps run eagerly
+    runner = ModelRunner(model, num_pages=6, num_slots=2, max_model_len=256)
+    w = as_numpy(load_model_tensors(folder))
+    tokens = [int(t) for t in np.random.default_rng(1).integers(0, 70, size=150)]
+    want = toy_routed_reference(raw, w, tokens)
+    whole = runner.step([("a", tokens, list(range(150)))]).cpu().numpy()
+    runner.finish("a")
+    scale = max(1.0, np.abs(want).max())
+    assert np.abs(whole - want).max() <= 1e-4 * scale
+    parts, at = [], 0
+    for n in [5, 64, 2, 40, 1, 1, 37]:
+        parts.append(runner.step([("b", tokens[at:at + n], list(range(n)))]).cpu().numpy())
+        at += n
+    runner.finish("b")
+    assert np.abs(np.concatenate(parts) - want).max() <= 1e-4 * scale
+    runner.cache.check()
