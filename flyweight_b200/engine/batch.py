@@ -15,6 +15,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -27,28 +28,56 @@ class Segment:
     want: List[int] = field(default_factory=list)     # indices into ``tokens``
 
 
+class _PinnedStaging:
+    """A small ring of pinned host buffers for the step's int32 arrays.  Page-locking memory is a
+    system call that costs more than the whole upload, so the buffers are kept and grown; an
+    event per buffer says when the copy that last read it has finished."""
+
+    def __init__(self, slots: int = 4):
+        self._buffers = [None] * slots
+        self._events = [None] * slots
+        self._turn = 0
+
+    def upload(self, values: np.ndarray, device) -> torch.Tensor:
+        turn = self._turn
+        self._turn = (turn + 1) % len(self._buffers)
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()
+        buffer = self._buffers[turn]
+        if buffer is None or buffer.numel() < values.size:
+            buffer = self._buffers[turn] = torch.empty(max(4096, 2 * values.size), dtype=torch.int32).pin_memory()
+        host = buffer[:values.size]
+        host.numpy()[:] = values
+        dev = host.to(device, non_blocking=True)
+        if self._events[turn] is None:
+            self._events[turn] = torch.cuda.Event()
+        self._events[turn].record()
+        return dev
+
+
+_staging = {}
+
+
+def _to_device(values: np.ndarray, device, pinned: bool) -> torch.Tensor:
+    if device is None or torch.device(device).type != "cuda":
+        return torch.from_numpy(values.copy())
+    if not pinned:
+        return torch.from_numpy(values.copy()).to(device)
+    key = str(device)
+    if key not in _staging:
+        _staging[key] = _PinnedStaging()
+    return _staging[key].upload(values, device)
+
+
 class StepBatch:
     def __init__(self, segments: Sequence[Segment], block_tables_host: Sequence[List[List[int]]],
                  device, pinned: bool = True):
         self.segments = list(segments)
         self.n_segments = S = len(self.segments)
-        token_ids: List[int] = []
-        positions: List[int] = []
-        tok_seg: List[int] = []
-        seg_start = [0]
-        logit_rows: List[int] = []
-        for index, seg in enumerate(self.segments):
-            base = len(token_ids)
-            token_ids.extend(seg.tokens)
-            positions.extend(range(seg.pos0, seg.pos0 + len(seg.tokens)))
-            tok_seg.extend([index] * len(seg.tokens))
-            seg_start.append(base + len(seg.tokens))
-            logit_rows.extend(base + w for w in seg.want)
-        self.n_tokens = T = len(token_ids)
-        self.n_logit_rows = R = len(logit_rows)
-        seg_slot = [seg.slot for seg in self.segments]
-        seg_pos0 = [seg.pos0 for seg in self.segments]
-        flat = token_ids + positions + tok_seg + seg_start + seg_slot + seg_pos0 + logit_rows
+        lengths = [len(seg.tokens) for seg in self.segments]
+        self.n_tokens = T = sum(lengths)
+        wanted = sum(len(seg.want) for seg in self.segments)
+        self.n_logit_rows = R = wanted
         offsets = {}
         cursor = 0
         for name, count in (("token_ids", T), ("positions", T), ("tok_seg", T),
@@ -60,29 +89,49 @@ class StepBatch:
         for rows in block_tables_host:
             width = len(rows[0]) if rows else 1
             table_slices.append((cursor, S, width))
-            for row in rows:
-                flat.extend(row)
             cursor += S * width
-        host = torch.tensor(flat, dtype=torch.int32)
-        self.h2d_bytes = host.numel() * 4
-        if device is not None and torch.device(device).type == "cuda":
-            if pinned:
-                host = host.pin_memory()
-            dev = host.to(device, non_blocking=True)
-        else:
-            dev = host
-        self._host = host
+        flat = np.empty(cursor, dtype=np.int32)
+        ids, positions, tok_seg = (flat[offsets[name][0]:offsets[name][0] + T]
+                                   for name in ("token_ids", "positions", "tok_seg"))
+        seg_start = flat[offsets["seg_start"][0]:offsets["seg_start"][0] + S + 1]
+        logit_rows = flat[offsets["logit_rows"][0]:offsets["logit_rows"][0] + R]
+        seg_start[0] = 0
+        base = row = 0
+        for index, (seg, n) in enumerate(zip(self.segments, lengths)):
+            if n == 1:
+                ids[base] = seg.tokens[0]
+                positions[base] = seg.pos0
+                tok_seg[base] = index
+            else:
+                ids[base:base + n] = seg.tokens
+                positions[base:base + n] = np.arange(seg.pos0, seg.pos0 + n, dtype=np.int32)
+                tok_seg[base:base + n] = index
+            for w in seg.want:
+                logit_rows[row] = base + w
+                row += 1
+            base += n
+            seg_start[index + 1] = base
+        start = offsets["seg_slot"][0]
+        flat[start:start + S] = [seg.slot for seg in self.segments]
+        start = offsets["seg_pos0"][0]
+        flat[start:start + S] = [seg.pos0 for seg in self.segments]
+        for (start, s, w), rows in zip(table_slices, block_tables_host):
+            if s:
+                flat[start:start + s * w] = np.asarray(rows, dtype=np.int32).reshape(-1)
+        self.h2d_bytes = flat.size * 4
+        dev = _to_device(flat, device, pinned)
         self._dev = dev
         for name, (start, count) in offsets.items():
             setattr(self, name, dev[start:start + count])
         self.block_tables = [dev[start:start + s * w].view(s, w) for start, s, w in table_slices]
-        self.max_context = max((seg.pos0 + len(seg.tokens) for seg in self.segments), default=0)
-        self.max_segment = max((len(seg.tokens) for seg in self.segments), default=0)
+        self.max_context = max((seg.pos0 + n for seg, n in zip(self.segments, lengths)), default=0)
+        self.max_segment = max(lengths, default=0)
         self._device = device
+        self._pinned = pinned
         self._tiles = {}
 
     def attention_tiles(self, tokens_per_tile: int):
-        """Row tiles for the tiled attention kernel: every segment cut into runs of at most
+        """Row tiles for the tiled attention kernels: every segment cut into runs of at most
         ``tokens_per_tile`` tokens.  Returns (tile_seg, tile_tok0, n_tiles), int32 on the
         device; made once per step and tile size."""
         cached = self._tiles.get(tokens_per_tile)
@@ -90,17 +139,16 @@ class StepBatch:
             seg_of, tok0 = [], []
             base = 0
             for index, seg in enumerate(self.segments):
-                for start in range(0, len(seg.tokens), tokens_per_tile):
-                    seg_of.append(index)
-                    tok0.append(base + start)
-                base += len(seg.tokens)
-            host = torch.tensor(seg_of + tok0, dtype=torch.int32)
-            self.h2d_bytes += host.numel() * 4
-            if self._device is not None and torch.device(self._device).type == "cuda":
-                dev = host.pin_memory().to(self._device, non_blocking=True)
-            else:
-                dev = host
-            n = len(seg_of)
+                n = len(seg.tokens)
+                starts = np.arange(base, base + n, tokens_per_tile, dtype=np.int32)
+                seg_of.append(np.full(starts.size, index, dtype=np.int32))
+                tok0.append(starts)
+                base += n
+            seg_of = np.concatenate(seg_of) if seg_of else np.empty(0, dtype=np.int32)
+            n = seg_of.size
+            host = np.concatenate([seg_of] + tok0) if n else np.empty(0, dtype=np.int32)
+            self.h2d_bytes += host.size * 4
+            dev = _to_device(host, self._device, self._pinned)
             cached = self._tiles[tokens_per_tile] = (dev[:n], dev[n:], n)
         return cached
 
