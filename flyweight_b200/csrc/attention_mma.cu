@@ -467,7 +467,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
 }
 
-// grid (nkv, T), block 128: sum the splits in ascending order.
+// grid (nkv, T), block 128: sum the splits in ascending order.  The loads of eight splits are
+// issued together (they do not depend on one another), then combined one after the other.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int group, int hd,
                                        int splits) {
@@ -477,13 +478,31 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     for (int i = threadIdx.x; i < group * hd; i += blockDim.x) {
         const int r = i / hd, d = i - r * hd;
         float mm = -INFINITY;
-        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[((base_at + s) * group + r) * 2]);
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float m8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                m8[j] = s0 + j < splits ? part_ml[((base_at + s0 + j) * group + r) * 2] : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mm = fmaxf(mm, m8[j]);
+        }
         float acc = 0.0f, ll = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const size_t at = (base_at + s) * group + r;
-            const float c = exp2f(part_ml[at * 2] - mm);    // a split without keys: 2^(-inf) = 0
-            acc += c * part_o[at * hd + d];
-            ll += c * part_ml[at * 2 + 1];
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float m8[8], l8[8], o8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool on = s0 + j < splits;
+                const size_t at = (base_at + s0 + j) * group + r;
+                m8[j] = on ? part_ml[at * 2] : -INFINITY;
+                l8[j] = on ? part_ml[at * 2 + 1] : 0.0f;
+                o8[j] = on ? part_o[at * hd + d] : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float c = exp2f(m8[j] - mm);          // a split without keys: 2^(-inf) = 0
+                acc += c * o8[j];
+                ll += c * l8[j];
+            }
         }
         out[((size_t)tok * nh + kvh * group + r) * hd + d] = __float2bfloat16_rn(acc / ll);
     }

@@ -48,8 +48,11 @@ def decode_splits(n_tokens: int, n_kv: int, max_tiles: int):
     # per slice, at most 16 slices.  While the launch has few CTAs (small batches), up to 8 slices
     # that merge inside the kernel as a cluster beat more slices with a merge kernel; with many
     # CTAs the clusters' placement costs more than the second launch.
-    splits = max(1, min(16, -(-max_tiles // 8)))
-    in_cluster = n_tokens * n_kv * min(splits, 8) <= CLUSTER_MERGE_CTAS
+    # a step with few (token, KV head) pairs and a very long context may cut it finer, up to 64 slices
+    # of at least four tiles, until the launch has about four CTAs per SM
+    most = max(16, min(64, -(-4 * SM_COUNT // max(1, n_tokens * n_kv))))
+    splits = max(1, min(most, -(-max_tiles // 8)))
+    in_cluster = n_tokens * n_kv * min(splits, 8) <= CLUSTER_MERGE_CTAS and splits <= 16
     if in_cluster:
         splits = min(8, splits)
     tiles_per_split = -(-max_tiles // splits)
