@@ -141,12 +141,27 @@ class CacheManager:
                     cache.v_pool = torch.zeros(shape, dtype=cache_dtype, device=device)
             elif isinstance(spec, FixedState):
                 self._fixed_positions.append(position)
-                if device is not None:
-                    cache.state = torch.zeros((self.num_slots, *spec.shape), dtype=torch.float32,
-                                              device=device)
             elif spec is not None:
                 raise TypeError(f"schedule position {position}: unknown state spec {spec!r}")
             self.layer_caches.append(cache)
+        # All fixed-size states of a slot lie side by side in one allocation, [num_slots][total],
+        # and every execution sees its share as [num_slots][...]: admission clears one span.
+        self._all_states: Optional[torch.Tensor] = None
+        if device is not None and self._fixed_positions:
+            sizes = []
+            for position in self._fixed_positions:
+                count = 1
+                for extent in self.layer_caches[position].spec.shape:
+                    count *= int(extent)
+                sizes.append(count)
+            self._all_states = torch.zeros((self.num_slots, sum(sizes)), dtype=torch.float32, device=device)
+            offset = 0
+            for position, count in zip(self._fixed_positions, sizes):
+                shape = tuple(self.layer_caches[position].spec.shape)
+                self.layer_caches[position].state = (
+                    self._all_states[:, offset:offset + count].unflatten(1, shape) if shape
+                    else self._all_states[:, offset])
+                offset += count
 
     # ------------------------------------------------------------------ requests
     def live(self) -> Tuple[Hashable, ...]:
@@ -183,10 +198,8 @@ class CacheManager:
         self.slots_high_water = max(self.slots_high_water, len(self._slot_of))
         for group in self.groups:
             group.tables[request] = []
-        for position in self._fixed_positions:
-            state = self.layer_caches[position].state
-            if state is not None:
-                state[slot].zero_()
+        if self._all_states is not None:
+            self._all_states[slot].zero_()
         return slot
 
     def release_passed(self, request: Hashable) -> int:

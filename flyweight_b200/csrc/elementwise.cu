@@ -20,10 +20,41 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
         out[(size_t)t * H + c] = ok ? to_f32<TW>(table[(size_t)id * H + c]) : 0.0f;
 }
 
+// bfloat16 table, H a multiple of 8: a thread widens 8 adjacent entries (one 16-byte load, two
+// 16-byte stores); one block per token.
+__global__ void embed_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int H, int V, int* bad) {
+    fwb::pdl_entry();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0 && bad) atomicExch(bad, 1);
+    const __nv_bfloat16* row = table + (size_t)(ok ? id : 0) * H;
+    float* dst = out + (size_t)t * H;
+    for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+        float4 lo = make_float4(0, 0, 0, 0), hi = lo;
+        if (ok) {
+            const uint4 v = *reinterpret_cast<const uint4*>(row + c);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+            const float2 e = __bfloat1622float2(h[2]), f = __bfloat1622float2(h[3]);
+            lo = make_float4(a.x, a.y, b.x, b.y);
+            hi = make_float4(e.x, e.y, f.x, f.y);
+        }
+        *reinterpret_cast<float4*>(dst + c) = lo;
+        *reinterpret_cast<float4*>(dst + c + 4) = hi;
+    }
+}
+
 FWB_API int fwb_embed(const void* table, int table_bf16, const int* ids, float* out, int T, int H,
                       int V, int* bad, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!table || !ids || !out || H <= 0 || V <= 0 || T > 65535) return FWB_BAD_ARGUMENT;
+    if (table_bf16 && (H & 7) == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+        const int threads = H / 8 < 256 ? ((H / 8 + 31) / 32) * 32 : 256;
+        fwb::pdl(embed_bf16x8_kernel, T, threads, 0, stream)((const __nv_bfloat16*)table, ids, out, H, V, bad);
+        return fwb_launch_status();
+    }
     dim3 grid((H + 255) / 256 > 64 ? 64 : (H + 255) / 256, T);
     if (table_bf16)
         fwb::pdl(embed_kernel<__nv_bfloat16>, grid, 256, 0, stream)(

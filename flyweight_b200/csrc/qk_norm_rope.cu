@@ -136,7 +136,8 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
     }
     const int half_lanes = rot >> 4, rot_lanes = rot >> 3;
     const int partner = gl < half_lanes ? lane + half_lanes : (gl < rot_lanes ? lane - half_lanes : lane);
-    for (int h0 = (blockIdx.y * WARPS + warp) * per_warp; h0 < heads; h0 += gridDim.y * WARPS * per_warp) {
+    const int block_warps = blockDim.x >> 5;
+    for (int h0 = (blockIdx.y * block_warps + warp) * per_warp; h0 < heads; h0 += gridDim.y * block_warps * per_warp) {
         const int h = h0 + sub;
         const bool valid = sub < per_warp && h < heads;
         float v[8];

@@ -27,7 +27,7 @@ __global__ void shortconv_kernel(const TP* __restrict__ p, const float* __restri
                                  const float* __restrict__ bias, float* __restrict__ state,
                                  const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                                  const int* __restrict__ tok_seg, TZ* __restrict__ z, int T, int S,
-                                 int H, int L, int body_blocks) {
+                                 int H, int L, int body_blocks, size_t slot_stride) {
     fwb::pdl_entry();
     const int ld = 3 * H;
     if ((int)blockIdx.x < body_blocks) {
@@ -48,7 +48,7 @@ __global__ void shortconv_kernel(const TP* __restrict__ p, const float* __restri
     if (idx >= (size_t)S * H) return;
     const int s = (int)(idx / H), c = (int)(idx - (size_t)s * H);
     const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
-    float* st = state + ((size_t)seg_slot[s] * H + c) * (L - 1);
+    float* st = state + (size_t)seg_slot[s] * slot_stride + (size_t)c * (L - 1);
     // hist[0..L-2] = state (oldest first), hist[L-1..] = u of the first tokens.
     float hist[2 * MAX_TAPS];
     float w[MAX_TAPS];
@@ -91,12 +91,13 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 __device__ __forceinline__ void conv_head_bf16(const __nv_bfloat16* __restrict__ p, const float* __restrict__ taps,
                                                const float* __restrict__ bias, float* __restrict__ state,
                                                const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
-                                               __nv_bfloat16* __restrict__ z, int S, int H, int L, size_t idx) {
+                                               __nv_bfloat16* __restrict__ z, int S, int H, int L, size_t idx,
+                                               size_t slot_stride) {
     const int ld = 3 * H;
     if (idx >= (size_t)S * H) return;
     const int s = (int)(idx / H), c = (int)(idx - (size_t)s * H);
     const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
-    float* st = state + ((size_t)seg_slot[s] * H + c) * (L - 1);
+    float* st = state + (size_t)seg_slot[s] * slot_stride + (size_t)c * (L - 1);
     float hist[2 * MAX_TAPS];
     float w[MAX_TAPS];
     for (int k = 0; k < L; ++k) w[k] = taps[c * L + k];
@@ -123,7 +124,7 @@ __global__ void shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, con
                                         const float* __restrict__ bias, float* __restrict__ state,
                                         const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                                         const int* __restrict__ tok_seg, __nv_bfloat16* __restrict__ z,
-                                        int T, int S, int H, int L, int body_blocks) {
+                                        int T, int S, int H, int L, int body_blocks, size_t slot_stride) {
     fwb::pdl_entry();
     const int ld = 3 * H;
     if ((int)blockIdx.x < body_blocks) {
@@ -154,7 +155,7 @@ __global__ void shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, con
         return;
     }
     conv_head_bf16(p, taps, bias, state, seg_start, seg_slot, z, S, H, L,
-                   (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x);
+                   (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x, slot_stride);
 }
 
 // Prompt-sized bfloat16 launches: a body thread owns 8 adjacent channels over a run of
@@ -163,17 +164,18 @@ __global__ void shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, con
 // at its start; a run that crosses into another segment carries products of the previous
 // segment only into outputs with j < L-1, which the head threads own.  The sum runs in the
 // same order as everywhere else: bias, then taps oldest first.
-template <int L>
+template <int L, int RUN>
 __global__ void __launch_bounds__(128)
 shortconv_bf16_run_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ taps,
                           const float* __restrict__ bias, float* __restrict__ state,
                           const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                           const int* __restrict__ tok_seg, __nv_bfloat16* __restrict__ z, int T, int S,
-                          int H, int body_blocks, int run) {
+                          int H, int body_blocks, size_t slot_stride) {
     fwb::pdl_entry();
     const int ld = 3 * H;
     if ((int)blockIdx.x < body_blocks) {
         const int groups = H >> 3;
+        constexpr int run = RUN;
         const int runs = (T + run - 1) / run;
         const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
         if (idx >= (size_t)runs * groups) return;
@@ -201,67 +203,82 @@ shortconv_bf16_run_kernel(const __nv_bfloat16* __restrict__ p, const float* __re
                 for (int i = 0; i < 8; ++i) hist[k][i] = 0.0f;
             }
         }
-        for (int t = t0; t < t1; ++t) {
+        // every load of the run goes out before the first product is formed
+        uint4 vb[RUN], vx[RUN], vc[RUN];
+        int first[RUN];
+#pragma unroll
+        for (int i = 0; i < RUN; ++i) {
+            const int t = t0 + i < T ? t0 + i : T - 1;
             const __nv_bfloat16* row = p + (size_t)t * ld;
+            vb[i] = *reinterpret_cast<const uint4*>(row + c);
+            vx[i] = *reinterpret_cast<const uint4*>(row + 2 * H + c);
+            vc[i] = *reinterpret_cast<const uint4*>(row + H + c);
+            first[i] = seg_start[tok_seg[t]];
+        }
+#pragma unroll
+        for (int i = 0; i < RUN; ++i) {
+            const int t = t0 + i;
+            if (t >= t1) break;
             float b[8], x[8], u[8];
-            unpack8(*reinterpret_cast<const uint4*>(row + c), b);
-            unpack8(*reinterpret_cast<const uint4*>(row + 2 * H + c), x);
+            unpack8(vb[i], b);
+            unpack8(vx[i], x);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) u[i] = b[i] * x[i];
-            const int j = t - seg_start[tok_seg[t]];
-            if (j >= L - 1) {
+            for (int k = 0; k < 8; ++k) u[k] = b[k] * x[k];
+            if (t - first[i] >= L - 1) {
                 float g[8], y[8];
-                unpack8(*reinterpret_cast<const uint4*>(row + H + c), g);
+                unpack8(vc[i], g);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    y[i] = b0[i];
+                for (int k8 = 0; k8 < 8; ++k8) {
+                    y[k8] = b0[k8];
 #pragma unroll
-                    for (int k = 0; k < L - 1; ++k) y[i] = fmaf(w[k][i], hist[k][i], y[i]);
-                    y[i] = fmaf(w[L - 1][i], u[i], y[i]);
+                    for (int k = 0; k < L - 1; ++k) y[k8] = fmaf(w[k][k8], hist[k][k8], y[k8]);
+                    y[k8] = fmaf(w[L - 1][k8], u[k8], y[k8]);
                 }
                 uint4 out;
                 __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    o[i] = __floats2bfloat162_rn(g[2 * i] * y[2 * i], g[2 * i + 1] * y[2 * i + 1]);
+                for (int k = 0; k < 4; ++k)
+                    o[k] = __floats2bfloat162_rn(g[2 * k] * y[2 * k], g[2 * k + 1] * y[2 * k + 1]);
                 *reinterpret_cast<uint4*>(z + (size_t)t * H + c) = out;
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int k8 = 0; k8 < 8; ++k8) {
 #pragma unroll
-                for (int k = 0; k + 1 < L - 1; ++k) hist[k][i] = hist[k + 1][i];
-                hist[L - 2][i] = u[i];
+                for (int k = 0; k + 1 < L - 1; ++k) hist[k][k8] = hist[k + 1][k8];
+                hist[L - 2][k8] = u[k8];
             }
         }
         return;
     }
     conv_head_bf16(p, taps, bias, state, seg_start, seg_slot, z, S, H, L,
-                   (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x);
+                   (size_t)(blockIdx.x - body_blocks) * blockDim.x + threadIdx.x, slot_stride);
 }
 
 }  // namespace
 
 // p: [T][3H] (fp32 or bf16); taps: [H][L] fp32; bias: [H] fp32 or null;
-// state: [num_slots][H][L-1] fp32; seg_start: [S+1]; seg_slot: [S]; tok_seg: [T];
+// state: fp32 [H][L-1] per slot, slots `state_slot_stride` floats apart; seg_start: [S+1]; seg_slot: [S]; tok_seg: [T];
 // z: [T][H] (fp32 or bf16).
 FWB_API int fwb_shortconv(const void* p, int p_bf16, const float* taps, const float* bias,
                           float* state, const int* seg_start, const int* seg_slot,
                           const int* tok_seg, void* z, int z_bf16, int T, int S, int H, int L,
-                          cudaStream_t stream) {
+                          long long state_slot_stride, cudaStream_t stream) {
     if (T <= 0 || S <= 0) return FWB_OK;
     if (!p || !taps || !state || !seg_start || !seg_slot || !tok_seg || !z || H <= 0)
         return FWB_BAD_ARGUMENT;
     if (L < 2 || L > MAX_TAPS) return FWB_UNSUPPORTED;
+    if (state_slot_stride < (long long)H * (L - 1)) return FWB_BAD_ARGUMENT;
+    const size_t slot_stride = (size_t)state_slot_stride;
     const int threads = 128;
     if (p_bf16 && z_bf16 && (H & 7) == 0 && ((uintptr_t)p & 15) == 0 && ((uintptr_t)z & 15) == 0) {
         const int head = (int)(((size_t)S * H + threads - 1) / threads);
         if (T >= 256 && L >= 2 && L <= 4) {
-            const int run = 4;
+            constexpr int run = 4;
             const int body = (int)(((size_t)((T + run - 1) / run) * (H >> 3) + threads - 1) / threads);
 #define FWB_CONV_RUN(LL)                                                                          \
-    fwb::pdl(shortconv_bf16_run_kernel<LL>, body + head, threads, 0, stream)(                     \
+    fwb::pdl(shortconv_bf16_run_kernel<LL, run>, body + head, threads, 0, stream)(                \
         (const __nv_bfloat16*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (__nv_bfloat16*)z, T, S, \
-        H, body, run)
+        H, body, slot_stride)
             if (L == 2) FWB_CONV_RUN(2);
             else if (L == 3) FWB_CONV_RUN(3);
             else FWB_CONV_RUN(4);
@@ -271,7 +288,7 @@ FWB_API int fwb_shortconv(const void* p, int p_bf16, const float* taps, const fl
         const int body = (int)(((size_t)T * (H >> 3) + threads - 1) / threads);
         fwb::pdl(shortconv_bf16x8_kernel, body + head, threads, 0, stream)(
             (const __nv_bfloat16*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (__nv_bfloat16*)z, T, S,
-            H, L, body);
+            H, L, body, slot_stride);
         return fwb_launch_status();
     }
     const int body_blocks = (int)(((size_t)T * H + threads - 1) / threads);
@@ -281,7 +298,7 @@ FWB_API int fwb_shortconv(const void* p, int p_bf16, const float* taps, const fl
 #define FWB_CONV(TP, TZ)                                                                          \
     fwb::pdl(shortconv_kernel<TP, TZ>, blocks, threads, 0, stream)(                                     \
         (const TP*)p, taps, bias, state, seg_start, seg_slot, tok_seg, (TZ*)z, T, S, H, L,        \
-        body_blocks)
+        body_blocks, slot_stride)
     if (p_bf16 && z_bf16) FWB_CONV(bf, bf);
     else if (!p_bf16 && z_bf16) FWB_CONV(float, bf);
     else if (!p_bf16 && !z_bf16) FWB_CONV(float, float);

@@ -157,15 +157,18 @@ def shortconv(p: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor],
     check_tensor("conv taps", taps, torch.float32, (H, L))
     if bias is not None:
         check_tensor("conv bias", bias, torch.float32, (H,))
-    check_tensor("conv state", state, torch.float32)
-    if tuple(state.shape[1:]) != (H, L - 1):
-        raise KernelError(f"conv state must be [slots][{H}][{L - 1}], got {tuple(state.shape)}")
+    if not state.is_cuda or state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, L - 1):
+        raise KernelError(f"conv state must be CUDA fp32 [slots][{H}][{L - 1}], got {tuple(state.shape)}")
+    if state.stride(2) != 1 or state.stride(1) != L - 1 or (state.shape[0] > 1 and state.stride(0) < H * (L - 1)):
+        raise KernelError("a slot of the conv state must be contiguous")
+    slot_stride = state.stride(0) if state.shape[0] > 1 else H * (L - 1)
     _i32("seg_start", seg_start, n_segments + 1)
     _i32("seg_slot", seg_slot, n_segments)
     _i32("tok_seg", tok_seg, T)
     out = torch.empty((T, H), dtype=out_dtype, device=p.device)
     lib.call("fwb_shortconv", ptr(p), is_bf16(p), ptr(taps), ptr(bias), ptr(state), ptr(seg_start),
-             ptr(seg_slot), ptr(tok_seg), ptr(out), is_bf16(out), T, n_segments, H, L, stream())
+             ptr(seg_slot), ptr(tok_seg), ptr(out), is_bf16(out), T, n_segments, H, L,
+             c_longlong(slot_stride), stream())
     return out
 
 
