@@ -170,6 +170,20 @@ class ModelRunner(StepPlanner):
         self.h2d_bytes += batch.h2d_bytes
         return logits
 
+    def check_health(self) -> None:
+        """Raise if a kernel recorded a failure since the last check: a bounded wait inside a
+        tensor-core kernel that gave up (the results of its step are not to be trusted), or a
+        token id outside the vocabulary that reached the embedding.  Reads two words from the
+        device, so it waits for the work queued so far."""
+        from ..kernels import KernelError, tensorcore
+        code = tensorcore.status()
+        if code:
+            raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}); "
+                              "the logits of that step are not valid")
+        if int(self.bad_token_flag.item()):
+            self.bad_token_flag.zero_()
+            raise KernelError("a token id outside the vocabulary reached the embedding kernel")
+
     def step_same_requests(self, tokens: Sequence[int]) -> torch.Tensor:
         """The decode step that follows the last one for exactly the same requests, none of
         which needs a new page: lengths grow by one, the captured graph is replayed."""

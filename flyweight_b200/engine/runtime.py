@@ -99,8 +99,9 @@ class Runtime:
         self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
 
     def close(self) -> None:
-        self.runner = None
-        self.scheduler = None
+        runner, self.runner, self.scheduler = self.runner, None, None
+        if runner is not None:
+            runner.check_health()
 
     def __enter__(self):
         return self
@@ -178,8 +179,13 @@ class Runtime:
         host = self._read_tokens(tokens)              # the step's only device->host read
         self._counters["d2h_bytes"] += 4 * len(host)
         self._counters["sampling_seconds"] += time.perf_counter() - sampled
+        finished = False
         for task, token in zip(need, host):
-            events.extend(self.scheduler.accept(task, token))
+            accepted = self.scheduler.accept(task, token)
+            finished = finished or len(accepted) > 1
+            events.extend(accepted)
+        if finished:
+            self.runner.check_health()          # once per finished request: kernels fail loudly
 
     def _same_requests_again(self):
         """The running tasks, if the next step is the last one moved on by one token: nobody

@@ -51,6 +51,7 @@ def main(argv=None) -> int:
         logits = runner.step(entries)
         if logits.shape[0]:
             data = logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False)
+            runner.check_health()          # a kernel that gave up must not leave a file that looks fine
             data.tofile(out_dir / f"{step}.f32")
         for request in record.get("end", []):
             runner.finish(request)
