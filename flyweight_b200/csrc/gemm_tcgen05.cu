@@ -624,6 +624,26 @@ FWB_API int fwb_gemm_tcgen05_status() {
     return value;
 }
 
+namespace {
+// One thread waits, with a short limit, on a barrier that nobody will ever arrive on: the wait
+// must give up, leave its code in the status word and let the kernel end normally.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned limit, int code) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait(&bar, 0, &abort_flag, code, status, limit);
+}
+}  // namespace
+
+// Exercises the path a stuck pipeline takes, without sticking anything: returns once the kernel
+// has given up (a few thousand polls); afterwards fwb_gemm_tcgen05_status() returns `code`.
+FWB_API int fwb_selftest_bounded_wait(int code, cudaStream_t stream) {
+    bounded_wait_selftest_kernel<<<1, 1, 0, stream>>>(status_word(), 4096u, code);
+    return fwb_launch_status();
+}
+
 // Programmatic dependent launch for every kernel of the library: 1 = on (default), 0 = off.
 FWB_API int fwb_set_pdl(int enabled) {
     fwb::pdl_enabled() = enabled != 0;

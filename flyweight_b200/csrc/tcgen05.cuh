@@ -66,8 +66,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 }
 // Bounded wait.  Returns false if it gave up (or somebody else in the CTA did).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int code, int* status) {
-    for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
+                                          int code, int* status, unsigned limit = WAIT_LIMIT) {
+    for (unsigned spin = 0; spin < limit; ++spin) {
         if (mbar_test(bar, parity)) return true;
         if (*abort_flag) return false;
         if (spin > 2048) __nanosleep(64);

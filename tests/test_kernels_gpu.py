@@ -582,6 +582,29 @@ def test_tcgen05_swiglu_with_the_norm_folded_in(M, F, K):
         close(got, want, 2.0 ** -6, f"normed swiglu splits={splits}")
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """Every wait in the tensor-core kernels is bounded.  A one-thread kernel waits on a barrier
+    that nothing arrives on; it must give up, leave its code in the status word that the
+    runner's health check raises on, and the next product must run as usual."""
+    from flyweight_b200.kernels import KernelError, lib, tensorcore
+    from flyweight_b200.kernels.lib import stream
+    assert tensorcore.status() == 0
+    lib.call("fwb_selftest_bounded_wait", 77, stream())
+    torch.cuda.synchronize()
+    assert tensorcore.status() == 77
+    assert tensorcore.status() == 0                          # reading clears it
+    lib.call("fwb_selftest_bounded_wait", 78, stream())
+    checker = type("R", (), {})()
+    checker.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    from flyweight_b200.engine.runner import ModelRunner
+    with pytest.raises(KernelError, match="gave up"):
+        ModelRunner.check_health(checker)
+    g = torch.Generator().manual_seed(1)
+    x, w = torch.randn(8, 256, generator=g).to(torch.bfloat16), torch.randn(128, 256, generator=g).to(torch.bfloat16)
+    close(tensorcore.gemm(dev(x), dev(w), torch.float32), x.double() @ w.double().T, 1e-5, "after the self-test")
+    assert tensorcore.status() == 0
+
+
 def test_tcgen05_refuses_what_tma_cannot_address():
     from flyweight_b200.kernels import KernelError, tensorcore as tc
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K not a multiple of 8
