@@ -72,8 +72,20 @@ argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
     fwb::pdl_entry();
     __shared__ unsigned long long scratch[33];
     const float* row = logits + (size_t)blockIdx.x * V;
+    const bool vectorised = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+    const int quads = vectorised ? V >> 2 : 0;
     unsigned long long best = 0ull;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+#pragma unroll 4
+    for (int qd = threadIdx.x; qd < quads; qd += blockDim.x) {
+        const float4 l4 = reinterpret_cast<const float4*>(row)[qd];
+        const float l[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned long long key = make_key(l[j], 4 * qd + j);
+            best = key > best ? key : best;
+        }
+    }
+    for (int i = 4 * quads + threadIdx.x; i < V; i += blockDim.x) {
         const unsigned long long key = make_key(row[i], i);
         best = key > best ? key : best;
     }
@@ -196,121 +208,327 @@ __device__ int draw_sorted(const unsigned long long* keys, int n, const RowParam
     return key_id(keys[keep - 1]);
 }
 
-// One block per row.  Rows whose candidate count is <= SMALL_K are finished here; rows
-// that need more are finished by sample_large_kernel (they are marked in `out` by -1).
-__global__ void __launch_bounds__(THREADS)
-sample_small_kernel(const float* __restrict__ logits, int V, const RowParams* __restrict__ params,
-                    const double* __restrict__ uniform, const int* __restrict__ recent,
-                    int recent_stride, int* __restrict__ out) {
+// ------------------------------------------------------------------ the sampling kernel
+// A row is worked on by a thread-block cluster of CLUSTER CTAs; CTA c owns every CLUSTER-th group
+// of four logits.  Nothing is sorted except the (at most 1024) candidates of a top-k row.
+//
+// "The k-th largest key" and "the first candidate, in descending order, at which the running
+// mass reaches T" are the same question -- the largest key x with weight{keys > x} < T <=
+// weight{keys >= x} -- and x is found digit by digit from the top, eight bits a pass: every CTA
+// makes a histogram of weight per digit over its share of the row (weight 1 for top-k, the
+// probability mass for top-p and for the draw), the CTAs read one another's histograms through
+// distributed shared memory, and all of them take the same step down.  Masses are 64-bit fixed
+// point (p * 2^40 with p = exp((l - l0)/t) in double, p0 = 1), so every sum is an exact integer
+// whatever the order of addition: the draw is reproducible.  Against the sequential double sums
+// of the definition the kept prefix and the drawn token can differ only when a threshold falls
+// within ~2^-40 of the boundary between two candidates.
+constexpr int CLUSTER = 8;
+constexpr int CTA_THREADS = 512;
+constexpr int CTA_WARPS = CTA_THREADS / 32;
+constexpr double MASS_ONE = 1099511627776.0;     // 2^40
+
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned peer_address(const void* local, unsigned rank) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(remote)
+                 : "r"((unsigned)__cvta_generic_to_shared(local)), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ unsigned long long peer_load_u64(const void* local, unsigned rank) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(peer_address(local, rank)) : "memory");
+    return v;
+}
+
+// What a CTA keeps in shared memory for the walks and the reductions.
+struct Shared {
+    unsigned long long total[256];                 // this CTA's histogram of the pass (peers read it)
+    unsigned long long per_warp[CTA_WARPS][256];   // one histogram per warp, summed into `total`
+    unsigned long long all[256];                   // the cluster's histogram
+    unsigned long long slot;                       // this CTA's share of a cluster-wide sum or maximum
+    unsigned long long pick[2];                    // digits chosen so far, what is left of the target
+    unsigned long long scratch[33];
+    unsigned long long keys[SMALL_K];              // the candidates of a top-k row (rank 0 sorts and draws)
+    double probs[SMALL_K];
+    unsigned count;
+};
+
+// Sum (or maximum) over the cluster of one value per thread.
+template <bool MAXIMUM>
+__device__ unsigned long long cluster_reduce(unsigned long long v, Shared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = MAXIMUM ? (other > v ? other : v) : v + other;
+    }
+    __syncthreads();
+    if (lane == 0) sh.scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long t = lane < CTA_WARPS ? sh.scratch[lane] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, t, o);
+            t = MAXIMUM ? (other > t ? other : t) : t + other;
+        }
+        if (lane == 0) sh.slot = t;
+    }
+    cluster_barrier();
+    unsigned long long all = 0ull;
+    for (unsigned r = 0; r < CLUSTER; ++r) {
+        const unsigned long long part = peer_load_u64(&sh.slot, r);
+        all = MAXIMUM ? (part > all ? part : all) : all + part;
+    }
+    cluster_barrier();                              // nobody overwrites its slot while a peer still reads it
+    return all;
+}
+
+// Calls f(logit, index, mass) for every element of the row this CTA owns: groups of four logits
+// (one 16-byte load, several loads in flight), dealt round robin to the CTAs of the cluster.
+template <bool WITH_MASS, typename F>
+__device__ __forceinline__ void sweep(const float* __restrict__ row, const unsigned long long* __restrict__ mass,
+                                      int V, unsigned rank, F f) {
+    const bool vectorised = (reinterpret_cast<uintptr_t>(row) & 15) == 0 &&
+                            (!WITH_MASS || (reinterpret_cast<uintptr_t>(mass) & 15) == 0);
+    const int quads = vectorised ? V >> 2 : 0;
+#pragma unroll 2
+    for (int qd = rank * CTA_THREADS + threadIdx.x; qd < quads; qd += CLUSTER * CTA_THREADS) {
+        const float4 l4 = reinterpret_cast<const float4*>(row)[qd];
+        ulonglong2 ma = make_ulonglong2(0ull, 0ull), mb = ma;
+        if (WITH_MASS) {
+            ma = reinterpret_cast<const ulonglong2*>(mass)[2 * qd];
+            mb = reinterpret_cast<const ulonglong2*>(mass)[2 * qd + 1];
+        }
+        f(l4.x, 4 * qd, ma.x);
+        f(l4.y, 4 * qd + 1, ma.y);
+        f(l4.z, 4 * qd + 2, mb.x);
+        f(l4.w, 4 * qd + 3, mb.y);
+    }
+    for (int i = 4 * quads + rank * CTA_THREADS + threadIdx.x; i < V; i += CLUSTER * CTA_THREADS)
+        f(row[i], i, WITH_MASS ? mass[i] : 0ull);
+}
+
+// The largest key x among the row's members with weight{members > x} < target <= weight{members >= x}.
+// Members: keys >= low_cut whose mass is >= floor_mass; COUNT: every member weighs 1 (mass unused).
+// 1 <= target <= the members' weight.  Every CTA of the cluster returns the same key.
+template <bool COUNT>
+__device__ unsigned long long descend(const float* __restrict__ row, int V, const unsigned long long* __restrict__ mass,
+                                      unsigned long long low_cut, unsigned long long floor_mass,
+                                      unsigned long long target, unsigned rank, Shared& sh) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        sh.pick[0] = 0ull;
+        sh.pick[1] = target;
+    }
+    unsigned long long* mine = sh.per_warp[threadIdx.x >> 5];
+    for (int pass = 0; pass < 8; ++pass) {
+        const int shift = 56 - 8 * pass;
+        for (int i = threadIdx.x; i < CTA_WARPS * 256; i += CTA_THREADS) (&sh.per_warp[0][0])[i] = 0ull;
+        __syncthreads();
+        const unsigned long long prefix = sh.pick[0];
+        const unsigned long long mask = pass == 0 ? 0ull : (~0ull << (shift + 8));
+        // in the first pass nearly all keys share two or three digits (the sign and the top of the
+        // exponent): a thread keeps four digits' sums in registers and touches the histogram only
+        // when a fifth digit turns up
+        int held[4] = {-1, -1, -1, -1};
+        unsigned long long sums[4] = {0ull, 0ull, 0ull, 0ull};
+        int victim = 0;
+        sweep<!COUNT>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
+            const unsigned long long key = make_key(logit, i);
+            if ((key & mask) != prefix || key < low_cut) return;
+            if (COUNT) m = 1ull;
+            else if (m < floor_mass) return;
+            const int digit = (int)((key >> shift) & 0xffull);
+            bool hit = false;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (held[c] == digit) {
+                    sums[c] += m;
+                    hit = true;
+                }
+            if (!hit) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (c == victim) {
+                        if (held[c] >= 0) atomicAdd(&mine[held[c]], sums[c]);
+                        held[c] = digit;
+                        sums[c] = m;
+                    }
+                victim = (victim + 1) & 3;
+            }
+        });
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (held[c] >= 0) atomicAdd(&mine[held[c]], sums[c]);
+        __syncthreads();
+        for (int d = threadIdx.x; d < 256; d += CTA_THREADS) {
+            unsigned long long all = 0ull;
+#pragma unroll
+            for (int w = 0; w < CTA_WARPS; ++w) all += sh.per_warp[w][d];
+            sh.total[d] = all;
+        }
+        cluster_barrier();
+        for (int d = threadIdx.x; d < 256; d += CTA_THREADS) {
+            unsigned long long all = 0ull;
+            for (unsigned r = 0; r < CLUSTER; ++r) all += peer_load_u64(&sh.total[d], r);
+            sh.all[d] = all;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            // the digit at which the running weight, from digit 255 down, reaches what is left of
+            // the target: a lane adds up eight digits, a scan over the lanes finds the lane, the
+            // lane its digit
+            const int lane = threadIdx.x;
+            const unsigned long long left = sh.pick[1];
+            unsigned long long eight = 0ull;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) eight += sh.all[255 - 8 * lane - j];
+            unsigned long long upto = eight;               // inclusive, lanes 0..lane
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long other = __shfl_up_sync(0xffffffffu, upto, o);
+                if (lane >= o) upto += other;
+            }
+            const unsigned crossed = __ballot_sync(0xffffffffu, upto >= left);
+            const int owner = crossed ? __ffs(crossed) - 1 : 31;
+            if (lane == owner) {
+                unsigned long long rest = left - (upto - eight);
+                int digit = 255 - 8 * lane;
+                for (int j = 0; j < 7; ++j, --digit) {
+                    if (sh.all[digit] >= rest) break;
+                    rest -= sh.all[digit];
+                }
+                sh.pick[0] = prefix | ((unsigned long long)digit << shift);
+                sh.pick[1] = rest;
+            }
+        }
+        cluster_barrier();                          // peers have read this CTA's histogram; pick is set
+    }
+    return sh.pick[0];
+}
+
+// Grid (CLUSTER, R), cluster (CLUSTER, 1, 1).  mass_all: [R][Vpad] 64-bit words of scratch, needed
+// by rows with more than SMALL_K candidates (null: such rows are refused on the host).
+__global__ void __launch_bounds__(CTA_THREADS)
+sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams* __restrict__ params,
+              const double* __restrict__ uniform, const int* __restrict__ recent, int recent_stride,
+              unsigned long long* __restrict__ mass_all, int* __restrict__ out) {
     fwb::pdl_entry();
-    __shared__ unsigned long long keys[SMALL_K];
-    __shared__ unsigned long long scratch[33];
-    __shared__ double probs[SMALL_K];
-    __shared__ int hist[256];
-    __shared__ unsigned long long prefix_s;
-    __shared__ int remaining_s, count_s;
-    const int r = blockIdx.x;
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    Shared& sh = *reinterpret_cast<Shared*>(shared_raw);
+    unsigned long long* keys = sh.keys;
+    double* probs = sh.probs;
+    const unsigned rank = cluster_cta_rank();
+    const int r = blockIdx.y;
     const RowParams prm = params[r];
     const float* row = logits + (size_t)r * V;
     const bool penalize = prm.n_recent > 0 && (prm.repetition_penalty != 1.0f ||
                           prm.presence_penalty != 0.0f || prm.frequency_penalty != 0.0f);
-    int k = prm.top_k > 0 ? (prm.top_k < V ? prm.top_k : V) : V;
-    if ((!(prm.temperature > 0.0f) && !penalize) || k == 1) {
-        unsigned long long best = 0ull;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const unsigned long long key = make_key(row[i], i);
-            best = key > best ? key : best;
-        }
-        best = block_max_key(best, scratch);
-        if (threadIdx.x == 0) out[r] = key_id(best);
-        return;
-    }
-    if (k > SMALL_K) {
-        if (threadIdx.x == 0) out[r] = -1;
-        return;
-    }
-    // radix select: the k-th largest key, 8 bits at a time from the top
-    if (threadIdx.x == 0) {
-        prefix_s = 0ull;
-        remaining_s = k;
-    }
-    for (int pass = 0; pass < 8; ++pass) {
-        const int shift = 56 - 8 * pass;
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-        __syncthreads();
-        const unsigned long long prefix = prefix_s;
-        const unsigned long long mask = pass == 0 ? 0ull : (~0ull << (shift + 8));
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const unsigned long long key = make_key(row[i], i);
-            if ((key & mask) == prefix) atomicAdd(&hist[(int)((key >> shift) & 0xffull)], 1);
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int remaining = remaining_s;
-            int digit = 255;
-            for (; digit > 0; --digit) {
-                if (hist[digit] >= remaining) break;
-                remaining -= hist[digit];
-            }
-            prefix_s = prefix | ((unsigned long long)digit << shift);
-            remaining_s = remaining;
-        }
-        __syncthreads();
-    }
-    const unsigned long long kth = prefix_s;     // keys are distinct: exactly k keys are >= kth
-    int padded = 1;
-    while (padded < k) padded <<= 1;
-    for (int i = threadIdx.x; i < padded; i += blockDim.x) keys[i] = 0ull;
-    if (threadIdx.x == 0) count_s = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const unsigned long long key = make_key(row[i], i);
-        if (key >= kth) {
-            const int at = atomicAdd(&count_s, 1);
-            if (at < SMALL_K) keys[at] = key;
-        }
-    }
-    __syncthreads();
-    bitonic_sort_desc(keys, padded);
-    if (penalize) {
-        const int* rec = recent + (size_t)r * recent_stride;
-        for (int i = threadIdx.x; i < k; i += blockDim.x) {
-            const int id = key_id(keys[i]);
-            int occurrences = 0;
-            for (int j = 0; j < prm.n_recent; ++j) occurrences += rec[j] == id;
-            if (occurrences) {
-                float logit = key_logit(keys[i]);
-                if (prm.repetition_penalty != 1.0f)
-                    logit = logit > 0.0f ? logit / prm.repetition_penalty
-                                         : logit * prm.repetition_penalty;
-                logit -= prm.presence_penalty;
-                logit -= prm.frequency_penalty * (float)occurrences;
-                keys[i] = make_key(logit, id);
-            }
-        }
-        __syncthreads();
-        bitonic_sort_desc(keys, padded);
-    }
-    if (threadIdx.x == 0) out[r] = draw_sorted(keys, k, prm, uniform[r], probs);
-}
-
-// Rows that the small kernel left (out[r] == -1): sort the whole row in global scratch.
-// keys: [R][Vpad] (Vpad = power of two >= V), probs: [R][Vpad] doubles.
-__global__ void __launch_bounds__(THREADS)
-sample_large_kernel(const float* __restrict__ logits, int V, int Vpad,
-                    const RowParams* __restrict__ params, const double* __restrict__ uniform,
-                    unsigned long long* __restrict__ keys_all, double* __restrict__ probs_all,
-                    int* __restrict__ out) {
-    fwb::pdl_entry();
-    const int r = blockIdx.x;
-    if (out[r] != -1) return;
-    const RowParams prm = params[r];
-    const float* row = logits + (size_t)r * V;
-    unsigned long long* keys = keys_all + (size_t)r * Vpad;
-    for (int i = threadIdx.x; i < Vpad; i += blockDim.x) keys[i] = i < V ? make_key(row[i], i) : 0ull;
-    bitonic_sort_desc(keys, Vpad);
     const int k = prm.top_k > 0 ? (prm.top_k < V ? prm.top_k : V) : V;
-    if (threadIdx.x == 0) out[r] = draw_sorted(keys, k, prm, uniform[r], probs_all + (size_t)r * Vpad);
+
+    unsigned long long best = 0ull;
+    sweep<false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+        const unsigned long long key = make_key(logit, i);
+        best = key > best ? key : best;
+    });
+    best = cluster_reduce<true>(best, sh);
+    if ((!(prm.temperature > 0.0f) && !penalize) || k == 1) {
+        if (rank == 0 && threadIdx.x == 0) out[r] = key_id(best);
+        return;
+    }
+
+    if (k <= SMALL_K) {
+        // the candidates are the k largest keys: find the k-th, gather them in rank 0, sort, draw
+        const unsigned long long kth = descend<true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k, rank, sh);
+        if (rank == 0) {
+            for (int i = threadIdx.x; i < SMALL_K; i += CTA_THREADS) keys[i] = 0ull;
+            if (threadIdx.x == 0) sh.count = 0u;
+        }
+        cluster_barrier();
+        const unsigned keys_at_0 = peer_address(keys, 0), count_at_0 = peer_address(&sh.count, 0);
+        sweep<false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+            const unsigned long long key = make_key(logit, i);
+            if (key < kth) return;                  // keys are distinct: exactly k keys pass
+            unsigned at;
+            asm volatile("atom.shared::cluster.add.u32 %0, [%1], 1;" : "=r"(at) : "r"(count_at_0) : "memory");
+            if (at < (unsigned)SMALL_K)
+                asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(keys_at_0 + at * 8u), "l"(key) : "memory");
+        });
+        cluster_barrier();
+        if (rank != 0) return;
+        int padded = 1;
+        while (padded < k) padded <<= 1;
+        bitonic_sort_desc(keys, padded);
+        if (penalize) {
+            const int* rec = recent + (size_t)r * recent_stride;
+            for (int i = threadIdx.x; i < k; i += CTA_THREADS) {
+                const int id = key_id(keys[i]);
+                int occurrences = 0;
+                for (int j = 0; j < prm.n_recent; ++j) occurrences += rec[j] == id;
+                if (occurrences) {
+                    float logit = key_logit(keys[i]);
+                    if (prm.repetition_penalty != 1.0f)
+                        logit = logit > 0.0f ? logit / prm.repetition_penalty
+                                             : logit * prm.repetition_penalty;
+                    logit -= prm.presence_penalty;
+                    logit -= prm.frequency_penalty * (float)occurrences;
+                    keys[i] = make_key(logit, id);
+                }
+            }
+            __syncthreads();
+            bitonic_sort_desc(keys, padded);
+        }
+        if (threadIdx.x == 0) out[r] = draw_sorted(keys, k, prm, uniform[r], probs);
+        return;
+    }
+
+    // more than SMALL_K candidates (the whole vocabulary among them): no sort at all
+    unsigned long long* mass = mass_all + (size_t)r * Vpad;
+    unsigned long long low_cut = 0ull;
+    if (k < V) low_cut = descend<true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k, rank, sh);
+    const double t = (double)prm.temperature;
+    const double maximum = (double)key_logit(best) / t;
+    unsigned long long mine = 0ull;
+    sweep<false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+        unsigned long long m = 0ull;
+        if (make_key(logit, i) >= low_cut) {
+            const double scaled = (double)logit / t;
+            const double p = isfinite(scaled) ? exp(scaled - maximum) : 0.0;
+            m = (unsigned long long)llrint(p * MASS_ONE);
+        }
+        mass[i] = m;                                // read again only by this CTA, in the same order
+        mine += m;
+    });
+    const unsigned long long total = cluster_reduce<false>(mine, sh);     // >= 2^40: the first candidate weighs 1
+    if (prm.top_p < 1.0f) {
+        // the shortest prefix whose mass reaches top_p of the total
+        unsigned long long target = (unsigned long long)ceil((double)prm.top_p * (double)total);
+        target = target < 1ull ? 1ull : (target > total ? total : target);
+        const unsigned long long cut = descend<false>(row, V, mass, low_cut, 0ull, target, rank, sh);
+        low_cut = cut > low_cut ? cut : low_cut;
+    }
+    // min_p: of that prefix, the candidates that weigh at least min_p of the first
+    unsigned long long floor_mass = 0ull;
+    if (prm.min_p > 0.0f) floor_mass = (unsigned long long)ceil((double)prm.min_p * MASS_ONE);
+    unsigned long long kept_mine = 0ull;
+    sweep<true>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
+        if (make_key(logit, i) >= low_cut && m >= floor_mass) kept_mine += m;
+    });
+    const unsigned long long kept = cluster_reduce<false>(kept_mine, sh);
+    unsigned long long target = (unsigned long long)ceil(uniform[r] * (double)kept);
+    target = target < 1ull ? 1ull : (target > kept ? kept : target);
+    const unsigned long long drawn = descend<false>(row, V, mass, low_cut, floor_mass, target, rank, sh);
+    if (rank == 0 && threadIdx.x == 0) out[r] = key_id(drawn);
 }
 
 }  // namespace
@@ -333,21 +551,40 @@ FWB_API int fwb_argmax(const float* logits, int R, int V, int* out, void* partia
 // params: [R] records of 8 x 4 bytes {temperature f32, top_k i32, top_p f32, min_p f32,
 // repetition f32, presence f32, frequency f32, n_recent i32}; uniform: [R] doubles in [0,1);
 // recent: [R][recent_stride] token ids (only the first n_recent of a row are read).
-// keys_scratch / probs_scratch: [R][Vpad] each, needed only if some row keeps more than
-// 1024 candidates (pass null to refuse such rows).
+// keys_scratch: [R][Vpad] 64-bit words, needed only if some row keeps more than 1024 candidates
+// (`need_large`); probs_scratch is not used any more.
 FWB_API int fwb_sample(const float* logits, int R, int V, const void* params, const double* uniform,
                        const int* recent, int recent_stride, int* out, void* keys_scratch,
                        double* probs_scratch, int Vpad, int need_large, cudaStream_t stream) {
+    (void)probs_scratch;
     if (R <= 0) return FWB_OK;
     if (!logits || !out || !params || !uniform || V <= 0) return FWB_BAD_ARGUMENT;
     if (recent_stride > MAX_RECENT || (recent_stride > 0 && !recent)) return FWB_BAD_ARGUMENT;
-    fwb::pdl(sample_small_kernel, R, THREADS, 0, stream)(logits, V, (const RowParams*)params, uniform,
-                                                   recent, recent_stride, out);
-    int status = fwb_launch_status();
-    if (status != FWB_OK || !need_large) return status;
-    if (!keys_scratch || !probs_scratch || Vpad < V || (Vpad & (Vpad - 1))) return FWB_BAD_ARGUMENT;
-    fwb::pdl(sample_large_kernel, R, THREADS, 0, stream)(logits, V, Vpad, (const RowParams*)params, uniform,
-                                                   (unsigned long long*)keys_scratch, probs_scratch,
-                                                   out);
-    return fwb_launch_status();
+    if (need_large && (!keys_scratch || Vpad < V)) return FWB_BAD_ARGUMENT;
+    if (V > (1 << 23)) return FWB_TOO_LARGE;      // the fixed-point masses of a row must fit 64 bits
+    if (R > 65535) return FWB_TOO_LARGE;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)sizeof(Shared));
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(CLUSTER, R);
+    config.blockDim = dim3(CTA_THREADS);
+    config.dynamicSmemBytes = sizeof(Shared);
+    config.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = fwb::pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, sample_kernel, logits, V, Vpad, (const RowParams*)params, uniform,
+                                       recent, recent_stride, (unsigned long long*)keys_scratch, out);
+    return e == cudaSuccess ? fwb_launch_status() : (int)e;
 }

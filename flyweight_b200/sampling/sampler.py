@@ -86,8 +86,7 @@ def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Se
         vpad = 1
         while vpad < V:
             vpad <<= 1
-        keys = torch.empty((R, vpad), dtype=torch.int64, device=device)
-        probs = torch.empty((R, vpad), dtype=torch.float64, device=device)
+        keys = torch.empty((R, vpad), dtype=torch.int64, device=device)     # fixed-point masses
     lib.call("fwb_sample", ptr(logits), R, V, ptr(params), ptr(uni), ptr(recent_dev), stride,
              ptr(out), ptr(keys), ptr(probs), vpad, 1 if need_large else 0, stream(),
              launches=2 if need_large else 1)
