@@ -3,14 +3,15 @@
 One launch for a batch of greedy rows (argmax, ties to the lowest id -- the order
 flyweight's fused argmax gives, native/include/flyweight_v2_qwen_kernels.hpp:2392-2398);
 one launch for rows that sample (top-k, penalties, temperature, top-p, min-p, draw: the
-order of native/src/v2_runtime.cpp:29331-29744), plus a second one only if some row keeps
-more than 1024 candidates.
+order of native/src/v2_runtime.cpp:29331-29744); rows that keep more than 1024 candidates
+(the whole vocabulary among them) need a scratch word per logit and are not sorted at all.
 """
 from __future__ import annotations
 
 import struct
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..kernels import lib
@@ -32,6 +33,28 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 
 
 _scratch = {}
+_staging = {}
+
+
+def _stage(values: "np.ndarray", device) -> torch.Tensor:
+    """Bytes to the device through a kept ring of pinned buffers (no pageable copy, which would
+    make the host wait for the stream)."""
+    key = str(device)
+    ring = _staging.setdefault(key, {"buffers": [None] * 4, "events": [None] * 4, "turn": 0})
+    turn = ring["turn"]
+    ring["turn"] = (turn + 1) % 4
+    if ring["events"][turn] is not None:
+        ring["events"][turn].synchronize()
+    buffer = ring["buffers"][turn]
+    if buffer is None or buffer.numel() < values.size:
+        buffer = ring["buffers"][turn] = torch.empty(max(4096, 2 * values.size), dtype=torch.uint8).pin_memory()
+    host = buffer[:values.size]
+    host.numpy()[:] = values
+    dev = host.to(device, non_blocking=True)
+    if ring["events"][turn] is None:
+        ring["events"][turn] = torch.cuda.Event()
+    ring["events"][turn].record()
+    return dev
 
 
 def _argmax_scratch(device, n_partial: int, n_rows: int):
@@ -73,12 +96,17 @@ def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Se
                             cfg.repetition_penalty, cfg.presence_penalty, cfg.frequency_penalty,
                             len(recent))
     device = logits.device
-    params = torch.frombuffer(blob, dtype=torch.uint8).to(device)
-    uni = torch.tensor(list(uniforms), dtype=torch.float64).to(device)
-    recent_dev = None
+    # one upload for the three small arrays: records (32 bytes a row), uniform numbers, recent tokens
+    blob += np.asarray(uniforms, dtype=np.float64).tobytes()
     if stride:
-        padded = [row + [-1] * (stride - len(row)) for row in rows]
-        recent_dev = torch.tensor(padded, dtype=torch.int32).to(device)
+        padded = np.full((R, stride), -1, dtype=np.int32)
+        for r, row in enumerate(rows):
+            padded[r, :len(row)] = row
+        blob += padded.tobytes()
+    staged = _stage(np.frombuffer(blob, dtype=np.uint8), device)
+    params = staged[:32 * R]
+    uni = staged[32 * R:40 * R].view(torch.float64)
+    recent_dev = staged[40 * R:].view(torch.int32) if stride else None
     out = torch.empty((R,), dtype=torch.int32, device=device)
     keys = probs = None
     vpad = 0
@@ -88,6 +116,5 @@ def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Se
             vpad <<= 1
         keys = torch.empty((R, vpad), dtype=torch.int64, device=device)     # fixed-point masses
     lib.call("fwb_sample", ptr(logits), R, V, ptr(params), ptr(uni), ptr(recent_dev), stride,
-             ptr(out), ptr(keys), ptr(probs), vpad, 1 if need_large else 0, stream(),
-             launches=2 if need_large else 1)
+             ptr(out), ptr(keys), ptr(probs), vpad, 1 if need_large else 0, stream())
     return out
