@@ -467,7 +467,9 @@ def test_sampling_equals_the_plain_sampler_draw_for_draw(V):
                 dict(temperature=1.0, top_k=0, top_p=0.9, min_p=0.01),
                 dict(temperature=0.0, top_k=20, top_p=0.95, min_p=0.0),
                 dict(temperature=2.0, top_k=1, top_p=1.0, min_p=0.0),
-                dict(temperature=1.0, top_k=300, top_p=1.0, min_p=0.5)]
+                dict(temperature=1.0, top_k=300, top_p=1.0, min_p=0.5),
+                dict(temperature=1.2, top_k=3000, top_p=0.8, min_p=0.0),     # more candidates than are ever sorted
+                dict(temperature=0.7, top_k=0, top_p=1.0, min_p=0.0)]        # the whole vocabulary, no cut at all
     for trial in range(6):
         logits = torch.randn(len(settings), V, generator=g) * 3
         logits[:, 11] = logits[:, 13]                          # ties inside the candidates
