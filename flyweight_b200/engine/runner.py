@@ -17,6 +17,8 @@ from typing import Hashable, List, Sequence, Tuple
 
 import torch
 
+from ..kernels import lib as kernel_lib
+
 from ..cache.manager import PAGE_SIZE, CacheManager, OutOfPages, OutOfSlots
 from ..kernels.lib import require_cuda
 from .batch import Segment, StepBatch, StepContext
@@ -118,6 +120,8 @@ class ModelRunner(StepPlanner):
         self.model = model
         self.precision = model.precision
         self.device = model.device
+        if torch.device(self.device).type == "cuda":
+            kernel_lib.use_device(self.device)
         if int(max_model_len) > model.spec.max_positions:
             raise StepError(f"max_model_len {max_model_len} exceeds the model's "
                             f"{model.spec.max_positions} positions")

@@ -61,7 +61,32 @@ def ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device = None
+
+
+def _device_index() -> int:
+    """The device whose current stream takes the launches: the one a runner was made for
+    (``use_device``), else the process's current device, looked up once."""
+    global _device
+    if _device is None:
+        _device = torch.cuda.current_device()
+    return _device
+
+
+def use_device(device) -> None:
+    """Launch on ``device``'s current stream from now on (a runner says so for its model's device)."""
+    global _device
+    index = torch.device(device).index
+    _device = torch.cuda.current_device() if index is None else index
+
+
 def stream() -> ctypes.c_void_p:
+    """The current CUDA stream of the engine's device (every launch goes there; CUDA-graph
+    capture switches it).  The raw query costs a fraction of a microsecond; the public one,
+    with its device bookkeeping, cost more than the launch itself."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(_device_index()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
