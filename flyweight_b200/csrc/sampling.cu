@@ -165,20 +165,24 @@ struct RowParams {
     int n_recent;
 };
 
-// The draw over `n` sorted candidates (keys descending).  One thread; double arithmetic.
-// `probs` is scratch for n doubles.
-__device__ int draw_sorted(const unsigned long long* keys, int n, const RowParams& prm, double u,
-                           double* probs) {
-    if (!(prm.temperature > 0.0f) || n == 1) return key_id(keys[0]);
+// The draw over `n` sorted candidates (keys descending), double arithmetic.  The exponentials
+// are formed by the whole block (`fill_probs`, then a barrier), the running sums by one thread
+// in candidate order, which is what makes a draw reproducible to the last bit.
+__device__ void fill_probs(const unsigned long long* keys, int n, const RowParams& prm, double* probs) {
+    if (!(prm.temperature > 0.0f)) return;
     const double t = (double)prm.temperature;
     const double maximum = (double)key_logit(keys[0]) / t;
-    double total = 0.0;
-    for (int i = 0; i < n; ++i) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const double scaled = (double)key_logit(keys[i]) / t;
-        const double p = isfinite(scaled) ? exp(scaled - maximum) : 0.0;
-        probs[i] = p;
-        total += p;
+        probs[i] = isfinite(scaled) ? exp(scaled - maximum) : 0.0;
     }
+}
+
+__device__ int draw_sorted(const unsigned long long* keys, int n, const RowParams& prm, double u,
+                           const double* probs) {
+    if (!(prm.temperature > 0.0f) || n == 1) return key_id(keys[0]);
+    double total = 0.0;
+    for (int i = 0; i < n; ++i) total += probs[i];
     if (!(total > 0.0) || !isfinite(total)) return key_id(keys[0]);
     int keep = n;
     if (prm.top_p < 1.0f) {
@@ -245,17 +249,21 @@ __device__ __forceinline__ unsigned peer_address(const void* local, unsigned ran
 }
 __device__ __forceinline__ unsigned long long peer_load_u64(const void* local, unsigned rank) {
     unsigned long long v;
-    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(peer_address(local, rank)) : "memory");
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(peer_address(local, rank)));
     return v;
 }
 
 // What a CTA keeps in shared memory for the walks and the reductions.
 struct Shared {
-    unsigned long long total[256];                 // this CTA's histogram of the pass (peers read it)
+    unsigned long long total[2][256];              // this CTA's histogram of the pass (peers read it); passes alternate
     unsigned long long per_warp[CTA_WARPS][256];   // one histogram per warp, summed into `total`
     unsigned long long all[256];                   // the cluster's histogram
-    unsigned long long slot;                       // this CTA's share of a cluster-wide sum or maximum
+    unsigned long long slot[2];                    // this CTA's share of a cluster-wide sum or maximum; calls alternate
+    unsigned turn;                                 // which of the two a reduction writes next
+    unsigned members[256];                         // pass 3 only: how many members fell into a digit ...
+    unsigned long long largest[256];               // ... and the largest key among them
     unsigned long long pick[2];                    // digits chosen so far, what is left of the target
+    unsigned settled;                              // pass 3 found the one key with the chosen logit
     unsigned long long scratch[33];
     unsigned long long keys[SMALL_K];              // the candidates of a top-k row (rank 0 sorts and draws)
     double probs[SMALL_K];
@@ -281,15 +289,21 @@ __device__ unsigned long long cluster_reduce(unsigned long long v, Shared& sh) {
             const unsigned long long other = __shfl_xor_sync(0xffffffffu, t, o);
             t = MAXIMUM ? (other > t ? other : t) : t + other;
         }
-        if (lane == 0) sh.slot = t;
+        if (lane == 0) sh.slot[sh.turn & 1] = t;
     }
+    // One barrier is enough: this slot is written again two reductions from now, and before that
+    // every CTA passes the barrier of the next reduction, which a peer reaches only after this read.
     cluster_barrier();
+    const unsigned which = sh.turn & 1;
+    unsigned long long part[CLUSTER];
+#pragma unroll
+    for (unsigned r = 0; r < CLUSTER; ++r) part[r] = peer_load_u64(&sh.slot[which], r);
     unsigned long long all = 0ull;
-    for (unsigned r = 0; r < CLUSTER; ++r) {
-        const unsigned long long part = peer_load_u64(&sh.slot, r);
-        all = MAXIMUM ? (part > all ? part : all) : all + part;
-    }
-    cluster_barrier();                              // nobody overwrites its slot while a peer still reads it
+#pragma unroll
+    for (unsigned r = 0; r < CLUSTER; ++r) all = MAXIMUM ? (part[r] > all ? part[r] : all) : all + part[r];
+    __syncthreads();
+    if (threadIdx.x == 0) sh.turn = which + 1;
+    __syncthreads();
     return all;
 }
 
@@ -334,6 +348,11 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
     for (int pass = 0; pass < 8; ++pass) {
         const int shift = 56 - 8 * pass;
         for (int i = threadIdx.x; i < CTA_WARPS * 256; i += CTA_THREADS) (&sh.per_warp[0][0])[i] = 0ull;
+        if (pass == 3)
+            for (int i = threadIdx.x; i < 256; i += CTA_THREADS) {
+                sh.members[i] = 0u;
+                sh.largest[i] = 0ull;
+            }
         __syncthreads();
         const unsigned long long prefix = sh.pick[0];
         const unsigned long long mask = pass == 0 ? 0ull : (~0ull << (shift + 8));
@@ -349,6 +368,10 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
             if (COUNT) m = 1ull;
             else if (m < floor_mass) return;
             const int digit = (int)((key >> shift) & 0xffull);
+            if (pass == 3) {                         // few keys share 24 bits of a logit: no contention
+                atomicAdd(&sh.members[digit], 1u);
+                atomicMax(&sh.largest[digit], key);
+            }
             bool hit = false;
 #pragma unroll
             for (int c = 0; c < 4; ++c)
@@ -375,12 +398,19 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
             unsigned long long all = 0ull;
 #pragma unroll
             for (int w = 0; w < CTA_WARPS; ++w) all += sh.per_warp[w][d];
-            sh.total[d] = all;
+            sh.total[pass & 1][d] = all;
         }
+        // one barrier a pass: the histogram of pass p is written again in pass p+2, after the
+        // barrier of pass p+1, which a peer reaches only when it has read pass p's
         cluster_barrier();
         for (int d = threadIdx.x; d < 256; d += CTA_THREADS) {
+            // all peers' words are requested before the first is used: one round trip, not eight
+            unsigned long long part[CLUSTER];
+#pragma unroll
+            for (unsigned r = 0; r < CLUSTER; ++r) part[r] = peer_load_u64(&sh.total[pass & 1][d], r);
             unsigned long long all = 0ull;
-            for (unsigned r = 0; r < CLUSTER; ++r) all += peer_load_u64(&sh.total[d], r);
+#pragma unroll
+            for (unsigned r = 0; r < CLUSTER; ++r) all += part[r];
             sh.all[d] = all;
         }
         __syncthreads();
@@ -410,10 +440,31 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
                 }
                 sh.pick[0] = prefix | ((unsigned long long)digit << shift);
                 sh.pick[1] = rest;
+                sh.settled = 0u;
+                if (pass == 3) {
+                    // the logit is settled.  If one key has it (nearly always), that is the answer
+                    // and the four passes over the id bits are not needed.
+                    unsigned count = 0u;
+                    unsigned long long top = 0ull;
+                    for (unsigned r = 0; r < CLUSTER; ++r) {
+                        unsigned c;
+                        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(c) : "r"(peer_address(&sh.members[digit], r)));
+                        const unsigned long long k = peer_load_u64(&sh.largest[digit], r);
+                        count += c;
+                        top = k > top ? k : top;
+                    }
+                    if (count == 1u) {
+                        sh.pick[0] = top;
+                        sh.settled = 1u;
+                    }
+                }
             }
         }
-        cluster_barrier();                          // peers have read this CTA's histogram; pick is set
+        __syncthreads();                            // pick is set
+        if (pass == 3 && sh.settled) break;
     }
+    // the walk's last histogram may still be read by a peer: the next walk or reduction of this
+    // kernel starts with writes to other words and passes a cluster barrier before it returns here
     return sh.pick[0];
 }
 
@@ -430,6 +481,8 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
     double* probs = sh.probs;
     const unsigned rank = cluster_cta_rank();
     const int r = blockIdx.y;
+    if (threadIdx.x == 0) sh.turn = 0u;
+    __syncthreads();
     const RowParams prm = params[r];
     const float* row = logits + (size_t)r * V;
     const bool penalize = prm.n_recent > 0 && (prm.repetition_penalty != 1.0f ||
@@ -444,6 +497,7 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
     best = cluster_reduce<true>(best, sh);
     if ((!(prm.temperature > 0.0f) && !penalize) || k == 1) {
         if (rank == 0 && threadIdx.x == 0) out[r] = key_id(best);
+        cluster_barrier();                          // no CTA leaves while a peer still reads its shared memory
         return;
     }
 
@@ -488,6 +542,9 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
             __syncthreads();
             bitonic_sort_desc(keys, padded);
         }
+        __syncthreads();
+        fill_probs(keys, k, prm, probs);
+        __syncthreads();
         if (threadIdx.x == 0) out[r] = draw_sorted(keys, k, prm, uniform[r], probs);
         return;
     }
@@ -529,6 +586,7 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
     target = target < 1ull ? 1ull : (target > kept ? kept : target);
     const unsigned long long drawn = descend<false>(row, V, mass, low_cut, floor_mass, target, rank, sh);
     if (rank == 0 && threadIdx.x == 0) out[r] = key_id(drawn);
+    cluster_barrier();                              // no CTA leaves while a peer still reads its shared memory
 }
 
 }  // namespace
