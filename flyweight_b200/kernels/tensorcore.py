@@ -132,6 +132,12 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm: input has {K} columns, weight has {w.shape[1]}")
+    if (_use_pairs and M > 128 and addend is None and out is None and splits is None and not stages
+            and not tile_tokens and wide == -1 and N >= 256):
+        # prompt-sized: CTA pairs (cta_group::2); two feature blocks per pair when single blocks
+        # would make more CTAs than the GPU holds at once (measured at 2,048 tokens on B200)
+        pairs = -(-N // 256) * -(-M // 256)
+        return gemm_pair(x, w, out_dtype, wide=pairs > SM_COUNT // 2)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     else:
@@ -141,12 +147,6 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
         epilogue = EPI_ADD_F32
     else:
         epilogue = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
-    if (_use_pairs and M > 128 and addend is None and splits is None and not stages
-            and not tile_tokens and wide == -1 and N >= 256):
-        # prompt-sized: CTA pairs (cta_group::2); two feature blocks per pair when single blocks
-        # would make more CTAs than the GPU holds at once (measured at 2,048 tokens on B200)
-        pairs = -(-N // 256) * -(-M // 256)
-        return gemm_pair(x, w, out_dtype, wide=pairs > SM_COUNT // 2)
     if M <= 64 and (N, K, 1) in TUNED and _forced_splits is None:
         tuned = TUNED[(N, K, 1)]
         splits = splits or tuned[0] or None
