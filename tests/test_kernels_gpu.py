@@ -607,6 +607,23 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
     assert tensorcore.status() == 0
 
 
+def test_tcgen05_swiglu_in_two_launches_cut_at_a_whole_wave():
+    """2,048 tokens x 8,192 features make 3.46 waves of CTAs: the product runs as 55 feature tiles
+    with 256-token tiles and 9 with 128-token tiles.  Same bits as one launch, right against fp64."""
+    from flyweight_b200.kernels import tensorcore
+    M, F, K = 2048, 8192, 64
+    assert tensorcore._wave_cut(M, F) == 55
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    two = tensorcore.swiglu_gate_up(dev(x), dev(w))
+    one = tensorcore.swiglu_gate_up(dev(x), dev(w), tile_tokens=256)
+    assert tensorcore.status() == 0
+    assert torch.equal(two, one)
+    gate, up = x.double() @ w[:F].double().T, x.double() @ w[F:].double().T
+    close(two, gate * torch.sigmoid(gate) * up, 2.0 ** -6, "swiglu in two launches")
+
+
 def test_tcgen05_refuses_what_tma_cannot_address():
     from flyweight_b200.kernels import KernelError, tensorcore as tc
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K not a multiple of 8
