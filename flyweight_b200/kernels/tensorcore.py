@@ -320,9 +320,37 @@ def gemm_pair(x, w, out_dtype, wide=False) -> torch.Tensor:
     if w.shape[1] != K:
         raise KernelError(f"gemm: input has {K} columns, weight has {w.shape[1]}")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w), ptr(out), M, N, K, N, N,
-             EPI_F32 if out_dtype == torch.float32 else EPI_BF16, 0, 1 if wide else 0, stream())
+    epilogue = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
+    cut = _pair_wave_cut(M, N) if wide else 0
+    if cut:
+        # the wide blocks of the whole rounds, then the rest as narrow pairs that fit one round
+        first = cut * 512
+        lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w), ptr(out), M, first, K, N, N, epilogue, 0, 1, stream())
+        lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w[first:]), ptr(out[:, first:]), M, N - first, K,
+                 N - first, N, epilogue, 0, 0, stream())
+        return out
+    lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w), ptr(out), M, N, K, N, N, epilogue, 0,
+             1 if wide else 0, stream())
     return out
+
+
+def _pair_wave_cut(M: int, N: int) -> int:
+    """For the wide CTA-pair form (512 features a pair): how many 512-feature blocks the first of
+    two launches takes (0: one launch).  74 pairs run at a time; when the last round would be less
+    than three quarters full and what is left fits one round of one-block pairs (half the length),
+    cutting there saves most of half a round (in_proj at 2,048 tokens: 96 pairs = 1.3 rounds)."""
+    slots = SM_COUNT // 2
+    token_tiles = -(-M // 256)
+    pairs = -(-N // 512) * token_tiles
+    whole = pairs // slots
+    left = pairs - whole * slots
+    if whole == 0 or left == 0 or left > 0.75 * slots:
+        return 0
+    cut = (whole * slots) // token_tiles
+    rest = N - cut * 512
+    if cut <= 0 or rest <= 0 or -(-rest // 256) * token_tiles > slots:
+        return 0
+    return cut
 
 
 def swiglu_gate_up_pair(x, w_gate_up) -> torch.Tensor:

@@ -624,6 +624,23 @@ def test_tcgen05_swiglu_in_two_launches_cut_at_a_whole_wave():
     close(two, gate * torch.sigmoid(gate) * up, 2.0 ** -6, "swiglu in two launches")
 
 
+def test_tcgen05_pair_gemm_in_two_launches_cut_at_a_whole_round():
+    """2,048 tokens x 6,144 features are 96 wide pairs, 1.3 rounds of 74: nine 512-feature blocks
+    run wide, the last three as one-block pairs.  Same bits as the one-launch forms."""
+    from flyweight_b200.kernels import tensorcore
+    M, N, K = 2048, 6144, 128
+    assert tensorcore._pair_wave_cut(M, N) == 9
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        two = tensorcore.gemm_pair(dev(x), dev(w), out_dtype, wide=True)
+        narrow = tensorcore.gemm_pair(dev(x), dev(w), out_dtype, wide=False)
+        assert tensorcore.status() == 0
+        assert torch.equal(two, narrow)
+        close(two, x.double() @ w.double().T, 1e-5 if out_dtype == torch.float32 else 2.0 ** -8, "pair gemm in two launches")
+
+
 def test_tcgen05_refuses_what_tma_cannot_address():
     from flyweight_b200.kernels import KernelError, tensorcore as tc
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K not a multiple of 8
