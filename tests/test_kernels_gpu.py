@@ -611,7 +611,12 @@ def test_tcgen05_swiglu_in_two_launches_cut_at_a_whole_wave():
     """2,048 tokens x 8,192 features make 3.46 waves of CTAs: the product runs as 55 feature tiles
     with 256-token tiles and 9 with 128-token tiles.  Same bits as one launch, right against fp64."""
     from flyweight_b200.kernels import tensorcore
-    M, F, K = 2048, 8192, 64
+    _swiglu_two_launches(2048, 8192, 64)
+    _swiglu_two_launches(2000, 8100, 72)         # ragged tokens and features on both sides of the cut
+
+
+def _swiglu_two_launches(M, F, K):
+    from flyweight_b200.kernels import tensorcore
     assert tensorcore._wave_cut(M, F) == 55
     g = torch.Generator().manual_seed(2)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
