@@ -15,6 +15,7 @@ from __future__ import annotations
 
 from typing import Hashable, List, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..kernels import lib as kernel_lib
@@ -29,6 +30,18 @@ Entry = Tuple[Hashable, Sequence[int], Sequence[int]]
 
 class StepError(ValueError):
     """An entry the step function refuses (bad token id, empty portion, over-long request)."""
+
+
+def _token_array(request, tokens) -> np.ndarray:
+    """The entry's token ids as one int64 array (a prompt portion is thousands of them: no
+    Python loop over tokens anywhere on the way to the device)."""
+    try:
+        array = np.asarray(tokens, dtype=np.int64)
+    except (OverflowError, TypeError, ValueError) as error:
+        raise StepError(f"request {request!r}: token ids must be integers ({error})") from None
+    if array.ndim != 1:
+        raise StepError(f"request {request!r}: tokens must be a flat list of ids")
+    return array
 
 
 class StepPlanner:
@@ -53,10 +66,10 @@ class StepPlanner:
             seen.add(request)
             if len(tokens) == 0:
                 raise StepError(f"request {request!r} brings no tokens")
-            for token in tokens:
-                if not 0 <= int(token) < vocab:       # native/src/v2_runtime.cpp:27530
-                    raise StepError(f"token id {token} of request {request!r} is outside "
-                                    f"[0, {vocab})")
+            if int(tokens.min()) < 0 or int(tokens.max()) >= vocab:      # native/src/v2_runtime.cpp:27530
+                token = int(tokens[np.nonzero((tokens < 0) | (tokens >= vocab))[0][0]])
+                raise StepError(f"token id {token} of request {request!r} is outside "
+                                f"[0, {vocab})")
             for place in want:
                 if not 0 <= int(place) < len(tokens):
                     raise StepError(f"request {request!r} wants logits at place {place} of "
@@ -90,7 +103,7 @@ class StepPlanner:
         slot or a page is lacking, nothing has changed when the error is raised.
         ``pages_checked``: the caller (the scheduler) has just asked ``pages_short`` for exactly
         these entries and got 0."""
-        entries = [(r, [int(t) for t in toks], [int(w) for w in want]) for r, toks, want in entries]
+        entries = [(r, _token_array(r, toks), [int(w) for w in want]) for r, toks, want in entries]
         self._check_entries(entries)
         new = [r for r, _, _ in entries if not self.cache.has(r)]
         if len(new) > self.cache.free_slots:
