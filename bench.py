@@ -36,6 +36,11 @@ LFM2_1P2B = {
     "conv_L_cache": 3, "conv_bias": False, "vocab_size": 65536, "rope_theta": 1000000.0,
     "norm_eps": 1e-5, "max_position_embeddings": 128000, "tie_embedding": True,
 }
+# The other two sizes the baseline names (same family; --sizes measures decode steps on them).
+LFM2_350M = dict(LFM2_1P2B, hidden_size=1024, num_attention_heads=16, intermediate_size=6656)
+LFM2_2P6B = dict(LFM2_1P2B, num_hidden_layers=30, full_attn_idxs=[2, 6, 10, 14, 18, 21, 24, 27],
+                 intermediate_size=10752)
+MODELS = {"lfm2-350m": LFM2_350M, "lfm2-1.2b": LFM2_1P2B, "lfm2-2.6b": LFM2_2P6B}
 CONTEXT = 4096
 BATCH = 8
 PREFILL_TOKENS = 2048
@@ -309,6 +314,31 @@ def run_ours(args) -> int:
     return 0
 
 
+def run_sizes(args) -> int:
+    """Decode steps at other sizes: ``--sizes lfm2-2.6b:8x32768,64x32768`` prints one JSON line
+    per BATCHxCONTEXT point (the same timer as the default run; not the contract's line)."""
+    import torch
+    from flyweight_b200.engine.runtime import Model
+    name, _, points = args.sizes.partition(":")
+    if name not in MODELS or not points:
+        print(json.dumps({"error": f"--sizes wants MODEL:BATCHxCONTEXT[,...] with MODEL in {sorted(MODELS)}"}))
+        return 1
+    peaks = read_peaks()
+    config = dict(MODELS[name])
+    model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
+    for point in points.split(","):
+        batch, context = (int(v) for v in point.lower().split("x"))
+        timed = time_decode(model, batch, context, args.steps, args.warmup, config["vocab_size"])
+        step_bytes = model.weight_bytes(with_embedding_rows=batch) + batch * context * kv_bytes_per_token(model)
+        achieved = step_bytes / (timed["ms_per_step"] / 1e3) / 1e9
+        print(json.dumps({"sizes": True, "model": name, "parameters": model.parameter_count(),
+                          "batch": batch, "context": context, "ms_per_step": timed["ms_per_step"],
+                          "tokens_per_s": timed["tokens_per_s"], "bytes_per_step": step_bytes,
+                          "hbm_gbs": achieved, "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"]}),
+              flush=True)
+    return 0
+
+
 def run_profile_step(args) -> int:
     """One step (decode at batch 8 / context 4,096, or a 2,048-token prefill) between
     cudaProfilerStart/Stop after warm-up, with CUDA graphs off so that every kernel is a launch
@@ -368,6 +398,8 @@ def main() -> int:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--layers", type=int, default=0,
                         help="run fewer layers than the configuration has (both counts are reported)")
+    parser.add_argument("--sizes", default=None, metavar="MODEL:BxCTX[,BxCTX...]",
+                        help="decode steps of lfm2-350m / lfm2-1.2b / lfm2-2.6b at other batches and contexts")
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run one step inside cudaProfilerStart/Stop (for a profiler) and exit")
     args = parser.parse_args()
@@ -377,6 +409,8 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.profile:
         return run_profile_step(args)
+    if args.sizes:
+        return run_sizes(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

@@ -5,6 +5,8 @@ back to the SIMT kernel otherwise, so every shape the configuration allows still
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import lib
@@ -197,12 +199,17 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
         first = cut * 128
         lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, first, K, F2, F,
                  EPI_SWIGLU_BF16, F, 1, 0, 256, -1, stream())
-        lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up[first:]), ptr(out[:, first:]), ptr(None), M,
+        lib.call("fwb_gemm_tcgen05", ptr(x), _offset(w_gate_up, first * K), _offset(out, first), ptr(None), M,
                  F - first, K, F2 - first, F, EPI_SWIGLU_BF16, F, 1, 0, 128, -1, stream())
         return out
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, F, K, F2, F,
              EPI_SWIGLU_BF16, F, splits, stages, tile_tokens, -1, stream())
     return out
+
+
+def _offset(tensor, elements: int):
+    """The address ``elements`` into a contiguous tensor (a slice without making a view)."""
+    return ctypes.c_void_p(tensor.data_ptr() + elements * tensor.element_size())
 
 
 def _wave_cut(M: int, F: int) -> int:
@@ -326,7 +333,7 @@ def gemm_pair(x, w, out_dtype, wide=False) -> torch.Tensor:
         # the wide blocks of the whole rounds, then the rest as narrow pairs that fit one round
         first = cut * 512
         lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w), ptr(out), M, first, K, N, N, epilogue, 0, 1, stream())
-        lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w[first:]), ptr(out[:, first:]), M, N - first, K,
+        lib.call("fwb_gemm_tcgen05_pair", ptr(x), _offset(w, first * K), _offset(out, first), M, N - first, K,
                  N - first, N, epilogue, 0, 0, stream())
         return out
     lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w), ptr(out), M, N, K, N, N, epilogue, 0,
