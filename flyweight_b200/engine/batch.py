@@ -126,30 +126,33 @@ class StepBatch:
         self.block_tables = [dev[start:start + s * w].view(s, w) for start, s, w in table_slices]
         self.max_context = max((seg.pos0 + n for seg, n in zip(self.segments, lengths)), default=0)
         self.max_segment = max(lengths, default=0)
+        # segments of one token at the head of the batch (the scheduler puts decoding requests first)
+        self.leading_singles = next((i for i, n in enumerate(lengths) if n != 1), S)
         self._device = device
         self._pinned = pinned
         self._tiles = {}
 
-    def attention_tiles(self, tokens_per_tile: int):
-        """Row tiles for the tiled attention kernels: every segment cut into runs of at most
-        ``tokens_per_tile`` tokens.  Returns (tile_seg, tile_tok0, n_tiles), int32 on the
-        device; made once per step and tile size."""
-        cached = self._tiles.get(tokens_per_tile)
+    def attention_tiles(self, tokens_per_tile: int, first_segment: int = 0):
+        """Row tiles for the tiled attention kernels: every segment from ``first_segment`` on cut
+        into runs of at most ``tokens_per_tile`` tokens.  Returns (tile_seg, tile_tok0, n_tiles),
+        int32 on the device; made once per step, tile size and first segment."""
+        cached = self._tiles.get((tokens_per_tile, first_segment))
         if cached is None:
             seg_of, tok0 = [], []
             base = 0
             for index, seg in enumerate(self.segments):
                 n = len(seg.tokens)
-                starts = np.arange(base, base + n, tokens_per_tile, dtype=np.int32)
-                seg_of.append(np.full(starts.size, index, dtype=np.int32))
-                tok0.append(starts)
+                if index >= first_segment:
+                    starts = np.arange(base, base + n, tokens_per_tile, dtype=np.int32)
+                    seg_of.append(np.full(starts.size, index, dtype=np.int32))
+                    tok0.append(starts)
                 base += n
             seg_of = np.concatenate(seg_of) if seg_of else np.empty(0, dtype=np.int32)
             n = seg_of.size
             host = np.concatenate([seg_of] + tok0) if n else np.empty(0, dtype=np.int32)
             self.h2d_bytes += host.size * 4
             dev = _to_device(host, self._device, self._pinned)
-            cached = self._tiles[tokens_per_tile] = (dev[:n], dev[n:], n)
+            cached = self._tiles[(tokens_per_tile, first_segment)] = (dev[:n], dev[n:], n)
         return cached
 
 

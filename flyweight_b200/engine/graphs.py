@@ -52,6 +52,7 @@ class DecodeBatch:
                              for start in self._table_offsets]
         self.segments: List[Segment] = []
         self.max_segment = 1
+        self.leading_singles = batch_size
         self.max_context = 0
         self.h2d_bytes = cursor * 4
         # host mirror of the arrays; the parts that never change are written once

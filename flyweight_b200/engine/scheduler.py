@@ -65,6 +65,16 @@ class Task:
     def pending(self) -> int:
         return len(self.prompt) + len(self.generated) - self.computed
 
+    def tokens_from(self, start: int, count: int) -> List[int]:
+        """``text[start:start + count]`` without joining the two lists first (a long prompt
+        would be copied once per step and request)."""
+        known = len(self.prompt)
+        if start + count <= known:
+            return self.prompt[start:start + count]
+        if start >= known:
+            return self.generated[start - known:start - known + count]
+        return self.prompt[start:] + self.generated[:start + count - known]
+
 
 @dataclass
 class ScheduledStep:
@@ -151,7 +161,7 @@ class Scheduler:
 
     def _portion(self, task: Task, budget: int):
         n = min(task.pending, budget)
-        tokens = task.text[task.computed:task.computed + n]
+        tokens = task.tokens_from(task.computed, n)
         want = [n - 1] if n == task.pending else []
         return (task.id, tokens, want)
 
@@ -191,7 +201,7 @@ class Scheduler:
             task = self.waiting[0]
             if step.preempted and task.id in step.preempted:
                 break                                   # just evicted: not in the same step
-            whole = (task.id, task.text, [])
+            whole = (task.id, range(len(task.prompt) + len(task.generated)), [])   # only its length counts
             spare = [(("spare", task.id), [0] * PAGE_SIZE, [])]
             if self.planner.pages_short(entries + [whole] + spare):
                 if chosen or self.running:

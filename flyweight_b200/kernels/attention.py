@@ -34,6 +34,15 @@ def set_tcgen05_enabled(flag: bool) -> None:
 
 
 
+_split_mixed = True
+
+
+def set_mixed_split(flag: bool) -> None:
+    """Decoding requests at the head of a mixed step through the decode kernel (on by default)."""
+    global _split_mixed
+    _split_mixed = bool(flag)
+
+
 def force_tiled(flag: bool) -> None:
     """Send single decode tokens through the tiled kernel too.  A row of that kernel is summed
     in one order whatever else is in the step, so tests can compare cuts bit by bit."""
@@ -74,18 +83,30 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
                                             block_table, n_heads, window, scale, splits,
                                             tiles_per_split, in_cluster)
         group = n_heads // n_kv
+        out = None
+        first = 0
+        if batch.leading_singles and not _force_tiled and _split_mixed:
+            # a mixed step: the decoding requests at its head run the split-context kernel (a tile
+            # of the prompt kernels would hold one token and walk the whole context alone), the
+            # portions of prompts behind them the tiled kernels; both write their rows of `out`
+            first = batch.leading_singles
+            out = torch.empty_like(q)
+            splits, tiles_per_split, in_cluster = decode_splits(first, n_kv, block_table.shape[1])
+            ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg, block_table,
+                                     n_heads, window, scale, splits, tiles_per_split, in_cluster,
+                                     out=out, n_tokens=first)
         if (_use_tcgen05 and not _force_tiled and ops.attention_tcgen05_shape_ok(n_heads, n_kv, head_dim, page_size)
                 and 2 * batch.max_segment * group >= 128):
             # prompt portions that fill at least half of a 128-row tile: S and PV in tensor memory
             tokens_per_tile = max(1, 128 // group)
-            tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile)
+            tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile, first)
             return ops.attention_prefill_tcgen05(q, k_pool, v_pool, batch.positions, batch.seg_start,
                                                  tile_seg, tile_tok0, n_tiles, tokens_per_tile,
-                                                 block_table, n_heads, window, scale)
+                                                 block_table, n_heads, window, scale, out=out)
         tokens_per_tile = max(1, 64 // group)
-        tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile)
+        tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile, first)
         return ops.attention_prefill_mma(q, k_pool, v_pool, batch.positions, batch.seg_start,
                                          tile_seg, tile_tok0, n_tiles, tokens_per_tile, block_table,
-                                         n_heads, window, scale)
+                                         n_heads, window, scale, out=out)
     return ops.attention_simt(q, k_pool, v_pool, batch.positions, batch.tok_seg, block_table,
                               n_heads, window, scale, out_dtype)

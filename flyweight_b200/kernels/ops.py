@@ -245,8 +245,9 @@ def attention_mma_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size: in
 
 
 def attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
-                          tokens_per_tile, block_table, n_heads, window, scale) -> torch.Tensor:
-    """Causal GQA of prompt portions (any mix of segments) on tensor cores; all bf16."""
+                          tokens_per_tile, block_table, n_heads, window, scale, out=None) -> torch.Tensor:
+    """Causal GQA of prompt portions (any mix of segments) on tensor cores; all bf16.  Only the
+    rows of the given tiles are written (``out``: a tensor like q that other rows already live in)."""
     check_tensor("q", q, torch.bfloat16)
     check_tensor("k pool", k_pool, torch.bfloat16)
     check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
@@ -259,7 +260,10 @@ def attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg, til
     _i32("tile_seg", tile_seg, n_tiles)
     _i32("tile_tok0", tile_tok0, n_tiles)
     _i32("block table", block_table)
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        check_tensor("attention output", out, torch.bfloat16, q.shape)
     lib.call("fwb_attention_prefill_mma", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
              ptr(seg_start), ptr(tile_seg), ptr(tile_tok0), ptr(block_table), block_table.shape[1],
              page_size, ptr(out), n_tiles, n_heads, n_kv, head_dim, tokens_per_tile, window,
@@ -274,7 +278,7 @@ def attention_tcgen05_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size
 
 
 def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
-                              tokens_per_tile, block_table, n_heads, window, scale) -> torch.Tensor:
+                              tokens_per_tile, block_table, n_heads, window, scale, out=None) -> torch.Tensor:
     """The same operation on tcgen05 tensor cores: 128 query rows per CTA, S and PV in tensor
     memory (head sizes 64 and 128); all bf16."""
     check_tensor("q", q, torch.bfloat16)
@@ -289,7 +293,10 @@ def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg,
     _i32("tile_seg", tile_seg, n_tiles)
     _i32("tile_tok0", tile_tok0, n_tiles)
     _i32("block table", block_table)
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        check_tensor("attention output", out, torch.bfloat16, q.shape)
     lib.call("fwb_attention_prefill_tcgen05", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
              ptr(seg_start), ptr(tile_seg), ptr(tile_tok0), ptr(block_table), block_table.shape[1],
              page_size, num_pages, ptr(out), n_tiles, n_heads, n_kv, head_dim, tokens_per_tile, window,
@@ -298,22 +305,29 @@ def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg,
 
 
 def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_heads, window, scale,
-                         splits: int, tiles_per_split: int, merge_in_cluster: bool = False) -> torch.Tensor:
+                         splits: int, tiles_per_split: int, merge_in_cluster: bool = False,
+                         out=None, n_tokens=None) -> torch.Tensor:
     """Causal GQA of single decode tokens on tensor cores, the context cut into ``splits``
     slices of ``tiles_per_split`` 64-key tiles that run as separate CTAs and are merged: inside
     the kernel (``merge_in_cluster``, up to 8 slices as a thread-block cluster) or through scratch
-    and a second kernel."""
+    and a second kernel.  ``n_tokens``: only the first that many rows of q are decode tokens (the
+    head of a mixed step); the other rows of ``out`` are left alone."""
     check_tensor("q", q, torch.bfloat16)
     check_tensor("k pool", k_pool, torch.bfloat16)
     check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
-    T = q.shape[0]
+    T = q.shape[0] if n_tokens is None else int(n_tokens)
+    if not 0 < T <= q.shape[0]:
+        raise KernelError(f"{T} decode tokens of {q.shape[0]} rows")
     _, n_kv, page_size, head_dim = k_pool.shape
     if q.shape[1] != n_heads * head_dim:
         raise KernelError(f"q has {q.shape[1]} columns, expected {n_heads * head_dim}")
     _i32("positions", positions, T)
     _i32("tok_seg", tok_seg, T)
     _i32("block table", block_table)
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        check_tensor("attention output", out, torch.bfloat16, q.shape)
     part_o = part_ml = None
     in_cluster = merge_in_cluster and 1 < splits <= 8
     if splits > 1 and not in_cluster:

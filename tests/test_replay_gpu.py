@@ -209,3 +209,46 @@ def test_bfloat16_cuts_agree_to_one_roundoff_when_the_sums_keep_one_order(name):
         tensorcore.force_splits(None)
         tensorcore.set_norm_fusion(True)
         attention.force_tiled(False)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_decoding_requests_at_the_head_of_a_mixed_step(name):
+    """Three requests decode beside portions of a fourth: their tokens, first in the step, run
+    the split-context kernel and the portions the tiled one, into one output; with the split
+    switched off the tiled kernel runs all of it.  Both follow the plain implementation."""
+    from flyweight_b200.kernels import attention
+    dtype = "bfloat16"
+    seqs = [random_tokens(name, n, seed=40 + i) for i, n in enumerate((150, 97, 70, 130))]
+    want = [plain_logits(name, dtype, s) for s in seqs]
+    tail = 20
+    results = {}
+    for split in (True, False):
+        attention.set_mixed_split(split)
+        try:
+            runner = new_runner(name, dtype, num_pages=16, num_slots=4)
+            runner.use_graphs = False
+            for i in range(3):
+                runner.step([(f"d{i}", seqs[i][:-tail], [])])
+            got = {i: [] for i in range(4)}
+            pos = 0
+            for k in range(tail):
+                entries = [(f"d{i}", [seqs[i][len(seqs[i]) - tail + k]], [0]) for i in range(3)]
+                portion = seqs[3][pos:pos + (7, 2, 16, 1, 9)[k % 5]]
+                if portion:
+                    entries.append(("p", portion, list(range(len(portion)))))
+                    pos += len(portion)
+                out = runner.step(entries).cpu().numpy()
+                for i in range(3):
+                    got[i].append(out[i:i + 1])
+                if portion:
+                    got[3].append(out[3:])
+            for i in range(3):
+                assert_close(np.concatenate(got[i]), want[i][-tail:], TOL_ORACLE[dtype],
+                             f"{name} split={split}: decoding request {i} in mixed steps")
+            assert_close(np.concatenate(got[3]), want[3][:pos], TOL_ORACLE[dtype],
+                         f"{name} split={split}: portions beside decoding requests")
+            results[split] = np.concatenate([np.concatenate(got[i]) for i in range(4)])
+            runner.cache.check()
+        finally:
+            attention.set_mixed_split(True)
+    assert_close(results[True], results[False], TOL_CUTS[dtype], f"{name} split on against off")
