@@ -13,7 +13,7 @@ host may run several steps ahead of the device.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -111,13 +111,15 @@ class DecodeBatch:
         self.max_context = int(pos0.max()) + 1
 
 
-    def upload_next(self, tokens: Sequence[int]) -> None:
+    def upload_next(self, tokens: Optional[Sequence[int]]) -> None:
         """The same requests one position further (no page changes): only the token ids and the
-        positions move."""
+        positions move.  ``tokens`` None: the ids are put into ``token_ids`` on the device by the
+        caller, after this upload."""
         B = self.n_segments
         values = self._current
         ids, _, pos0 = self._views
-        ids[:] = tokens
+        if tokens is not None:
+            ids[:] = tokens
         pos0 += 1
         start = self._offsets["positions"][0]
         values[start:start + B] = pos0
@@ -167,9 +169,13 @@ class DecodeGraph:
         add_launches(self.kernels)
         return self.logits
 
-    def run_next(self, tokens: Sequence[int]) -> torch.Tensor:
-        """Replay for the same requests, each one token further."""
+    def run_next(self, tokens: Optional[Sequence[int]] = None,
+                 device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Replay for the same requests, each one token further; the tokens come from the host
+        or, as int32 on the device, straight from the sampler of the step before."""
         self.batch.upload_next(tokens)
+        if device_tokens is not None:
+            self.batch.token_ids.copy_(device_tokens)
         self.graph.replay()
         add_launches(self.kernels)
         return self.logits

@@ -13,7 +13,7 @@ flyweight has two forwards instead, one token of one sequence
 """
 from __future__ import annotations
 
-from typing import Hashable, List, Sequence, Tuple
+from typing import Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -201,15 +201,17 @@ class ModelRunner(StepPlanner):
             self.bad_token_flag.zero_()
             raise KernelError("a token id outside the vocabulary reached the embedding kernel")
 
-    def step_same_requests(self, tokens: Sequence[int]) -> torch.Tensor:
+    def step_same_requests(self, tokens: Optional[Sequence[int]] = None,
+                           device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The decode step that follows the last one for exactly the same requests, none of
-        which needs a new page: lengths grow by one, the captured graph is replayed."""
+        which needs a new page: lengths grow by one, the captured graph is replayed.  The tokens
+        are given by the host, or on the device (int32, one per request, in the batch's order)."""
         graph = self.last_decode_graph
         for seg in graph.batch.segments:
             self.cache.bump(seg.request)
-        logits = graph.run_next(tokens)
+        logits = graph.run_next(tokens, device_tokens)
         self.graph_replays += 1
         self.steps += 1
-        self.tokens_run += len(tokens)
+        self.tokens_run += graph.batch.n_segments
         self.h2d_bytes += graph.batch.h2d_bytes
         return logits

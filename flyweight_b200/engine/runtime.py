@@ -81,6 +81,9 @@ class Runtime:
         self._counters = {"engine_steps": 0, "steady_steps": 0, "step_seconds": 0.0,
                           "sampling_seconds": 0.0, "d2h_bytes": 0}
         self.steady_decode = True          # take the short way when a step repeats the last one
+        self.run_ahead = True              # ... and launch the step after it before reading this one's tokens
+        self._ahead = None                 # a decode step already launched whose tokens were not read yet
+        self._token_ring = None            # pinned buffers for the sampled ids of two steps in flight
         self.prepare()
 
     # ------------------------------------------------------------------ life cycle
@@ -95,11 +98,13 @@ class Runtime:
 
     def reset(self) -> None:
         """Forget every request and give back everything the cache holds."""
+        self._ahead = None
         self.runner.cache.reset()
         self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
 
     def close(self) -> None:
         runner, self.runner, self.scheduler = self.runner, None, None
+        self._ahead = None
         if runner is not None:
             runner.check_health()
 
@@ -142,17 +147,13 @@ class Runtime:
         that was due.  Returns events ``(task id, token or count, kind)``."""
         scheduler, runner = self.scheduler, self.runner
         started = time.perf_counter()
-        need = self._same_requests_again() if self.steady_decode else None
-        if need is not None:
-            self._counters["steady_steps"] += 1
-            # steady decoding: nothing to schedule, no page to map; replay one position further
-            logits = runner.step_same_requests([task.generated[-1] for task in need])
-            scheduler.advance_decode(need)
-            events = []
-            self._sample_and_accept(need, logits, events)
-            self._counters["engine_steps"] += 1
-            self._counters["step_seconds"] += time.perf_counter() - started
-            return events
+        if self._ahead is not None or self.steady_decode:
+            events = self._steady_step()
+            if events is not None:
+                self._counters["steady_steps"] += 1
+                self._counters["engine_steps"] += 1
+                self._counters["step_seconds"] += time.perf_counter() - started
+                return events
         step = scheduler.schedule()
         events = list(step.events)
         if not step.entries:
@@ -186,6 +187,94 @@ class Runtime:
             events.extend(accepted)
         if finished:
             self.runner.check_health()          # once per finished request: kernels fail loudly
+
+    # ------------------------------------------------------------------ steady decoding
+    def _steady_step(self):
+        """Steady decoding: nothing to schedule, no page to map, the captured graph replayed one
+        position further.  With greedy requests the step after this one is launched as well before
+        this one's tokens are read: its token ids go from the sampler's output to the embedding on
+        the device, so the device does not wait for the host between steps.  Returns the events
+        of one step, or None when the next step is not a repeat of the last one."""
+        current = self._ahead
+        self._ahead = None
+        if current is None:
+            need = self._same_requests_again()
+            if need is None:
+                return None
+            logits = self.runner.step_same_requests([task.generated[-1] for task in need])
+            self.scheduler.advance_decode(need)
+            if not (self.run_ahead and all(task.sampling.greedy for task in need)):
+                events = []
+                self._sample_and_accept(need, logits, events)
+                return events
+            current = self._sample_greedy_async(need, logits)
+        if self.run_ahead and self.steady_decode and self._may_follow(current["tasks"]):
+            logits = self.runner.step_same_requests(device_tokens=current["device"])
+            self.scheduler.advance_decode(current["tasks"])
+            self._ahead = self._sample_greedy_async(current["tasks"], logits)
+        return self._accept_async(current)
+
+    def _may_follow(self, tasks) -> bool:
+        """Whether the step after the one in flight may be launched now: the same requests go
+        on (nobody waits, is cancelled, or is known to end with the token in flight), and none
+        of them needs a new page or reaches the limit."""
+        scheduler, runner = self.scheduler, self.runner
+        if scheduler.waiting or len(scheduler.running) != len(tasks):
+            return False
+        cache = runner.cache
+        for task, running in zip(tasks, scheduler.running):
+            if task is not running or task.cancelled or len(task.generated) + 1 >= task.max_tokens:
+                return False
+            length = cache.length(task.id)
+            if length % PAGE_SIZE == 0 or length + 1 > runner.max_model_len:
+                return False
+            if len(task.prompt) + len(task.generated) + 1 >= self.scheduler.max_model_len:
+                return False
+        return True
+
+    def _sample_greedy_async(self, tasks, logits):
+        """Arg-max on the device and the copy of the ids to pinned memory, both queued; nobody
+        waits here."""
+        tokens = device_sampler.argmax(logits)
+        if self._token_ring is None:
+            self._token_ring = {"buffers": [torch.empty(256, dtype=torch.int32).pin_memory() for _ in range(2)],
+                                "events": [torch.cuda.Event() for _ in range(2)], "turn": 0}
+        ring = self._token_ring
+        turn = ring["turn"]
+        ring["turn"] = turn ^ 1
+        count = tokens.numel()
+        if ring["buffers"][turn].numel() < count:
+            ring["buffers"][turn] = torch.empty(2 * count, dtype=torch.int32).pin_memory()
+        view = ring["buffers"][turn][:count]
+        view.copy_(tokens, non_blocking=True)
+        ring["events"][turn].record()
+        return {"tasks": list(tasks), "device": tokens, "host": view, "event": ring["events"][turn]}
+
+    def _accept_async(self, step) -> List[Tuple[int, int, int]]:
+        """Wait for the ids of a launched step and hand them to their requests.  A request that
+        ended while the step was in flight (a stop token in the step before, a cancellation)
+        drops its id."""
+        sampled = time.perf_counter()
+        step["event"].synchronize()
+        host = step["host"].tolist()
+        self._counters["d2h_bytes"] += 4 * len(host)
+        self._counters["sampling_seconds"] += time.perf_counter() - sampled
+        events: List[Tuple[int, int, int]] = []
+        finished = False
+        for task in step["tasks"]:
+            if task.cancelled and task.state == "running":     # cancelled while the step was in flight
+                self.scheduler._finish(task, "cancelled")
+                events.append((task.id, 0, EVENT_FINISHED))
+                finished = True
+        for task, token in zip(step["tasks"], host):
+            if task.state != "running":
+                continue
+            accepted = self.scheduler.accept(task, token)
+            finished = finished or len(accepted) > 1
+            events.extend(accepted)
+        if finished:
+            self.runner.check_health()
+        return events
 
     def _same_requests_again(self):
         """The running tasks, if the next step is the last one moved on by one token: nobody

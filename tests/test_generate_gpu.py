@@ -153,3 +153,34 @@ def test_the_steady_decode_shortcut_changes_nothing():
     slow, none = run(False)
     assert fast == slow
     assert steady_steps > 40 and none == 0
+
+
+def test_launching_the_next_step_before_reading_this_one_changes_nothing():
+    """Greedy requests in steady decoding: the runtime launches step k+1, fed on the device from
+    the sampler of step k, before it reads step k's tokens.  Requests that end on a stop token
+    (seen one step late), on their token count, across page edges, and one that is cancelled
+    half way must produce the same tokens and events as without it."""
+    name = "A"
+    prompts = [random_tokens(name, n, seed=90 + n) for n in (20, 50, 63, 90)]
+
+    def run(ahead, stop):
+        with open_runtime(name, "float32", context_limit=256, parallel_sequences=4) as runtime:
+            runtime.run_ahead = ahead
+            ids = [runtime.task_submit(p, 60 + 13 * i, stop) for i, p in enumerate(prompts)]
+            log = []
+            steps = 0
+            while runtime.has_work():
+                log.extend(runtime.engine_step())
+                steps += 1
+                if steps == 30:
+                    runtime.task_cancel(ids[1])
+            return [runtime.task(i).generated for i in ids], log, runtime.info["steady_steps"]
+
+    plain, _, _ = run(False, ())
+    # a token that request 2 produces half way becomes everybody's stop token
+    stop = (plain[2][25],)
+    slow, slow_log, _ = run(False, stop)
+    fast, fast_log, steady = run(True, stop)
+    assert fast == slow and fast_log == slow_log
+    assert steady > 20
+    assert len(slow[2]) <= 26 and any(len(a) < len(b) for a, b in zip(slow, plain))
