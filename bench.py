@@ -339,6 +339,24 @@ def run_sizes(args) -> int:
     return 0
 
 
+def run_prefill_lengths(args) -> int:
+    """One prompt of each given length through one step (``--prefill-lengths 128,512,8192``): a
+    JSON line per length, the timer and the flop count of the default run's prefill figure."""
+    import torch
+    from flyweight_b200.engine.runtime import Model
+    peaks = read_peaks()
+    model = Model.random(dict(LFM2_1P2B), seed=0, dtype="bfloat16", device="cuda:0").module
+    for n_tokens in (int(v) for v in args.prefill_lengths.split(",")):
+        ms = time_prefill(model, n_tokens, LFM2_1P2B["vocab_size"])
+        flops = (model_flops_per_token(model) * n_tokens + attention_flops(model, n_tokens)
+                 + 2.0 * model.head.numel())
+        print(json.dumps({"prefill_lengths": True, "model": "lfm2-1.2b", "tokens": n_tokens, "ms": ms,
+                          "tokens_per_s": n_tokens / (ms / 1e3), "tflops": flops / (ms / 1e3) / 1e12,
+                          "frac": flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "of": peaks["source"]}),
+              flush=True)
+    return 0
+
+
 def run_profile_step(args) -> int:
     """One step (decode at batch 8 / context 4,096, or a 2,048-token prefill) between
     cudaProfilerStart/Stop after warm-up, with CUDA graphs off so that every kernel is a launch
@@ -400,6 +418,8 @@ def main() -> int:
                         help="run fewer layers than the configuration has (both counts are reported)")
     parser.add_argument("--sizes", default=None, metavar="MODEL:BxCTX[,BxCTX...]",
                         help="decode steps of lfm2-350m / lfm2-1.2b / lfm2-2.6b at other batches and contexts")
+    parser.add_argument("--prefill-lengths", default=None, metavar="N[,N...]",
+                        help="time one prompt of each length through one step (lfm2-1.2b)")
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run one step inside cudaProfilerStart/Stop (for a profiler) and exit")
     args = parser.parse_args()
@@ -411,6 +431,8 @@ def main() -> int:
         return run_profile_step(args)
     if args.sizes:
         return run_sizes(args)
+    if args.prefill_lengths:
+        return run_prefill_lengths(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

@@ -505,7 +505,7 @@ int launch_epi(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, cons
 
 // X: [M][K] bf16; W: [rows][K] bf16 (rows = N, or >= up_row_offset + N for SwiGLU);
 // Y: [M][ldy] (fp32 for epilogues 0 and 2, bf16 for 1 and 3).  `splits` (1..8) CTAs share the
-// K range of a tile as a cluster; with splits > 1 the token tile must be <= 64 wide.
+// K range of a tile as a cluster; with splits > 1 the token tile must be <= 128 wide (64 for SwiGLU).
 // `stages` sets the depth of the shared-memory ring (0: the default).  `tile_tokens` (0: by M)
 // may ask for a smaller token tile than M would pick (more CTAs); `wide` gives a CTA two feature tiles.
 // K must be a multiple of 8 (TMA strides are multiples of 16 bytes) and both base
@@ -536,7 +536,9 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
         if (epilogue == EPI_F32) epilogue = EPI_F32_WIDE;
         else if (epilogue == EPI_BF16) epilogue = EPI_BF16_WIDE;
     }
-    if (splits > 1 && bn_eff > 64) return FWB_UNSUPPORTED;
+    // the slices' partial tiles are parked in the ring's shared memory (columns x 128 rows of fp32):
+    // up to 128 columns fit any ring depth, so 128-token tiles split too, with one accumulator
+    if (splits > 1 && (bn_eff > 128 || (bn_eff == 128 && epilogue == EPI_SWIGLU_BF16))) return FWB_UNSUPPORTED;
     if ((N + BM - 1) / BM > 65535) return FWB_TOO_LARGE;
     const int total_kb = (K + BK - 1) / BK;
     if (splits > total_kb) splits = total_kb;

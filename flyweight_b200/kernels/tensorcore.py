@@ -115,6 +115,31 @@ def _splits_for(M: int, N: int, K: int, accumulators: int) -> int:
     return splits
 
 
+MID_SIZE_PAIRS = 12        # fewer 256 x 256 tiles than this, and
+MID_SIZE_K = 4096          # at least this long a K: the split form wins
+_mid_size_split = True
+
+
+def set_mid_size_split(flag: bool) -> None:
+    """Products of 65 to about a thousand tokens with few output tiles on single CTAs with a
+    split K (on by default); off: CTA pairs or one CTA per tile, as before."""
+    global _mid_size_split
+    _mid_size_split = bool(flag)
+
+
+def _mid_size_splits(M: int, N: int, K: int) -> int:
+    """Slices of K (a cluster, a power of two <= 8) for 128-token tiles: until the product has
+    about one CTA per SM, as long as a slice keeps sixteen 64-wide blocks."""
+    if _forced_splits is not None:
+        return 1
+    tiles = -(-N // 128) * -(-M // 128)
+    k_blocks = -(-K // 64)
+    splits = 1
+    while splits < 8 and tiles * splits < 120 and k_blocks >= splits * 2 * 16:
+        splits *= 2
+    return splits
+
+
 def adds_in_place(x, w, residual) -> bool:
     """Whether ``gemm(x, w, fp32, addend=residual, out=residual)`` is available: the single-CTA
     kernel has the epilogue (every element is read and written by the same thread), the
@@ -134,12 +159,21 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm: input has {K} columns, weight has {w.shape[1]}")
-    if (_use_pairs and M > 128 and addend is None and out is None and splits is None and not stages
-            and not tile_tokens and wide == -1 and N >= 256):
+    free_choice = splits is None and not stages and not tile_tokens and wide == -1
+    # 65 to a few hundred tokens against a narrow matrix with a long K (w2 at 256 tokens: 8 CTA
+    # pairs, each walking all 8,192 columns): 128-token tiles on single CTAs with K cut across a
+    # cluster put work on every SM.  Measured on B200 for 2,048 features x 8,192: 128 tokens
+    # 52 -> 28 us, 256 tokens 44 -> 24 us; from 512 tokens on, and for K of 2,048, the pairs win.
+    mid_size = (free_choice and _mid_size_split and 64 < M and K >= MID_SIZE_K
+                and -(-N // 256) * -(-M // 256) < MID_SIZE_PAIRS)
+    if _use_pairs and M > 128 and addend is None and out is None and free_choice and N >= 256 and not mid_size:
         # prompt-sized: CTA pairs (cta_group::2); two feature blocks per pair when single blocks
         # would make more CTAs than the GPU holds at once (measured at 2,048 tokens on B200)
         pairs = -(-N // 256) * -(-M // 256)
         return gemm_pair(x, w, out_dtype, wide=pairs > SM_COUNT // 2)
+    if mid_size:
+        tile_tokens = 128
+        splits = _mid_size_splits(M, N, K)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     else:

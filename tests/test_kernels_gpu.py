@@ -513,7 +513,7 @@ def test_tcgen05_gemm(M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
-@pytest.mark.parametrize("M", [1, 16, 40, 64])
+@pytest.mark.parametrize("M", [1, 16, 40, 64, 100, 128, 300])
 def test_tcgen05_split_k_over_a_cluster(splits, M):
     from flyweight_b200.kernels import tensorcore as tc
     g = torch.Generator().manual_seed(splits * 100 + M)
@@ -522,10 +522,11 @@ def test_tcgen05_split_k_over_a_cluster(splits, M):
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
     add = torch.randn(M, N, generator=g)
     want = x.double() @ w.double().T
-    first = tc.gemm(dev(x), dev(w), torch.float32, None, splits)
+    tile = 128 if M > 64 else 0                      # more than 64 tokens: 128-token tiles
+    first = tc.gemm(dev(x), dev(w), torch.float32, None, splits, 0, tile)
     close(first, want, 1e-5, f"split {splits}")
-    assert torch.equal(first, tc.gemm(dev(x), dev(w), torch.float32, None, splits))   # deterministic
-    close(tc.gemm(dev(x), dev(w), torch.float32, dev(add), splits), want + add.double(), 1e-5, "addend")
+    assert torch.equal(first, tc.gemm(dev(x), dev(w), torch.float32, None, splits, 0, tile))   # deterministic
+    close(tc.gemm(dev(x), dev(w), torch.float32, dev(add), splits, 0, tile), want + add.double(), 1e-5, "addend")
     assert tc.status() == 0
 
 
@@ -787,4 +788,28 @@ def test_tcgen05_cta_pair_swiglu(M, F, K):
     gu = x.double() @ w.double().T
     want = torch.from_numpy(P.silu(gu[:, :F].numpy())) * gu[:, F:]
     close(tc.swiglu_gate_up_pair(dev(x), dev(w)), want, 2.0 ** -8, "pair swiglu")
+    assert tc.status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(65, 2048, 8192), (128, 384, 4168), (300, 2048, 4096), (256, 2048, 8192),
+                                   (700, 260, 4104), (200, 1000, 5000)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_tcgen05_mid_size_products_split_k_over_128_token_tiles(M, N, K, out_dtype):
+    """A few hundred tokens against a narrow matrix: 128-token tiles on single CTAs with K cut
+    across a cluster instead of a handful of CTA pairs; the same numbers as with it switched off."""
+    from flyweight_b200.kernels import tensorcore as tc
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    # fp32 out: the tensor core's accumulator loses a little with every block of K it adds
+    tol = 1e-5 * max(1.0, K / 2048) if out_dtype == torch.float32 else 2.0 ** -8
+    assert tc._mid_size_splits(256, 2048, 8192) == 4 and tc._mid_size_splits(128, 2048, 8192) == 8
+    got = tc.gemm(dev(x), dev(w), out_dtype)
+    close(got, want, tol, "mid-size split")
+    tc.set_mid_size_split(False)
+    try:
+        close(tc.gemm(dev(x), dev(w), out_dtype), want, tol, "mid-size, as before")
+    finally:
+        tc.set_mid_size_split(True)
     assert tc.status() == 0
