@@ -69,3 +69,34 @@ def test_mixed_batches_at_real_tile_shapes(runners):
     want = replay_in_process(runners["float32"], steps)
     for rid in tokens:
         assert_close(got[rid], want[rid], TOL_ORACLE["bfloat16"], f"medium mixed {rid}")
+
+
+def test_a_hundred_tokens_against_a_wide_feed_forward(tmp_path):
+    """A feed-forward width of 4,352: at 65 to a few hundred tokens its down projection (long K,
+    few output tiles) runs 128-token tiles with K cut across a cluster; the 32-bit path is the
+    oracle, and the portions must agree with the whole prompt."""
+    from flyweight_b200.engine import ModelRunner, load_model
+    from flyweight_b200.kernels import tensorcore
+    config = dict(MEDIUM, num_hidden_layers=2, layer_types=["conv", "full_attention"],
+                  intermediate_size=4352)
+    assert tensorcore._mid_size_splits(100, 1024, 4352) > 1
+    folder = make_model_dir(tmp_path / "wide", config, seed=6, dtype=torch.bfloat16)
+    made = {dtype: ModelRunner(load_model(folder, dtype), num_pages=12, num_slots=2, max_model_len=512,
+                               max_batched_tokens=512) for dtype in ("float32", "bfloat16")}
+    rng = np.random.default_rng(1)
+    tokens = [int(t) for t in rng.integers(0, config["vocab_size"], size=300)]
+    rows = list(range(0, 300, 5)) + [299]
+    oracle = made["float32"].step([("o", tokens, rows)]).cpu().numpy()
+    runner = made["bfloat16"]
+    whole = runner.step([("w", tokens, rows)]).cpu().numpy()
+    runner.finish("w")
+    assert_close(whole, oracle, TOL_ORACLE["bfloat16"], "wide feed-forward, 300 tokens at once")
+    parts = []
+    for start, stop in ((0, 100), (100, 228), (228, 300)):          # 100, 128 and 72 tokens
+        want = [r - start for r in rows if start <= r < stop]
+        parts.append(runner.step([("p", tokens[start:stop], want)]).cpu().numpy())
+    runner.finish("p")
+    got = np.concatenate(parts)
+    assert_close(got, oracle, TOL_ORACLE["bfloat16"], "wide feed-forward, portions of about a hundred")
+    assert_close(got, whole, TOL_CUTS["bfloat16"], "wide feed-forward, cuts")
+    assert tensorcore.status() == 0
