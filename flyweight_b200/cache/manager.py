@@ -25,6 +25,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import FixedState, PagedKV
@@ -144,6 +145,7 @@ class CacheManager:
             elif spec is not None:
                 raise TypeError(f"schedule position {position}: unknown state spec {spec!r}")
             self.layer_caches.append(cache)
+        self._rows: List[Dict[Hashable, tuple]] = [{} for _ in self.groups]   # block-table rows as arrays
         # All fixed-size states of a slot lie side by side in one allocation, [num_slots][total],
         # and every execution sees its share as [num_slots][...]: admission clears one span.
         self._all_states: Optional[torch.Tensor] = None
@@ -261,10 +263,11 @@ class CacheManager:
         slot = self._slot_of.pop(request)
         del self._length[request]
         del self._serial[request]
-        for group in self.groups:
+        for index, group in enumerate(self.groups):
             for page in group.tables.pop(request):
                 if page >= 0:
                     group.pool.release(page)
+            self._rows[index].pop(request, None)
         self._free_slots.append(slot)
 
     def reset(self) -> None:
@@ -283,6 +286,26 @@ class CacheManager:
                 raise ValueError("block table wider than the step's width")
             rows.append(table + [-1] * (width - len(table)))
         return rows
+
+    def block_table_array(self, group_index: int, requests: Sequence[Hashable], width: int) -> np.ndarray:
+        """The same rows as one int32 array [requests][width].  A request's row is kept as an
+        array between steps and made again only when its table changed (a table grows by a page
+        every 64 tokens), so a step with many decoding requests does not walk their lists."""
+        group = self.groups[group_index]
+        out = np.full((len(requests), width), -1, dtype=np.int32)
+        kept = self._rows[group_index]
+        for index, request in enumerate(requests):
+            table = group.tables[request]
+            stamp = (self._serial[request], len(table),
+                     sum(1 for page in table if page < 0) if group.window else 0)
+            entry = kept.get(request)
+            if entry is None or entry[0] != stamp:
+                entry = kept[request] = (stamp, np.asarray(table, dtype=np.int32))
+            row = entry[1]
+            if row.size > width:
+                raise ValueError("block table wider than the step's width")
+            out[index, :row.size] = row
+        return out
 
     def max_table_len(self, requests: Sequence[Hashable]) -> int:
         width = 1

@@ -87,7 +87,7 @@ class StepBatch:
             cursor += count
         table_slices = []
         for rows in block_tables_host:
-            width = len(rows[0]) if rows else 1
+            width = len(rows[0]) if len(rows) else 1
             table_slices.append((cursor, S, width))
             cursor += S * width
         flat = np.empty(cursor, dtype=np.int32)

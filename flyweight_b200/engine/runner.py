@@ -32,9 +32,15 @@ class StepError(ValueError):
     """An entry the step function refuses (bad token id, empty portion, over-long request)."""
 
 
-def _token_array(request, tokens) -> np.ndarray:
+def _token_array(request, tokens):
     """The entry's token ids as one int64 array (a prompt portion is thousands of them: no
-    Python loop over tokens anywhere on the way to the device)."""
+    Python loop over tokens anywhere on the way to the device); a single decoded token stays
+    a list of one int, which costs less than an array."""
+    if len(tokens) == 1 and not isinstance(tokens, np.ndarray):
+        try:
+            return [int(tokens[0])]
+        except (TypeError, ValueError) as error:
+            raise StepError(f"request {request!r}: token ids must be integers ({error})") from None
     try:
         array = np.asarray(tokens, dtype=np.int64)
     except (OverflowError, TypeError, ValueError) as error:
@@ -66,8 +72,12 @@ class StepPlanner:
             seen.add(request)
             if len(tokens) == 0:
                 raise StepError(f"request {request!r} brings no tokens")
-            if int(tokens.min()) < 0 or int(tokens.max()) >= vocab:      # native/src/v2_runtime.cpp:27530
-                token = int(tokens[np.nonzero((tokens < 0) | (tokens >= vocab))[0][0]])
+            if len(tokens) == 1:
+                low = high = int(tokens[0])
+            else:
+                low, high = int(tokens.min()), int(tokens.max())
+            if low < 0 or high >= vocab:                                 # native/src/v2_runtime.cpp:27530
+                token = next(int(t) for t in tokens if not 0 <= int(t) < vocab)
                 raise StepError(f"token id {token} of request {request!r} is outside "
                                 f"[0, {vocab})")
             for place in want:
@@ -178,7 +188,7 @@ class ModelRunner(StepPlanner):
             self.h2d_bytes += graph.batch.h2d_bytes
             return logits
         self.last_decode_graph = None
-        tables = [self.cache.block_table(g, requests, width) for g in range(n_groups)]
+        tables = [self.cache.block_table_array(g, requests, width) for g in range(n_groups)]
         batch = StepBatch(segments, tables, self.device)
         ctx = StepContext(batch, self.precision, self.device, self.bad_token_flag)
         logits = self.model.forward(ctx, self.cache.layer_caches)

@@ -136,3 +136,26 @@ def test_random_orders_keep_every_invariant():
             m.release(name)
         m.check()
         assert all(g.pool.n_used == 0 for g in m.groups) and m.free_slots == m.num_slots
+
+
+def test_block_table_rows_as_one_array_follow_the_lists():
+    """The array form keeps a request's row between steps: it must notice growth, pages a
+    window handed back, and a name that comes back after a release."""
+    import numpy as np
+    from flyweight_b200.cache.manager import CacheManager
+    from flyweight_b200.parts.base import PagedKV
+    cache = CacheManager([PagedKV(2, 16, 0), PagedKV(2, 16, 100)], num_pages=12, num_slots=3)
+    cache.admit("a"); cache.admit("b")
+    cache.extend("a", 70); cache.extend("b", 10)
+    for _ in range(3):
+        for g in range(2):
+            want = np.asarray(cache.block_table(g, ["a", "b"], 5), dtype=np.int32)
+            assert np.array_equal(cache.block_table_array(g, ["a", "b"], 5), want)
+        cache.extend("a", cache.length("a") + 90)          # grows; the window group lets pages go
+        cache.release_passed("a")
+    cache.release("a")
+    cache.admit("a"); cache.extend("a", 5)                   # the name is back with other pages
+    for g in range(2):
+        want = np.asarray(cache.block_table(g, ["b", "a"], 3), dtype=np.int32)
+        assert np.array_equal(cache.block_table_array(g, ["b", "a"], 3), want)
+    cache.check() if hasattr(cache, "check") else None
