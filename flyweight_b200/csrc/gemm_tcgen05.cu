@@ -90,7 +90,7 @@ struct Tile {
     static constexpr int DEFAULT_STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
     static constexpr int COLS = BN * NACC;                      // TMEM columns in use
     static constexpr int TMEM_COLS = COLS <= 32 ? 32 : (COLS <= 64 ? 64 : (COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512)));
-    static constexpr int PARTIAL_BYTES = BN <= 64 ? COLS * BM * 4 : 0;   // fp32 partial tile for split-K
+    static constexpr int PARTIAL_BYTES = (BN <= 64 || NACC == 1) ? COLS * BM * 4 : 0;   // fp32 partial tile for split-K
     static constexpr int data_bytes(int stages) {
         return stages * STAGE_BYTES > PARTIAL_BYTES ? stages * STAGE_BYTES : PARTIAL_BYTES;
     }
@@ -405,6 +405,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (epi_warp && column_half == 0) {
             const uint32_t rank = cluster_rank();
             const uint32_t base = smem_u32(partial);
+            if constexpr (BN >= 64 && NACC == 1 && !NORMED) {
+                // wide token tiles: a CTA merges BN / splits columns.  Four columns' worth of peer
+                // values are requested before the first is used, so the merge costs a quarter of
+                // the round trips through distributed shared memory (same sums, same order).
+                constexpr int BATCH = 4;
+                for (int col0 = (int)rank; col0 < BN; col0 += splits * BATCH) {
+                    float add[BATCH], pg[BATCH][8];
+#pragma unroll
+                    for (int b = 0; b < BATCH; ++b) {
+                        const int col = col0 + b * splits;
+                        add[b] = 0.0f;
+                        if (EPI == EPI_ADD_F32 && col < BN && tok0 + col < prm.M && f < prm.N)
+                            add[b] = prm.addend[(size_t)(tok0 + col) * prm.ldy + f];
+#pragma unroll
+                        for (int r = 0; r < 8; ++r)
+                            pg[b][r] = (r < splits && col < BN)
+                                           ? ld_dsmem_f32(base + (uint32_t)((col * BM + row) * 4), (uint32_t)r) : 0.0f;
+                    }
+#pragma unroll
+                    for (int b = 0; b < BATCH; ++b) {
+                        const int col = col0 + b * splits;
+                        if (col >= BN) break;
+                        float g = 0.0f;
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) g += pg[b][r];
+                        if (!*abort_flag) finish(col, g, EPI == EPI_ADD_F32 ? add[b] : 0.0f, 1.0f);
+                    }
+                }
+            } else
             for (int col = (int)rank; col < BN; col += splits) {
                 // the addend's load is in flight while the partial tiles are fetched
                 float add = 0.0f;
@@ -536,9 +565,10 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
         if (epilogue == EPI_F32) epilogue = EPI_F32_WIDE;
         else if (epilogue == EPI_BF16) epilogue = EPI_BF16_WIDE;
     }
-    // the slices' partial tiles are parked in the ring's shared memory (columns x 128 rows of fp32):
-    // up to 128 columns fit any ring depth, so 128-token tiles split too, with one accumulator
-    if (splits > 1 && (bn_eff > 128 || (bn_eff == 128 && epilogue == EPI_SWIGLU_BF16))) return FWB_UNSUPPORTED;
+    // the slices' partial tiles are parked in the ring's shared memory (columns x 128 rows of fp32,
+    // which the ring is sized for): token tiles up to 128 split, with one accumulator (256-token
+    // tiles were measured too: a cluster of CTAs that each fill an SM gains nothing over the pairs)
+    if (splits > 1 && (bn_eff > 128 || (bn_eff == 128 && epi_accumulators(epilogue) == 2))) return FWB_UNSUPPORTED;
     if ((N + BM - 1) / BM > 65535) return FWB_TOO_LARGE;
     const int total_kb = (K + BK - 1) / BK;
     if (splits > total_kb) splits = total_kb;
