@@ -6,6 +6,7 @@
     python -m flyweight_b200.kernels.microbench attention-prefill --tokens 2048
     python -m flyweight_b200.kernels.microbench shortconv --tokens 2048
     python -m flyweight_b200.kernels.microbench qk-norm-rope --tokens 2048
+    python -m flyweight_b200.kernels.microbench sample --rows 8 --top-k 40
 
 It is what the ncu summaries under ``profiles/`` were captured from (small cases of the same
 kernels the engine runs), and a quick way to see what a shape costs.  Weight matrices are
@@ -158,6 +159,28 @@ def run_qk_norm_rope(args) -> dict:
             "gb_s": T * (nh + 2 * nkv) * hd * 2 * 2 / us / 1e3}
 
 
+def run_sample(args) -> dict:
+    from ..sampling import sampler
+    from ..sampling.config import SamplingConfig
+    rows, vocab = args.rows, args.vocab
+    # enough copies of the logits that the timed reads come from HBM
+    copies = max(2, min(16, int(160e6 // (rows * vocab * 4)) + 1))
+    logits = [torch.randn(rows, vocab, device="cuda") * 3.0 for _ in range(copies)]
+    config = SamplingConfig(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=0.0, seed=1)
+    uniforms = [((i * 37) % 97) / 97.0 for i in range(rows)]
+    turn = [0]
+
+    def step():
+        turn[0] = (turn[0] + 1) % copies
+        if args.temperature <= 0.0:
+            return sampler.argmax(logits[turn[0]])
+        return sampler.sample(logits[turn[0]], [config] * rows, uniforms)
+
+    us = _time(step, args.repeat)
+    return {"kernel": "argmax" if args.temperature <= 0.0 else "sample_kernel", "rows": rows, "vocab": vocab,
+            "top_k": args.top_k, "top_p": args.top_p, "us": us, "gb_s": rows * vocab * 4 / us / 1e3}
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m flyweight_b200.kernels.microbench",
                                      description=__doc__,
@@ -193,12 +216,18 @@ def main(argv=None) -> int:
     rope.add_argument("--heads", type=int, default=32)
     rope.add_argument("--kv-heads", type=int, default=8)
     rope.add_argument("--head-dim", type=int, default=64)
+    smp = sub.add_parser("sample")
+    smp.add_argument("--rows", type=int, default=8)
+    smp.add_argument("--vocab", type=int, default=65536)
+    smp.add_argument("--temperature", type=float, default=0.8, help="0: arg-max")
+    smp.add_argument("--top-k", type=int, default=40, help="0: the whole vocabulary")
+    smp.add_argument("--top-p", type=float, default=0.95)
     for p in sub.choices.values():
         p.add_argument("--repeat", type=int, default=20)
     args = parser.parse_args(argv)
     runner = {"gemm": run_gemm, "attention-decode": run_attention_decode,
               "attention-prefill": run_attention_prefill, "shortconv": run_shortconv,
-              "qk-norm-rope": run_qk_norm_rope}[args.kernel]
+              "qk-norm-rope": run_qk_norm_rope, "sample": run_sample}[args.kernel]
     print(json.dumps(runner(args)))
     return 0
 
