@@ -357,6 +357,49 @@ def run_prefill_lengths(args) -> int:
     return 0
 
 
+def run_chunked_prefill(args) -> int:
+    """One long prompt in portions (``--chunked-prefill lfm2-2.6b:32768x2048``): every portion
+    timed with CUDA events, one JSON line with the whole prompt's rate and what the attention over
+    the cached keys adds between the first and the last portion."""
+    import torch
+    from flyweight_b200.engine import ModelRunner
+    from flyweight_b200.engine.runtime import Model
+    name, _, shape = args.chunked_prefill.partition(":")
+    if name not in MODELS or "x" not in shape:
+        print(json.dumps({"error": f"--chunked-prefill wants MODEL:CONTEXTxPORTION with MODEL in {sorted(MODELS)}"}))
+        return 1
+    context, portion = (int(v) for v in shape.lower().split("x"))
+    peaks = read_peaks()
+    config = dict(MODELS[name])
+    model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
+    runner = ModelRunner(model, num_pages=context // 64 + 2, num_slots=1, max_model_len=context + 64,
+                         max_batched_tokens=portion, use_graphs=False)
+    prompt = torch.randint(0, config["vocab_size"], (context,), generator=torch.Generator().manual_seed(0)).tolist()
+    for _ in range(2):                                  # the second pass is the timed one
+        events = []
+        for start in range(0, context, portion):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            last = start + portion >= context
+            runner.step([("p", prompt[start:start + portion], [len(prompt[start:start + portion]) - 1] if last else [])])
+            end.record()
+            events.append((begin, end))
+        torch.cuda.synchronize()
+        runner.finish("p")
+    ms = [begin.elapsed_time(end) for begin, end in events]
+    heads, head_dim, layers = config["num_attention_heads"], model.config.head_dim, len(config["full_attn_idxs"])
+    attention = sum(4.0 * min(portion, context - s) * (s + min(portion, context - s) / 2) * heads * head_dim * layers
+                    for s in range(0, context, portion))
+    flops = model_flops_per_token(model) * context + attention
+    total = sum(ms)
+    print(json.dumps({"chunked_prefill": True, "model": name, "context": context, "portion": portion,
+                      "ms": total, "tokens_per_s": context / (total / 1e3), "tflops": flops / (total / 1e3) / 1e12,
+                      "frac": flops / (total / 1e3) / (peaks["bf16_tflops"] * 1e12), "of": peaks["source"],
+                      "first_portion_ms": ms[0], "last_portion_ms": ms[-1],
+                      "attention_tflop": attention / 1e12, "portions_ms": [round(m, 2) for m in ms]}))
+    return 0
+
+
 def run_profile_step(args) -> int:
     """One step (decode at batch 8 / context 4,096, or a 2,048-token prefill) between
     cudaProfilerStart/Stop after warm-up, with CUDA graphs off so that every kernel is a launch
@@ -420,6 +463,8 @@ def main() -> int:
                         help="decode steps of lfm2-350m / lfm2-1.2b / lfm2-2.6b at other batches and contexts")
     parser.add_argument("--prefill-lengths", default=None, metavar="N[,N...]",
                         help="time one prompt of each length through one step (lfm2-1.2b)")
+    parser.add_argument("--chunked-prefill", default=None, metavar="MODEL:CONTEXTxPORTION",
+                        help="one long prompt read in portions, e.g. lfm2-2.6b:32768x2048")
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run one step inside cudaProfilerStart/Stop (for a profiler) and exit")
     args = parser.parse_args()
@@ -433,6 +478,8 @@ def main() -> int:
         return run_sizes(args)
     if args.prefill_lengths:
         return run_prefill_lengths(args)
+    if args.chunked_prefill:
+        return run_chunked_prefill(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
