@@ -8,6 +8,7 @@ status; a refusal (a size or dtype the kernel was not written for) becomes a
 from __future__ import annotations
 
 import ctypes
+import re
 from typing import Optional
 
 import torch
@@ -26,7 +27,33 @@ _STATUS = {
 }
 
 _lib: Optional[ctypes.CDLL] = None
+_functions = {}
 _launch_count = 0
+
+
+_C_TYPES = (("*", ctypes.c_void_p), ("cudaStream_t", ctypes.c_void_p), ("unsigned long long", ctypes.c_ulonglong),
+            ("long long", ctypes.c_longlong), ("float", ctypes.c_float), ("unsigned", ctypes.c_uint),
+            ("long", ctypes.c_long), ("int", ctypes.c_int))
+_SIGNATURE = re.compile(r"^FWB_API\s+int\s+(\w+)\s*\(([^)]*)\)", re.MULTILINE)
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    """Argument types of every exported launcher, read from the declarations in the sources
+    (``FWB_API int name(type arg, ...)``): with them a pointer goes in as a plain integer and a
+    call costs no wrapper objects."""
+    for source in _build.sources():
+        for name, params in _SIGNATURE.findall(source.read_text()):
+            types = []
+            for param in (p.strip() for p in params.split(",")):
+                if not param or param == "void":
+                    continue
+                types.append(next(ctype for mark, ctype in _C_TYPES if mark in param))
+            try:
+                function = getattr(lib, name)
+            except AttributeError:
+                continue
+            function.argtypes = types
+            function.restype = ctypes.c_int
 
 
 def library() -> ctypes.CDLL:
@@ -37,6 +64,7 @@ def library() -> ctypes.CDLL:
             _lib = ctypes.CDLL(str(path))
         except OSError as error:
             raise KernelError(f"cannot load the compiled kernels from {path}: {error}") from None
+        _declare(_lib)
     return _lib
 
 
@@ -57,8 +85,9 @@ def require_cuda() -> None:
                           "and there is no CPU fallback")
 
 
-def ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+def ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    """The device address as the launchers take it (None: a null pointer)."""
+    return None if tensor is None else tensor.data_ptr()
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -81,13 +110,13 @@ def use_device(device) -> None:
     _device = torch.cuda.current_device() if index is None else index
 
 
-def stream() -> ctypes.c_void_p:
+def stream() -> int:
     """The current CUDA stream of the engine's device (every launch goes there; CUDA-graph
     capture switches it).  The raw query costs a fraction of a microsecond; the public one,
     with its device bookkeeping, cost more than the launch itself."""
     if _raw_stream is not None:
-        return ctypes.c_void_p(_raw_stream(_device_index()))
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _raw_stream(_device_index()) or None
+    return torch.cuda.current_stream().cuda_stream or None
 
 
 def is_bf16(tensor: torch.Tensor) -> int:
@@ -112,7 +141,10 @@ def check_tensor(name: str, tensor: torch.Tensor, dtype=None, shape=None) -> Non
 def call(name: str, *args, launches: int = 1) -> None:
     """Call launcher ``name`` with ctypes arguments and raise on a non-zero status."""
     global _launch_count
-    status = getattr(library(), name)(*args)
+    function = _functions.get(name)
+    if function is None:
+        function = _functions[name] = getattr(library(), name)
+    status = function(*args)
     if status != 0:
         if status < 0:
             raise KernelError(f"{name} refused its arguments: {_STATUS.get(status, status)}")

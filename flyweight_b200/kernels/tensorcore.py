@@ -5,8 +5,6 @@ back to the SIMT kernel otherwise, so every shape the configuration allows still
 """
 from __future__ import annotations
 
-import ctypes
-
 import torch
 
 from . import lib
@@ -243,7 +241,7 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
 
 def _offset(tensor, elements: int):
     """The address ``elements`` into a contiguous tensor (a slice without making a view)."""
-    return ctypes.c_void_p(tensor.data_ptr() + elements * tensor.element_size())
+    return tensor.data_ptr() + elements * tensor.element_size()
 
 
 def _wave_cut(M: int, F: int) -> int:
