@@ -317,13 +317,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int max_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int group, int tiles_per_split,
                         int window, float scale) {
-    fwb::pdl_entry();
+    fwb::pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __shared__ float merge_ml[WARPS][16][2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, tok = blockIdx.z;
+    // positions, segments and block tables were uploaded before the step's first kernel started,
+    // and every key tile but the token's last one was written by earlier steps: the first tile
+    // of a slice that does not hold the token itself is fetched before the wait for the previous
+    // kernel (which writes this step's keys and the queries)
     const int pos = positions[tok];
     const int lo_key = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
     const int* table = block_table + (size_t)tok_seg[tok] * max_pages;
@@ -331,6 +335,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int tile_begin = first_tile + split * tiles_per_split;
     int tile_end = tile_begin + tiles_per_split;
     if (tile_end > last_tile + 1) tile_end = last_tile + 1;
+
+    auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
+    auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
+    auto issue = [&](int tile, int s) {
+        const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
+        load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
+        cp_async_commit();
+    };
+    const bool early = tile_begin < tile_end && tile_begin < last_tile;
+    if (early) issue(tile_begin, 0);
+    fwb::pdl_wait();
 
     // rows 0..group-1 are the group's query heads; the rest are padding
     const __nv_bfloat16* qrow0 = g < group ? q + ((size_t)tok * nh + kvh * group + g) * HD : nullptr;
@@ -347,14 +362,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         for (int j = 0; j < 4; ++j) o[n][j] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
-    auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
-    auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
-    auto issue = [&](int tile, int s) {
-        const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
-        load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
-        cp_async_commit();
-    };
-    if (tile_begin < tile_end) issue(tile_begin, 0);
+    if (tile_begin < tile_end && !early) issue(tile_begin, 0);
     for (int tile = tile_begin; tile < tile_end; ++tile) {
         const int s = (tile - tile_begin) & 1;
         if (tile + 1 < tile_end) {
