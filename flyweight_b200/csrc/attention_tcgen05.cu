@@ -9,10 +9,11 @@
 //                  128-byte swizzle), D = S [128 x 64] fp32 in tensor memory
 //   softmax        four warps, one query row per thread (tcgen05.ld gives a thread its row, so
 //                  the row maximum and sum need no shuffles): scale, causal/window mask,
-//                  P = 2^(S - m) rounded to bfloat16 into shared memory
-//   O += P V       tcgen05.mma, A = P [128 x 64], B = V [64 keys x hd] exactly as TMA left it (the
-//                  head dimension contiguous: an MN-major operand), D = O [128 x hd] fp32, which
-//                  accumulates in tensor memory over all key tiles
+//                  P = 2^(S - m) rounded to bfloat16 and stored back (tcgen05.st) into the columns
+//                  of tensor memory the scores came from
+//   O += P V       tcgen05.mma, A = P [128 x 64] read from tensor memory, B = V [64 keys x hd] exactly
+//                  as TMA left it (the head dimension contiguous: an MN-major operand), D = O
+//                  [128 x hd] fp32, which accumulates in tensor memory over all key tiles
 //
 // m is the maximum the exponents are taken against.  It is moved to the row's true running
 // maximum only when that has grown by more than 2^8 since m was set; then the row's O in tensor
@@ -21,7 +22,8 @@
 // softmax warps' loop is: load S, maximum, exponentials, store P -- no pass over O per tile.
 //
 // The scores of tile j+1 are computed (into a second S buffer) while the softmax of tile j runs,
-// and P has two buffers, so neither the tensor core nor the softmax warps wait for the other.
+// and P lives in its own tile's buffer, so neither the tensor core nor the softmax warps wait for
+// the other; P never passes through shared memory (no proxy fence, no shared-memory traffic).
 //
 // A CTA takes two work items (row tile, KV head): the heaviest and the lightest that are left,
 // which evens out what the causal mask makes uneven.
@@ -56,12 +58,10 @@ struct Layout {
     static constexpr int BOXES = HD / 64;                    // 64-element (128-byte) column blocks
     static constexpr int Q_BOX = ROWS * 128;
     static constexpr int Q_BYTES = BOXES * Q_BOX;
-    static constexpr int P_BOX = ROWS * 128;
-    static constexpr int P_BYTES = 2 * P_BOX;                // P of tile g in buffer g & 1
     static constexpr int KV_BOX = KEYS * 128;
     static constexpr int KV_BYTES = BOXES * KV_BOX;          // one K or one V tile
-    static constexpr int STAGES = 3;                         // ring slots, each one K tile and one V tile
-    static constexpr int DATA = Q_BYTES + P_BYTES + 2 * STAGES * KV_BYTES;
+    static constexpr int STAGES = 4;                         // ring slots, each one K tile and one V tile
+    static constexpr int DATA = Q_BYTES + 2 * STAGES * KV_BYTES;
     static constexpr int SMEM = DATA + 1024 + 256;           // alignment slack + barriers
     static constexpr int S_COLS = 2 * KEYS;                  // two S buffers at column 0, PV behind them
     static constexpr int TMEM_COLS = 256;
@@ -123,6 +123,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// A x B with A (P, bfloat16 pairs in 32-bit columns) read from tensor memory.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 template <int HD>
 __global__ void __launch_bounds__(THREADS, HD == 64 ? 2 : 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
@@ -131,14 +142,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_s = base;
-    uint8_t* p_s = q_s + L::Q_BYTES;
-    uint8_t* k_s = p_s + L::P_BYTES;
+    uint8_t* k_s = q_s + L::Q_BYTES;
     uint8_t* v_s = k_s + L::STAGES * L::KV_BYTES;
     uint64_t* full = reinterpret_cast<uint64_t*>(base + L::DATA);
     uint64_t* empty = full + L::STAGES;
     uint64_t* q_ready = empty + L::STAGES;
     uint64_t* s_ready = q_ready + 1;                       // [2]: one per S buffer
-    uint64_t* p_ready = s_ready + 2;                       // [2]: one per P buffer
+    uint64_t* p_ready = s_ready + 2;                       // [2]: P of a tile is in its S buffer
     uint64_t* pv_ready = p_ready + 2;                      // [2]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_ready + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -213,12 +223,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             constexpr uint32_t idesc_qk = make_idesc_mn(ROWS, KEYS);
             constexpr uint32_t idesc_pv = make_idesc_mn(ROWS, HD) | IDESC_B_MN_MAJOR;
             const uint32_t tmem_pv = tmem_base + L::S_COLS;
-            const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+            const uint32_t q_addr = smem_u32(q_s);
             bool ok = true;
             // S of tile g goes to buffer g & 1, so that the softmax of one tile runs while the
             // tensor core already computes the scores of the next.  One thread issues everything,
             // so a commit also covers every product issued before it: when S of tile g is ready,
-            // PV of tile g-2 has read its P buffer, the one P of tile g will overwrite.
+            // PV of tile g-2 has read its P, which lay in the buffer S and P of tile g use.
             auto wait_step = [&](int u) {
                 const int s = u % L::STAGES;
                 ok = ok && mbar_wait(&full[s], (u / L::STAGES) & 1, abort_flag, 13, prm.status);
@@ -254,10 +264,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                     const uint32_t v_addr = smem_u32(v_s + (size_t)s * L::KV_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < KEYS / UMMA_K; ++kk) {
-                        const uint64_t a = make_smem_desc(p_addr + (g & 1) * L::P_BOX) + 2 * kk;
                         // 16 keys further: two 8-row groups of 1024 bytes
                         const uint64_t b = make_smem_desc_mn_major(v_addr + kk * 2048, L::KV_BOX);
-                        umma_bf16(tmem_pv, a, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);   // O accumulates over the item's tiles
+                        const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;               // O accumulates over the item's tiles
+                        // P of tile g lies in the first 32 columns of its S buffer: 16 keys = 8 columns
+                        umma_bf16_a_tmem(tmem_pv, tmem_base + (g & 1) * KEYS + kk * 8, b, idesc_pv, acc);
                     }
                     umma_commit(&pv_ready[g & 1]);
                     if (j + LEAD < item.n_tiles) issue_qk(g + LEAD, s);
@@ -359,13 +370,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                     packed[i >> 1] = pack2(p0, p1);
                 }
                 l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-                // this P buffer was read by PV of the tile before the last, which had completed when
-                // this tile's S was ready (see the MMA issuer)
-                uint8_t* p_row = p_s + buf * L::P_BOX + row * 128;
+                // P goes back into the columns its scores came from (bfloat16 pairs in the first 32 of
+                // the buffer's 64 columns): the PV product reads it from tensor memory.  The buffer's
+                // last reader, PV of the tile before the last, had completed when this tile's S was
+                // ready, and PV of this tile is issued before the scores of tile g + 2 overwrite it
+                float as_bits[KEYS / 2];
 #pragma unroll
-                for (int c = 0; c < KEYS / 8; ++c)
-                    *reinterpret_cast<uint4*>(p_row + ((c ^ swz) << 4)) =
-                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                for (int i = 0; i < KEYS / 2; ++i) as_bits[i] = __uint_as_float(packed[i]);
+                tmem_st32(lane_addr + buf * KEYS, as_bits);
+                tc_fence_before();
                 const int seen = item.pos_last - key0 + 1;                // keys of this tile anybody may see
                 if (seen < KEYS) {
                     // only the last tile: clear the V rows beyond it (whole 128-byte rows of every box)
@@ -377,7 +390,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                         for (int i = threadIdx.x - 64; i < chunks; i += 32 * SOFTMAX_WARPS)
                             *reinterpret_cast<uint4*>(v_tile + b * L::KV_BOX + seen * 128 + i * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
-                fence_proxy_async();
+                if (seen < KEYS) fence_proxy_async();        // the cleared V rows, for the tensor core
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[buf]);
             }
