@@ -184,3 +184,45 @@ def test_launching_the_next_step_before_reading_this_one_changes_nothing():
     assert fast == slow and fast_log == slow_log
     assert steady > 20
     assert len(slow[2]) <= 26 and any(len(a) < len(b) for a, b in zip(slow, plain))
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_random_workloads_through_the_runtime(name):
+    """A few dozen random workloads (how many requests at a time, how many pages, which token
+    budget, which lengths are all drawn): every request's greedy tokens equal the plain
+    implementation's, whatever the scheduler made of them (portions, mixed steps, graphs,
+    steady decoding one step ahead, pages used again)."""
+    import random
+    cfg, w = plain_model(name, "float32")
+    rnd = random.Random(17)
+    from flyweight_b200 import Model
+    model = Model(model_dir(name, "float32"), dtype="float32")
+    checked = 0
+    for _ in range(12):
+        limit = rnd.choice([128, 192, 320])
+        runtime = model.native_runtime(context_limit=limit, parallel_sequences=rnd.choice([1, 2, 3, 4]),
+                                       max_batched_tokens=rnd.choice([16, 48, 256]))
+        requests = {}
+        for _ in range(rnd.randint(1, 6)):
+            new = rnd.randint(1, 40)
+            prompt = [rnd.randrange(cfg["vocab_size"]) for _ in range(min(rnd.randint(1, 90), limit - new - 1))]
+            requests[runtime.task_submit(prompt, new)] = (prompt, new, [])
+        steps = 0
+        while runtime.has_work():
+            for task, token, kind in runtime.engine_step():
+                assert kind != 2, runtime.task_error(task)
+                if kind == 0:
+                    requests[task][2].append(token)
+            steps += 1
+            assert steps < 5000, "the runtime does not finish"
+        runtime.close()
+        for prompt, new, got in requests.values():
+            want = P.greedy_generate(cfg, w, prompt, new)
+            if got != want:
+                # 32-bit against float64: only a near-tie between the two best logits may differ
+                k = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), min(len(got), len(want)))
+                top = np.sort(P.forward(cfg, w, prompt + want[:k])[-1])[-2:]
+                assert len(got) == len(want) and top[1] - top[0] <= 1e-4 * max(1.0, abs(top[1])), \
+                    f"{name}: request of {len(prompt)} + {new} tokens: got {got}, want {want}"
+            checked += 1
+    assert checked >= 12
