@@ -106,7 +106,8 @@ def run_portions(runner, rid, tokens, sizes) -> np.ndarray:
     return np.concatenate(outs)
 
 
-def mixed_trace(lengths, vocab, num_pages, max_live=4, seed=0, tail=32, name_prefix="r"):
+def mixed_trace(lengths, vocab, num_pages, max_live=4, seed=0, tail=32, name_prefix="r",
+                sizes=(1, 2, 3, 7, 16, 33, 64, 2, 5)):
     """A trace of steps over several requests: up to ``max_live`` live at a time, portions of
     changing size for the body of each request and its last ``tail`` tokens one by one,
     requests starting as soon as the pool has pages for their whole length (so pages and
@@ -121,7 +122,7 @@ def mixed_trace(lengths, vocab, num_pages, max_live=4, seed=0, tail=32, name_pre
     live, done_pos = [], {}
     free = num_pages
     steps = []
-    sizes = [1, 2, 3, 7, 16, 33, 64, 2, 5]
+    sizes = list(sizes)
     while waiting or live:
         while waiting and len(live) < max_live and pages_of[waiting[0]] <= free:
             rid = waiting.pop(0)

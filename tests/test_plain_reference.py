@@ -106,3 +106,23 @@ def test_host_rng_equals_the_plain_one():
     for seed in (1, 7, 2 ** 63 + 5, 0):
         mine, plain = XorShift64Star(seed), P.XorShift64Star(seed)
         assert [mine.uniform() for _ in range(5)] == [plain.uniform() for _ in range(5)]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_the_torch_spelling_of_the_plain_forward_equals_the_numpy_one(name, tmp_path):
+    """``plain_lfm2_torch`` (float64 torch, used at real layer sizes on the GPU) and
+    ``plain_lfm2`` (float64 numpy) on both tiny configurations: same logits, and the same rows
+    when only some positions are asked for."""
+    import torch
+    import plain_lfm2_torch as PT
+    from tiny_configs import TINY, make_model_dir
+    folder = make_model_dir(tmp_path / name, TINY[name], seed=5, dtype=torch.bfloat16)
+    tokens = [int(t) for t in np.random.default_rng(3).integers(0, TINY[name]["vocab_size"], size=70)]
+    cfg, w = P.load_model_dir(folder)
+    want = P.forward(cfg, w, tokens)
+    cfg_t, w_t = PT.load_model_dir(folder)
+    got = PT.forward(cfg_t, w_t, tokens)
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-10 * max(1.0, np.abs(want).max()))
+    rows = [0, 1, 33, 69]
+    np.testing.assert_allclose(PT.forward(cfg_t, w_t, tokens, rows=rows), want[rows], rtol=0,
+                               atol=1e-10 * max(1.0, np.abs(want).max()))
