@@ -485,9 +485,12 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
     __syncthreads();
     const RowParams prm = params[r];
     const float* row = logits + (size_t)r * V;
-    const bool penalize = prm.n_recent > 0 && (prm.repetition_penalty != 1.0f ||
-                          prm.presence_penalty != 0.0f || prm.frequency_penalty != 0.0f);
     const int k = prm.top_k > 0 ? (prm.top_k < V ? prm.top_k : V) : V;
+    // a row with more than SMALL_K candidates arrives with its penalties already applied to its
+    // logits (fwb_penalize_rows), so its history is not looked at here
+    const bool penalize = k <= SMALL_K && prm.n_recent > 0 &&
+                          (prm.repetition_penalty != 1.0f || prm.presence_penalty != 0.0f ||
+                           prm.frequency_penalty != 0.0f);
 
     unsigned long long best = 0ull;
     sweep<false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
@@ -589,6 +592,39 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
     cluster_barrier();                              // no CTA leaves while a peer still reads its shared memory
 }
 
+// Rows that keep more than SMALL_K candidates (the whole vocabulary among them) are never sorted,
+// so their penalties cannot act on a sorted candidate list.  For those rows the penalties are
+// applied to the row's logits themselves, over the whole vocabulary and before any cut, which is
+// the order of flyweight's host sampler (src/flyweight/v2.py:1497-1518); the sampler then sees
+// the row without a history.  One block per row; the thread that holds the first occurrence of
+// a token id in the history applies all of that id's penalties.
+__global__ void __launch_bounds__(MAX_RECENT)
+penalize_rows_kernel(float* __restrict__ logits, int V, const RowParams* __restrict__ params,
+                     const int* __restrict__ recent, int recent_stride) {
+    fwb::pdl_entry();
+    const int r = blockIdx.x;
+    const RowParams prm = params[r];
+    const int k = prm.top_k > 0 ? (prm.top_k < V ? prm.top_k : V) : V;
+    if (prm.n_recent <= 0 || k <= SMALL_K) return;
+    const int* rec = recent + (size_t)r * recent_stride;
+    const int j = threadIdx.x;
+    if (j >= prm.n_recent) return;
+    const int id = rec[j];
+    if (id < 0 || id >= V) return;
+    int occurrences = 0;
+    for (int i = 0; i < prm.n_recent; ++i) {
+        if (rec[i] != id) continue;
+        if (i < j) return;                          // an earlier thread owns this id
+        ++occurrences;
+    }
+    float logit = logits[(size_t)r * V + id];
+    if (prm.repetition_penalty != 1.0f)
+        logit = logit > 0.0f ? logit / prm.repetition_penalty : logit * prm.repetition_penalty;
+    logit -= prm.presence_penalty;
+    logit -= prm.frequency_penalty * (float)occurrences;
+    logits[(size_t)r * V + id] = logit;
+}
+
 }  // namespace
 
 // With scratch (partial: R*chunks keys of 8 bytes, counters: R zeroed ints) a row is cut into
@@ -645,4 +681,18 @@ FWB_API int fwb_sample(const float* logits, int R, int V, const void* params, co
     cudaError_t e = cudaLaunchKernelEx(&config, sample_kernel, logits, V, Vpad, (const RowParams*)params, uniform,
                                        recent, recent_stride, (unsigned long long*)keys_scratch, out);
     return e == cudaSuccess ? fwb_launch_status() : (int)e;
+}
+
+// In place on a copy of the logits that the caller owns: the penalties of every row that keeps
+// more than 1024 candidates (see penalize_rows_kernel).  Same params and recent arrays as
+// fwb_sample, which is then called with those rows' histories emptied.
+FWB_API int fwb_penalize_rows(float* logits, int R, int V, const void* params, const int* recent,
+                              int recent_stride, cudaStream_t stream) {
+    if (R <= 0 || recent_stride <= 0) return FWB_OK;
+    if (!logits || !params || !recent || V <= 0) return FWB_BAD_ARGUMENT;
+    if (recent_stride > MAX_RECENT) return FWB_BAD_ARGUMENT;
+    if (R > 65535) return FWB_TOO_LARGE;
+    fwb::pdl(penalize_rows_kernel, R, MAX_RECENT, 0, stream)(logits, V, (const RowParams*)params, recent,
+                                                             recent_stride);
+    return fwb_launch_status();
 }

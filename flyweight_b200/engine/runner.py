@@ -29,7 +29,12 @@ Entry = Tuple[Hashable, Sequence[int], Sequence[int]]
 
 
 class StepError(ValueError):
-    """An entry the step function refuses (bad token id, empty portion, over-long request)."""
+    """An entry the step function refuses (bad token id, empty portion, over-long request).
+    ``request`` names the entry at fault when there is one (None: the step as a whole)."""
+
+    def __init__(self, message: str, request: Hashable = None):
+        super().__init__(message)
+        self.request = request
 
 
 def _token_array(request, tokens):
@@ -40,13 +45,13 @@ def _token_array(request, tokens):
         try:
             return [int(tokens[0])]
         except (TypeError, ValueError) as error:
-            raise StepError(f"request {request!r}: token ids must be integers ({error})") from None
+            raise StepError(f"request {request!r}: token ids must be integers ({error})", request) from None
     try:
         array = np.asarray(tokens, dtype=np.int64)
     except (OverflowError, TypeError, ValueError) as error:
-        raise StepError(f"request {request!r}: token ids must be integers ({error})") from None
+        raise StepError(f"request {request!r}: token ids must be integers ({error})", request) from None
     if array.ndim != 1:
-        raise StepError(f"request {request!r}: tokens must be a flat list of ids")
+        raise StepError(f"request {request!r}: tokens must be a flat list of ids", request)
     return array
 
 
@@ -68,10 +73,10 @@ class StepPlanner:
         total = 0
         for request, tokens, want in entries:
             if request in seen:
-                raise StepError(f"request {request!r} appears twice in one step")
+                raise StepError(f"request {request!r} appears twice in one step", request)
             seen.add(request)
             if len(tokens) == 0:
-                raise StepError(f"request {request!r} brings no tokens")
+                raise StepError(f"request {request!r} brings no tokens", request)
             if len(tokens) == 1:
                 low = high = int(tokens[0])
             else:
@@ -79,15 +84,15 @@ class StepPlanner:
             if low < 0 or high >= vocab:                                 # native/src/v2_runtime.cpp:27530
                 token = next(int(t) for t in tokens if not 0 <= int(t) < vocab)
                 raise StepError(f"token id {token} of request {request!r} is outside "
-                                f"[0, {vocab})")
+                                f"[0, {vocab})", request)
             for place in want:
                 if not 0 <= int(place) < len(tokens):
                     raise StepError(f"request {request!r} wants logits at place {place} of "
-                                    f"{len(tokens)} tokens")
+                                    f"{len(tokens)} tokens", request)
             have = self.cache.length(request) if self.cache.has(request) else 0
             if have + len(tokens) > self.max_model_len:
                 raise StepError(f"request {request!r} would reach {have + len(tokens)} tokens, "
-                                f"beyond max_model_len {self.max_model_len}")
+                                f"beyond max_model_len {self.max_model_len}", request)
             total += len(tokens)
         if total > self.max_batched_tokens:
             raise StepError(f"step of {total} tokens exceeds max_batched_tokens "
@@ -99,12 +104,17 @@ class StepPlanner:
         cache = self.cache
         needs = [0] * len(cache.groups)
         for request, tokens, _ in entries:
-            have = 0
-            if cache.has(request):
-                cache.release_passed(request)
-                have = cache.length(request)
-            for g, need in enumerate(cache.pages_needed(request, have + len(tokens))):
-                needs[g] += need
+            try:
+                have = 0
+                if cache.has(request):
+                    cache.release_passed(request)
+                    have = cache.length(request)
+                for g, need in enumerate(cache.pages_needed(request, have + len(tokens))):
+                    needs[g] += need
+            except Exception as error:
+                if getattr(error, "request", None) is None:
+                    error.request = request         # whose bookkeeping failed: it alone is given up
+                raise
         return sum(max(0, need - group.pool.n_free) for need, group in zip(needs, cache.groups))
 
     # ------------------------------------------------------------------ planning

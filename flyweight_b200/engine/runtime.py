@@ -23,7 +23,7 @@ from ..config.registry import load_config
 from ..sampling import sampler as device_sampler
 from ..sampling.config import GREEDY, SamplingConfig
 from .loading import load_model, parse_dtype, random_model
-from .runner import ModelRunner
+from .runner import ModelRunner, StepError
 from .scheduler import (EVENT_ERROR, EVENT_FINISHED, EVENT_PROGRESS, EVENT_TOKEN, Scheduler, Task)
 
 
@@ -155,10 +155,18 @@ class Runtime:
                 self._counters["step_seconds"] += time.perf_counter() - started
                 return events
         step = scheduler.schedule()
+        logits = None
+        while step.entries and logits is None:
+            try:
+                logits = runner.step(step.entries, pages_checked=True)
+            except StepError as error:
+                # the step function refuses one request's entry before anything is launched or
+                # mapped: that request fails alone, the step runs without it
+                if not scheduler.fail_scheduled(step, error.request, str(error)):
+                    raise
         events = list(step.events)
         if not step.entries:
             return events
-        logits = runner.step(step.entries, pages_checked=True)
         need = scheduler.advance(step)
         for task in step.tasks:
             if task not in need:
@@ -182,11 +190,20 @@ class Runtime:
         self._counters["sampling_seconds"] += time.perf_counter() - sampled
         finished = False
         for task, token in zip(need, host):
-            accepted = self.scheduler.accept(task, token)
+            accepted = self._accept(task, token)
             finished = finished or len(accepted) > 1
             events.extend(accepted)
         if finished:
             self.runner.check_health()          # once per finished request: kernels fail loudly
+
+    def _accept(self, task, token) -> List[Tuple[int, int, int]]:
+        """Hand a sampled token to its request.  An exception in one request's host bookkeeping
+        ends that request with an error event; the others are not touched.  (A device error is
+        another matter: ``check_health`` raises for the whole engine.)"""
+        try:
+            return self.scheduler.accept(task, token)
+        except Exception as error:
+            return self.scheduler.fail(task, f"{type(error).__name__}: {error}")
 
     # ------------------------------------------------------------------ steady decoding
     def _steady_step(self):
@@ -269,7 +286,7 @@ class Runtime:
         for task, token in zip(step["tasks"], host):
             if task.state != "running":
                 continue
-            accepted = self.scheduler.accept(task, token)
+            accepted = self._accept(task, token)
             finished = finished or len(accepted) > 1
             events.extend(accepted)
         if finished:

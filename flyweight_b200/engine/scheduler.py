@@ -150,6 +150,53 @@ class Scheduler:
         task.error = error
         self.stats["failed" if error else "finished"] += 1
 
+    def fail(self, task: Task, message: str) -> List[Tuple[int, int, int]]:
+        """Give up ``task`` alone with an error event: what it holds goes back, the others go on
+        (per-task catch of native/src/v2_runtime.cpp:33788-33797).  If even the release of what it
+        holds raises, the task is still taken off the lists, so that it cannot be scheduled again."""
+        if task.state == "finished":
+            return []
+        try:
+            self._finish(task, "error", message)
+        except Exception as error:                         # its own bookkeeping is what is broken
+            if task in self.running:
+                self.running.remove(task)
+            if task in self.waiting:
+                self.waiting.remove(task)
+            task.state, task.finish_reason = "finished", "error"
+            task.error = f"{message}; while giving back what it held: {error}"
+            self.stats["failed"] += 1
+        return [(task.id, 0, EVENT_ERROR)]
+
+    def fail_scheduled(self, step: "ScheduledStep", request, message: str) -> bool:
+        """The step function refused the entry of ``request``: fail that task, take its entry out
+        of the step.  False if the step holds no such entry."""
+        for index, task in enumerate(step.tasks):
+            if task.id == request:
+                del step.tasks[index], step.entries[index]
+                step.events.extend(self.fail(task, message))
+                step.failed.append(task.id)
+                return True
+        return False
+
+    def _pages_short(self, entries, chosen: List[Task], step: "ScheduledStep", extra=()) -> int:
+        """``planner.pages_short`` for the step's entries (and ``extra`` ones, asked about but not
+        part of the step).  A request whose own bookkeeping raises there fails alone: its entry
+        leaves the step, and the question is asked again without it."""
+        while True:
+            try:
+                return self.planner.pages_short(entries + list(extra))
+            except Exception as error:
+                task = self.tasks.get(getattr(error, "request", None))
+                if task is None or task.state == "finished":
+                    raise
+                step.events.extend(self.fail(task, f"{type(error).__name__}: {error}"))
+                step.failed.append(task.id)
+                if task in chosen:
+                    index = chosen.index(task)
+                    del chosen[index], entries[index]
+                extra = [entry for entry in extra if entry[0] != task.id and entry[0] != ("spare", task.id)]
+
     def _preempt(self, task: Task) -> None:
         self.running.remove(task)
         self.planner.finish(task.id)
@@ -174,15 +221,20 @@ class Scheduler:
         chosen: List[Task] = []
         entries = []
         for decoding in (True, False):
-            for task in self.running:
+            for task in list(self.running):
                 if (task.pending == 1) != decoding or budget <= 0 or task in chosen:
                     continue
-                entry = self._portion(task, budget)
+                try:
+                    entry = self._portion(task, budget)
+                except Exception as error:
+                    step.events.extend(self.fail(task, f"{type(error).__name__}: {error}"))
+                    step.failed.append(task.id)
+                    continue
                 budget -= len(entry[1])
                 chosen.append(task)
                 entries.append(entry)
         # make the step of the running requests fit, preempting the newest if it does not
-        while entries and self.planner.pages_short(entries):
+        while entries and self._pages_short(entries, chosen, step):
             victim = max(self.running, key=lambda t: t.admitted_at)
             if len(self.running) == 1:
                 self._finish(victim, "error", "the request does not fit the cache pool")
@@ -203,7 +255,10 @@ class Scheduler:
                 break                                   # just evicted: not in the same step
             whole = (task.id, range(len(task.prompt) + len(task.generated)), [])   # only its length counts
             spare = [(("spare", task.id), [0] * PAGE_SIZE, [])]
-            if self.planner.pages_short(entries + [whole] + spare):
+            short = self._pages_short(entries, chosen, step, [whole] + spare)
+            if task.state == "finished":
+                continue                                # its own bookkeeping failed: it is gone
+            if short:
                 if chosen or self.running:
                     break                               # wait until someone finishes
                 # nothing else is live: it gets the pool to itself, or can never run

@@ -4,7 +4,8 @@ One launch for a batch of greedy rows (argmax, ties to the lowest id -- the orde
 flyweight's fused argmax gives, native/include/flyweight_v2_qwen_kernels.hpp:2392-2398);
 one launch for rows that sample (top-k, penalties, temperature, top-p, min-p, draw: the
 order of native/src/v2_runtime.cpp:29331-29744); rows that keep more than 1024 candidates
-(the whole vocabulary among them) need a scratch word per logit and are not sorted at all.
+(the whole vocabulary among them) need a scratch word per logit and are not sorted at all,
+and take their penalties on the whole row before the cut (src/flyweight/v2.py:1497-1518).
 """
 from __future__ import annotations
 
@@ -83,15 +84,14 @@ def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Se
         recent = list(recents[r])[-cfg.penalty_window:] if (recents and cfg.penalizes) else []
         rows.append(recent)
         stride = max(stride, len(recent))
-    need_large = False
+    need_large = penalize_rows = False
     blob = bytearray()
     for cfg, recent in zip(configs, rows):
         k = min(cfg.top_k, V) if cfg.top_k > 0 else V
         sampled = (cfg.temperature > 0.0 or bool(recent)) and k > 1
         if sampled and k > SMALL_K:
-            if recent:
-                raise KernelError("penalties need 0 < top_k <= 1024 (they act on the candidates)")
             need_large = True
+            penalize_rows = penalize_rows or bool(recent)
         blob += struct.pack("<fifffffi", cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p,
                             cfg.repetition_penalty, cfg.presence_penalty, cfg.frequency_penalty,
                             len(recent))
@@ -115,6 +115,12 @@ def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Se
         while vpad < V:
             vpad <<= 1
         keys = torch.empty((R, vpad), dtype=torch.int64, device=device)     # fixed-point masses
+    if penalize_rows:
+        # rows that are never sorted take their penalties on the logits themselves, over the whole
+        # vocabulary and before any cut (src/flyweight/v2.py:1497-1518); on a copy, the caller's
+        # logits stay as they are
+        logits = logits.clone()
+        lib.call("fwb_penalize_rows", ptr(logits), R, V, ptr(params), ptr(recent_dev), stride, stream())
     lib.call("fwb_sample", ptr(logits), R, V, ptr(params), ptr(uni), ptr(recent_dev), stride,
              ptr(out), ptr(keys), ptr(probs), vpad, 1 if need_large else 0, stream())
     return out

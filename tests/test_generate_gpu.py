@@ -226,3 +226,60 @@ def test_random_workloads_through_the_runtime(name):
                     f"{name}: request of {len(prompt)} + {new} tokens: got {got}, want {want}"
             checked += 1
     assert checked >= 12
+
+
+def test_one_bad_request_fails_alone():
+    """A request whose text is damaged after it was queued (a token id outside the vocabulary: the
+    step function refuses the entry before anything is launched), and one whose host bookkeeping
+    raises when its token is accepted: each ends with an error event and its message, what it held
+    goes back, and the other requests produce the tokens they produce without them."""
+    name = "A"
+    cfg, w = plain_model(name, "float32")
+    prompts = [random_tokens(name, n, seed=70 + n) for n in (12, 30, 45, 9)]
+    with open_runtime(name, "float32", context_limit=128, parallel_sequences=4,
+                      max_batched_tokens=16) as runtime:
+        ids = [runtime.task_submit(p, 10) for p in prompts]
+        runtime.task(ids[1]).prompt[20] = cfg["vocab_size"] + 5      # reached in its second portion
+        runtime.task(ids[3]).stop_tokens = None                      # `token in None` raises
+        events = []
+        steps = 0
+        while runtime.has_work():
+            events.extend(runtime.engine_step())
+            steps += 1
+            assert steps < 500
+        assert events.count((ids[1], 0, 2)) == 1 and events.count((ids[3], 0, 2)) == 1
+        assert "outside" in runtime.task_error(ids[1])
+        assert "TypeError" in runtime.task_error(ids[3])
+        for i in (0, 2):
+            assert runtime.task(ids[i]).generated == P.greedy_generate(cfg, w, prompts[i], 10)
+            assert runtime.task_error(ids[i]) is None
+        info = runtime.info
+        assert info["failed"] == 2 and info["cache"]["slots_in_use"] == 0
+        assert info["cache"]["groups"][0]["pages_in_use"] == 0
+        # the runtime goes on serving
+        assert runtime.generate(prompts[0], 10) == P.greedy_generate(cfg, w, prompts[0], 10)
+
+
+def test_penalties_with_the_whole_vocabulary_as_candidates_run_to_the_end():
+    """top_k 0 (every token a candidate) or above 1,024 together with penalties: accepted at
+    submit and sampled on the device like any other request, beside a greedy neighbour."""
+    name = "B"
+    cfg, w = plain_model(name, "float32")
+    prompts = [random_tokens(name, n, seed=75 + n) for n in (8, 20, 14)]
+    with open_runtime(name, "float32", context_limit=96, parallel_sequences=3) as runtime:
+        a = runtime.task_submit(prompts[0], 30, temperature=0.7, top_k=0, top_p=0.9, min_p=0.0, seed=4,
+                                repetition_penalty=1.4, frequency_penalty=0.3)
+        b = runtime.task_submit(prompts[1], 30)
+        c = runtime.task_submit(prompts[2], 30, temperature=0.0, top_k=0, repetition_penalty=2.0,
+                                presence_penalty=1.0)
+        steps = 0
+        while runtime.has_work():
+            for task, _, kind in runtime.engine_step():
+                assert kind != 2, runtime.task_error(task)
+            steps += 1
+            assert steps < 200
+        assert len(runtime.task(a).generated) == 30 and len(runtime.task(c).generated) == 30
+        assert runtime.task(b).generated == P.greedy_generate(cfg, w, prompts[1], 30)
+        # greedy under a strong repetition penalty does not settle into a loop of one token
+        tail = runtime.task(c).generated[-10:]
+        assert len(set(tail)) > 1

@@ -493,6 +493,51 @@ def test_penalties_act_on_the_candidates():
     assert got == [4, 4]              # 5-0.5=4.5 ties 4.5 -> lower id; 5-0.8=4.2 > 4.5-1.1
 
 
+def test_penalties_over_the_whole_vocabulary_and_above_1024_candidates():
+    """Rows that keep more than 1,024 candidates are never sorted; their penalties act on the row
+    itself before the cut (src/flyweight/v2.py:1497-1518).  Against that rule in numpy followed by
+    the plain sampler, draw for draw, beside rows of the sorted path in the same launch."""
+    from collections import Counter
+    from flyweight_b200.sampling import SamplingConfig, sampler
+    V = 5000
+    g = torch.Generator().manual_seed(77)
+    settings = [dict(temperature=0.9, top_k=0, top_p=0.9, min_p=0.0, repetition_penalty=1.7,
+                     presence_penalty=0.5, frequency_penalty=0.25),
+                dict(temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, repetition_penalty=2.0),
+                dict(temperature=1.1, top_k=3000, top_p=1.0, min_p=0.01, frequency_penalty=1.5, penalty_window=5),
+                dict(temperature=0.8, top_k=40, top_p=0.95, min_p=0.05, repetition_penalty=1.3)]
+    for trial in range(5):
+        logits = torch.randn(len(settings), V, generator=g) * 3
+        best = [int(i) for i in logits.argmax(dim=1)]
+        recents = [[best[0], best[0], 17, best[0], 4999], [best[1], 3], [1, 2, best[2], best[2], best[2], best[2], 9],
+                   [best[3], 11]]
+        uniforms = [P.XorShift64Star(300 + trial * 10 + i).uniform() for i in range(len(settings))]
+        want = []
+        for i, s in enumerate(settings):
+            row = logits[i].numpy().copy()
+            cfg = SamplingConfig(**s)
+            if (s["top_k"] or V) > 1024:
+                window = recents[i][-cfg.penalty_window:]
+                for t, count in Counter(window).items():
+                    value = row[t]
+                    if cfg.repetition_penalty != 1.0:
+                        value = value / np.float32(cfg.repetition_penalty) if value > 0 else value * np.float32(cfg.repetition_penalty)
+                    value = np.float32(value) - np.float32(cfg.presence_penalty)
+                    row[t] = np.float32(value) - np.float32(cfg.frequency_penalty) * np.float32(count)
+                want.append(P.sample(row, rng=P.XorShift64Star(300 + trial * 10 + i), temperature=s["temperature"],
+                                     top_k=s["top_k"], top_p=s["top_p"], min_p=s["min_p"]))
+            else:
+                want.append(None)
+        device_logits = dev(logits)
+        kept = device_logits.clone()
+        got = sampler.sample(device_logits, [SamplingConfig(**s) for s in settings], uniforms, recents).tolist()
+        assert torch.equal(device_logits, kept)                    # the caller's logits are not touched
+        assert got[:3] == want[:3], (trial, got, want)
+        assert got[1] != best[1]                                   # the repeated best token lost its place
+        alone = sampler.sample(dev(logits[3:]), [SamplingConfig(**settings[3])], uniforms[3:], recents[3:]).tolist()
+        assert got[3] == alone[0]                                  # the sorted path is as it was
+
+
 # ------------------------------------------------------------------ tcgen05 matrix products
 TC_SHAPES = [(1, 128, 64), (16, 128, 256), (8, 2048, 2048), (64, 6144, 2048), (100, 200, 96),
              (17, 100, 72), (300, 1000, 264), (129, 384, 96), (2048, 2048, 512), (8, 512, 8192)]

@@ -178,3 +178,66 @@ def test_random_workloads_always_drain():
         assert not sched.has_work()
         assert all(sched.tasks[i].state == "finished" for i in ids)
         assert planner.cache.groups[0].pool.n_used == 0
+
+
+def test_a_request_whose_bookkeeping_raises_between_steps_fails_alone():
+    """An exception raised for one request while the scheduler plans a step (here: the page
+    arithmetic of that request, made to raise by the planner stand-in) ends that request with an
+    error event and gives back what it held; the others run to the end with the tokens they would
+    have had anyway (native/src/v2_runtime.cpp:33788-33797)."""
+    class FaultyPlanner(StepPlanner):
+        poisoned = None
+
+        def pages_short(self, entries):
+            for request, _, _ in entries:
+                if request == self.poisoned:
+                    error = RuntimeError("injected: this request's page table is broken")
+                    error.request = request
+                    raise error
+            return super().pages_short(entries)
+
+    def run(poison_at):
+        cache = CacheManager([PagedKV(1, 16), FixedState((4, 2))], 12, 4, device=None)
+        planner = FaultyPlanner(cache, VOCAB, 512, 32)
+        sched = Scheduler(planner, 32, 512)
+        ids = [sched.submit([3 + i] * (20 + 7 * i), 12, (), GREEDY) for i in range(4)]
+        events, steps = [], 0
+        while sched.has_work():
+            if steps == poison_at:
+                planner.poisoned = ids[1]
+            step = sched.schedule()
+            events.extend(step.events)
+            if step.entries:
+                planner.plan(step.entries)
+                for task in sched.advance(step):
+                    events.extend(sched.accept(task, fake_token(task)))
+            planner.cache.check()
+            steps += 1
+            assert steps < 200
+        return sched, ids, events
+
+    clean, ids, _ = run(None)
+    for when in (0, 2, 6):                     # before admission, in its prompt, while decoding
+        sched, ids, events = run(when)
+        victim = sched.tasks[ids[1]]
+        assert victim.state == "finished" and victim.finish_reason == "error"
+        assert "injected" in victim.error
+        assert events.count((ids[1], 0, EVENT_ERROR)) == 1
+        for tid in (ids[0], ids[2], ids[3]):
+            assert sched.tasks[tid].generated == clean.tasks[tid].generated
+            assert sched.tasks[tid].finish_reason == "length"
+        assert sched.planner.cache.free_slots == 4 and sched.planner.cache.groups[0].pool.n_used == 0
+        assert sched.stats["failed"] == 1
+
+
+def test_fail_takes_a_task_off_the_lists_even_if_the_release_raises():
+    sched, planner = make()
+    tid = sched.submit([1, 2, 3], 4, (), GREEDY)
+    run_step(sched, planner)
+    task = sched.tasks[tid]
+    original = planner.finish
+    planner.finish = lambda request: (_ for _ in ()).throw(RuntimeError("release failed"))
+    assert sched.fail(task, "first fault") == [(tid, 0, EVENT_ERROR)]
+    planner.finish = original
+    assert task.state == "finished" and "first fault" in task.error and "release failed" in task.error
+    assert not sched.has_work() and sched.fail(task, "again") == []
