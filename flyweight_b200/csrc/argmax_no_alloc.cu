@@ -37,7 +37,7 @@ int fail(int code, const char* text) {
 __device__ __forceinline__ unsigned long long make_key(float v, int id) {
     unsigned bits = 0u;
     if (v == v) {                                 // NaN keeps 0: it loses against everything
-        bits = __float_as_uint(v);
+        bits = __float_as_uint(v + 0.0f);         // -0 becomes +0: equal values, equal keys
         bits = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
     }
     return ((unsigned long long)bits << 32) | (unsigned long long)(0xffffffffu - (unsigned)id);
@@ -126,6 +126,17 @@ int fwb_argmax_no_alloc(const float* logits, int rows, int vocab, int* out, cuda
                  "fwb_argmax_no_alloc serves at most %d rows of %d entries (asked: %d x %d); "
                  "use fwb_argmax with scratch of your own", MAX_ROWS, FWB_NO_ALLOC_MAX_VOCAB, rows, vocab);
         return FWB_TOO_LARGE;
+    }
+    if (stream) {
+        // the scratch address below is that of the current device: the stream must live there
+        int current = -1, of_stream = -1;
+        if (cudaGetDevice(&current) == cudaSuccess && cudaStreamGetDevice(stream, &of_stream) == cudaSuccess &&
+            current != of_stream) {
+            snprintf(g_error, sizeof(g_error),
+                     "the stream belongs to device %d but device %d is current; make the stream's device "
+                     "current before the call", of_stream, current);
+            return FWB_BAD_ARGUMENT;
+        }
     }
     Scratch* scratch = nullptr;
     int status = scratch_for_current_device(&scratch);

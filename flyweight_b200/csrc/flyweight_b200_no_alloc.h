@@ -25,11 +25,12 @@ extern "C" {
 #define FWB_NO_ALLOC_MAX_VOCAB 1048576 /* entries per row */
 
 /* Greedy sampling: out[r] = index of the largest value of logits[r][0..vocab), the lowest
- * index among equal values (NaN counts as smallest).  Same result as fwb_argmax.
+ * index among equal values (-0 equals +0; NaN counts as smallest).  Same result as fwb_argmax.
  *
  *   logits  [rows][vocab] float32, device memory, row-major, contiguous
  *   out     [rows] int32, device memory
- *   stream  the stream the work is enqueued on
+ *   stream  the stream the work is enqueued on; its device must be the current device of the
+ *           calling thread (the scratch array is found for the current device), else -1
  *
  * The slices of a row are scanned by separate thread blocks; their partial results and a
  * per-row arrival counter live in a scratch array that is part of the library image

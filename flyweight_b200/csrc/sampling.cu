@@ -26,7 +26,7 @@ constexpr int MAX_RECENT = 256;
 
 __device__ __forceinline__ unsigned ordered_bits(float v) {
     if (v != v) return 0u;                       // NaN sorts last
-    const unsigned b = __float_as_uint(v);
+    const unsigned b = __float_as_uint(v + 0.0f);    // -0 becomes +0: equal values get equal bits
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 __device__ __forceinline__ float unordered_bits(unsigned o) {

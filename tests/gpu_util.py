@@ -166,3 +166,63 @@ def replay_in_process(runner, steps):
             runner.finish(rid)
         runner.cache.check()
     return {rid: np.concatenate(parts) for rid, parts in out.items()}
+
+
+class GuardedOutputs:
+    """Guard bands around everything a kernel's Python face allocates (the stand-in for a memory
+    checker): while active, every CUDA tensor that Python code makes with ``torch.empty`` or
+    ``torch.empty_like`` lies in the middle of a larger buffer whose margins hold a canary byte,
+    and is itself filled with 0xFF bytes (NaN in fp32 and bfloat16, -1 in int32), so an output
+    element that no thread wrote shows up in the comparison.  ``check()`` waits for the device and
+    fails if a byte of any margin changed: a kernel wrote before or past its output."""
+    MARGIN = 1 << 16
+    CANARY = 0xA5
+
+    def __init__(self):
+        self._empty = torch.empty
+        self._empty_like = torch.empty_like
+        self._held = []
+
+    def _guarded(self, shape, dtype, device):
+        count = 1
+        for extent in shape:
+            count *= int(extent)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        padded = -(-nbytes // 256) * 256
+        buffer = self._empty(2 * self.MARGIN + padded, dtype=torch.uint8, device=device)
+        buffer.fill_(self.CANARY)
+        buffer[self.MARGIN:self.MARGIN + nbytes].fill_(0xFF)
+        self._held.append((buffer, nbytes, tuple(shape), dtype))
+        return buffer[self.MARGIN:self.MARGIN + nbytes].view(dtype).view(tuple(shape))
+
+    def __enter__(self):
+        def empty(*size, dtype=None, device=None, **kwargs):
+            if device is None or torch.device(device).type != "cuda" or kwargs.get("pin_memory"):
+                return self._empty(*size, dtype=dtype, device=device, **kwargs)
+            shape = tuple(size[0]) if len(size) == 1 and not isinstance(size[0], int) else tuple(size)
+            return self._guarded(shape, dtype or torch.get_default_dtype(), device)
+
+        def empty_like(other, **kwargs):
+            if not other.is_cuda or kwargs:
+                return self._empty_like(other, **kwargs)
+            return self._guarded(tuple(other.shape), other.dtype, other.device)
+
+        torch.empty, torch.empty_like = empty, empty_like
+        return self
+
+    def __exit__(self, *exc):
+        torch.empty, torch.empty_like = self._empty, self._empty_like
+        return False
+
+    def check(self):
+        torch.cuda.synchronize()
+        for buffer, nbytes, shape, dtype in self._held:
+            for name, band in (("before", buffer[:self.MARGIN]), ("after", buffer[self.MARGIN + nbytes:])):
+                bad = (band != self.CANARY).nonzero()
+                if bad.numel():
+                    at = int(bad[0])
+                    where = at - self.MARGIN if name == "before" else at
+                    raise AssertionError(f"a kernel wrote {name} its output of shape {shape} ({dtype}): "
+                                         f"{bad.numel()} bytes changed, the first at offset {where} "
+                                         f"{'from its start' if name == 'before' else 'past its end'}")
+        self._held.clear()

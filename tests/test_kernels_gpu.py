@@ -27,6 +27,15 @@ def close(got, want, rel, what=""):
     assert math.isfinite(err) and err <= rel * scale, f"{what}: max|delta| {err:.3e} > {rel:.1e}*{scale:.3g}"
 
 
+@pytest.fixture(autouse=True)
+def guard_bands():
+    """Every test of this file runs with canaries around the outputs its kernels allocate."""
+    from gpu_util import GuardedOutputs
+    with GuardedOutputs() as guard:
+        yield guard
+        guard.check()
+
+
 def bf16_round(t):
     return t.to(torch.bfloat16).to(t.dtype)
 
@@ -211,6 +220,46 @@ def test_shortconv_prompt_sized_bfloat16(H, L, bias):
         parts.append(ops.shortconv(dev(p[lo:hi]), dev(taps), None if b is None else dev(b), sd2,
                                    dev(ss), dev(sl), dev(ts), len(segs), torch.bfloat16))
     assert torch.equal(torch.cat(parts), z) and torch.equal(sd2, sd)
+
+
+@pytest.mark.parametrize("T", [1, 2, 3])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_shortconv_of_one_two_and_three_tokens_stays_inside_its_buffers(T, dtype, guard_bands):
+    """The smallest steps there are, as one segment and as T segments of one token, with the state
+    (read and advanced in place) inside guard bands as well as the output."""
+    from flyweight_b200.kernels import ops
+    H, L = 72, 3
+    g = torch.Generator().manual_seed(T)
+    for segments in ([(1, T)], [(slot, 1) for slot in range(T)]):
+        p = torch.randn(T, 3 * H, generator=g).to(dtype)
+        taps = torch.randn(H, L, generator=g)
+        state = torch.randn(3, H, L - 1, generator=g)
+        seg_start = torch.tensor(np.cumsum([0] + [n for _, n in segments]), dtype=torch.int32)
+        seg_slot = torch.tensor([s for s, _ in segments], dtype=torch.int32)
+        tok_seg = torch.tensor([i for i, (_, n) in enumerate(segments) for _ in range(n)], dtype=torch.int32)
+        want_z, want_state = conv_reference(p, taps, None, state, segments)
+        sd = torch.empty(state.shape, dtype=torch.float32, device=DEV).copy_(state)      # guarded
+        z = ops.shortconv(dev(p), dev(taps), None, sd, dev(seg_start), dev(seg_slot), dev(tok_seg),
+                          len(segments), dtype)
+        close(z, want_z, 1e-5 if dtype == torch.float32 else 2.0 ** -7, "conv output")
+        close(sd, want_state, 1e-6, "conv state")
+        guard_bands.check()
+
+
+def test_the_guard_bands_notice_a_write_past_an_output(guard_bands):
+    out = torch.empty((5, 7), dtype=torch.float32, device=DEV)
+    assert torch.isnan(out).all()                           # unwritten elements read as NaN
+    out.zero_()
+    guard_bands.check()
+    out.as_strided((36,), (1,)).fill_(1.0)                  # one element past the end
+    with pytest.raises(AssertionError, match="past its end"):
+        guard_bands.check()
+    guard_bands._held.clear()
+    out = torch.empty(16, dtype=torch.int32, device=DEV)
+    out.as_strided((4,), (1,), out.storage_offset() - 4).fill_(3)    # four elements before the start
+    with pytest.raises(AssertionError, match="before its output"):
+        guard_bands.check()
+    guard_bands._held.clear()
 
 
 def test_shortconv_cut_anywhere_gives_the_same_bits():
