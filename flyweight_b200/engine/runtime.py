@@ -84,6 +84,10 @@ class Runtime:
         self.run_ahead = True              # ... and launch the step after it before reading this one's tokens
         self._ahead = None                 # a decode step already launched whose tokens were not read yet
         self._token_ring = None            # pinned buffers for the sampled ids of two steps in flight
+        # tracing hook: called as observer(tasks, logits) with the fp32 logits [len(tasks)][vocab]
+        # every time tokens are about to be sampled from them (the tensor is overwritten by the
+        # next step: copy what is to be kept)
+        self.logits_observer: Optional[Callable] = None
         self.prepare()
 
     # ------------------------------------------------------------------ life cycle
@@ -179,6 +183,8 @@ class Runtime:
 
     def _sample_and_accept(self, need, logits, events) -> None:
         sampled = time.perf_counter()
+        if self.logits_observer is not None:
+            self.logits_observer(need, logits)
         if all(task.sampling.greedy for task in need):
             tokens = device_sampler.argmax(logits)
         else:
@@ -252,6 +258,8 @@ class Runtime:
     def _sample_greedy_async(self, tasks, logits):
         """Arg-max on the device and the copy of the ids to pinned memory, both queued; nobody
         waits here."""
+        if self.logits_observer is not None:
+            self.logits_observer(tasks, logits)
         tokens = device_sampler.argmax(logits)
         if self._token_ring is None:
             self._token_ring = {"buffers": [torch.empty(256, dtype=torch.int32).pin_memory() for _ in range(2)],

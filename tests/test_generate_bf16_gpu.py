@@ -102,32 +102,33 @@ def test_preemption_in_bfloat16():
 
 
 def test_seeded_sampling_in_bfloat16_draws_what_the_plain_sampler_draws():
-    """Each request's draws are replayed with the plain sampler on the oracle's logits of the text
-    the engine produced.  A draw that lands beside a boundary of the cumulative distribution may
-    go to the neighbouring candidate in bfloat16, so: every token must be one the plain sampler
-    could have kept, and nine in ten must be the very token it draws."""
+    """The runtime's tracing hook hands over the very logits each token was sampled from.  Those
+    rows must be the oracle's logits of the text so far (within the bfloat16 bound), and the plain
+    sampler, given the same rows and the request's own random numbers in order, must draw the
+    very tokens the engine produced: the right row reaches the right request, its generator
+    advances once per token, whatever else is in the batch."""
     name = "B"
-    cfg, _ = plain_model(name, DTYPE)
     prompts = [random_tokens(name, n, seed=140 + n) for n in (1, 7, 64, 100, 129)]
     settings = dict(temperature=0.8, top_k=40, top_p=0.95, min_p=0.05)
+    seen = {}
+
+    def observer(tasks, logits):
+        rows = logits.cpu().numpy()
+        for task, row in zip(tasks, rows):
+            seen.setdefault(task.id, []).append(row.copy())
+
     with open_runtime(name, context_limit=192, parallel_sequences=4, max_batched_tokens=16) as runtime:
+        runtime.logits_observer = observer
         ids = [runtime.task_submit(p, 24, seed=7 + i, **settings) for i, p in enumerate(prompts)]
         drain(runtime)
         texts = [runtime.task(i).generated for i in ids]
-    same = total = 0
-    for i, (prompt, generated) in enumerate(zip(prompts, texts)):
-        assert len(generated) == 24
-        logits = plain_logits(name, DTYPE, prompt + generated)
-        scale = max(1.0, float(np.abs(logits).max()))
+    for i, (tid, prompt, generated) in enumerate(zip(ids, prompts, texts)):
+        assert len(generated) == 24 and len(seen[tid]) == 24
+        want = plain_logits(name, DTYPE, prompt + generated)[len(prompt) - 1:-1]
+        assert_close(np.stack(seen[tid]), want, TOL_ORACLE[DTYPE], f"request {i}: the logits it was sampled from")
         rng = P.XorShift64Star(7 + i)
-        for j, token in enumerate(generated):
-            row = logits[len(prompt) - 1 + j]
-            drawn = P.sample(row.astype(np.float32), rng=rng, **settings)
-            kth = np.sort(row)[-settings["top_k"]]
-            assert row[token] >= kth - BOUND * scale, f"request {i}, token {j}: outside the top {settings['top_k']}"
-            same += drawn == token
-            total += 1
-    assert same >= 0.9 * total, f"only {same} of {total} draws equal the plain sampler's"
+        drawn = [P.sample(row, rng=rng, **settings) for row in seen[tid]]
+        assert drawn == generated, f"request {i}"
 
 
 def test_steady_decoding_and_the_step_launched_ahead_in_bfloat16():
