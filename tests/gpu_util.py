@@ -225,4 +225,6 @@ class GuardedOutputs:
                     raise AssertionError(f"a kernel wrote {name} its output of shape {shape} ({dtype}): "
                                          f"{bad.numel()} bytes changed, the first at offset {where} "
                                          f"{'from its start' if name == 'before' else 'past its end'}")
+
+    def forget(self):
         self._held.clear()

@@ -34,6 +34,7 @@ def guard_bands():
     with GuardedOutputs() as guard:
         yield guard
         guard.check()
+        guard.forget()
 
 
 def bf16_round(t):
@@ -254,12 +255,12 @@ def test_the_guard_bands_notice_a_write_past_an_output(guard_bands):
     out.as_strided((36,), (1,)).fill_(1.0)                  # one element past the end
     with pytest.raises(AssertionError, match="past its end"):
         guard_bands.check()
-    guard_bands._held.clear()
+    guard_bands.forget()
     out = torch.empty(16, dtype=torch.int32, device=DEV)
     out.as_strided((4,), (1,), out.storage_offset() - 4).fill_(3)    # four elements before the start
     with pytest.raises(AssertionError, match="before its output"):
         guard_bands.check()
-    guard_bands._held.clear()
+    guard_bands.forget()
 
 
 def test_shortconv_cut_anywhere_gives_the_same_bits():
