@@ -114,34 +114,21 @@ class ClockSampler:
 
 
 def model_flops_per_token(model) -> float:
-    """2 x (weights of every matrix product a token passes through), head excluded."""
-    spec = model.spec
-    total = 0
-    for entry in spec.schedule:
-        layer = model.layers[entry.layer]
-        for part in (layer.mixer, layer.feed_forward):
-            for name in ("w_qkv", "w_o", "w_in", "w_out", "w_gate_up", "w_down"):
-                weight = getattr(part, name, None)
-                if weight is not None:
-                    total += weight.numel()
-    return 2.0 * total
+    """2 x (weights of every matrix product a token passes through), head excluded: every part
+    states its own."""
+    return model.flops_per_token()
 
 
 def attention_flops(model, n_tokens: int) -> float:
     """Causal attention of one n-token prompt: QK^T and PV, 2 * n^2 * heads * head_dim a layer
-    (4 flops per query-key pair and channel, half of the pairs masked)."""
-    total = 0.0
-    for entry in model.spec.schedule:
-        mixer = model.layers[entry.layer].mixer
-        if hasattr(mixer, "n_heads"):
-            total += 2.0 * n_tokens * n_tokens * mixer.n_heads * mixer.head_dim
-    return total
+    (4 flops per query-key pair and channel, half of the pairs masked), as the mixers state it."""
+    return model.context_flops(n_tokens)
 
 
 def kv_bytes_per_token(model) -> int:
     total = 0
     for entry in model.spec.schedule:
-        spec = model.layers[entry.layer].mixer.state_spec() if entry.cache_of is None else None
+        spec = model.layers[entry.layer].state_spec() if entry.cache_of is None else None
         if spec is not None and hasattr(spec, "n_kv_heads"):
             total += 2 * spec.n_kv_heads * spec.head_dim * model.precision.cache_dtype.itemsize
     return total

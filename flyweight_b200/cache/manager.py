@@ -13,8 +13,8 @@ members grow in step.  A request's pages go back to the pool when it ends, and i
 window group also as soon as the window has passed them.
 
 Fixed-size state (the short convolution's rolling inputs here; any recurrent state in
-general) lives in *slots*: every such execution owns one ``[num_slots][...]`` fp32
-tensor, and a request holds one slot id, zeroed when it is handed out, for as long as
+general) lives in *slots*: every such execution owns one ``[num_slots][...]`` tensor in the
+dtype its spec names (fp32 by default), and a request holds one slot id, zeroed when it is handed out, for as long as
 it lives (flyweight zeroes the whole arena on reset, native/src/v2_runtime.cpp:20438-20440).
 
 All bookkeeping is host-side and can be tested without a GPU (``device=None`` makes
@@ -90,7 +90,7 @@ class LayerCache:
     group: Optional[int] = None              # index of its page group (block table to use)
     k_pool: Optional[torch.Tensor] = None
     v_pool: Optional[torch.Tensor] = None
-    state: Optional[torch.Tensor] = None     # [num_slots][...] fp32
+    state: Optional[torch.Tensor] = None     # [num_slots][...] in the spec's dtype (fp32 by default)
     spec: object = None
 
 
@@ -146,24 +146,27 @@ class CacheManager:
                 raise TypeError(f"schedule position {position}: unknown state spec {spec!r}")
             self.layer_caches.append(cache)
         self._rows: List[Dict[Hashable, tuple]] = [{} for _ in self.groups]   # block-table rows as arrays
-        # All fixed-size states of a slot lie side by side in one allocation, [num_slots][total],
-        # and every execution sees its share as [num_slots][...]: admission clears one span.
-        self._all_states: Optional[torch.Tensor] = None
+        # All fixed-size states of one dtype lie side by side in one allocation, [num_slots][total],
+        # and every execution sees its share as [num_slots][...]: admission clears one span per dtype.
+        self._all_states: Dict[torch.dtype, torch.Tensor] = {}
         if device is not None and self._fixed_positions:
-            sizes = []
+            by_dtype: Dict[torch.dtype, List[Tuple[int, int]]] = {}
             for position in self._fixed_positions:
+                spec = self.layer_caches[position].spec
                 count = 1
-                for extent in self.layer_caches[position].spec.shape:
+                for extent in spec.shape:
                     count *= int(extent)
-                sizes.append(count)
-            self._all_states = torch.zeros((self.num_slots, sum(sizes)), dtype=torch.float32, device=device)
-            offset = 0
-            for position, count in zip(self._fixed_positions, sizes):
-                shape = tuple(self.layer_caches[position].spec.shape)
-                self.layer_caches[position].state = (
-                    self._all_states[:, offset:offset + count].unflatten(1, shape) if shape
-                    else self._all_states[:, offset])
-                offset += count
+                by_dtype.setdefault(spec.dtype, []).append((position, count))
+            for dtype, members in by_dtype.items():
+                pool = torch.zeros((self.num_slots, sum(count for _, count in members)), dtype=dtype,
+                                   device=device)
+                self._all_states[dtype] = pool
+                offset = 0
+                for position, count in members:
+                    shape = tuple(self.layer_caches[position].spec.shape)
+                    self.layer_caches[position].state = (
+                        pool[:, offset:offset + count].unflatten(1, shape) if shape else pool[:, offset])
+                    offset += count
 
     # ------------------------------------------------------------------ requests
     def live(self) -> Tuple[Hashable, ...]:
@@ -200,8 +203,8 @@ class CacheManager:
         self.slots_high_water = max(self.slots_high_water, len(self._slot_of))
         for group in self.groups:
             group.tables[request] = []
-        if self._all_states is not None:
-            self._all_states[slot].zero_()
+        for pool in self._all_states.values():
+            pool[slot].zero_()
         return slot
 
     def release_passed(self, request: Hashable) -> int:

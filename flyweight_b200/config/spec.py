@@ -26,15 +26,38 @@ class PartSpec:
     tensors: Mapping[str, str] = field(default_factory=dict)
 
 
-@dataclass(frozen=True)
+@dataclass(frozen=True, init=False)
 class LayerSpec:
-    """One layer: an arrangement (how norms, mixer and feed-forward are wired around
-    the residual stream) and the four parts it wires."""
+    """One layer: an arrangement (how its parts are wired around the residual stream) and the
+    parts it wires, by role.  Which roles there are is the arrangement's business: the pre-norm
+    residual block has ``mixer_norm``, ``mixer``, ``ffn_norm`` and ``feed_forward``; another
+    arrangement may ask for more (post-norms), fewer (no feed-forward) or others.
+
+        LayerSpec("prenorm_residual", mixer_norm, mixer, ffn_norm, feed_forward)     # the four, in order
+        LayerSpec("my_arrangement", parts={"norm": ..., "feed_forward": ...})        # any roles
+    """
     arrangement: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    feed_forward: PartSpec
+    parts: Mapping[str, PartSpec]
+
+    def __init__(self, arrangement: str, mixer_norm: Optional[PartSpec] = None,
+                 mixer: Optional[PartSpec] = None, ffn_norm: Optional[PartSpec] = None,
+                 feed_forward: Optional[PartSpec] = None, *,
+                 parts: Optional[Mapping[str, PartSpec]] = None):
+        named = dict(parts or {})
+        for role, spec in (("mixer_norm", mixer_norm), ("mixer", mixer), ("ffn_norm", ffn_norm),
+                           ("feed_forward", feed_forward)):
+            if spec is not None:
+                if role in named:
+                    raise ValueError(f"layer part {role!r} is given twice")
+                named[role] = spec
+        object.__setattr__(self, "arrangement", arrangement)
+        object.__setattr__(self, "parts", named)
+
+    def __getattr__(self, role: str) -> PartSpec:
+        parts = self.__dict__.get("parts", {})
+        if role in parts:
+            return parts[role]
+        raise AttributeError(f"this layer ({self.__dict__.get('arrangement')!r}) has no part {role!r}")
 
 
 @dataclass(frozen=True)
@@ -61,10 +84,14 @@ class ModelSpec:
     head_tensor: Optional[str]          # None: the head is the embedding table (tied)
     layers: Tuple[LayerSpec, ...]
     schedule: Tuple[ScheduleEntry, ...]
+    embedding_scale: float = 1.0        # embedding rows are multiplied by this (LFM2: 1)
+    logit_softcap: float = 0.0          # > 0: logits = cap * tanh(logits / cap) (LFM2: off)
 
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
+        if self.logit_softcap < 0 or not self.embedding_scale == self.embedding_scale:
+            raise ValueError("logit_softcap must not be negative")
         for position, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule position {position} names layer {entry.layer}, "

@@ -5,25 +5,26 @@
 using namespace fwb;
 
 // ------------------------------------------------------------------ embedding
-// out[t][:] = table[ids[t]][:] widened to fp32.  An id outside [0, V) writes
+// out[t][:] = scale * table[ids[t]][:] widened to fp32 (scale 1: the row as it is; some
+// architectures multiply the embedding by sqrt(H)).  An id outside [0, V) writes
 // zeros and raises *bad (the host refuses such ids before upload; this is the
 // second fence).
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int T, int H, int V, int* bad) {
+                             float* __restrict__ out, int T, int H, int V, int* bad, float scale) {
     fwb::pdl_entry();
     const int t = blockIdx.y;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
     if (!ok && threadIdx.x == 0 && blockIdx.x == 0 && bad) atomicExch(bad, 1);
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < H; c += gridDim.x * blockDim.x)
-        out[(size_t)t * H + c] = ok ? to_f32<TW>(table[(size_t)id * H + c]) : 0.0f;
+        out[(size_t)t * H + c] = ok ? scale * to_f32<TW>(table[(size_t)id * H + c]) : 0.0f;
 }
 
 // bfloat16 table, H a multiple of 8: a thread widens 8 adjacent entries (one 16-byte load, two
 // 16-byte stores); one block per token.
 __global__ void embed_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int H, int V, int* bad) {
+                                    float* __restrict__ out, int H, int V, int* bad, float scale) {
     fwb::pdl_entry();
     const int t = blockIdx.x;
     const int id = ids[t];
@@ -38,8 +39,8 @@ __global__ void embed_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, con
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
             const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
             const float2 e = __bfloat1622float2(h[2]), f = __bfloat1622float2(h[3]);
-            lo = make_float4(a.x, a.y, b.x, b.y);
-            hi = make_float4(e.x, e.y, f.x, f.y);
+            lo = make_float4(scale * a.x, scale * a.y, scale * b.x, scale * b.y);
+            hi = make_float4(scale * e.x, scale * e.y, scale * f.x, scale * f.y);
         }
         *reinterpret_cast<float4*>(dst + c) = lo;
         *reinterpret_cast<float4*>(dst + c + 4) = hi;
@@ -47,20 +48,20 @@ __global__ void embed_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, con
 }
 
 FWB_API int fwb_embed(const void* table, int table_bf16, const int* ids, float* out, int T, int H,
-                      int V, int* bad, cudaStream_t stream) {
+                      int V, int* bad, float scale, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!table || !ids || !out || H <= 0 || V <= 0 || T > 65535) return FWB_BAD_ARGUMENT;
     if (table_bf16 && (H & 7) == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
         const int threads = H / 8 < 256 ? ((H / 8 + 31) / 32) * 32 : 256;
-        fwb::pdl(embed_bf16x8_kernel, T, threads, 0, stream)((const __nv_bfloat16*)table, ids, out, H, V, bad);
+        fwb::pdl(embed_bf16x8_kernel, T, threads, 0, stream)((const __nv_bfloat16*)table, ids, out, H, V, bad, scale);
         return fwb_launch_status();
     }
     dim3 grid((H + 255) / 256 > 64 ? 64 : (H + 255) / 256, T);
     if (table_bf16)
         fwb::pdl(embed_kernel<__nv_bfloat16>, grid, 256, 0, stream)(
-            (const __nv_bfloat16*)table, ids, out, T, H, V, bad);
+            (const __nv_bfloat16*)table, ids, out, T, H, V, bad, scale);
     else
-        fwb::pdl(embed_kernel<float>, grid, 256, 0, stream)((const float*)table, ids, out, T, H, V, bad);
+        fwb::pdl(embed_kernel<float>, grid, 256, 0, stream)((const float*)table, ids, out, T, H, V, bad, scale);
     return fwb_launch_status();
 }
 
@@ -257,5 +258,22 @@ FWB_API int fwb_cast(const void* in, int in_bf16, void* out, int out_bf16, long 
     else
         fwb::pdl(cast_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream)((const float*)in,
                                                                        (__nv_bfloat16*)out, (size_t)n);
+    return fwb_launch_status();
+}
+
+// ------------------------------------------------------------------ logit soft-cap
+// x = cap * tanh(x / cap), in place on fp32 (a head whose logits are squashed into (-cap, cap)).
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+    fwb::pdl_entry();
+    const float inv = 1.0f / cap;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+FWB_API int fwb_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return FWB_OK;
+    if (!x || !(cap > 0.0f)) return FWB_BAD_ARGUMENT;
+    const long long blocks = (n + 255) / 256;
+    fwb::pdl(softcap_kernel, (int)(blocks > 4096 ? 4096 : blocks), 256, 0, stream)(x, n, cap);
     return fwb_launch_status();
 }

@@ -3,8 +3,9 @@
 //
 //   qkv[t] = [ q: nh*hd | k: nkv*hd | v: nkv*hd ]
 //   q^ = rope(rmsnorm_hd(q_head) * wq),  k^ = rope(rmsnorm_hd(k_head) * wk),  v unchanged
-//   rope (half-split over the first `rot` channels of a head): pair (i, i+rot/2),
-//       out[i] = a*cos - b*sin,  out[i+rot/2] = b*cos + a*sin,  (cos,sin) = table[pos][i]
+//   rope over the first `rot` channels of a head, pair i of rot/2 turning by table[pos][i]:
+//       a' = a*cos - b*sin,  b' = b*cos + a*sin
+//   with (a, b) = channels (i, i+rot/2) for half-split pairing (0), (2i, 2i+1) for interleaved (1)
 //   K[page][kvh][off][:] = k^,  V[page][kvh][off][:] = v   with page = block_table[seg][pos/P],
 //                                                          off = pos % P
 // Norm, angle lookup and rotation are fp32; only the stores round to the cache type.
@@ -26,7 +27,7 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
                     const int* __restrict__ positions, const int* __restrict__ tok_seg,
                     const int* __restrict__ block_table, int max_pages, int page_size,
                     TQ* __restrict__ q_out, TC* __restrict__ k_pool, TC* __restrict__ v_pool, int nh,
-                    int nkv, int hd, int rot, float eps, int use_norm) {
+                    int nkv, int hd, int rot, float eps, int use_norm, int pairing) {
     fwb::pdl_entry();
     extern __shared__ float smem[];
     const int t = blockIdx.x;
@@ -65,22 +66,24 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
         if (is_q) {
             TQ* dst = q_out + ((size_t)t * nh + h) * hd;
             for (int i = lane; i < half; i += 32) {
-                const float a = use_norm ? (buf[i] * inv) * w[i] : buf[i];
-                const float b = use_norm ? (buf[i + half] * inv) * w[i + half] : buf[i + half];
+                const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+                const float a = use_norm ? (buf[ia] * inv) * w[ia] : buf[ia];
+                const float b = use_norm ? (buf[ib] * inv) * w[ib] : buf[ib];
                 const float2 c = cs[i];
-                dst[i] = from_f32<TQ>(a * c.x - b * c.y);
-                dst[i + half] = from_f32<TQ>(b * c.x + a * c.y);
+                dst[ia] = from_f32<TQ>(a * c.x - b * c.y);
+                dst[ib] = from_f32<TQ>(b * c.x + a * c.y);
             }
             for (int i = rot + lane; i < hd; i += 32)
                 dst[i] = from_f32<TQ>(use_norm ? (buf[i] * inv) * w[i] : buf[i]);
         } else {
             TC* dst = k_pool + cache_base + (size_t)(h - nh) * page_size * hd;
             for (int i = lane; i < half; i += 32) {
-                const float a = use_norm ? (buf[i] * inv) * w[i] : buf[i];
-                const float b = use_norm ? (buf[i + half] * inv) * w[i + half] : buf[i + half];
+                const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+                const float a = use_norm ? (buf[ia] * inv) * w[ia] : buf[ia];
+                const float b = use_norm ? (buf[ib] * inv) * w[ib] : buf[ib];
                 const float2 c = cs[i];
-                dst[i] = from_f32<TC>(a * c.x - b * c.y);
-                dst[i + half] = from_f32<TC>(b * c.x + a * c.y);
+                dst[ia] = from_f32<TC>(a * c.x - b * c.y);
+                dst[ib] = from_f32<TC>(b * c.x + a * c.y);
             }
             for (int i = rot + lane; i < hd; i += 32)
                 dst[i] = from_f32<TC>(use_norm ? (buf[i] * inv) * w[i] : buf[i]);
@@ -119,7 +122,7 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
                            const int* __restrict__ block_table, int max_pages, int page_size,
                            __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
                            __nv_bfloat16* __restrict__ v_pool, int nh, int nkv, int hd, int rot, float eps,
-                           int use_norm) {
+                           int use_norm, int pairing) {
     fwb::pdl_entry();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -165,7 +168,17 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
 #pragma unroll
         for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, v[i], partner);
         if (!valid) continue;
-        if (!is_v && gl < rot_lanes) {
+        if (!is_v && gl < rot_lanes && pairing) {
+            // interleaved pairs lie side by side in this lane's eight channels
+            const float2* c = cs + gl * 4;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 a = c[j];
+                const float x0 = v[2 * j], x1 = v[2 * j + 1];
+                v[2 * j] = x0 * a.x - x1 * a.y;
+                v[2 * j + 1] = x1 * a.x + x0 * a.y;
+            }
+        } else if (!is_v && gl < rot_lanes) {
             const bool low = gl < half_lanes;
             const float2* c = cs + (low ? gl : gl - half_lanes) * 8;
 #pragma unroll
@@ -186,13 +199,14 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
 
 // qkv: [T][(nh+2*nkv)*hd] fp32 or bf16.  wq, wk: [hd] fp32 (ignored when use_norm == 0).
 // table: [max_pos][rot/2] float2 (cos, sin).  positions, tok_seg: [T].
+// pairing: 0 half-split (i, i+rot/2), 1 interleaved (2i, 2i+1).
 // block_table: [S][max_pages] page ids.  q_out: [T][nh*hd].  k_pool, v_pool:
 // [pages][nkv][page_size][hd].  Dtype flags: 0 fp32, 1 bf16.
 FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, const float* wk,
                              const void* table, const int* positions, const int* tok_seg,
                              const int* block_table, int max_pages, int page_size, void* q_out,
                              int q_bf16, void* k_pool, void* v_pool, int cache_bf16, int T, int nh,
-                             int nkv, int hd, int rot, float eps, int use_norm,
+                             int nkv, int hd, int rot, float eps, int use_norm, int pairing,
                              cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!qkv || !table || !positions || !q_out || nh <= 0 || nkv < 0) return FWB_BAD_ARGUMENT;
@@ -200,6 +214,7 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
         return FWB_BAD_ARGUMENT;
     if (use_norm && (!wq || (nkv > 0 && !wk))) return FWB_BAD_ARGUMENT;
     if (hd <= 0 || hd > MAX_HD || (hd & 1) || rot < 0 || rot > hd || (rot & 1)) return FWB_UNSUPPORTED;
+    if (pairing != 0 && pairing != 1) return FWB_UNSUPPORTED;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
     // one warp per head; few tokens (decode) spread their heads over several blocks
     const int head_blocks = T >= 256 ? 1 : (nh + 2 * nkv + WARPS - 1) / WARPS;
@@ -209,7 +224,7 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
 #define FWB_QK(TI, TQ, TC)                                                                        \
     fwb::pdl(qk_norm_rope_kernel<TI, TQ, TC>, grid, WARPS * 32, smem, stream)(                             \
         (const TI*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table, max_pages, \
-        page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm)
+        page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm, pairing)
     const int key = (in_bf16 ? 4 : 0) | (q_bf16 ? 2 : 0) | (cache_bf16 ? 1 : 0);
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
     if (key == 7 && (hd & 7) == 0 && hd <= 256 && (rot & 15) == 0 && aligned) {
@@ -218,7 +233,7 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
         fwb::pdl(qk_norm_rope_bf16x8_kernel, vgrid, WARPS * 32, 0, stream)(
             (const __nv_bfloat16*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table,
             max_pages, page_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh,
-            nkv, hd, rot, eps, use_norm);
+            nkv, hd, rot, eps, use_norm, pairing);
         return fwb_launch_status();
     }
     switch (key) {

@@ -20,15 +20,16 @@ def _i32(name: str, tensor: torch.Tensor, count: Optional[int] = None) -> None:
 
 
 # ------------------------------------------------------------------ embedding
-def embed(table: torch.Tensor, ids: torch.Tensor, bad_flag: Optional[torch.Tensor] = None
-          ) -> torch.Tensor:
-    """Rows ``ids`` of ``table`` ([V][H], fp32 or bf16) widened to fp32: [T][H]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, bad_flag: Optional[torch.Tensor] = None,
+          scale: float = 1.0) -> torch.Tensor:
+    """Rows ``ids`` of ``table`` ([V][H], fp32 or bf16) widened to fp32 and multiplied by
+    ``scale``: [T][H]."""
     check_tensor("embedding table", table)
     _i32("token ids", ids)
     T, (V, H) = ids.numel(), table.shape
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     lib.call("fwb_embed", ptr(table), is_bf16(table), ptr(ids), ptr(out), T, H, V, ptr(bad_flag),
-             stream())
+             c_float(scale), stream())
     return out
 
 
@@ -61,6 +62,15 @@ def add_(x: torch.Tensor, delta: torch.Tensor) -> None:
     check_tensor("residual", x, torch.float32)
     check_tensor("delta", delta, torch.float32, x.shape)
     lib.call("fwb_add", ptr(x), ptr(delta), c_longlong(x.numel()), stream())
+
+
+def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """``cap * tanh(logits / cap)`` in place on fp32."""
+    check_tensor("logits", logits, torch.float32)
+    if not cap > 0:
+        raise KernelError("a soft-cap must be positive")
+    lib.call("fwb_softcap", ptr(logits), c_longlong(logits.numel()), c_float(cap), stream())
+    return logits
 
 
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -173,22 +183,32 @@ def shortconv(p: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor],
 
 
 # ------------------------------------------------------------------ attention
+ROPE_PAIRINGS = {"half_split": 0, "interleaved": 1}
+
+
 def qk_norm_rope(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
                  table: torch.Tensor, positions: torch.Tensor, tok_seg: torch.Tensor,
                  block_table: Optional[torch.Tensor], k_pool: Optional[torch.Tensor],
                  v_pool: Optional[torch.Tensor], n_heads: int, n_kv_in: int, head_dim: int,
-                 rotary_dim: int, eps: float, q_dtype: torch.dtype) -> torch.Tensor:
+                 rotary_dim: int, eps: float, q_dtype: torch.dtype, pairing: str = "half_split"
+                 ) -> torch.Tensor:
     """Per-head RMSNorm + RoPE of q and k, k/v written to their pages; returns q [T][nh*hd].
 
     ``n_kv_in`` is the number of KV heads present in ``qkv`` (0: queries only).
-    ``table`` is [max_pos][rotary_dim/2][2] fp32 (cos, sin)."""
+    ``table`` is [max_pos][rotary_dim/2][2] fp32 (cos, sin); pair i turns by entry i.
+    ``pairing``: which two channels pair i is made of -- "half_split" (i, i + rotary_dim/2) or
+    "interleaved" (2i, 2i + 1)."""
+    try:
+        pairing_code = ROPE_PAIRINGS[pairing]
+    except KeyError:
+        raise KernelError(f"unknown rotary pairing {pairing!r}; known: " + ", ".join(ROPE_PAIRINGS)) from None
     check_tensor("qkv", qkv)
     T = qkv.shape[0]
     if qkv.shape[1] != (n_heads + 2 * n_kv_in) * head_dim:
         raise KernelError(f"qkv has {qkv.shape[1]} columns, expected "
                           f"{(n_heads + 2 * n_kv_in) * head_dim}")
     check_tensor("rope table", table, torch.float32)
-    if table.dim() != 3 or table.shape[1] != rotary_dim // 2 or table.shape[2] != 2:
+    if table.dim() != 3 or table.shape[1] != max(1, rotary_dim // 2) or table.shape[2] != 2:
         raise KernelError("rope table must be [positions][rotary_dim/2][2]")
     use_norm = 1 if q_norm is not None else 0
     if use_norm:
@@ -213,7 +233,7 @@ def qk_norm_rope(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Opti
     lib.call("fwb_qk_norm_rope", ptr(qkv), is_bf16(qkv), ptr(q_norm), ptr(k_norm), ptr(table),
              ptr(positions), ptr(tok_seg), ptr(block_table), max_pages, page_size, ptr(q_out),
              is_bf16(q_out), ptr(k_pool), ptr(v_pool), cache_bf16, T, n_heads, n_kv_in, head_dim,
-             rotary_dim, c_float(eps), use_norm, stream())
+             rotary_dim, c_float(eps), use_norm, pairing_code, stream())
     return q_out
 
 

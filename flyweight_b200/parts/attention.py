@@ -44,7 +44,7 @@ class GQAttention(Mixer):
         if self.head_dim % 16:
             raise ValueError(f"head size {self.head_dim}: the attention kernels take head sizes "
                              "in steps of 16")
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.rope_table = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     @property
     def _kv_in(self) -> int:
@@ -83,23 +83,28 @@ class GQAttention(Mixer):
         return (self.w_qkv.numel() * self.w_qkv.element_size()
                 + self.w_o.numel() * self.w_o.element_size())
 
+    def flops_per_token(self):
+        return 2.0 * (self.w_qkv.numel() + self.w_o.numel())
+
+    def context_flops(self, n_tokens):
+        # QK^T and PV: 4 operations per (query, visible key, channel); half the pairs are masked
+        return 2.0 * n_tokens * n_tokens * self.n_heads * self.head_dim
+
     def state_spec(self):
         return None if self.shares_cache else PagedKV(self.n_kv, self.head_dim, self.window)
 
     def prepare(self, max_positions, device):
-        self.rope_table = self.position.table(max_positions, device)
+        self.position.prepare(max_positions, device)
 
     def forward(self, ctx, h, cache, residual=None):
         act = ctx.precision.act_dtype
         # q|k|v in the activation dtype; the head norm and the rotation widen it to fp32
         qkv = ops.linear(h, self.w_qkv, act)
         block_table = ctx.batch.block_tables[cache.group]
-        q = ops.qk_norm_rope(
-            qkv, self.q_norm, self.k_norm, self.rope_table, ctx.batch.positions,
-            ctx.batch.tok_seg, block_table if self._kv_in else None,
-            cache.k_pool if self._kv_in else None, cache.v_pool if self._kv_in else None,
-            self.n_heads, self._kv_in, self.head_dim, self.position.rotary_dim,
-            float(self.eps or 0.0), act)
+        # positions are the position part's business: it norms, encodes and writes the pages
+        q = self.position.encode(ctx, qkv, n_heads=self.n_heads, n_kv_in=self._kv_in,
+                                 head_dim=self.head_dim, q_norm=self.q_norm, k_norm=self.k_norm,
+                                 eps=self.eps, cache=cache, block_table=block_table)
         from ..kernels import attention as attention_kernels
         out = attention_kernels.paged_attention(ctx, q, cache, block_table, self.n_heads,
                                                 self.window, self.scale, act)

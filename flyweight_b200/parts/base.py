@@ -21,7 +21,9 @@ Interfaces
 ``FeedForward.forward(ctx, h)`` -> fp32 [T][H]
     A mixer or feed-forward with ``adds_residual`` is called with ``residual=x`` as well and
     may add its delta into x itself (its last product's epilogue); it then returns None.
-``PositionEncoding.table(n_positions, device)`` -> what its kernel reads.
+``PositionEncoding.encode(ctx, qkv, ...)`` -> q; keys and values are in the cache afterwards.
+    The default is the fused norm + rotation + page-write kernel fed by ``table(n_positions,
+    device)``, ``rotary_dim`` and ``pairing``.
 ``Arrangement.forward(ctx, x, pending, cache)`` -> (x, pending)
     wires norms, mixer and feed-forward around the residual stream; ``pending`` is
     a delta not yet added to x, handed to the next norm so that the sum and the
@@ -85,8 +87,10 @@ class PagedKV:
 
 @dataclass(frozen=True)
 class FixedState:
-    """Per-request state of fixed size (fp32), zero when a request starts."""
+    """Per-request state of fixed size, zero when a request starts.  ``dtype``: fp32 unless the
+    part says otherwise (a recurrent state kept in bfloat16, a counter in int32)."""
     shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
 
 
 # ------------------------------------------------------------------ a norm not yet applied
@@ -138,6 +142,15 @@ class Part:
         """Bytes of device weights a step reads (for roofline accounting)."""
         return 0
 
+    def flops_per_token(self) -> float:
+        """Floating-point operations of this part's matrix products for one token (2 per weight)."""
+        return 0.0
+
+    def context_flops(self, n_tokens: int) -> float:
+        """Operations that grow with the context, for one causal prompt of ``n_tokens``
+        (attention: scores and weighted values over the visible keys); 0 for most parts."""
+        return 0.0
+
 
 class Norm(Part):
     def forward(self, ctx, x, delta=None, rows=None):
@@ -150,8 +163,33 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """How positions enter an attention mixer.  The mixer hands its fused q|k|v rows to
+    ``encode`` and gets the queries back; keys and values are in the cache afterwards.  The
+    default ``encode`` is the fused kernel (per-head q/k norm, rotation from ``table``, page
+    write) with this part's ``rotary_dim`` and ``pairing``, so a rotary encoding only has to
+    supply its table; an encoding that is no rotation overrides ``encode``."""
+    rotary_dim: int = 0                 # channels of a head that turn (0: none)
+    pairing: str = "half_split"         # "half_split" (i, i + rotary_dim/2) | "interleaved" (2i, 2i+1)
+
     def table(self, n_positions: int, device):
+        """[n_positions][rotary_dim/2][2] fp32 (cos, sin); pair i of a head turns by entry i."""
         raise NotImplementedError
+
+    def prepare(self, max_positions: int, device) -> None:
+        self._table = (self.table(max_positions, device) if self.rotary_dim > 0
+                       else torch.zeros((1, 1, 2), dtype=torch.float32, device=device))
+
+    def encode(self, ctx, qkv, *, n_heads: int, n_kv_in: int, head_dim: int, q_norm, k_norm,
+               eps: float, cache, block_table):
+        """qkv: [T][(n_heads + 2 n_kv_in) head_dim] in the activation dtype (``n_kv_in`` 0: queries
+        only, for a mixer that reads another execution's cache).  Returns q [T][n_heads head_dim]."""
+        from ..kernels import ops
+        batch = ctx.batch
+        return ops.qk_norm_rope(
+            qkv, q_norm, k_norm, self._table, batch.positions, batch.tok_seg,
+            block_table if n_kv_in else None, cache.k_pool if n_kv_in else None,
+            cache.v_pool if n_kv_in else None, n_heads, n_kv_in, head_dim, self.rotary_dim,
+            float(eps or 0.0), ctx.precision.act_dtype, pairing=self.pairing)
 
 
 class Mixer(Part):
@@ -171,15 +209,49 @@ class FeedForward(Part):
 
 
 class Arrangement:
+    """How a layer's parts are wired around the residual stream.  ``ROLES`` maps each role name
+    the arrangement knows to the family its part is built from (``norm``, ``mixer``,
+    ``feed_forward``) and says whether the layer must have it; the built parts become attributes
+    named after their roles (absent optional ones are None)."""
+    ROLES: Dict[str, Tuple[str, bool]] = {          # role -> (family, required)
+        "mixer_norm": ("norm", True), "mixer": ("mixer", True),
+        "ffn_norm": ("norm", True), "feed_forward": ("feed_forward", True)}
+
     def __init__(self, layer: LayerSpec):
         self.layer = layer
-        self.mixer_norm = build_norm(layer.mixer_norm)
-        self.mixer = build_mixer(layer.mixer)
-        self.ffn_norm = build_norm(layer.ffn_norm)
-        self.feed_forward = build_feed_forward(layer.feed_forward)
+        unknown = sorted(set(layer.parts) - set(self.ROLES))
+        missing = sorted(role for role, (_, required) in self.ROLES.items()
+                         if required and role not in layer.parts)
+        if unknown or missing:
+            raise ValueError(f"arrangement {layer.arrangement!r}: "
+                             + (f"unknown parts {unknown}; " if unknown else "")
+                             + (f"missing parts {missing}; " if missing else "")
+                             + "it wires " + ", ".join(self.ROLES))
+        builders = {"norm": build_norm, "mixer": build_mixer, "feed_forward": build_feed_forward}
+        self._built = []
+        for role, (family, _) in self.ROLES.items():
+            part = builders[family](layer.parts[role]) if role in layer.parts else None
+            setattr(self, role, part)
+            if part is not None:
+                self._built.append(part)
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return tuple(self._built)
+
+    def stateful_part(self):
+        """The part whose ``state_spec()`` says what one execution of this layer keeps in the
+        cache manager (None: nothing)."""
+        return getattr(self, "mixer", None)
+
+    def state_spec(self):
+        part = self.stateful_part()
+        return part.state_spec() if part is not None else None
+
+    def prepare(self, max_positions: int, device) -> None:
+        for part in self._built:
+            prepare = getattr(part, "prepare", None)
+            if prepare is not None:
+                prepare(max_positions, device)
 
     def forward(self, ctx, x, pending, cache):
         raise NotImplementedError

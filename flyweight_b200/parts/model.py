@@ -1,7 +1,9 @@
 """A decoder model put together from a ``ModelSpec``: embedding, the layers in the
 order its schedule names them, a final norm and the head.
 
-Embedding rows are taken without scaling (native/src/v2_runtime.cpp:27951-27956); the
+LFM2 takes embedding rows without scaling (native/src/v2_runtime.cpp:27951-27956) and has
+no soft-cap on its logits; ``ModelSpec.embedding_scale`` and ``logit_softcap`` are there for
+architectures that have them.  The
 head is the embedding table when the spec names none (native/src/v2_runtime.cpp:4190-4191);
 the final norm and the head run only on the rows whose logits were asked for.
 """
@@ -28,11 +30,11 @@ class DecoderModel:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         for position, entry in enumerate(spec.schedule):
-            mixer = self.layers[entry.layer].mixer
-            if entry.cache_of is not None and mixer.state_spec() is not None:
+            layer = self.layers[entry.layer]
+            if entry.cache_of is not None and layer.state_spec() is not None:
                 raise ValueError(
                     f"schedule position {position} reads the cache of position {entry.cache_of}, "
-                    f"but its mixer ({mixer.kind}) keeps a cache of its own")
+                    f"but its mixer ({layer.stateful_part().kind}) keeps a cache of its own")
 
     # ------------------------------------------------------------------ weights
     def declare(self) -> Dict[str, TensorDecl]:
@@ -67,11 +69,11 @@ class DecoderModel:
 
     def prepare(self, max_positions: int) -> None:
         for layer in self.layers:
-            layer.mixer.prepare(max_positions, self.device)
+            layer.prepare(max_positions, self.device)
 
     def state_specs(self) -> list:
         """What each schedule position keeps in the cache manager."""
-        return [None if entry.cache_of is not None else self.layers[entry.layer].mixer.state_spec()
+        return [None if entry.cache_of is not None else self.layers[entry.layer].state_spec()
                 for entry in self.spec.schedule]
 
     def weight_bytes(self, with_embedding_rows: int = 0) -> int:
@@ -84,6 +86,20 @@ class DecoderModel:
             total += sum(part.weight_bytes() for part in self.layers[entry.layer].parts())
         return total
 
+    def flops_per_token(self, with_head: bool = False) -> float:
+        """Operations of the matrix products one token passes through (every scheduled layer
+        once; the head only if asked: it runs on the wanted rows alone)."""
+        total = sum(part.flops_per_token() for entry in self.spec.schedule
+                    for part in self.layers[entry.layer].parts())
+        if with_head:
+            total += 2.0 * self.spec.vocab_size * self.spec.hidden_size
+        return total
+
+    def context_flops(self, n_tokens: int) -> float:
+        """Operations that grow with the context, for one causal prompt of ``n_tokens``."""
+        return sum(part.context_flops(n_tokens) for entry in self.spec.schedule
+                   for part in self.layers[entry.layer].parts())
+
     def parameter_count(self) -> int:
         return sum(int(torch.tensor(decl.shape).prod()) for decl in self.declare().values())
 
@@ -92,7 +108,7 @@ class DecoderModel:
         """Logits [R][V] fp32 at ``ctx.batch.logit_rows`` (an empty tensor if R == 0).
         ``caches[i]`` is the ``LayerCache`` of schedule position i."""
         batch = ctx.batch
-        x = ops.embed(self.embedding, batch.token_ids, ctx.bad_token_flag)
+        x = ops.embed(self.embedding, batch.token_ids, ctx.bad_token_flag, self.spec.embedding_scale)
         pending = None
         for position, entry in enumerate(self.spec.schedule):
             source = position if entry.cache_of is None else entry.cache_of
@@ -102,4 +118,7 @@ class DecoderModel:
         n = self.final_norm.defer(ctx, x, rows=batch.logit_rows) if pending is None else None
         if n is None:
             n = self.final_norm.forward(ctx, x, delta=pending, rows=batch.logit_rows)
-        return ops.linear(n, self.head, torch.float32)
+        logits = ops.linear(n, self.head, torch.float32)
+        if self.spec.logit_softcap > 0:
+            ops.softcap_(logits, self.spec.logit_softcap)
+        return logits

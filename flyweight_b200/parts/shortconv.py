@@ -52,6 +52,9 @@ class GatedShortConv(Mixer):
         return (self.w_in.numel() * self.w_in.element_size()
                 + self.w_out.numel() * self.w_out.element_size() + self.taps.numel() * 4)
 
+    def flops_per_token(self):
+        return 2.0 * (self.w_in.numel() + self.w_out.numel() + self.taps.numel())
+
     def state_spec(self):
         return FixedState((self.hidden, self.taps_len - 1))
 

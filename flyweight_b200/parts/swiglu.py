@@ -41,6 +41,9 @@ class SwiGLU(FeedForward):
         return (self.w_gate_up.numel() * self.w_gate_up.element_size()
                 + self.w_down.numel() * self.w_down.element_size())
 
+    def flops_per_token(self):
+        return 2.0 * (self.w_gate_up.numel() + self.w_down.numel())
+
     def forward(self, ctx, h, residual=None):
         act = ctx.precision.act_dtype
         if not isinstance(h, torch.Tensor):                   # a norm not yet applied

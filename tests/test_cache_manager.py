@@ -159,3 +159,20 @@ def test_block_table_rows_as_one_array_follow_the_lists():
         want = np.asarray(cache.block_table(g, ["b", "a"], 3), dtype=np.int32)
         assert np.array_equal(cache.block_table_array(g, ["b", "a"], 3), want)
     cache.check() if hasattr(cache, "check") else None
+
+
+def test_fixed_states_of_different_dtypes_get_pools_of_their_own_and_are_zeroed_together():
+    import torch
+    specs = [FixedState((4, 2)), PagedKV(1, 16), FixedState((3,), dtype=torch.bfloat16), FixedState((5,))]
+    cache = CacheManager(specs, num_pages=4, num_slots=3, device="cpu")
+    states = [cache.layer_caches[i].state for i in (0, 2, 3)]
+    assert [s.dtype for s in states] == [torch.float32, torch.bfloat16, torch.float32]
+    assert [tuple(s.shape) for s in states] == [(3, 4, 2), (3, 3), (3, 5)]
+    for state in states:
+        state.fill_(7)
+    slot = cache.admit("a")
+    for state in states:
+        assert float(state[slot].float().abs().sum()) == 0.0            # the slot handed out is clean
+        assert all(float(state[other].float().min()) == 7.0 for other in range(3) if other != slot)
+    states[0][slot].fill_(1)
+    assert float(states[2][slot].sum()) == 0.0 and float(states[1][slot].float().sum()) == 0.0   # no overlap

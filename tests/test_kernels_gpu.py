@@ -299,7 +299,8 @@ def rope_table(theta, rot, n):
                                            (8, 2, 128, 64), (2, 2, 256, 256)])
 @pytest.mark.parametrize("dtype,bf16_input", [(torch.float32, False), (torch.bfloat16, False),
                                               (torch.bfloat16, True)])
-def test_qk_norm_rope_and_cache_write(nh, nkv, hd, rot, dtype, bf16_input):
+@pytest.mark.parametrize("pairing", ["half_split", "interleaved"])
+def test_qk_norm_rope_and_cache_write(nh, nkv, hd, rot, dtype, bf16_input, pairing):
     from flyweight_b200.kernels import ops
     g = torch.Generator().manual_seed(nh * hd)
     T, pages, P_ = 6, 5, 64
@@ -316,13 +317,18 @@ def test_qk_norm_rope_and_cache_write(nh, nkv, hd, rot, dtype, bf16_input):
     v_pool = torch.full((pages, nkv, P_, hd), 7.0).to(dtype)
     kd, vd = dev(k_pool), dev(v_pool)
     q = ops.qk_norm_rope(dev(qkv), dev(wq), dev(wk), dev(table), dev(positions), dev(tok_seg),
-                         dev(table_rows), kd, vd, nh, nkv, hd, rot, eps, dtype)
+                         dev(table_rows), kd, vd, nh, nkv, hd, rot, eps, dtype, pairing=pairing)
 
     def norm_rope(x, w, pos):                                 # x: [heads, hd] float64
         x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
         cs = table[pos].double()
-        a, b = x[:, :rot // 2], x[:, rot // 2:rot]
         out = x.clone()
+        if pairing == "interleaved":                          # pair i = channels (2i, 2i + 1)
+            a, b = x[:, 0:rot:2], x[:, 1:rot:2]
+            out[:, 0:rot:2] = a * cs[:, 0] - b * cs[:, 1]
+            out[:, 1:rot:2] = b * cs[:, 0] + a * cs[:, 1]
+            return out
+        a, b = x[:, :rot // 2], x[:, rot // 2:rot]            # pair i = channels (i, i + rot/2)
         out[:, :rot // 2] = a * cs[:, 0] - b * cs[:, 1]
         out[:, rot // 2:rot] = b * cs[:, 0] + a * cs[:, 1]
         return out

@@ -170,7 +170,7 @@ def toy_architecture():
             self.w = get(self.names["w"]).to(device=device, dtype=torch.float32)
 
         def state_spec(self):
-            return FixedState((self.hidden,))
+            return FixedState((self.hidden,), dtype=torch.float64)     # a state that is not fp32
 
         def forward(self, ctx, h, cache):
             out = torch.empty(h.shape, dtype=torch.float32, device=h.device)
@@ -178,8 +178,9 @@ def toy_architecture():
             for seg in ctx.batch.segments:          # test code: plain torch, token by token
                 s = cache.state[seg.slot]
                 for t in range(start, start + len(seg.tokens)):
-                    s.mul_(self.decay).add_(h[t].float())
-                    out[t] = self.w @ s
+                    assert s.dtype == torch.float64
+                    s.mul_(self.decay).add_(h[t].double())
+                    out[t] = self.w @ s.float()
                 start += len(seg.tokens)
             return out
 
@@ -212,7 +213,8 @@ def toy_architecture():
                            for i, m in enumerate(mixers))
             # layer 0 runs twice (two states), layer 2 reads the cache that layer 1 wrote
             schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2, cache_of=1), ScheduleEntry(0))
-            return ModelSpec("ToyForCausalLM", H, V, 512, "embed", norm("final"), None, layers, schedule)
+            return ModelSpec("ToyForCausalLM", H, V, 512, "embed", norm("final"), None, layers, schedule,
+                             embedding_scale=1.5, logit_softcap=6.0)
 
     class ToyForCausalLM(DecoderModel):
         def __init__(self, config, precision, device):
@@ -228,7 +230,7 @@ def toy_reference(raw, w, tokens):
     H = raw["hidden_size"]
     hd = H // 2
     T = len(tokens)
-    x = w["embed"][np.asarray(tokens)]
+    x = 1.5 * w["embed"][np.asarray(tokens)]                   # ModelSpec.embedding_scale
     window = raw.get("window", 0)
 
     def ffn(h, i):
@@ -271,14 +273,16 @@ def toy_reference(raw, w, tokens):
             delta = attend(q, kv["k"], kv["v"]) @ w[f"l{layer}.attn.o"].T
         x = x + delta
         x = x + ffn(P.rms_norm(x, w[f"l{layer}.n2"], 1e-5), layer)
-    return P.rms_norm(x, w["final"], 1e-5) @ w["embed"].T
+    logits = P.rms_norm(x, w["final"], 1e-5) @ w["embed"].T
+    return 6.0 * np.tanh(logits / 6.0)                         # ModelSpec.logit_softcap
 
 
 @pytest.mark.parametrize("window", [0, 40])
 def test_a_toy_architecture_defined_in_the_test(window, tmp_path):
     """Registered mixer with its own state, a layer scheduled twice, a layer reading another
-    layer's cache, partial rotary, no q/k norm, a sliding window with its own page group --
-    without touching a file of the framework."""
+    layer's cache, partial rotary, no q/k norm, a sliding window with its own page group, a state
+    that is not fp32, a scaled embedding and soft-capped logits -- without touching a file of the
+    framework."""
     from flyweight_b200.engine import ModelRunner, load_model
     from flyweight_b200.weights import load_model_tensors
     from tiny_configs import make_model_dir
@@ -288,6 +292,7 @@ def test_a_toy_architecture_defined_in_the_test(window, tmp_path):
     specs = model.state_specs()
     assert [type(s).__name__ for s in specs] == ["FixedState", "PagedKV", "NoneType", "FixedState"]
     runner = ModelRunner(model, num_pages=4, num_slots=2, max_model_len=256)
+    assert runner.cache.layer_caches[0].state.dtype == torch.float64
     assert runner.cache.groups[0].window == window
     w = as_numpy(load_model_tensors(folder))
     tokens = [int(t) for t in np.random.default_rng(0).integers(0, 50, size=200)]
@@ -318,7 +323,8 @@ def toy_routed_architecture():
     by its probability) and a position encoding of its own (rotary angles at pos / 4, full
     head), in a model whose two layers differ (dense SwiGLU in one, routed experts in the other)."""
     from flyweight_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
-    from flyweight_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position
+    from flyweight_b200.parts import (Arrangement, FeedForward, PositionEncoding, register_arrangement,
+                                      register_feed_forward, register_position)
     from flyweight_b200.parts.model import DecoderModel
     from flyweight_b200.weights import TensorDecl
 
@@ -334,6 +340,20 @@ def toy_routed_architecture():
             inv = 50.0 ** (-torch.arange(half, dtype=torch.float64) * 2 / self.rotary_dim)
             angle = (torch.arange(n_positions, dtype=torch.float64) / self.slowdown)[:, None] * inv[None]
             return torch.stack([angle.cos(), angle.sin()], -1).float().contiguous().to(device)
+
+    @register_arrangement("toy_post_norm_ffn_only")
+    class PostNormFfnOnly(Arrangement):
+        """A layer with no mixer and a norm *after* its feed-forward: x += norm(ffn(x)).  Two parts
+        where the pre-norm block has four; it keeps nothing in the cache."""
+        ROLES = {"feed_forward": ("feed_forward", True), "post_norm": ("norm", True)}
+
+        def forward(self, ctx, x, pending, cache):
+            from flyweight_b200.kernels import ops
+            if pending is not None:
+                ops.add_(x, pending)
+            delta = self.feed_forward.forward(ctx, x)           # this toy's experts read fp32 rows
+            normed = self.post_norm.forward(ctx, delta.contiguous())
+            return x, normed.float()
 
     @register_feed_forward("toy_top1_experts")
     class Top1Experts(FeedForward):
@@ -376,18 +396,24 @@ def toy_routed_architecture():
         def model_spec(self):
             H, V = self.raw["hidden_size"], self.raw["vocab_size"]
             norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-6}, {"weight": name})
+            positions = [PartSpec("toy_slow_rope", {"rotary_dim": 16, "slowdown": 4.0}),
+                         # the framework's rotary part with the other pairing, on half of the head
+                         PartSpec("rope", {"theta": 50.0, "rotary_dim": 8, "pairing": "interleaved"})]
             attn = lambda i: PartSpec("gqa_attention", {
                 "hidden_size": H, "num_heads": 3, "num_kv_heads": 3, "head_dim": 16, "qk_norm_eps": None,
-                "position": PartSpec("toy_slow_rope", {"rotary_dim": 16, "slowdown": 4.0})},
+                "position": positions[i]},
                 {k: f"l{i}.attn.{k}" for k in ("q", "k", "v", "o")})
+            routed2 = PartSpec("toy_top1_experts", {"hidden_size": H, "width": 24, "experts": 3},
+                               {"router": "l2.router", "up": "l2.experts.up", "down": "l2.experts.down"})
             dense = PartSpec("swiglu", {"hidden_size": H, "ffn_dim": 80},
                              {"gate": "l0.gate", "up": "l0.up", "down": "l0.down"})
             routed = PartSpec("toy_top1_experts", {"hidden_size": H, "width": 24, "experts": 3},
                               {"router": "l1.router", "up": "l1.experts.up", "down": "l1.experts.down"})
             layers = (LayerSpec("prenorm_residual", norm("l0.n1"), attn(0), norm("l0.n2"), dense),
-                      LayerSpec("prenorm_residual", norm("l1.n1"), attn(1), norm("l1.n2"), routed))
+                      LayerSpec("prenorm_residual", norm("l1.n1"), attn(1), norm("l1.n2"), routed),
+                      LayerSpec("toy_post_norm_ffn_only", parts={"feed_forward": routed2, "post_norm": norm("l2.post")}))
             return ModelSpec("ToyRoutedForCausalLM", H, V, 512, "embed", norm("final"), "head", layers,
-                             (ScheduleEntry(0), ScheduleEntry(1)))
+                             (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2)))
 
     class ToyRoutedForCausalLM(DecoderModel):
         def __init__(self, config, precision, device):
@@ -411,9 +437,21 @@ def toy_routed_reference(raw, w, tokens):
         a, b = v[..., :half], v[..., half:]
         return np.concatenate([a * cos - b * sin, b * cos + a * sin], -1)
 
+    def rope_interleaved(v):                       # pairs (2i, 2i + 1) of the first 8 channels, base 50
+        rot = 8
+        inv = 50.0 ** (-np.arange(rot // 2) * 2.0 / rot)
+        ang = pos[:, None] * inv[None]
+        cos, sin = np.cos(ang)[:, None], np.sin(ang)[:, None]
+        out = v.copy()
+        a, b = v[..., 0:rot:2], v[..., 1:rot:2]
+        out[..., 0:rot:2] = a * cos - b * sin
+        out[..., 1:rot:2] = b * cos + a * sin
+        return out
+
     def attend(h, i):
-        q = rope((h @ w[f"l{i}.attn.q"].T).reshape(T, nh, hd))
-        k = rope((h @ w[f"l{i}.attn.k"].T).reshape(T, nh, hd))
+        turn = rope if i == 0 else rope_interleaved
+        q = turn((h @ w[f"l{i}.attn.q"].T).reshape(T, nh, hd))
+        k = turn((h @ w[f"l{i}.attn.k"].T).reshape(T, nh, hd))
         v = (h @ w[f"l{i}.attn.v"].T).reshape(T, nh, hd)
         out = np.zeros((T, nh, hd))
         ok = pos[None] <= pos[:, None]
@@ -423,12 +461,12 @@ def toy_routed_reference(raw, w, tokens):
             out[:, head] = (p / p.sum(-1, keepdims=True)) @ v[:, head]
         return out.reshape(T, nh * hd) @ w[f"l{i}.attn.o"].T
 
-    def experts(h):
-        logits = h @ w["l1.router"].T
+    def experts(h, i=1):
+        logits = h @ w[f"l{i}.router"].T
         prob = np.exp(logits - logits.max(-1, keepdims=True))
         prob /= prob.sum(-1, keepdims=True)
-        up = w["l1.experts.up"].reshape(3, 24, H)
-        down = w["l1.experts.down"].reshape(3, H, 24)
+        up = w[f"l{i}.experts.up"].reshape(3, 24, H)
+        down = w[f"l{i}.experts.down"].reshape(3, H, 24)
         out = np.zeros_like(h)
         for t in range(T):
             e = int(prob[t].argmax())
@@ -440,13 +478,16 @@ def toy_routed_reference(raw, w, tokens):
     x = x + (P.silu(h @ w["l0.gate"].T) * (h @ w["l0.up"].T)) @ w["l0.down"].T
     x = x + attend(P.rms_norm(x, w["l1.n1"], 1e-6), 1)
     x = x + experts(P.rms_norm(x, w["l1.n2"], 1e-6))
+    x = x + P.rms_norm(experts(x, 2), w["l2.post"], 1e-6)      # the layer without a mixer, norm after
     return P.rms_norm(x, w["final"], 1e-6) @ w["head"].T
 
 
 def test_a_routed_feed_forward_and_another_position_encoding_defined_in_the_test(tmp_path):
-    """A feed-forward with routing and a position encoding of its own are registered here,
-    named by a toy configuration layer by layer (one dense, one routed), and the model is
-    built, loaded, stepped whole and in portions, and decoded through the framework."""
+    """A feed-forward with routing, a position encoding of its own and an arrangement of its own
+    (no mixer, a norm after the feed-forward: two parts instead of four) are registered here,
+    named by a toy configuration layer by layer (one dense, one routed, one without a mixer; one
+    attention with the toy's positions, one with the framework's rotary part in interleaved
+    pairing), and the model is built, loaded, stepped whole and in portions through the framework."""
     from flyweight_b200.engine import ModelRunner, load_model
     from flyweight_b200.weights import load_model_tensors
     from tiny_configs import make_model_dir
@@ -454,6 +495,7 @@ def test_a_routed_feed_forward_and_another_position_encoding_defined_in_the_test
     folder = make_model_dir(tmp_path / "routed", raw, seed=4, dtype=torch.float32)
     model = load_model(folder, "float32")
     assert not model.graph_safe                     # a part defined elsewhere: decode steps run eagerly
+    assert [type(spec).__name__ for spec in model.state_specs()] == ["PagedKV", "PagedKV", "NoneType"]
     runner = ModelRunner(model, num_pages=6, num_slots=2, max_model_len=256)
     w = as_numpy(load_model_tensors(folder))
     tokens = [int(t) for t in np.random.default_rng(1).integers(0, 70, size=150)]
