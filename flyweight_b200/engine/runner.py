@@ -24,6 +24,7 @@ from ..cache.manager import PAGE_SIZE, CacheManager, OutOfPages, OutOfSlots
 from ..kernels.lib import require_cuda
 from .batch import Segment, StepBatch, StepContext
 from .graphs import DecodeGraph
+from .plan import build_plan
 
 Entry = Tuple[Hashable, Sequence[int], Sequence[int]]
 
@@ -148,7 +149,7 @@ class StepPlanner:
 
 class ModelRunner(StepPlanner):
     def __init__(self, model, num_pages: int, num_slots: int, max_model_len: int,
-                 max_batched_tokens: int = 8192, use_graphs: bool = True):
+                 max_batched_tokens: int = 8192, use_graphs: bool = True, use_plan: bool = True):
         require_cuda()
         self.model = model
         self.precision = model.precision
@@ -163,6 +164,10 @@ class ModelRunner(StepPlanner):
                              cache_dtype=self.precision.cache_dtype, device=self.device)
         super().__init__(cache, model.spec.vocab_size, max_model_len, max_batched_tokens)
         self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the forward pass of a step as one native call, when every part of the model has that form
+        self.use_plan = bool(use_plan)
+        self.plan = build_plan(model, cache.layer_caches, self.max_batched_tokens, self.max_batched_tokens,
+                               num_slots, len(cache.groups), self.bad_token_flag) if use_plan else None
         # decode steps replay a CUDA graph per (batch size, block-table width)
         self.use_graphs = bool(use_graphs) and model.graph_safe
         self.max_graph_batch = 256
@@ -199,6 +204,12 @@ class ModelRunner(StepPlanner):
             return logits
         self.last_decode_graph = None
         tables = [self.cache.block_table_array(g, requests, width) for g in range(n_groups)]
+        if self.plan is not None and self.use_plan:
+            logits = self.plan.run(segments, tables)
+            self.steps += 1
+            self.tokens_run += self.plan._step.T
+            self.h2d_bytes += self.plan.h2d_bytes
+            return logits
         batch = StepBatch(segments, tables, self.device)
         ctx = StepContext(batch, self.precision, self.device, self.bad_token_flag)
         logits = self.model.forward(ctx, self.cache.layer_caches)

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from . import ops
+from . import lib, ops
 
 SM_COUNT = 148
 CLUSTER_MERGE_CTAS = 1024
@@ -21,6 +21,7 @@ def set_mma_enabled(flag: bool) -> None:
     """Tests switch the tensor-core kernels off to compare them with the SIMT kernel."""
     global _use_mma
     _use_mma = bool(flag)
+    lib.set_option("attention_mma", _use_mma)
 
 
 _force_tiled = False
@@ -31,6 +32,7 @@ def set_tcgen05_enabled(flag: bool) -> None:
     """Prompt portions through the mma.sync kernel instead of the tcgen05 one (for comparisons)."""
     global _use_tcgen05
     _use_tcgen05 = bool(flag)
+    lib.set_option("attention_tcgen05", _use_tcgen05)
 
 
 
@@ -41,6 +43,13 @@ def set_mixed_split(flag: bool) -> None:
     """Decoding requests at the head of a mixed step through the decode kernel (on by default)."""
     global _split_mixed
     _split_mixed = bool(flag)
+    lib.set_option("mixed_split", _split_mixed)
+
+
+def heads_the_decode_kernel() -> bool:
+    """Whether the decoding requests at the head of a mixed step go to the decode kernel (the tile
+    lists of the prompt kernels then start behind them)."""
+    return _split_mixed and not _force_tiled
 
 
 def force_tiled(flag: bool) -> None:
@@ -48,6 +57,7 @@ def force_tiled(flag: bool) -> None:
     in one order whatever else is in the step, so tests can compare cuts bit by bit."""
     global _force_tiled
     _force_tiled = bool(flag)
+    lib.set_option("force_tiled", _force_tiled)
 
 
 def decode_splits(n_tokens: int, n_kv: int, max_tiles: int):

@@ -152,6 +152,19 @@ def call(name: str, *args, launches: int = 1) -> None:
     _launch_count += launches
 
 
+# Switches of the native dispatch (csrc/plan.cu: enum Option); the Python setters of
+# kernels/tensorcore.py and kernels/attention.py keep both sides equal.
+OPTIONS = {"tensorcore": 0, "forced_splits": 1, "pairs": 2, "mid_size_split": 3, "fuse_norm": 4,
+           "add_in_place": 5, "fuse_always": 6, "attention_mma": 7, "force_tiled": 8,
+           "attention_tcgen05": 9, "mixed_split": 10}
+
+
+def set_option(name: str, value: int) -> None:
+    status = library().fwb_set_option(OPTIONS[name], int(value))
+    if status != 0:
+        raise KernelError(f"the library knows no option {name!r}")
+
+
 c_int = ctypes.c_int
 c_float = ctypes.c_float
 c_longlong = ctypes.c_longlong

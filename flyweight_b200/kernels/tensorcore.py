@@ -19,6 +19,7 @@ def set_enabled(flag: bool) -> None:
     """Tests switch the tensor-core path off to compare it with the SIMT path."""
     global _enabled
     _enabled = bool(flag)
+    lib.set_option("tensorcore", _enabled)
 
 
 def _aligned(t: torch.Tensor) -> bool:
@@ -46,6 +47,7 @@ def set_pairs_enabled(flag: bool) -> None:
     """Prompt-sized products on CTA pairs (on by default); off: the single-CTA kernel."""
     global _use_pairs
     _use_pairs = bool(flag)
+    lib.set_option("pairs", _use_pairs)
 
 # Per-shape overrides found by measurement: (features, K, accumulators) -> (splits, stages);
 # 0 keeps the rule's choice.  Only decode-sized token counts (<= 64) consult it.
@@ -58,6 +60,7 @@ def force_splits(splits) -> None:
     lets tests compare ways of cutting the work bit by bit."""
     global _forced_splits
     _forced_splits = splits
+    lib.set_option("forced_splits", splits or 0)
 
 
 def pick_splits(M: int, N: int, K: int) -> int:
@@ -123,6 +126,7 @@ def set_mid_size_split(flag: bool) -> None:
     split K (on by default); off: CTA pairs or one CTA per tile, as before."""
     global _mid_size_split
     _mid_size_split = bool(flag)
+    lib.set_option("mid_size_split", _mid_size_split)
 
 
 def _mid_size_splits(M: int, N: int, K: int) -> int:
@@ -277,6 +281,7 @@ def fuse_always(flag: bool) -> None:
     """Fold norms and residual sums at every decode-sized token count (tests of that path)."""
     global _fuse_always
     _fuse_always = bool(flag)
+    lib.set_option("fuse_always", _fuse_always)
 
 
 
@@ -286,6 +291,8 @@ def set_norm_fusion(flag: bool) -> None:
     switch it off so that every cut runs the same arithmetic."""
     global _fuse_norm, _add_in_place
     _fuse_norm = _add_in_place = bool(flag)
+    lib.set_option("fuse_norm", _fuse_norm)
+    lib.set_option("add_in_place", _add_in_place)
 
 
 def normed_accepts(M: int, K: int, w, accumulators: int, N: int) -> bool:

@@ -109,3 +109,23 @@ class GQAttention(Mixer):
         out = attention_kernels.paged_attention(ctx, q, cache, block_table, self.n_heads,
                                                 self.window, self.scale, act)
         return ops.linear_into_residual(out, self.w_o, residual)
+
+    def plan(self, builder, norm, cache):
+        """The same operations for the native step plan (``engine/plan.py``)."""
+        from ..engine.plan import EPI_ACT, NotPlannable
+        act = builder.act_dtype
+        plan_position = getattr(self.position, "plan", None)
+        if plan_position is None:
+            raise NotPlannable(f"position encoding {self.position.kind!r} has no native form")
+        width = self.n_heads * self.head_dim
+        qkv = builder.tokens(width + 2 * self._kv_in * self.head_dim, act)
+        builder.norm_linear(norm, self.w_qkv, EPI_ACT, qkv, "q|k|v")
+        q = builder.tokens(width, act)
+        plan_position(builder, qkv, q, n_heads=self.n_heads, n_kv_in=self._kv_in, head_dim=self.head_dim,
+                      q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, cache=cache)
+        builder.free(qkv)
+        out = builder.tokens(width, act)
+        builder.attention(q, cache, out, self.n_heads, self.window, self.scale)
+        builder.free(q)
+        builder.linear_residual(out, self.w_o, "attention out_proj")
+        builder.free(out)

@@ -191,6 +191,17 @@ class PositionEncoding(Part):
             cache.v_pool if n_kv_in else None, n_heads, n_kv_in, head_dim, self.rotary_dim,
             float(eps or 0.0), ctx.precision.act_dtype, pairing=self.pairing)
 
+    def plan(self, builder, qkv, q_out, *, n_heads: int, n_kv_in: int, head_dim: int, q_norm, k_norm,
+             eps, cache) -> None:
+        """``encode`` for the native step plan.  Only an encoding that keeps the default ``encode``
+        has this form; one that overrides ``encode`` leaves its model on the Python path unless it
+        overrides ``plan`` as well."""
+        from ..engine.plan import NotPlannable
+        if type(self).encode is not PositionEncoding.encode:
+            raise NotPlannable(f"position encoding {self.kind!r} encodes in its own way")
+        builder.qk_rope(qkv, q_norm, k_norm, self._table, q_out, cache, n_heads, n_kv_in, head_dim,
+                        self.rotary_dim, self.pairing, eps)
+
 
 class Mixer(Part):
     def state_spec(self):

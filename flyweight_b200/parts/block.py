@@ -24,3 +24,13 @@ class PreNormResidual(Arrangement):
         delta = mixer.forward(ctx, h, cache, residual=x) if mixer.adds_residual else mixer.forward(ctx, h, cache)
         h = _normed(self.ffn_norm, ffn, ctx, x, delta)
         return x, (ffn.forward(ctx, h, residual=x) if ffn.adds_residual else ffn.forward(ctx, h))
+
+    def plan(self, builder, cache):
+        """This block's operations for the native step plan: the mixer behind its norm, the
+        feed-forward behind its norm; the residual sums ride on the products."""
+        from ..engine.plan import NotPlannable
+        for part in (self.mixer, self.feed_forward):
+            if getattr(part, "plan", None) is None:
+                raise NotPlannable(f"part {part.kind!r} has no native form")
+        self.mixer.plan(builder, self.mixer_norm, cache)
+        self.feed_forward.plan(builder, self.ffn_norm)

@@ -37,3 +37,7 @@ class RMSNorm(Norm):
 
     def defer(self, ctx, x, rows=None):
         return DeferredNorm(x, self.weight, self.eps, rows)
+
+    def plan_params(self):
+        """(weight, eps): what the native step plan needs to run this norm in front of a product."""
+        return self.weight, self.eps

@@ -65,3 +65,15 @@ class GatedShortConv(Mixer):
         z = ops.shortconv(p, self.taps, self.bias, cache.state, batch.seg_start, batch.seg_slot,
                           batch.tok_seg, batch.n_segments, ctx.precision.act_dtype)
         return ops.linear_into_residual(z, self.w_out, residual)
+
+    def plan(self, builder, norm, cache):
+        """The same three operations for the native step plan (``engine/plan.py``)."""
+        from ..engine.plan import EPI_ACT
+        act = builder.act_dtype
+        p = builder.tokens(3 * self.hidden, act)
+        builder.norm_linear(norm, self.w_in, EPI_ACT, p, "conv in_proj")
+        z = builder.tokens(self.hidden, act)
+        builder.shortconv(p, self.taps, self.bias, cache.state, z)
+        builder.free(p)
+        builder.linear_residual(z, self.w_out, "conv out_proj")
+        builder.free(z)

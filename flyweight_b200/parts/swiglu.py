@@ -60,3 +60,11 @@ class SwiGLU(FeedForward):
             gate_up = ops.linear(h, self.w_gate_up, act)
             a = ops.silu_mul(gate_up, act)
         return ops.linear_into_residual(a, self.w_down, residual)
+
+    def plan(self, builder, norm):
+        """Norm, gate|up with silu(g)*u, down with the residual sum, for the native step plan."""
+        from ..engine.plan import EPI_SWIGLU
+        a = builder.tokens(self.ffn_dim, builder.act_dtype)
+        builder.norm_linear(norm, self.w_gate_up, EPI_SWIGLU, a, "gate|up")
+        builder.linear_residual(a, self.w_down, "down")
+        builder.free(a)
