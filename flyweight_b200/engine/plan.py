@@ -322,7 +322,7 @@ class StepPlan:
         # tiles of the two prompt attention kernels: every segment from `first` on cut into runs
         first = leading if (max_segment > 1 and attention_kernels.heads_the_decode_kernel()) else 0
         tiles = []
-        if max_segment > 1:
+        if max_segment > 1 or attention_kernels.tiled_forced():
             for per_tile in self.tokens_per_tile:
                 seg_of, tok0 = [], []
                 base = 0

@@ -166,7 +166,7 @@ class ModelRunner(StepPlanner):
         self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the forward pass of a step as one native call, when every part of the model has that form
         self.use_plan = bool(use_plan)
-        self.plan = build_plan(model, cache.layer_caches, self.max_batched_tokens, self.max_batched_tokens,
+        self.step_plan = build_plan(model, cache.layer_caches, self.max_batched_tokens, self.max_batched_tokens,
                                num_slots, len(cache.groups), self.bad_token_flag) if use_plan else None
         # decode steps replay a CUDA graph per (batch size, block-table width)
         self.use_graphs = bool(use_graphs) and model.graph_safe
@@ -204,11 +204,11 @@ class ModelRunner(StepPlanner):
             return logits
         self.last_decode_graph = None
         tables = [self.cache.block_table_array(g, requests, width) for g in range(n_groups)]
-        if self.plan is not None and self.use_plan:
-            logits = self.plan.run(segments, tables)
+        if self.step_plan is not None and self.use_plan:
+            logits = self.step_plan.run(segments, tables)
             self.steps += 1
-            self.tokens_run += self.plan._step.T
-            self.h2d_bytes += self.plan.h2d_bytes
+            self.tokens_run += self.step_plan._step.T
+            self.h2d_bytes += self.step_plan.h2d_bytes
             return logits
         batch = StepBatch(segments, tables, self.device)
         ctx = StepContext(batch, self.precision, self.device, self.bad_token_flag)

@@ -46,6 +46,11 @@ def set_mixed_split(flag: bool) -> None:
     lib.set_option("mixed_split", _split_mixed)
 
 
+def tiled_forced() -> bool:
+    """Whether single decode tokens go through the tiled kernel too (``force_tiled``)."""
+    return _force_tiled
+
+
 def heads_the_decode_kernel() -> bool:
     """Whether the decoding requests at the head of a mixed step go to the decode kernel (the tile
     lists of the prompt kernels then start behind them)."""

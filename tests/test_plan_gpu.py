@@ -19,7 +19,7 @@ def pair_of_runners(model, num_pages=24, num_slots=6, max_model_len=1024, max_ba
     made = [ModelRunner(model, num_pages=num_pages, num_slots=num_slots, max_model_len=max_model_len,
                         max_batched_tokens=max_batched_tokens, use_graphs=False, use_plan=use_plan)
             for use_plan in (False, True)]
-    assert made[0].plan is None and made[1].plan is not None, getattr(model, "not_plannable", "")
+    assert made[0].step_plan is None and made[1].step_plan is not None, getattr(model, "not_plannable", "")
     return made
 
 
@@ -62,7 +62,7 @@ def test_tiny_models_step_for_step(name, dtype):
     for r in runners:
         r.cache.check()
         r.check_health()
-    assert runners[1].plan.n_ops > 10
+    assert runners[1].step_plan.n_ops > 10
 
 
 def test_decoding_requests_at_the_head_of_a_step_beside_portions():
@@ -133,7 +133,7 @@ def test_real_tile_shapes_step_for_step(tmp_path):
     draw = lambda n: [int(t) for t in rng.integers(0, MEDIUM["vocab_size"], size=n)]
     steps = []
     for n in (700, 256, 100, 64, 33, 17, 16, 8, 1, 300, 513, 2048):
-        steps.append({"entries": [{"id": "a", "tokens": draw(n), "want": [0, n - 1]}], "end": []})
+        steps.append({"entries": [{"id": "a", "tokens": draw(n), "want": sorted({0, n - 1})}], "end": []})
     steps[-1]["end"] = ["a"]
     same_steps(runners, steps, "medium, one request")
     # three requests decoding at a long context beside a portion of a fourth
@@ -150,19 +150,19 @@ def test_real_tile_shapes_step_for_step(tmp_path):
 
 
 def test_many_decoding_requests_whose_slices_a_second_kernel_merges(tmp_path):
-    """36 requests of 600 cached tokens decode together: too many CTAs for the in-cluster merge, so
+    """36 requests of 3,700 cached tokens decode together: too many CTAs for the in-cluster merge, so
     the slices go through scratch memory (the plan's own, inside its arena) and a merge kernel."""
     from flyweight_b200.engine import load_model
     from flyweight_b200.kernels import attention
     folder = make_model_dir(tmp_path / "medium", dict(MEDIUM, num_hidden_layers=2, layer_types=["full_attention", "conv"]),
                             seed=9, dtype=torch.bfloat16)
     model = load_model(folder, "bfloat16")
-    runners = pair_of_runners(model, num_pages=400, num_slots=40, max_model_len=1024, max_batched_tokens=1024)
-    splits, _, in_cluster = attention.decode_splits(36, 4, 10)
+    runners = pair_of_runners(model, num_pages=2200, num_slots=40, max_model_len=4096, max_batched_tokens=4096)
+    splits, _, in_cluster = attention.decode_splits(36, 4, 58)
     assert splits > 1 and not in_cluster
     rng = np.random.default_rng(5)
     draw = lambda n: [int(t) for t in rng.integers(0, MEDIUM["vocab_size"], size=n)]
-    steps = [{"entries": [{"id": f"d{i}", "tokens": draw(600), "want": []}], "end": []} for i in range(36)]
+    steps = [{"entries": [{"id": f"d{i}", "tokens": draw(3700), "want": []}], "end": []} for i in range(36)]
     for _ in range(3):
         steps.append({"entries": [{"id": f"d{i}", "tokens": draw(1), "want": [0]} for i in range(36)], "end": []})
     steps[-1]["end"] = [f"d{i}" for i in range(36)]
@@ -175,6 +175,6 @@ def test_a_model_with_a_part_defined_elsewhere_keeps_the_python_path():
     raw = toy_architecture()
     model = random_model(raw, seed=1, dtype="float32", preset="unit", stored_dtype=torch.float32)
     runner = ModelRunner(model, num_pages=4, num_slots=2, max_model_len=128)
-    assert runner.plan is None and "toy_decay" in model.not_plannable
+    assert runner.step_plan is None and "toy_decay" in model.not_plannable
     out = runner.step([("a", [1, 2, 3], [2])])
     assert out.shape == (1, raw["vocab_size"]) and torch.isfinite(out).all()
