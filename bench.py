@@ -427,6 +427,116 @@ def run_profile_step(args) -> int:
     return 0
 
 
+def run_mixed(args) -> int:
+    """``--mixed lfm2-350m``: the baseline's mixed workload through the public runtime.  64 requests
+    with prompt lengths drawn uniformly from 128 to 8,192 tokens are queued at once; the scheduler
+    reads the prompts in portions under a budget of 512 tokens a step beside the requests that
+    already decode; every request generates 256 tokens (greedy).  One JSON line: end-to-end tokens
+    a second (prompt and generated tokens over the wall time), generated tokens a second, and per
+    step the host's share (the time ``engine_step`` spends before it waits for the device) and
+    the wait."""
+    import random
+    import torch
+    from flyweight_b200.engine.runtime import Model
+    name = args.mixed
+    if name not in MODELS:
+        print(json.dumps({"error": f"--mixed wants one of {sorted(MODELS)}"}))
+        return 1
+    config = dict(MODELS[name])
+    model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0")
+    requests, new_tokens, budget = 64, 256, 512
+    rnd = random.Random(0)
+    lengths = [rnd.randint(128, 8192) for _ in range(requests)]
+    generator = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, config["vocab_size"], (n,), generator=generator).tolist() for n in lengths]
+    results = []
+    for attempt in range(2):                      # the first pass warms up (graphs are recorded), the second counts
+        runtime = model.native_runtime(context_limit=8192 + new_tokens + 8, parallel_sequences=requests,
+                                       max_batched_tokens=budget)
+        for prompt in prompts:
+            runtime.task_submit(prompt, new_tokens, temperature=0.0)
+        torch.cuda.synchronize()
+        clock = ClockSampler(0)
+        clock.start()
+        begun = time.perf_counter()
+        steps = generated = 0
+        while runtime.has_work():
+            for _, _, kind in runtime.engine_step():
+                generated += kind == 0
+            steps += 1
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - begun
+        clocks = clock.stop()
+        info = runtime.info
+        runtime.close()
+        results.append((wall, steps, generated, info, clocks))
+    wall, steps, generated, info, clocks = results[-1]
+    waited = info["sampling_seconds"]
+    print(json.dumps({
+        "mixed": name, "parameters": model.module.parameter_count(), "requests": requests,
+        "prompt_tokens": sum(lengths), "generated_tokens": generated, "token_budget": budget,
+        "seconds": round(wall, 4), "steps": steps,
+        "tokens_per_s": round((sum(lengths) + generated) / wall, 1),
+        "generated_tokens_per_s": round(generated / wall, 1),
+        "ms_per_step": round(1e3 * wall / steps, 4),
+        "host_ms_per_step": round(1e3 * (info["step_seconds"] - waited) / steps, 4),
+        "wait_ms_per_step": round(1e3 * waited / steps, 4),
+        "steady_steps": info["steady_steps"], "preemptions": info["preemptions"],
+        "first_pass_seconds": round(results[0][0], 4), "clocks": clocks,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, seeded random weights"}))
+    return 0
+
+
+def run_kernel_times(args) -> int:
+    """``--kernel-times decode|prefill|TOKENS``: one step of LFM2-1.2B launched kernel by kernel with
+    a pair of CUDA events around every launch; prints {kernel, calls, us, share} by falling time,
+    launches per step and the host time spent inside the launchers, as one JSON line.  The events
+    keep kernels from overlapping their neighbours, so the sum is above the step's real time
+    (printed beside it, from a second, unbracketed run of the same step)."""
+    import torch
+    from flyweight_b200.engine import ModelRunner
+    from flyweight_b200.engine.runtime import Model
+    from flyweight_b200.kernels import lib as kernel_lib
+    from flyweight_b200.sampling import sampler
+    model = Model.random(dict(LFM2_1P2B), seed=0, dtype="bfloat16", device="cuda:0").module
+    vocab = LFM2_1P2B["vocab_size"]
+    rng = torch.Generator().manual_seed(0)
+    what = args.kernel_times
+    if what == "decode":
+        total = CONTEXT + 16
+        runner = ModelRunner(model, num_pages=BATCH * (-(-total // 64)), num_slots=BATCH, max_model_len=total,
+                             max_batched_tokens=2048, use_graphs=False, use_plan=False)
+        requests = [f"b{i}" for i in range(BATCH)]
+        fill_context(runner, requests, CONTEXT, vocab, rng)
+        tokens = BATCH
+
+        def step():
+            sampler.argmax(runner.step([(r, [7], [0]) for r in requests]))
+    else:
+        tokens = PREFILL_TOKENS if what == "prefill" else int(what)
+        runner = ModelRunner(model, num_pages=tokens // 64 + 2, num_slots=1, max_model_len=tokens + 64,
+                             max_batched_tokens=tokens, use_graphs=False, use_plan=False)
+        prompt = torch.randint(0, vocab, (tokens,), generator=rng).tolist()
+
+        def step():
+            runner.step([("p", prompt, [tokens - 1])])
+            runner.finish("p")
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    step()
+    stop.record()
+    torch.cuda.synchronize()
+    kernel_lib.profile_start()
+    step()
+    report = kernel_lib.profile_stop()
+    report.update({"kernel_times": what, "tokens": tokens, "step_us_unbracketed": round(1e3 * start.elapsed_time(stop), 1)})
+    print(json.dumps(report))
+    return 0
+
+
 def run_reference(args) -> int:
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     try:
@@ -454,6 +564,11 @@ def main() -> int:
                         help="one long prompt read in portions, e.g. lfm2-2.6b:32768x2048")
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run one step inside cudaProfilerStart/Stop (for a profiler) and exit")
+    parser.add_argument("--mixed", default=None, metavar="MODEL",
+                        help="64 requests, prompts of 128 to 8,192 tokens in portions of 512 beside decoding "
+                             "requests, 256 new tokens each, through the public runtime (e.g. lfm2-350m)")
+    parser.add_argument("--kernel-times", default=None, metavar="decode|prefill|TOKENS",
+                        help="one step with CUDA events around every launch: time per kernel as JSON")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (N=1 only)")
@@ -461,6 +576,10 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.profile:
         return run_profile_step(args)
+    if args.kernel_times:
+        return run_kernel_times(args)
+    if args.mixed:
+        return run_mixed(args)
     if args.sizes:
         return run_sizes(args)
     if args.prefill_lengths:

@@ -138,13 +138,60 @@ def check_tensor(name: str, tensor: torch.Tensor, dtype=None, shape=None) -> Non
         raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(tensor.shape)}")
 
 
-def call(name: str, *args, launches: int = 1) -> None:
-    """Call launcher ``name`` with ctypes arguments and raise on a non-zero status."""
+_profile = None          # None, or the records of the launches since ``profile_start``
+
+
+def profile_start() -> None:
+    """From now on every launch made through ``call`` is bracketed by two CUDA events on the
+    launching stream and its host time is taken (flyweight's FLYWEIGHT_KERNEL_PROFILE,
+    native/src/v2_runtime.cpp:27590-27728).  The events stand between the kernels, so kernels
+    do not overlap their neighbours as they do otherwise: the figures are each kernel alone."""
+    global _profile
+    _profile = []
+
+
+def profile_stop() -> dict:
+    """Stop bracketing and return ``{"kernels": [{kernel, calls, us, share, host_us}], "launches",
+    "device_us", "host_launch_us"}``, kernels by falling device time; waits for the device."""
+    global _profile
+    records, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    by_name = {}
+    for name, tag, first, last, host, launches in records:
+        key = name if tag is None else f"{name}[{tag}]"
+        entry = by_name.setdefault(key, {"kernel": key, "calls": 0, "launches": 0, "us": 0.0, "host_us": 0.0})
+        entry["calls"] += 1
+        entry["launches"] += launches
+        entry["us"] += 1e3 * first.elapsed_time(last)
+        entry["host_us"] += 1e6 * host
+    total = sum(entry["us"] for entry in by_name.values()) or 1.0
+    kernels = sorted(by_name.values(), key=lambda entry: -entry["us"])
+    for entry in kernels:
+        entry["share"] = round(entry["us"] / total, 4)
+        entry["us"] = round(entry["us"], 2)
+        entry["host_us"] = round(entry["host_us"], 2)
+    return {"kernels": kernels, "launches": sum(entry["launches"] for entry in kernels),
+            "device_us": round(total, 2), "host_launch_us": round(sum(entry["host_us"] for entry in kernels), 2)}
+
+
+def call(name: str, *args, launches: int = 1, tag: Optional[str] = None) -> None:
+    """Call launcher ``name`` with ctypes arguments and raise on a non-zero status.  ``tag``
+    tells launches of one launcher apart in a profile (the shape of a product, say)."""
     global _launch_count
     function = _functions.get(name)
     if function is None:
         function = _functions[name] = getattr(library(), name)
-    status = function(*args)
+    if _profile is not None:
+        import time
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first.record()
+        begun = time.perf_counter()
+        status = function(*args)
+        host = time.perf_counter() - begun
+        last.record()
+        _profile.append((name, tag, first, last, host, launches))
+    else:
+        status = function(*args)
     if status != 0:
         if status < 0:
             raise KernelError(f"{name} refused its arguments: {_STATUS.get(status, status)}")

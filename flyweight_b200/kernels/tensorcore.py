@@ -197,7 +197,7 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
         stages = stages or _ring_depth(M, N, splits, 1)
         tile_tokens = tile_tokens or _decode_tile(M, N)
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w), ptr(out), ptr(addend), M, N, K, N, N, epilogue, 0,
-             splits, stages, tile_tokens, wide, stream())
+             splits, stages, tile_tokens, wide, stream(), tag=f"{N}x{K} splits {splits}")
     return out
 
 
@@ -234,12 +234,12 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
         # as many CTAs of half the length, which fit one wave and start as the first launch drains.
         first = cut * 128
         lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, first, K, F2, F,
-                 EPI_SWIGLU_BF16, F, 1, 0, 256, -1, stream())
+                 EPI_SWIGLU_BF16, F, 1, 0, 256, -1, stream(), tag=f"swiglu {F}x{K} first")
         lib.call("fwb_gemm_tcgen05", ptr(x), _offset(w_gate_up, first * K), _offset(out, first), ptr(None), M,
-                 F - first, K, F2 - first, F, EPI_SWIGLU_BF16, F, 1, 0, 128, -1, stream())
+                 F - first, K, F2 - first, F, EPI_SWIGLU_BF16, F, 1, 0, 128, -1, stream(), tag=f"swiglu {F}x{K} rest")
         return out
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, F, K, F2, F,
-             EPI_SWIGLU_BF16, F, splits, stages, tile_tokens, -1, stream())
+             EPI_SWIGLU_BF16, F, splits, stages, tile_tokens, -1, stream(), tag=f"swiglu {F}x{K} splits {splits}")
     return out
 
 
@@ -324,7 +324,7 @@ def gemm_normed(x_res, norm_weight, eps, w, out_dtype, rows=None, n_rows=None, s
     tile_tokens = tile_tokens or _decode_tile(M, N)
     lib.call("fwb_gemm_tcgen05_normed", ptr(x_res), ptr(norm_weight), ptr(rows), lib.c_float(eps), ptr(w),
              ptr(out), M, N, K, N, N, EPI_F32 if out_dtype == torch.float32 else EPI_BF16, 0, splits,
-             stages, tile_tokens, stream())
+             stages, tile_tokens, stream(), tag=f"normed {N}x{K} splits {splits}")
     return out
 
 
@@ -346,7 +346,7 @@ def swiglu_gate_up_normed(x_res, norm_weight, eps, w_gate_up, splits=None, stage
     tile_tokens = tile_tokens or _decode_tile(M, F)
     lib.call("fwb_gemm_tcgen05_normed", ptr(x_res), ptr(norm_weight), ptr(None), lib.c_float(eps),
              ptr(w_gate_up), ptr(out), M, F, K, F2, F, EPI_SWIGLU_BF16, F, splits, stages, tile_tokens,
-             stream())
+             stream(), tag=f"normed swiglu {F}x{K} splits {splits}")
     return out
 
 
@@ -376,7 +376,7 @@ def gemm_pair(x, w, out_dtype, wide=False) -> torch.Tensor:
                  N - first, N, epilogue, 0, 0, stream())
         return out
     lib.call("fwb_gemm_tcgen05_pair", ptr(x), ptr(w), ptr(out), M, N, K, N, N, epilogue, 0,
-             1 if wide else 0, stream())
+             1 if wide else 0, stream(), tag=f"{N}x{K}")
     return out
 
 
