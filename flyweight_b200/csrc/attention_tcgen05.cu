@@ -76,6 +76,7 @@ struct AttnParams {
     const int* tile_tok0;        // [n_tiles]
     const int* block_table;      // [S][max_pages]
     int max_pages, nh, nkv, group, tokens_per_tile, window, n_row_tiles;
+    int items_per_cta;           // 2: CTA c takes items c and n-1-c; 1: one item each (few items)
     float scale_log2;            // softmax scale * log2(e)
     int* status;
 };
@@ -181,7 +182,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     // last row tiles of a prompt walk the most keys.  CTA c takes item c and item n-1-c, the
     // heaviest left and the lightest left, so every CTA walks about the same number of key tiles.
     const int n_items = prm.n_row_tiles * prm.nkv;
-    const int second_item = n_items - 1 - (int)blockIdx.x;
+    // (With fewer items than a wave of such pairs would hold, every CTA takes one item: half
+    // the walk per CTA and twice the CTAs.)
+    const int second_item = prm.items_per_cta == 2 ? n_items - 1 - (int)blockIdx.x : -1;
     const int n_local = second_item > (int)blockIdx.x ? 2 : 1;
     // Barrier phases and ring slots follow a count g of key tiles that runs on over both items.
     // The barriers between the softmax warps and the MMA issuer come in pairs used by alternate
@@ -444,7 +447,8 @@ int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const AttnParams&
         configured = true;
     }
     const int n_items = n_tiles * prm.nkv;
-    fwb::pdl(kernel, dim3((n_items + 1) / 2), THREADS, L::SMEM, stream)(map_k, map_v, prm);
+    fwb::pdl(kernel, dim3(prm.items_per_cta == 2 ? (n_items + 1) / 2 : n_items), THREADS, L::SMEM, stream)(
+        map_k, map_v, prm);
     return fwb_launch_status();
 }
 
@@ -490,6 +494,9 @@ FWB_API int fwb_attention_prefill_tcgen05(const void* q, const void* k_pool, con
     prm.tokens_per_tile = tokens_per_tile;
     prm.window = window;
     prm.n_row_tiles = n_tiles;
+    // one CTA per SM is resident (the tiles fill shared memory): pairs of items even out the causal
+    // triangle when there are waves of them; up to one wave of single items, single items finish sooner
+    prm.items_per_cta = (long)n_tiles * nkv <= 148 ? 1 : 2;
     prm.scale_log2 = scale * LOG2E;
     prm.status = status_word();
     return hd == 64 ? launch<64>(map_k, map_v, prm, n_tiles, stream)

@@ -75,7 +75,6 @@ enum Option {
 };
 int g_option[OPT_COUNT] = {1, 0, 1, 1, 1, 1, 0, 1, 0, 1, 1};
 constexpr int FUSE_FROM_TOKENS = 16;
-constexpr int MID_SIZE_PAIRS = 12, MID_SIZE_K = 4096;
 constexpr int CLUSTER_MERGE_CTAS = 1024;
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -118,13 +117,40 @@ int pick_splits(int M, int N, int K) {
     return splits_for(M, N, K, 1);
 }
 
-int mid_size_splits(int M, int N, int K) {
-    if (g_option[OPT_FORCED_SPLITS] > 0) return 1;
-    const int tiles = ceil_div(N, 128) * ceil_div(M, 128);
-    const int k_blocks = ceil_div(K, 64);
-    int splits = 1;
-    while (splits < 8 && tiles * splits < 120 && k_blocks >= splits * 2 * 16) splits *= 2;
-    return splits;
+// 65 to 512 tokens: the cost model of kernels/tensorcore.py (mid_size_choice), in hundredths of a
+// microsecond.  Returns true for CTA pairs, else sets the token tile and the slices of K.
+constexpr int MID_FROM = 65, MID_TO = 512;
+bool mid_size_choice(int M, int N, int K, int accumulators, bool pair_ok, int& tile_out, int& splits_out) {
+    static const int tiles[3] = {64, 128, 256};
+    static const int block_cost[2][3] = {{38, 38, 42}, {63, 58, 84}};
+    const int k_blocks = ceil_div(K, 64), feature_tiles = ceil_div(N, 128);
+    long best = -1;
+    bool pair = false;
+    for (int ti = 0; ti < 3; ++ti) {
+        const int tile = tiles[ti];
+        if (tile == 256 && M <= 128) continue;
+        for (int splits = 1; splits <= 4; splits *= 2) {
+            if (splits > 1 && (tile > 128 || accumulators == 2 || g_option[OPT_FORCED_SPLITS] > 0 ||
+                               k_blocks < 4 * splits))
+                continue;
+            const int ctas = feature_tiles * ceil_div(M, tile) * splits;
+            const int waves = ceil_div(ctas, SM_COUNT);
+            if (splits > 1 && waves > 1) continue;
+            long cost = 310 + (long)block_cost[accumulators - 1][ti] * ceil_div(k_blocks, splits) * waves;
+            if (splits > 1) cost += tile == 128 ? (splits == 2 ? 750 : 430) : (splits == 2 ? 320 : 270);
+            if (best < 0 || cost < best) {
+                best = cost;
+                tile_out = tile;
+                splits_out = splits;
+            }
+        }
+    }
+    if (pair_ok) {
+        const int pairs = ceil_div(N, 256) * ceil_div(M, 256);
+        const long cost = 310 + 36L * k_blocks * ceil_div(pairs, SM_COUNT / 2);
+        if (cost < best) pair = true;
+    }
+    return pair;
 }
 
 int wave_cut(int M, int F) {
@@ -182,12 +208,17 @@ const char* offset(const void* base, long long elements, int bytes) {
 void tc_gemm(Launches& L, const void* x, const void* w, void* out, int out_bf16, const float* addend, int M,
              int N, int K, cudaStream_t stream) {
     const bool in_place = addend && (const void*)addend == out;
-    const bool mid_size = g_option[OPT_MID_SIZE_SPLIT] && M > 64 && K >= MID_SIZE_K &&
-                          ceil_div(N, 256) * ceil_div(M, 256) < MID_SIZE_PAIRS;
     const int epilogue = addend ? EPI_ADD_F32 : (out_bf16 ? EPI_BF16 : EPI_F32);
-    if (g_option[OPT_PAIRS] && M > 128 && !addend && !in_place && N >= 256 && !mid_size) {
-        const int pairs = ceil_div(N, 256) * ceil_div(M, 256);
-        const bool wide = pairs > SM_COUNT / 2;
+    const bool pair_ok = g_option[OPT_PAIRS] && M > 128 && !addend && !in_place && N >= 256;
+    int splits = 0, stages = 0, tile_tokens = 0;
+    bool pair = false, wide = false;
+    if (g_option[OPT_MID_SIZE_SPLIT] && M >= MID_FROM && M <= MID_TO) {
+        pair = mid_size_choice(M, N, K, 1, pair_ok, tile_tokens, splits);
+    } else if (pair_ok) {
+        pair = true;
+        wide = ceil_div(N, 256) * ceil_div(M, 256) > SM_COUNT / 2;
+    }
+    if (pair) {
         const int cut = wide ? pair_wave_cut(M, N) : 0;
         const int out_bytes = out_bf16 ? 2 : 4;
         if (cut) {
@@ -199,11 +230,6 @@ void tc_gemm(Launches& L, const void* x, const void* w, void* out, int out_bf16,
         }
         L.add(fwb_gemm_tcgen05_pair(x, w, out, M, N, K, N, N, epilogue, 0, wide ? 1 : 0, stream));
         return;
-    }
-    int splits = 0, stages = 0, tile_tokens = 0;
-    if (mid_size) {
-        tile_tokens = 128;
-        splits = mid_size_splits(M, N, K);
     }
     if (!splits) splits = pick_splits(M, N, K);
     if (M <= 64) {
@@ -221,7 +247,9 @@ void tc_swiglu(Launches& L, const void* x, const void* w, void* out, int M, int 
         stages = ring_depth(M, F, splits, 2);
         tile_tokens = decode_tile(M, F);
     }
-    const int cut = (M > 128 && splits == 1 && !stages && !tile_tokens) ? wave_cut(M, F) : 0;
+    const bool mid = g_option[OPT_MID_SIZE_SPLIT] && M >= MID_FROM && M <= MID_TO;
+    if (mid) mid_size_choice(M, F, K, 2, false, tile_tokens, splits);
+    const int cut = (M > 128 && splits == 1 && !stages && !tile_tokens && !mid) ? wave_cut(M, F) : 0;
     if (cut) {
         const int first = cut * 128;
         L.add(fwb_gemm_tcgen05(x, w, out, nullptr, M, first, K, 2 * F, F, EPI_SWIGLU_BF16, F, 1, 0, 256, -1, stream));

@@ -116,30 +116,60 @@ def _splits_for(M: int, N: int, K: int, accumulators: int) -> int:
     return splits
 
 
-MID_SIZE_PAIRS = 12        # fewer 256 x 256 tiles than this, and
-MID_SIZE_K = 4096          # at least this long a K: the split form wins
+# ---- 65 to 512 tokens: which tile, how many slices of K, or CTA pairs ----------------------
+# Between decode-sized steps (a weight streamer on every SM) and prompt-sized ones (256-token
+# tiles that fill the GPU) a product has few output tiles, and a CTA's walk over K is bound by
+# latency, not by bandwidth: about 0.38 us per 64-wide block whatever the tile (0.6 us with two
+# accumulators, 0.84 us for two accumulators of 256 tokens), 3 us of fixed cost, and a cluster
+# reduction that costs 2.7 to 7.5 us depending on the tile and the number of slices.  The choice
+# below evaluates that cost model (hundredths of a microsecond, fitted to products of LFM2-1.2B
+# and LFM2-350M at 65 to 1,024 tokens on B200) for every tile and split the kernels have and takes
+# the cheapest; a split is only considered when all its CTAs run at once (clusters in a second
+# wave were measured far slower than the model).  The native dispatch (csrc/plan.cu) has the same
+# table and the same loop.
+MID_FROM, MID_TO = 65, 512
+_MID_FIXED = 310
+_MID_BLOCK = {1: {64: 38, 128: 38, 256: 42}, 2: {64: 63, 128: 58, 256: 84}}
+_MID_PAIR_BLOCK = 36
+_MID_REDUCE = {(128, 2): 750, (128, 4): 430, (64, 2): 320, (64, 4): 270}
 _mid_size_split = True
 
 
 def set_mid_size_split(flag: bool) -> None:
-    """Products of 65 to about a thousand tokens with few output tiles on single CTAs with a
-    split K (on by default); off: CTA pairs or one CTA per tile, as before."""
+    """The cost-model choice for products of 65 to 512 tokens (on by default); off: CTA pairs
+    above 128 tokens and one CTA per 128-token tile below, without a split."""
     global _mid_size_split
     _mid_size_split = bool(flag)
     lib.set_option("mid_size_split", _mid_size_split)
 
 
-def _mid_size_splits(M: int, N: int, K: int) -> int:
-    """Slices of K (a cluster, a power of two <= 8) for 128-token tiles: until the product has
-    about one CTA per SM, as long as a slice keeps sixteen 64-wide blocks."""
-    if _forced_splits is not None:
-        return 1
-    tiles = -(-N // 128) * -(-M // 128)
+def mid_size_choice(M: int, N: int, K: int, accumulators: int, pair_ok: bool):
+    """For ``MID_FROM <= M <= MID_TO``: ("pair", 0, 1) or ("single", token tile, slices of K)."""
     k_blocks = -(-K // 64)
-    splits = 1
-    while splits < 8 and tiles * splits < 120 and k_blocks >= splits * 2 * 16:
-        splits *= 2
-    return splits
+    feature_tiles = -(-N // 128)
+    best = None
+    for tile in (64, 128, 256):
+        if tile == 256 and M <= 128:
+            continue
+        for splits in (1, 2, 4):
+            if splits > 1 and (tile > 128 or accumulators == 2 or _forced_splits is not None
+                               or k_blocks < 4 * splits):
+                continue
+            ctas = feature_tiles * -(-M // tile) * splits
+            waves = -(-ctas // SM_COUNT)
+            if splits > 1 and waves > 1:
+                continue
+            cost = _MID_FIXED + _MID_BLOCK[accumulators][tile] * -(-k_blocks // splits) * waves
+            if splits > 1:
+                cost += _MID_REDUCE[(tile, splits)]
+            if best is None or cost < best[0]:
+                best = (cost, "single", tile, splits)
+    if pair_ok:
+        pairs = -(-N // 256) * -(-M // 256)
+        cost = _MID_FIXED + _MID_PAIR_BLOCK * k_blocks * -(-pairs // (SM_COUNT // 2))
+        if cost < best[0]:
+            best = (cost, "pair", 0, 1)
+    return best[1:]
 
 
 def adds_in_place(x, w, residual) -> bool:
@@ -162,20 +192,16 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
     if w.shape[1] != K:
         raise KernelError(f"gemm: input has {K} columns, weight has {w.shape[1]}")
     free_choice = splits is None and not stages and not tile_tokens and wide == -1
-    # 65 to a few hundred tokens against a narrow matrix with a long K (w2 at 256 tokens: 8 CTA
-    # pairs, each walking all 8,192 columns): 128-token tiles on single CTAs with K cut across a
-    # cluster put work on every SM.  Measured on B200 for 2,048 features x 8,192: 128 tokens
-    # 52 -> 28 us, 256 tokens 44 -> 24 us; from 512 tokens on, and for K of 2,048, the pairs win.
-    mid_size = (free_choice and _mid_size_split and 64 < M and K >= MID_SIZE_K
-                and -(-N // 256) * -(-M // 256) < MID_SIZE_PAIRS)
-    if _use_pairs and M > 128 and addend is None and out is None and free_choice and N >= 256 and not mid_size:
+    pair_ok = _use_pairs and M > 128 and addend is None and out is None and N >= 256
+    if free_choice and _mid_size_split and MID_FROM <= M <= MID_TO:
+        kind, tile_tokens, splits = mid_size_choice(M, N, K, 1, pair_ok)
+        if kind == "pair":
+            return gemm_pair(x, w, out_dtype, wide=False)
+    elif pair_ok and free_choice:
         # prompt-sized: CTA pairs (cta_group::2); two feature blocks per pair when single blocks
         # would make more CTAs than the GPU holds at once (measured at 2,048 tokens on B200)
         pairs = -(-N // 256) * -(-M // 256)
         return gemm_pair(x, w, out_dtype, wide=pairs > SM_COUNT // 2)
-    if mid_size:
-        tile_tokens = 128
-        splits = _mid_size_splits(M, N, K)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     else:
@@ -222,12 +248,16 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
         stages = stages or tuned[1]
         if len(tuned) > 2:
             tile_tokens = tile_tokens or tuned[2]
+    free_choice = splits is None and not stages and not tile_tokens
     if splits is None:
         splits = (_forced_splits if _forced_splits is not None else _splits_for(M, F, K, 2)) if M <= 64 else 1
     if M <= 64:
         stages = stages or _ring_depth(M, F, splits, 2)
         tile_tokens = tile_tokens or _decode_tile(M, F)
-    cut = _wave_cut(M, F) if (M > 128 and splits == 1 and not stages and not tile_tokens) else 0
+    mid = free_choice and _mid_size_split and MID_FROM <= M <= MID_TO
+    if mid:
+        _, tile_tokens, splits = mid_size_choice(M, F, K, 2, False)
+    cut = _wave_cut(M, F) if (M > 128 and splits == 1 and not stages and not tile_tokens and not mid) else 0
     if cut:
         # Prompt-sized: 256-token tiles make a number of CTAs that ends in a part-filled wave.  The
         # feature tiles of the whole waves run as they are; the rest runs with 128-token tiles, twice

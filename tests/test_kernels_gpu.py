@@ -896,8 +896,9 @@ def test_tcgen05_cta_pair_swiglu(M, F, K):
                                    (700, 260, 4104), (200, 1000, 5000)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_tcgen05_mid_size_products_split_k_over_128_token_tiles(M, N, K, out_dtype):
-    """A few hundred tokens against a narrow matrix: 128-token tiles on single CTAs with K cut
-    across a cluster instead of a handful of CTA pairs; the same numbers as with it switched off."""
+    """A few hundred tokens against a narrow matrix: 64- or 128-token tiles on single CTAs with K
+    cut across a cluster instead of a handful of CTA pairs, whichever the cost model of that range
+    puts first; the same numbers as with it switched off."""
     from flyweight_b200.kernels import tensorcore as tc
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
@@ -905,7 +906,10 @@ def test_tcgen05_mid_size_products_split_k_over_128_token_tiles(M, N, K, out_dty
     want = x.double() @ w.double().T
     # fp32 out: the tensor core's accumulator loses a little with every block of K it adds
     tol = 1e-5 * max(1.0, K / 2048) if out_dtype == torch.float32 else 2.0 ** -8
-    assert tc._mid_size_splits(256, 2048, 8192) == 4 and tc._mid_size_splits(128, 2048, 8192) == 8
+    assert tc.mid_size_choice(256, 2048, 8192, 1, True) == ("single", 128, 4)      # w2 of LFM2-1.2B
+    assert tc.mid_size_choice(128, 2048, 2048, 1, False) == ("single", 64, 4)     # out_proj
+    assert tc.mid_size_choice(512, 6144, 2048, 1, True)[0] == "pair"              # in_proj
+    assert tc.mid_size_choice(256, 8192, 2048, 2, False) == ("single", 128, 1)    # gate|up
     got = tc.gemm(dev(x), dev(w), out_dtype)
     close(got, want, tol, "mid-size split")
     tc.set_mid_size_split(False)

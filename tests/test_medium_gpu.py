@@ -79,7 +79,7 @@ def test_a_hundred_tokens_against_a_wide_feed_forward(tmp_path):
     from flyweight_b200.kernels import tensorcore
     config = dict(MEDIUM, num_hidden_layers=2, layer_types=["conv", "full_attention"],
                   intermediate_size=4352)
-    assert tensorcore._mid_size_splits(100, 1024, 4352) > 1
+    assert tensorcore.mid_size_choice(100, 1024, 4352, 1, False)[2] > 1
     folder = make_model_dir(tmp_path / "wide", config, seed=6, dtype=torch.bfloat16)
     made = {dtype: ModelRunner(load_model(folder, dtype), num_pages=12, num_slots=2, max_model_len=512,
                                max_batched_tokens=512) for dtype in ("float32", "bfloat16")}
