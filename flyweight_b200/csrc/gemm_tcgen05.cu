@@ -323,7 +323,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // its index selects); with one slice of K they split the token columns between them, which
     // keeps several warps per scheduler busy during the stores instead of one
     const int column_group = (warp - 2) >> 2;
-    const int column_half = column_group;          // 0 for the warps that do the split-K reduction
     const int quarter = warp & 3;                  // the TMEM lanes this warp may read
     const int row = quarter * 32 + lane;           // feature inside the tile
     bool acc_ready = true;
@@ -384,12 +383,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
         }
     } else {
-        // park the partial tile in shared memory: partial[col][row], fp32 (the pipeline's
-        // stages are free: every MMA that read them has completed)
+        // park the partial tile in shared memory: partial[col][row], fp32 (the pipeline's stages
+        // are free: every MMA that read them has completed).  With sixteen epilogue warps each
+        // quarter of the rows is shared by four warps, a quarter of the columns each.
+        constexpr int GROUPS = epi_warps(BN) / 4;
         float* partial = reinterpret_cast<float*>(tiles);
-        if (epi_warp && column_half == 0) {
+        if (epi_warp) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < T::COLS; c0 += 16) {
+            for (int c0 = column_group * 16; c0 < T::COLS; c0 += 16 * GROUPS) {
                 float v[16];
                 if (n_kb > 0 && acc_ready) tmem_ld16(lane_addr + c0, v);
                 else {
@@ -402,63 +403,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         tc_fence_before();
         cluster_sync_all();
-        if (epi_warp && column_half == 0) {
+        if (epi_warp) {
+            // Column c of the tile is merged by rank c % splits, and among that rank's warps by
+            // column group (c / splits) % GROUPS.  A thread (one feature row) asks every peer for its
+            // values of BATCH columns before it uses the first -- one round trip through distributed
+            // shared memory for all of them -- and adds them in rank order, as every cut of the work does.
             const uint32_t rank = cluster_rank();
             const uint32_t base = smem_u32(partial);
-            if constexpr (BN >= 64 && NACC == 1 && !NORMED) {
-                // wide token tiles: a CTA merges BN / splits columns.  Four columns' worth of peer
-                // values are requested before the first is used, so the merge costs a quarter of
-                // the round trips through distributed shared memory (same sums, same order).
-                constexpr int BATCH = 4;
-                for (int col0 = (int)rank; col0 < BN; col0 += splits * BATCH) {
-                    float add[BATCH], pg[BATCH][8];
+            constexpr int BATCH = BN >= 64 ? 4 : 2;
+            const int col_step = splits * GROUPS;
+#pragma unroll 1
+            for (int col0 = (int)rank + column_group * splits; col0 < BN; col0 += col_step * BATCH) {
+                float pg[BATCH][8], pu[BATCH][8], ps[BATCH][8], add[BATCH];
 #pragma unroll
-                    for (int b = 0; b < BATCH; ++b) {
-                        const int col = col0 + b * splits;
-                        add[b] = 0.0f;
-                        if (EPI == EPI_ADD_F32 && col < BN && tok0 + col < prm.M && f < prm.N)
-                            add[b] = prm.addend[(size_t)(tok0 + col) * prm.ldy + f];
+                for (int b = 0; b < BATCH; ++b) {
+                    const int col = col0 + b * col_step;
+                    const bool live = col < BN;
+                    add[b] = 0.0f;
+                    if (EPI == EPI_ADD_F32 && live && tok0 + col < prm.M && f < prm.N)
+                        add[b] = prm.addend[(size_t)(tok0 + col) * prm.ldy + f];
 #pragma unroll
-                        for (int r = 0; r < 8; ++r)
-                            pg[b][r] = (r < splits && col < BN)
-                                           ? ld_dsmem_f32(base + (uint32_t)((col * BM + row) * 4), (uint32_t)r) : 0.0f;
-                    }
-#pragma unroll
-                    for (int b = 0; b < BATCH; ++b) {
-                        const int col = col0 + b * splits;
-                        if (col >= BN) break;
-                        float g = 0.0f;
-#pragma unroll
-                        for (int r = 0; r < 8; ++r) g += pg[b][r];
-                        if (!*abort_flag) finish(col, g, EPI == EPI_ADD_F32 ? add[b] : 0.0f, 1.0f);
+                    for (int r = 0; r < 8; ++r) {
+                        const bool on = live && r < splits;
+                        pg[b][r] = on ? ld_dsmem_f32(base + (uint32_t)((col * BM + row) * 4), (uint32_t)r) : 0.0f;
+                        pu[b][r] = (on && NACC == 2)
+                                       ? ld_dsmem_f32(base + (uint32_t)(((BN + col) * BM + row) * 4), (uint32_t)r) : 0.0f;
+                        ps[b][r] = (on && NORMED) ? ld_dsmem_f32(smem_u32(sum_sq) + (uint32_t)(col * 4), (uint32_t)r) : 0.0f;
                     }
                 }
-            } else
-            for (int col = (int)rank; col < BN; col += splits) {
-                // the addend's load is in flight while the partial tiles are fetched
-                float add = 0.0f;
-                if (EPI == EPI_ADD_F32 && tok0 + col < prm.M && f < prm.N)
-                    add = prm.addend[(size_t)(tok0 + col) * prm.ldy + f];
-                // all peers' values are requested before the first is used (one round trip through
-                // distributed shared memory, not one per peer), then summed in rank order
-                float pg[8], pu[8], ps[8];
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    const bool on = r < splits;
-                    pg[r] = on ? ld_dsmem_f32(base + (uint32_t)((col * BM + row) * 4), (uint32_t)r) : 0.0f;
-                    pu[r] = (on && NACC == 2) ? ld_dsmem_f32(base + (uint32_t)(((BN + col) * BM + row) * 4), (uint32_t)r) : 0.0f;
-                    ps[r] = (on && NORMED) ? ld_dsmem_f32(smem_u32(sum_sq) + (uint32_t)(col * 4), (uint32_t)r) : 0.0f;
-                }
-                float g = 0.0f, u = 0.0f, sq = 0.0f;
+                for (int b = 0; b < BATCH; ++b) {
+                    const int col = col0 + b * col_step;
+                    if (col >= BN) break;
+                    float g = 0.0f, u = 0.0f, sq = 0.0f;
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    g += pg[r];                      // + 0 beyond the last rank: exact
-                    u += pu[r];
-                    sq += ps[r];
+                    for (int r = 0; r < 8; ++r) {            // + 0 beyond the last rank: exact
+                        g += pg[b][r];
+                        u += pu[b][r];
+                        sq += ps[b][r];
+                    }
+                    if (EPI == EPI_ADD_F32) u = add[b];
+                    if (!*abort_flag)
+                        finish(col, g, u, NORMED ? rsqrtf(sq / (float)prm.K + prm.norm_eps) : 1.0f);
                 }
-                if (EPI == EPI_ADD_F32) u = add;
-                if (!*abort_flag)
-                    finish(col, g, u, NORMED ? rsqrtf(sq / (float)prm.K + prm.norm_eps) : 1.0f);
             }
         }
         cluster_sync_all();                        // nobody leaves while a peer still reads it

@@ -137,7 +137,7 @@ bool mid_size_choice(int M, int N, int K, int accumulators, bool pair_ok, int& t
             const int waves = ceil_div(ctas, SM_COUNT);
             if (splits > 1 && waves > 1) continue;
             long cost = 310 + (long)block_cost[accumulators - 1][ti] * ceil_div(k_blocks, splits) * waves;
-            if (splits > 1) cost += tile == 128 ? (splits == 2 ? 750 : 430) : (splits == 2 ? 320 : 270);
+            if (splits > 1) cost += tile == 128 ? (splits == 2 ? 360 : 260) : (splits == 2 ? 390 : 310);
             if (best < 0 || cost < best) {
                 best = cost;
                 tile_out = tile;

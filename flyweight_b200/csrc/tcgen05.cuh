@@ -199,6 +199,16 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank
     return v;
 }
 
+// Four consecutive floats of a peer CTA's shared memory (16-byte aligned) in one request.
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
 // silu for the bfloat16 epilogue: g / (1 + e^-g) with the hardware exponential and reciprocal.
 // The result is rounded to bfloat16 (8 bits) right away; their few-ulp fp32 error is far below
 // that.  For g << 0, e^-g overflows to +inf and the quotient is -0, the right limit.

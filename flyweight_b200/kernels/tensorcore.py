@@ -121,7 +121,7 @@ def _splits_for(M: int, N: int, K: int, accumulators: int) -> int:
 # tiles that fill the GPU) a product has few output tiles, and a CTA's walk over K is bound by
 # latency, not by bandwidth: about 0.38 us per 64-wide block whatever the tile (0.6 us with two
 # accumulators, 0.84 us for two accumulators of 256 tokens), 3 us of fixed cost, and a cluster
-# reduction that costs 2.7 to 7.5 us depending on the tile and the number of slices.  The choice
+# reduction that costs 2.6 to 3.9 us depending on the tile and the number of slices.  The choice
 # below evaluates that cost model (hundredths of a microsecond, fitted to products of LFM2-1.2B
 # and LFM2-350M at 65 to 1,024 tokens on B200) for every tile and split the kernels have and takes
 # the cheapest; a split is only considered when all its CTAs run at once (clusters in a second
@@ -131,7 +131,7 @@ MID_FROM, MID_TO = 65, 512
 _MID_FIXED = 310
 _MID_BLOCK = {1: {64: 38, 128: 38, 256: 42}, 2: {64: 63, 128: 58, 256: 84}}
 _MID_PAIR_BLOCK = 36
-_MID_REDUCE = {(128, 2): 750, (128, 4): 430, (64, 2): 320, (64, 4): 270}
+_MID_REDUCE = {(128, 2): 360, (128, 4): 260, (64, 2): 390, (64, 4): 310}
 _mid_size_split = True
 
 
