@@ -202,10 +202,18 @@ def run(args, config: dict, batch: int, context: int, backend: str = "cuda") -> 
             "vs_baseline": None, "dtype": "bf16 weights, f32 activations, f16 KV (reference defaults)",
             "data": "synthetic: uniform-random token ids, seeded random weights N(0, 0.02)",
             "config": {"model": "LFM2-1.2B", "layers": config["num_hidden_layers"],
-                       "hidden": config["hidden_size"], "ffn_dim": info["ffn_dim"], "vocab": vocab,
+                       "layers_full": config["num_hidden_layers"],
+                       "attention_layers": len(config["full_attn_idxs"]),
+                       "hidden": config["hidden_size"], "heads": config["num_attention_heads"],
+                       "kv_heads": config["num_key_value_heads"],
+                       "head_dim": config["hidden_size"] // config["num_attention_heads"],
+                       "ffn_dim": info["ffn_dim"], "conv_L_cache": config["conv_L_cache"], "vocab": vocab,
                        "global_batch": batch, "seq_len": context, "backend": selected,
                        "gguf_bytes": info["bytes"], "parallelism": "single GPU"},
-            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": None,
+            # per step the reference's runtime hands each sequence's last token id (4 bytes) to its
+            # decode kernels and reads the new id and its event back (8 bytes); the prompt ids went
+            # in with task_submit, before the timed region
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
                     "d2h_bytes_per_step": 8 * batch},
             "tokens_timed": tokens,
         }

@@ -144,7 +144,7 @@ def fill_context(runner, requests, context, vocab, rng, chunk=2048):
     return prompts
 
 
-def time_decode(model, batch, context, steps, warmup, vocab, seed=0):
+def time_decode(model, batch, context, steps, warmup, vocab, seed=0, per_step=False):
     """K decode steps of ``batch`` requests at ``context`` cached tokens each, timed with CUDA
     events on the launching stream: model step + greedy sampling, tokens given by the host."""
     import torch
@@ -163,11 +163,16 @@ def time_decode(model, batch, context, steps, warmup, vocab, seed=0):
         sampler.argmax(runner.step([(r, [tokens[i][j]], [0]) for j, r in enumerate(requests)]))
     torch.cuda.synchronize()
     launches = launch_count()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)] if per_step else None
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for i in range(warmup, warmup + steps):
+        if per_step:
+            marks[i - warmup].record()
         sampler.argmax(runner.step([(r, [tokens[i][j]], [0]) for j, r in enumerate(requests)]))
     stop.record()
+    if per_step:
+        marks[steps].record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop)
     launches = launch_count() - launches
@@ -175,8 +180,34 @@ def time_decode(model, batch, context, steps, warmup, vocab, seed=0):
         runner.finish(r)
     del runner
     torch.cuda.empty_cache()
-    return {"ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3),
-            "launches": launches}
+    out = {"ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3), "launches": launches}
+    if per_step:
+        out["step_ms"] = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+    return out
+
+
+def _percentile(values, q):
+    ordered = sorted(values)
+    return ordered[min(len(ordered) - 1, int(round(q * (len(ordered) - 1))))]
+
+
+def decode_spread(model, batch, context, vocab, regions=5, steps=200, warmup=5):
+    """``regions`` timed regions of ``steps`` decode steps each (a fresh runner and a fresh context
+    per region), every step between its own pair of events: median, p90 and p99 of the per-step
+    time, the regions' means, and the SM clock sampled meanwhile."""
+    clock = ClockSampler(0)
+    clock.start()
+    per_step, means = [], []
+    for region in range(regions):
+        timed = time_decode(model, batch, context, steps, warmup, vocab, seed=10 + region, per_step=True)
+        per_step += timed["step_ms"]
+        means.append(round(timed["ms_per_step"], 4))
+    clocks = clock.stop()
+    median = statistics.median(per_step)
+    return {"regions": regions, "steps_per_region": steps, "ms_median": round(median, 4),
+            "ms_p90": round(_percentile(per_step, 0.90), 4), "ms_p99": round(_percentile(per_step, 0.99), 4),
+            "region_means_ms": means, "tokens_per_s_median": round(batch / (median / 1e3), 1),
+            "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}
 
 
 def time_e2e(model, batch, context, steps, warmup, vocab, seed=1):
@@ -260,12 +291,13 @@ def run_ours(args) -> int:
     e2e = time_e2e(model, BATCH, CONTEXT, args.steps, args.warmup, vocab)
     points = {}
     for batch in (1, 64):
-        steps = max(8, args.steps // (4 if batch == 64 else 1))
-        points[f"decode_b{batch}"] = time_decode(model, batch, CONTEXT, steps, args.warmup,
+        points[f"decode_b{batch}"] = time_decode(model, batch, CONTEXT, args.steps, args.warmup,
                                                  vocab)["tokens_per_s"]
+    spread = {f"decode_b{batch}": decode_spread(model, batch, CONTEXT, vocab) for batch in (1, 8, 64)}
     prefill_ms = time_prefill(model, PREFILL_TOKENS, vocab)
     flops = (model_flops_per_token(model) * PREFILL_TOKENS + attention_flops(model, PREFILL_TOKENS)
              + 2.0 * model.head.numel())
+    prefill_tflops = flops / (prefill_ms / 1e3) / 1e12
     step_bytes = model.weight_bytes(with_embedding_rows=BATCH) + BATCH * CONTEXT * kv_bytes_per_token(model)
     achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
     line = {
@@ -289,13 +321,19 @@ def run_ours(args) -> int:
         "e2e": e2e,
         "gpu_launches": main["launches"],
         "clocks": clocks,
+        # the prefill step is a few milliseconds between two synchronisations: a burst, so `frac`
+        # is against the burst peak; the fraction of the sustained (power-capped) peak is beside it
         "prefill": {"value": PREFILL_TOKENS / (prefill_ms / 1e3), "tokens": PREFILL_TOKENS,
-                    "ms": prefill_ms, "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
-                    "flops": flops, "peak_tflops": peaks["bf16_tflops"]},
+                    "ms": prefill_ms, "frac": prefill_tflops / peaks.get("bf16_tflops_burst", peaks["bf16_tflops"]),
+                    "frac_of_burst_peak": prefill_tflops / peaks.get("bf16_tflops_burst", peaks["bf16_tflops"]),
+                    "frac_of_sustained_peak": prefill_tflops / peaks["bf16_tflops"],
+                    "flops": flops, "burst_peak_tflops": peaks.get("bf16_tflops_burst", peaks["bf16_tflops"]),
+                    "sustained_peak_tflops": peaks["bf16_tflops"]},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "bytes_per_step": step_bytes,
                      "of": peaks["source"]},
         "points": points,
+        "spread": spread,
     }
     print(json.dumps(line))
     return 0
@@ -551,7 +589,7 @@ def run_reference(args) -> int:
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--layers", type=int, default=0,

@@ -12,10 +12,10 @@ from .sampling.config import GREEDY, SamplingConfig  # noqa: E402
 
 def __getattr__(name):
     # the engine pulls in torch and the CUDA library; load it on first use
-    if name in ("Model", "Runtime", "GenerationResult"):
+    if name in ("Model", "Runtime", "GenerationResult", "EngineConfig"):
         from .engine import runtime as _runtime
         return getattr(_runtime, name)
     raise AttributeError(name)
 
 
-__all__ = ["GREEDY", "SamplingConfig", "Model", "Runtime", "GenerationResult", "__version__"]
+__all__ = ["GREEDY", "SamplingConfig", "Model", "Runtime", "GenerationResult", "EngineConfig", "__version__"]

@@ -44,6 +44,9 @@ class Lfm2Config:
     architectures: Tuple[str, ...] = ("Lfm2ForCausalLM",)
     model_type: str = "lfm2"
     extra: Mapping[str, Any] = field(default_factory=dict, compare=False)
+    # the feed-forward width read off the checkpoint's gate matrix when it differs from the rule
+    # below (flyweight never applies a rule: native/src/v2_runtime.cpp:3527-3535)
+    ffn_dim_from_checkpoint: Optional[int] = None
 
     # ------------------------------------------------------------------ derived sizes
     @property
@@ -57,6 +60,8 @@ class Lfm2Config:
         ``intermediate_size`` and the three ``block_*`` keys: with auto-adjust the
         width is 2/3 of it, times the optional multiplier, rounded up to a multiple
         of ``block_multiple_of``."""
+        if self.ffn_dim_from_checkpoint is not None:
+            return self.ffn_dim_from_checkpoint
         width = self.intermediate_size
         if self.block_auto_adjust_ff_dim:
             width = int(2 * width / 3)
@@ -132,9 +137,27 @@ class Lfm2Config:
         config.validate()
         return config
 
+    def reconciled_with(self, stored_shapes: Mapping[str, Tuple[int, ...]]) -> "Lfm2Config":
+        """This configuration, with the feed-forward width taken from the checkpoint where the two
+        disagree.  The width rule (2/3, multiplier, rounding) is restated from the config keys; a
+        checkpoint whose gate matrix has another number of rows (a config written with other
+        rounding habits) is believed over the rule, as flyweight believes the tensor
+        (native/src/v2_runtime.cpp:3527-3535).  Every layer must agree on the width."""
+        widths = {shape[0] for name, shape in stored_shapes.items()
+                  if name.startswith("model.layers.") and name.endswith(".feed_forward.w1.weight")
+                  and len(shape) == 2 and shape[1] == self.hidden_size}
+        if len(widths) != 1:
+            return self
+        (width,) = widths
+        if width == self.ffn_dim:
+            return self
+        from dataclasses import replace
+        return replace(self, ffn_dim_from_checkpoint=int(width))
+
     def to_dict(self) -> dict:
         out = asdict(self)
         out.pop("extra")
+        out.pop("ffn_dim_from_checkpoint")
         out["layer_types"] = list(self.layer_types)
         out["full_attn_idxs"] = list(self.attention_layers)
         out["architectures"] = list(self.architectures)

@@ -9,6 +9,7 @@ from .. import models as _models  # noqa: F401  (registers the architectures)
 from ..config.registry import architecture_name, load_config, lookup
 from ..parts.base import Precision
 from ..weights.loader import load_checkpoint
+from ..weights.safetensors_io import stored_shapes
 from ..weights.random_init import random_tensors
 
 
@@ -28,6 +29,10 @@ def parse_dtype(dtype) -> Precision:
 def load_model(model_dir, dtype="bfloat16", device="cuda:0"):
     """The model that ``config.json`` names, with ``model.safetensors`` bound by name."""
     arch, config = load_config(model_dir)
+    reconcile = getattr(config, "reconciled_with", None)
+    if reconcile is not None:
+        # sizes the config only states through a rule may be read off the stored tensors instead
+        config = reconcile(stored_shapes(model_dir))
     model = arch.model_class(config, parse_dtype(dtype), torch.device(device))
     model.load(load_checkpoint(model_dir, model.declare()))
     return model

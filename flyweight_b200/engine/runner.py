@@ -171,6 +171,7 @@ class ModelRunner(StepPlanner):
         # decode steps replay a CUDA graph per (batch size, block-table width)
         self.use_graphs = bool(use_graphs) and model.graph_safe
         self.max_graph_batch = 256
+        self.max_graphs = 32                # graphs kept; the one unused for longest goes first
         self._graphs = {}
         self.last_decode_graph = None      # the graph the last step replayed (None: it ran eagerly)
         self.graph_replays = 0
@@ -189,8 +190,17 @@ class ModelRunner(StepPlanner):
                 and all(len(seg.tokens) == 1 and seg.want == [0] for seg in segments)):
             bucket = 16 * (-(-width // 16))         # a new graph every 1,024 tokens of context
             key = (len(segments), bucket)
-            graph = self._graphs.get(key)
+            graph = self._graphs.pop(key, None)
+            if graph is not None:
+                self._graphs[key] = graph              # most recently used: last in the dict
             if graph is None:
+                # every graph keeps activations and a [batch][vocab] logits buffer of its own: a
+                # runtime whose batch sizes and contexts wander would otherwise grow without bound
+                while len(self._graphs) >= self.max_graphs:
+                    oldest = next(iter(self._graphs))
+                    if self._graphs[oldest] is self.last_decode_graph:
+                        self.last_decode_graph = None
+                    del self._graphs[oldest]
                 graph = self._graphs[key] = DecodeGraph(
                     self.model, self.cache.layer_caches, self.precision, self.device,
                     self.bad_token_flag, len(segments), n_groups, bucket)

@@ -37,6 +37,37 @@ class GenerationResult:
     preemptions: int = 0
 
 
+@dataclass(frozen=True)
+class EngineConfig:
+    """The limits and switches of one runtime, in one place (no environment variables on the
+    forward path).  ``context_limit``: most tokens (prompt + output) of one request;
+    ``parallel_sequences``: most requests live at a time (flyweight's ``--parallel``);
+    ``cache_tokens``: size of the KV pool in tokens (None: every live request at the context limit,
+    plus the spare page the scheduler keeps per admission); ``max_batched_tokens``: token budget of
+    one step; ``use_graphs``: CUDA graphs for steps of single tokens; ``use_plan``: the native step
+    plan for the others; ``steady_decode`` / ``run_ahead``: the short ways of ``engine_step``."""
+    context_limit: int = 4096
+    parallel_sequences: int = 1
+    cache_tokens: Optional[int] = None
+    max_batched_tokens: int = 2048
+    use_graphs: bool = True
+    use_plan: bool = True
+    steady_decode: bool = True
+    run_ahead: bool = True
+
+    def __post_init__(self):
+        if self.context_limit <= 0 or self.parallel_sequences <= 0 or self.max_batched_tokens <= 0:
+            raise ValueError("context_limit, parallel_sequences and max_batched_tokens must be positive")
+        if self.cache_tokens is not None and self.cache_tokens < PAGE_SIZE:
+            raise ValueError(f"cache_tokens must hold at least one page of {PAGE_SIZE} tokens")
+
+    @property
+    def pool_tokens(self) -> int:
+        if self.cache_tokens is not None:
+            return int(self.cache_tokens)
+        return self.parallel_sequences * (-(-self.context_limit // PAGE_SIZE) + 1) * PAGE_SIZE
+
+
 class Model:
     """A model folder (``config.json`` + ``model.safetensors``) opened on one GPU, or a
     configuration with seeded random weights (``Model.random``)."""
@@ -56,32 +87,34 @@ class Model:
 
     def native_runtime(self, context_limit: int = 4096, parallel_sequences: int = 1,
                        cache_tokens: Optional[int] = None, max_batched_tokens: int = 2048,
-                       ) -> "Runtime":
-        """``context_limit``: most tokens (prompt + output) of one request;
-        ``parallel_sequences``: most requests live at a time (flyweight's ``--parallel``);
-        ``cache_tokens``: size of the KV pool in tokens (default: every live request at
-        the context limit); ``max_batched_tokens``: token budget of one step."""
-        return Runtime(self, context_limit, parallel_sequences, cache_tokens, max_batched_tokens)
+                       config: Optional[EngineConfig] = None, **switches) -> "Runtime":
+        """A runtime over this model: pass an ``EngineConfig``, or its fields by name (flyweight's
+        ``native_runtime(context_limit=..., parallel_sequences=...)``, src/flyweight/v2.py:3297)."""
+        if config is None:
+            config = EngineConfig(context_limit=int(context_limit), parallel_sequences=max(1, int(parallel_sequences)),
+                                  cache_tokens=cache_tokens, max_batched_tokens=int(max_batched_tokens),
+                                  **switches)
+        return Runtime(self, config)
 
 
 class Runtime:
-    def __init__(self, model: Model, context_limit: int, parallel_sequences: int,
-                 cache_tokens: Optional[int], max_batched_tokens: int):
+    def __init__(self, model: Model, config: EngineConfig):
         self.model = model
-        self.context_limit = int(context_limit)
-        self.parallel_sequences = max(1, int(parallel_sequences))
-        if cache_tokens is None:
-            cache_tokens = self.parallel_sequences * (-(-self.context_limit // PAGE_SIZE)) * PAGE_SIZE
-        self.cache_tokens = int(cache_tokens)
-        self.max_batched_tokens = int(max_batched_tokens)
+        self.config = config
+        self.context_limit = config.context_limit
+        self.parallel_sequences = config.parallel_sequences
+        # the default pool has a page to spare per sequence: admission keeps one free page in hand,
+        # and requests that fill the context limit must still run side by side
+        self.cache_tokens = config.pool_tokens
+        self.max_batched_tokens = config.max_batched_tokens
         self.runner: Optional[ModelRunner] = None
         self.scheduler: Optional[Scheduler] = None
         self._token_buffer: Optional[torch.Tensor] = None
         self._token_event = None
         self._counters = {"engine_steps": 0, "steady_steps": 0, "step_seconds": 0.0,
                           "sampling_seconds": 0.0, "d2h_bytes": 0}
-        self.steady_decode = True          # take the short way when a step repeats the last one
-        self.run_ahead = True              # ... and launch the step after it before reading this one's tokens
+        self.steady_decode = config.steady_decode    # take the short way when a step repeats the last one
+        self.run_ahead = config.run_ahead            # ... and launch the step after it before reading this one's tokens
         self._ahead = None                 # a decode step already launched whose tokens were not read yet
         self._token_ring = None            # pinned buffers for the sampled ids of two steps in flight
         # tracing hook: called as observer(tasks, logits) with the fp32 logits [len(tasks)][vocab]
@@ -97,7 +130,8 @@ class Runtime:
         self.runner = ModelRunner(self.model.module, num_pages=max(1, self.cache_tokens // PAGE_SIZE),
                                   num_slots=self.parallel_sequences,
                                   max_model_len=self.context_limit,
-                                  max_batched_tokens=self.max_batched_tokens)
+                                  max_batched_tokens=self.max_batched_tokens,
+                                  use_graphs=self.config.use_graphs, use_plan=self.config.use_plan)
         self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
 
     def reset(self) -> None:

@@ -122,6 +122,24 @@ def load_model_tensors(model_dir) -> Dict[str, torch.Tensor]:
                             "model.safetensors.index.json")
 
 
+def stored_shapes(model_dir) -> Dict[str, tuple]:
+    """Tensor name -> stored shape for a model folder, from the headers alone (no payload read)."""
+    model_dir = Path(model_dir)
+    single = model_dir / "model.safetensors"
+    index = model_dir / "model.safetensors.index.json"
+    if single.is_file():
+        files = [single]
+    elif index.is_file():
+        weight_map = json.loads(index.read_text()).get("weight_map", {})
+        files = [model_dir / shard for shard in sorted(set(weight_map.values()))]
+    else:
+        return {}
+    shapes: Dict[str, tuple] = {}
+    for path in files:
+        shapes.update({name: tuple(entry.shape) for name, entry in read_header(path).items()})
+    return shapes
+
+
 def save_file(tensors: Mapping[str, torch.Tensor], path, metadata: Mapping[str, str] | None = None):
     header: Dict[str, object] = {}
     if metadata:

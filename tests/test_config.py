@@ -112,3 +112,23 @@ def test_schedule_validation():
         replace(spec, schedule=(ScheduleEntry(0, cache_of=1), ScheduleEntry(1))).validate()
     with pytest.raises(ValueError, match="names layer 7"):
         replace(spec, schedule=(ScheduleEntry(7),)).validate()
+
+
+def test_a_checkpoint_with_another_feed_forward_width_is_believed_over_the_rule(tmp_path):
+    """The width rule restates the config keys; a folder whose gate matrices have another number of
+    rows (here: written without the rounding) loads with the stored width, as flyweight reads the
+    width off the tensor (native/src/v2_runtime.cpp:3527-3535)."""
+    import torch
+    from flyweight_b200.config import Lfm2Config
+    from flyweight_b200.weights.safetensors_io import stored_shapes
+    from tiny_configs import TINY_A, make_model_dir
+    raw = dict(TINY_A, intermediate_size=200, block_auto_adjust_ff_dim=True, block_multiple_of=32)
+    config = Lfm2Config.from_dict(raw)
+    assert config.ffn_dim == 160                                   # 200 * 2 / 3 = 133 -> 160
+    folder = make_model_dir(tmp_path / "m", dict(TINY_A, intermediate_size=133), seed=1, dtype=torch.float32)
+    shapes = stored_shapes(folder)
+    assert shapes["model.layers.0.feed_forward.w1.weight"] == (133, 64)
+    reconciled = config.reconciled_with(shapes)
+    assert reconciled.ffn_dim == 133 and reconciled.model_spec().layers[0].feed_forward.params["ffn_dim"] == 133
+    assert config.reconciled_with({}) is config
+    assert "ffn_dim_from_checkpoint" not in reconciled.to_dict()

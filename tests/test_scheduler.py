@@ -241,3 +241,20 @@ def test_fail_takes_a_task_off_the_lists_even_if_the_release_raises():
     planner.finish = original
     assert task.state == "finished" and "first fault" in task.error and "release failed" in task.error
     assert not sched.has_work() and sched.fail(task, "again") == []
+
+
+def test_the_default_pool_runs_two_requests_that_fill_the_context_side_by_side():
+    """The default pool keeps one page to spare per sequence, so that admission's spare page does
+    not make requests that reach the context limit wait for one another."""
+    from flyweight_b200.engine.runtime import EngineConfig
+    config = EngineConfig(context_limit=256, parallel_sequences=2, max_batched_tokens=512)
+    assert config.pool_tokens == 2 * (256 // PAGE_SIZE + 1) * PAGE_SIZE
+    sched, planner = make(num_pages=config.pool_tokens // PAGE_SIZE, num_slots=2, budget=512, max_len=256)
+    ids = [sched.submit([1 + i] * 200, 56, (), GREEDY) for i in range(2)]
+    step = run_step(sched, planner)
+    assert [entry[0] for entry in step.entries] == ids          # both admitted in the first step
+    while sched.has_work():
+        run_step(sched, planner)
+    assert all(len(sched.tasks[i].generated) == 56 for i in ids) and sched.stats["preemptions"] == 0
+    with pytest.raises(ValueError):
+        EngineConfig(context_limit=0)
