@@ -277,3 +277,21 @@ FWB_API int fwb_softcap(float* x, long long n, float cap, cudaStream_t stream) {
     fwb::pdl(softcap_kernel, (int)(blocks > 4096 ? 4096 : blocks), 256, 0, stream)(x, n, cap);
     return fwb_launch_status();
 }
+
+// ------------------------------------------------------------------ token ids that were still on the device
+// token_ids[dst[i]] = source[src[i]]: a step that was planned before the step in front of it was
+// read gets the ids that step sampled straight from the sampler's output.
+__global__ void patch_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ dst,
+                                    const int* __restrict__ source, const int* __restrict__ src, int n) {
+    fwb::pdl_entry();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) token_ids[dst[i]] = source[src[i]];
+}
+
+FWB_API int fwb_patch_tokens(int* token_ids, const int* dst, const int* source, const int* src, int n,
+                             cudaStream_t stream) {
+    if (n <= 0) return FWB_OK;
+    if (!token_ids || !dst || !source || !src) return FWB_BAD_ARGUMENT;
+    fwb::pdl(patch_tokens_kernel, (n + 127) / 128, 128, 0, stream)(token_ids, dst, source, src, n);
+    return fwb_launch_status();
+}

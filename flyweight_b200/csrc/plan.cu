@@ -27,6 +27,7 @@ int fwb_embed(const void*, int, const int*, float*, int, int, int, int*, float, 
 int fwb_rmsnorm(float*, const float*, const float*, void*, int, const int*, int, int, float, cudaStream_t);
 int fwb_silu_mul(const void*, int, void*, int, int, int, cudaStream_t);
 int fwb_softcap(float*, long long, float, cudaStream_t);
+int fwb_patch_tokens(int*, const int*, const int*, const int*, int, cudaStream_t);
 int fwb_gemm_simt(const void*, int, const void*, int, void*, int, const float*, int, int, int, int, int,
                   cudaStream_t);
 int fwb_gemm_tcgen05(const void*, const void*, void*, const float*, int, int, int, int, int, int, int, int,
@@ -276,7 +277,7 @@ enum OpKind { OP_EMBED, OP_NORM_LINEAR, OP_LINEAR_RESIDUAL, OP_SHORTCONV, OP_QK_
 // ids of the step's int32 arrays (their offsets into the uploaded block come with every step)
 enum MetaArray { META_TOKEN_IDS, META_POSITIONS, META_TOK_SEG, META_SEG_START, META_SEG_SLOT, META_SEG_POS0,
                  META_LOGIT_ROWS, META_TILE_SEG_A, META_TILE_TOK0_A, META_TILE_SEG_B, META_TILE_TOK0_B,
-                 META_BLOCK_TABLE0 };
+                 META_PATCH_DST, META_PATCH_SRC, META_BLOCK_TABLE0 };
 constexpr int MAX_GROUPS = 8;
 constexpr int META_COUNT = META_BLOCK_TABLE0 + MAX_GROUPS;
 
@@ -367,6 +368,8 @@ struct FwbStep {
     int tokens_per_tile[2];     // of the two attention tile lists (A: 128 rows, B: 64 rows) ...
     int n_tiles[2];             // ... and how many tiles each holds
     void* logits;               // [R][vocab] fp32 out
+    const int* patch_source;    // n_patch > 0: token ids on the device (the sampler's output of the step
+    int n_patch;                // before) that go into token_ids[patch_dst[i]] from patch_source[patch_src[i]]
 };
 
 namespace {
@@ -692,6 +695,11 @@ FWB_API int fwb_plan_run(void* handle, const void* step_ptr, int* launches, cuda
         if (e != cudaSuccess) return (int)e;
     }
     Launches L;
+    if (step.n_patch > 0) {
+        if (!step.patch_source) return FWB_BAD_ARGUMENT;
+        L.add(fwb_patch_tokens(step.meta_dev + step.offsets[META_TOKEN_IDS], meta(step, META_PATCH_DST),
+                               step.patch_source, meta(step, META_PATCH_SRC), step.n_patch, stream));
+    }
     bool pending = false;                   // a delta written by the last product, not yet in x
     const int act_bf16 = plan.act_bf16;
     plan.failed_op = -1;

@@ -69,6 +69,18 @@ def _to_device(values: np.ndarray, device, pinned: bool) -> torch.Tensor:
     return _staging[key].upload(values, device)
 
 
+def patch_from_device(token_ids: torch.Tensor, places: Sequence[int], source: torch.Tensor,
+                      rows: Sequence[int], device) -> None:
+    """Put ``source[rows[i]]`` into ``token_ids[places[i]]`` on the device; the two small index
+    arrays go up through the pinned staging ring, so the host does not wait."""
+    from ..kernels import ops
+    n = len(places)
+    if n == 0:
+        return
+    both = _to_device(np.asarray(list(places) + list(rows), dtype=np.int32), device, True)
+    ops.patch_tokens_(token_ids, both[:n], source, both[n:])
+
+
 class StepBatch:
     def __init__(self, segments: Sequence[Segment], block_tables_host: Sequence[List[List[int]]],
                  device, pinned: bool = True):
@@ -118,6 +130,7 @@ class StepBatch:
         for (start, s, w), rows in zip(table_slices, block_tables_host):
             if s:
                 flat[start:start + s * w] = np.asarray(rows, dtype=np.int32).reshape(-1)
+        self.seg_start_host = seg_start.copy()
         self.h2d_bytes = flat.size * 4
         dev = _to_device(flat, device, pinned)
         self._dev = dev

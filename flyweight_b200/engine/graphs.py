@@ -149,11 +149,16 @@ class DecodeGraph:
         self.logits = None
         self.kernels = 0
 
-    def run(self, segments, cache) -> torch.Tensor:
+    def run(self, segments, cache, patch_source=None, patch=None) -> torch.Tensor:
         """The step for these segments.  The first call runs the kernels directly and then
         records the graph; later calls replay it.  The returned logits are a static buffer:
-        they are overwritten by the next step of the same batch size."""
+        they are overwritten by the next step of the same batch size.  ``patch``: (segment index,
+        row of ``patch_source``) pairs whose token ids are still on the device."""
         self.batch.upload(segments, cache)
+        if patch:
+            from .batch import patch_from_device
+            patch_from_device(self.batch.token_ids, [index for index, _ in patch], patch_source,
+                              [row for _, row in patch], self.batch._dev.device)
         if self.graph is None:
             logits = self.model.forward(self.ctx, self.caches)
             torch.cuda.current_stream().synchronize()

@@ -31,7 +31,7 @@ from .batch import Segment
 EPI_F32, EPI_ACT, EPI_SWIGLU = 0, 1, 3
 MAX_GROUPS = 8
 META_NAMES = ("token_ids", "positions", "tok_seg", "seg_start", "seg_slot", "seg_pos0", "logit_rows",
-              "tile_seg_a", "tile_tok0_a", "tile_seg_b", "tile_tok0_b")
+              "tile_seg_a", "tile_tok0_a", "tile_seg_b", "tile_tok0_b", "patch_dst", "patch_src")
 META_COUNT = len(META_NAMES) + MAX_GROUPS
 
 
@@ -49,7 +49,7 @@ class FwbStep(ctypes.Structure):
                 ("width", ctypes.c_int * MAX_GROUPS),
                 ("max_segment", ctypes.c_int), ("leading_singles", ctypes.c_int),
                 ("tokens_per_tile", ctypes.c_int * 2), ("n_tiles", ctypes.c_int * 2),
-                ("logits", ctypes.c_void_p)]
+                ("logits", ctypes.c_void_p), ("patch_source", ctypes.c_void_p), ("n_patch", ctypes.c_int)]
 
 
 class Buf:
@@ -309,7 +309,8 @@ class StepPlan:
     def arena_bytes(self) -> int:
         return self._arena.numel()
 
-    def pack(self, segments: Sequence[Segment], tables_host: Sequence[np.ndarray]) -> FwbStep:
+    def pack(self, segments: Sequence[Segment], tables_host: Sequence[np.ndarray],
+             patch: Optional[Sequence] = None) -> FwbStep:
         """The step's int32 arrays, one after the other in one block of host memory, and the
         counts the library needs; returns the filled ``FwbStep`` (reused from step to step)."""
         step = self._step
@@ -336,7 +337,9 @@ class StepPlan:
         else:
             empty = np.empty(0, dtype=np.int32)
             tiles = [(empty, empty), (empty, empty)]
-        counts = [T, T, T, S + 1, S, S, R, tiles[0][0].size, tiles[0][0].size, tiles[1][0].size, tiles[1][0].size]
+        n_patch = len(patch) if patch else 0
+        counts = [T, T, T, S + 1, S, S, R, tiles[0][0].size, tiles[0][0].size, tiles[1][0].size, tiles[1][0].size,
+                  n_patch, n_patch]
         widths = [int(rows.shape[1]) if rows.ndim == 2 and rows.shape[0] else 1 for rows in tables_host]
         counts += [S * w for w in widths]
         words = sum(counts)
@@ -376,6 +379,11 @@ class StepPlan:
             flat[o[7 + 2 * k]:o[7 + 2 * k] + n] = seg_of
             flat[o[8 + 2 * k]:o[8 + 2 * k] + n] = tok0
             step.n_tiles[k] = n
+        if n_patch:
+            # (segment index, row of the source): the segment's last token is the one in flight
+            flat[o[11]:o[11] + n_patch] = [int(seg_start[index + 1]) - 1 for index, _ in patch]
+            flat[o[12]:o[12] + n_patch] = [row for _, row in patch]
+        step.n_patch = n_patch
         for g, rows in enumerate(tables_host):
             start = o[len(META_NAMES) + g]
             if S and widths[g]:
@@ -389,10 +397,15 @@ class StepPlan:
         step.max_segment, step.leading_singles = max_segment, leading
         return step
 
-    def run(self, segments: Sequence[Segment], tables_host: Sequence[np.ndarray]) -> torch.Tensor:
+    def run(self, segments: Sequence[Segment], tables_host: Sequence[np.ndarray],
+            patch_source: Optional[torch.Tensor] = None, patch: Optional[Sequence] = None) -> torch.Tensor:
+        """``patch``: (segment index, row of ``patch_source``) pairs: the last token of those
+        segments is still on the device, in ``patch_source`` (int32), and is put into the step's
+        token ids there."""
         if len(tables_host) > MAX_GROUPS:
             raise KernelError(f"a plan serves at most {MAX_GROUPS} page groups")
-        step = self.pack(segments, tables_host)
+        step = self.pack(segments, tables_host, patch)
+        step.patch_source = patch_source.data_ptr() if (patch and patch_source is not None) else None
         if step.T > self.max_tokens or step.R > self.max_rows:
             raise KernelError(f"a step of {step.T} tokens and {step.R} wanted rows exceeds the plan's "
                               f"{self.max_tokens} and {self.max_rows}")

@@ -22,7 +22,7 @@ from ..kernels import lib as kernel_lib
 
 from ..cache.manager import PAGE_SIZE, CacheManager, OutOfPages, OutOfSlots
 from ..kernels.lib import require_cuda
-from .batch import Segment, StepBatch, StepContext
+from .batch import Segment, StepBatch, StepContext, patch_from_device
 from .graphs import DecodeGraph
 from .plan import build_plan
 
@@ -179,7 +179,11 @@ class ModelRunner(StepPlanner):
         self.tokens_run = 0
         self.h2d_bytes = 0
 
-    def step(self, entries: Sequence[Entry], pages_checked: bool = False) -> torch.Tensor:
+    def step(self, entries: Sequence[Entry], pages_checked: bool = False,
+             patch_source: Optional[torch.Tensor] = None, patch: Optional[Sequence] = None) -> torch.Tensor:
+        """``patch``: (entry index, row of ``patch_source``) pairs.  The last token of those entries
+        was sampled by the step before and has not been read by the host (the entry carries a
+        placeholder id); its value is taken from ``patch_source`` (int32, on the device) there."""
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         segments = self.plan(entries, pages_checked)
@@ -206,7 +210,7 @@ class ModelRunner(StepPlanner):
                     self.bad_token_flag, len(segments), n_groups, bucket)
             else:
                 self.graph_replays += 1
-            logits = graph.run(segments, self.cache)
+            logits = graph.run(segments, self.cache, patch_source, patch)
             self.last_decode_graph = graph
             self.steps += 1
             self.tokens_run += len(segments)
@@ -215,12 +219,15 @@ class ModelRunner(StepPlanner):
         self.last_decode_graph = None
         tables = [self.cache.block_table_array(g, requests, width) for g in range(n_groups)]
         if self.step_plan is not None and self.use_plan:
-            logits = self.step_plan.run(segments, tables)
+            logits = self.step_plan.run(segments, tables, patch_source, patch)
             self.steps += 1
             self.tokens_run += self.step_plan._step.T
             self.h2d_bytes += self.step_plan.h2d_bytes
             return logits
         batch = StepBatch(segments, tables, self.device)
+        if patch:
+            patch_from_device(batch.token_ids, [int(batch.seg_start_host[index + 1]) - 1 for index, _ in patch],
+                              patch_source, [row for _, row in patch], self.device)
         ctx = StepContext(batch, self.precision, self.device, self.bad_token_flag)
         logits = self.model.forward(ctx, self.cache.layer_caches)
         self.steps += 1

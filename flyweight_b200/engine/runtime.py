@@ -111,11 +111,12 @@ class Runtime:
         self.scheduler: Optional[Scheduler] = None
         self._token_buffer: Optional[torch.Tensor] = None
         self._token_event = None
-        self._counters = {"engine_steps": 0, "steady_steps": 0, "step_seconds": 0.0,
+        self._counters = {"engine_steps": 0, "steady_steps": 0, "pipelined_steps": 0, "step_seconds": 0.0,
                           "sampling_seconds": 0.0, "d2h_bytes": 0}
         self.steady_decode = config.steady_decode    # take the short way when a step repeats the last one
         self.run_ahead = config.run_ahead            # ... and launch the step after it before reading this one's tokens
         self._ahead = None                 # a decode step already launched whose tokens were not read yet
+        self._flight = None                # the same for a step of any kind (the pipelined way)
         self._token_ring = None            # pinned buffers for the sampled ids of two steps in flight
         # tracing hook: called as observer(tasks, logits) with the fp32 logits [len(tasks)][vocab]
         # every time tokens are about to be sampled from them (the tensor is overwritten by the
@@ -136,13 +137,13 @@ class Runtime:
 
     def reset(self) -> None:
         """Forget every request and give back everything the cache holds."""
-        self._ahead = None
+        self._ahead = self._flight = None
         self.runner.cache.reset()
         self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
 
     def close(self) -> None:
         runner, self.runner, self.scheduler = self.runner, None, None
-        self._ahead = None
+        self._ahead = self._flight = None
         if runner is not None:
             runner.check_health()
 
@@ -178,41 +179,128 @@ class Runtime:
         return self.scheduler.tasks[task_id].error
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._flight is not None
 
     def engine_step(self) -> List[Tuple[int, int, int]]:
         """One scheduling cycle: one batched model step and one token for every request
-        that was due.  Returns events ``(task id, token or count, kind)``."""
-        scheduler, runner = self.scheduler, self.runner
+        that was due.  Returns events ``(task id, token or count, kind)``.
+
+        Three ways, the shortest that applies: steady decoding (the same requests one token further:
+        no scheduling at all, see ``_steady_step``); the pipelined way (``run_ahead``): the step
+        after this one is scheduled and launched before this one's tokens are read -- the ids it
+        needs are still on the device and go from the sampler's output into its batch there -- so
+        the host's scheduling, packing and launching overlap the device's work; and the plain way,
+        which reads every step's tokens before it plans the next."""
         started = time.perf_counter()
-        if self._ahead is not None or self.steady_decode:
+        if self._flight is None and (self._ahead is not None or self.steady_decode):
             events = self._steady_step()
             if events is not None:
                 self._counters["steady_steps"] += 1
                 self._counters["engine_steps"] += 1
                 self._counters["step_seconds"] += time.perf_counter() - started
                 return events
+        events: List[Tuple[int, int, int]] = []
+        current = self._flight
+        self._flight = None
+        if current is None:
+            current = self._launch_scheduled(events, None)
+        if current is not None:
+            if self._may_pipeline(current):
+                self._flight = self._launch_scheduled(events, current)
+                if self._flight is not None:
+                    self._counters["pipelined_steps"] += 1
+            events.extend(self._accept_flight(current))
+        self._counters["engine_steps"] += 1
+        self._counters["step_seconds"] += time.perf_counter() - started
+        return events
+
+    def _launch_scheduled(self, events, after):
+        """Schedule a step, launch it and its sampling; nothing is waited for.  ``after``: the step
+        launched before it whose tokens are not read yet (its requests' next ids are taken from its
+        sampler's output on the device).  Returns the launched step's record, or None when the
+        step samples nothing (no tokens to read: nothing to wait for later either)."""
+        scheduler, runner = self.scheduler, self.runner
         step = scheduler.schedule()
         logits = None
         while step.entries and logits is None:
+            patch = None
+            if after is not None and step.in_flight:
+                rows = {id(task): row for row, task in enumerate(after["tasks"])}
+                patch = [(index, rows[id(task)]) for index, task in enumerate(step.tasks) if task.in_flight]
             try:
-                logits = runner.step(step.entries, pages_checked=True)
+                logits = runner.step(step.entries, pages_checked=True,
+                                     patch_source=after["device"] if patch else None, patch=patch)
             except StepError as error:
                 # the step function refuses one request's entry before anything is launched or
                 # mapped: that request fails alone, the step runs without it
                 if not scheduler.fail_scheduled(step, error.request, str(error)):
                     raise
-        events = list(step.events)
+        events.extend(step.events)
         if not step.entries:
-            return events
+            return None
         need = scheduler.advance(step)
         for task in step.tasks:
             if task not in need:
                 events.append((task.id, task.computed, EVENT_PROGRESS))
-        if need:
-            self._sample_and_accept(need, logits, events)
-        self._counters["engine_steps"] += 1
-        self._counters["step_seconds"] += time.perf_counter() - started
+        if not need:
+            return None
+        flight = self._sample_async(need, logits)
+        flight["graph_step"] = runner.last_decode_graph is not None
+        return flight
+
+    def _may_pipeline(self, current) -> bool:
+        """Whether the step after ``current`` may be planned before ``current``'s tokens are read.
+        Not when a request's penalties need the token values on the host; and not when steady
+        decoding is about to take over (the same requests, everybody decoding, nobody waiting):
+        that way is shorter still and starts from a step whose tokens have been read."""
+        if not self.run_ahead:
+            return False
+        scheduler = self.scheduler
+        if any(task.sampling.penalizes for task in scheduler.running) or \
+                any(task.sampling.penalizes for task in scheduler.waiting):
+            return False
+        if (self.steady_decode and current.get("graph_step") and not scheduler.waiting
+                and len(current["tasks"]) == len(scheduler.running)
+                and not any(group.window for group in self.runner.cache.groups)):
+            return False
+        return True
+
+    def _sample_async(self, need, logits):
+        """Sampling (arg-max or draws) and the copy of the ids to pinned memory, both queued;
+        nobody waits here.  The requests' tokens are in flight from now until ``_accept_flight``."""
+        if self.logits_observer is not None:
+            self.logits_observer(need, logits)
+        if all(task.sampling.greedy for task in need):
+            tokens = device_sampler.argmax(logits)
+        else:
+            uniforms = [0.0 if task.sampling.greedy else task.rng.uniform() for task in need]
+            tokens = device_sampler.sample(logits, [task.sampling for task in need], uniforms,
+                                           [task.generated for task in need])
+        flight = self._queue_read(need, tokens)
+        for task in need:
+            task.in_flight += 1
+        return flight
+
+    def _accept_flight(self, flight) -> List[Tuple[int, int, int]]:
+        """Wait for the ids of a launched step and hand them to their requests.  A request that
+        ended meanwhile (a stop token in the step before, a cancellation, a failure) drops its id; one
+        that was preempted meanwhile keeps it: it is part of its text when it is admitted again."""
+        sampled = time.perf_counter()
+        flight["event"].synchronize()
+        host = flight["host"].tolist()
+        self._counters["d2h_bytes"] += 4 * len(host)
+        self._counters["sampling_seconds"] += time.perf_counter() - sampled
+        events: List[Tuple[int, int, int]] = []
+        finished = False
+        for task, token in zip(flight["tasks"], host):
+            if task.state == "finished":
+                task.in_flight = 0
+                continue
+            accepted = self._accept(task, token)
+            finished = finished or len(accepted) > 1
+            events.extend(accepted)
+        if finished:
+            self.runner.check_health()          # once per finished request: kernels fail loudly
         return events
 
     def _sample_and_accept(self, need, logits, events) -> None:
@@ -294,7 +382,10 @@ class Runtime:
         waits here."""
         if self.logits_observer is not None:
             self.logits_observer(tasks, logits)
-        tokens = device_sampler.argmax(logits)
+        return self._queue_read(tasks, device_sampler.argmax(logits))
+
+    def _queue_read(self, tasks, tokens):
+        """The copy of sampled ids (int32 on the device) to one of two pinned buffers, queued."""
         if self._token_ring is None:
             self._token_ring = {"buffers": [torch.empty(256, dtype=torch.int32).pin_memory() for _ in range(2)],
                                 "events": [torch.cuda.Event() for _ in range(2)], "turn": 0}

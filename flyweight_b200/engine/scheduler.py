@@ -34,6 +34,7 @@ MAX_QUEUED = 256          # native/src/v2_runtime.cpp:32588
 
 # event kinds, as in native/include/flyweight_v2.h:413-417
 EVENT_TOKEN, EVENT_FINISHED, EVENT_ERROR, EVENT_PROGRESS = 0, 1, 2, 3
+IN_FLIGHT = 0             # placeholder id of a token whose value is still on the device
 
 
 class QueueFull(RuntimeError):
@@ -56,6 +57,7 @@ class Task:
     cancelled: bool = False
     preemptions: int = 0
     admitted_at: int = -1          # admission counter value (larger = admitted later)
+    in_flight: int = 0             # 1: its next token is sampled on the device but not read yet
 
     @property
     def text(self) -> List[int]:
@@ -63,17 +65,29 @@ class Task:
 
     @property
     def pending(self) -> int:
-        return len(self.prompt) + len(self.generated) - self.computed
+        """Tokens of its text that are not in the cache yet; a token still in flight counts: it is
+        the text's next token, only its value is not on the host yet."""
+        return len(self.prompt) + len(self.generated) + self.in_flight - self.computed
+
+    def ends_with_the_token_in_flight(self, max_model_len: int) -> bool:
+        """Whether the token in flight is known to be its last (token count or context limit)."""
+        return (len(self.generated) + self.in_flight >= self.max_tokens
+                or len(self.prompt) + len(self.generated) + self.in_flight >= max_model_len)
 
     def tokens_from(self, start: int, count: int) -> List[int]:
         """``text[start:start + count]`` without joining the two lists first (a long prompt
-        would be copied once per step and request)."""
+        would be copied once per step and request).  A token in flight stands as ``IN_FLIGHT``:
+        the step function puts the value in on the device."""
         known = len(self.prompt)
         if start + count <= known:
             return self.prompt[start:start + count]
         if start >= known:
-            return self.generated[start - known:start - known + count]
-        return self.prompt[start:] + self.generated[:start + count - known]
+            out = self.generated[start - known:start - known + count]
+        else:
+            out = self.prompt[start:] + self.generated[:start + count - known]
+        if len(out) < count:
+            out = out + [IN_FLIGHT] * (count - len(out))
+        return out
 
 
 @dataclass
@@ -83,6 +97,7 @@ class ScheduledStep:
     preempted: List[int] = field(default_factory=list)
     failed: List[int] = field(default_factory=list)
     events: List[Tuple[int, int, int]] = field(default_factory=list)   # made while scheduling
+    in_flight: List[Task] = field(default_factory=list)   # tasks whose entry ends in a token still on the device
 
 
 class Scheduler:
@@ -224,6 +239,8 @@ class Scheduler:
             for task in list(self.running):
                 if (task.pending == 1) != decoding or budget <= 0 or task in chosen:
                     continue
+                if task.in_flight and task.ends_with_the_token_in_flight(self.max_model_len):
+                    continue                        # it ends when that token is read: nothing more to run
                 try:
                     entry = self._portion(task, budget)
                 except Exception as error:
@@ -281,6 +298,7 @@ class Scheduler:
                 self.running.append(task)
                 self.stats["admitted"] += 1
         step.entries, step.tasks = entries, chosen
+        step.in_flight = [task for task in chosen if task.in_flight]
         return step
 
     # ------------------------------------------------------------------ after the step ran
@@ -311,6 +329,8 @@ class Scheduler:
         ``max_tokens`` or at the context limit (emit-then-stop order of
         native/src/v2_runtime.cpp:33775-33780)."""
         task.generated.append(int(token))
+        if task.in_flight:
+            task.in_flight -= 1
         events = [(task.id, int(token), EVENT_TOKEN)]
         reason = None
         if int(token) in task.stop_tokens:

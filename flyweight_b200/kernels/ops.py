@@ -33,6 +33,17 @@ def embed(table: torch.Tensor, ids: torch.Tensor, bad_flag: Optional[torch.Tenso
     return out
 
 
+def patch_tokens_(token_ids: torch.Tensor, dst: torch.Tensor, source: torch.Tensor, src: torch.Tensor) -> None:
+    """``token_ids[dst[i]] = source[src[i]]`` on the device (all int32): ids that the step before
+    sampled and the host has not read yet go straight into this step's batch."""
+    for name, tensor in (("token ids", token_ids), ("patch places", dst), ("patch source", source),
+                         ("patch rows", src)):
+        _i32(name, tensor)
+    if dst.numel() != src.numel():
+        raise KernelError("one source row per patched place is needed")
+    lib.call("fwb_patch_tokens", ptr(token_ids), ptr(dst), ptr(source), ptr(src), dst.numel(), stream())
+
+
 # ------------------------------------------------------------------ norms
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None

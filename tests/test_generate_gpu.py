@@ -283,3 +283,54 @@ def test_penalties_with_the_whole_vocabulary_as_candidates_run_to_the_end():
         # greedy under a strong repetition penalty does not settle into a loop of one token
         tail = runtime.task(c).generated[-10:]
         assert len(set(tail)) > 1
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_planning_the_next_step_before_this_one_is_read_changes_nothing(name):
+    """The pipelined way of ``engine_step``: prompts in portions beside decoding requests, sampled
+    and greedy requests, stop tokens (seen one step late), a cancellation, requests that end on their
+    token count, a pool so small that requests are preempted while a token of theirs is in flight.
+    Every request's tokens and its reason to finish equal the plain way's."""
+    import random
+    rnd = random.Random(5)
+    vocab = TINY[name]["vocab_size"]
+    prompts = [[rnd.randrange(vocab) for _ in range(n)] for n in (3, 70, 20, 130, 64, 1, 45, 90)]
+    settings = dict(temperature=0.9, top_k=50, top_p=0.95, min_p=0.0)
+
+    def run(ahead, stop, cache_tokens):
+        with open_runtime(name, "float32", context_limit=320, parallel_sequences=5, max_batched_tokens=48,
+                          cache_tokens=cache_tokens, run_ahead=ahead, steady_decode=ahead) as runtime:
+            ids = [runtime.task_submit(p, 40 + 12 * i, stop, seed=11 + i, **(settings if i % 3 == 0 else
+                                                                          dict(temperature=0.0)))
+                   for i, p in enumerate(prompts)]
+            steps = 0
+            while runtime.has_work():
+                runtime.engine_step()
+                steps += 1
+                if steps == 25:
+                    runtime.task_cancel(ids[3])
+                assert steps < 3000
+            info = runtime.info
+            assert info["cache"]["groups"][0]["pages_in_use"] == 0 and info["cache"]["slots_in_use"] == 0
+            tasks = [runtime.task(i) for i in ids]
+            return ([t.generated for t in tasks], [t.finish_reason for t in tasks], info)
+
+    plain, _, _ = run(False, (), None)
+    stop = (plain[1][12], plain[6][20])
+    for cache_tokens in (None, 6 * 64):
+        slow, slow_reasons, slow_info = run(False, stop, cache_tokens)
+        fast, fast_reasons, fast_info = run(True, stop, cache_tokens)
+        assert fast_info["pipelined_steps"] > 20 and slow_info["pipelined_steps"] == 0
+        if cache_tokens is None:
+            # the same schedule in both ways: the same tokens, bit for bit
+            assert fast == slow and fast_reasons == slow_reasons
+            assert "stop" in fast_reasons and "cancelled" in fast_reasons and "length" in fast_reasons
+        else:
+            # a small pool: the two ways preempt at different moments (a request that ends on a stop
+            # token holds its pages one step longer in the pipelined way), so recomputed prompts may
+            # differ in the last bits; greedy requests still produce the plain implementation's tokens
+            assert fast_info["preemptions"] > 0
+            cfg, w = plain_model(name, "float32")
+            for i, prompt in enumerate(prompts):
+                if i % 3 and fast_reasons[i] == "length":
+                    assert fast[i] == P.greedy_generate(cfg, w, prompt, len(fast[i]))
