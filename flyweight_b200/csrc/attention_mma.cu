@@ -60,11 +60,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Ring depth of the decode kernel when the launch is small (few CTAs: each should have more of
+// its slice in flight); as deep as leaves three CTAs to an SM.  Large launches keep two stages
+// and twice the CTAs per SM (measured at batch 8 and 64: the deep ring is 1 to 5 % slower there,
+// at batch 1 it is 2.6 % faster).
+template <int HD> constexpr int decode_stages() { return HD <= 64 ? 4 : (HD <= 96 ? 3 : 2); }
+
 template <int HD>
 struct Smem {
     static constexpr int ROW = HD + 8;                     // bf16 elements; +16 bytes: no bank conflicts
     static constexpr int TILE = KEYS * ROW;                // one K or V tile
     static constexpr int BYTES = 2 * 2 * TILE * 2;         // 2 stages x (K, V) x bf16
+    static constexpr int DEEP_BYTES = decode_stages<HD>() * 2 * TILE * 2;
 };
 
 // Copy one (page, kv head) tile of K and of V into shared memory (whole CTA).
@@ -309,7 +316,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 // grid (splits, nkv, T).  A split covers `tiles_per_split` key tiles; with splits == 1 the
 // result goes straight to `out`, else (acc, max, sum) go to the scratch buffers:
 //   part_o[t][kvh][split][group][HD] fp32 (not normalised), part_ml[t][kvh][split][group][2].
-template <int HD, bool CLUSTER>
+template <int HD, bool CLUSTER, bool DEEP>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
@@ -336,15 +343,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     int tile_end = tile_begin + tiles_per_split;
     if (tile_end > last_tile + 1) tile_end = last_tile + 1;
 
+    constexpr int DECODE_STAGES = DEEP ? decode_stages<HD>() : 2;
+    // A ring of DECODE_STAGES key/value tiles: a slice of eight tiles has half of its bytes in
+    // flight from the start (two stages left the memory pipe waiting on every tile's round trip).
     auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
     auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
     auto issue = [&](int tile, int s) {
-        const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
-        load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
-        cp_async_commit();
+        if (tile < tile_end) {
+            const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
+            load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
+        }
+        cp_async_commit();                                  // an empty group keeps the count in step
     };
-    const bool early = tile_begin < tile_end && tile_begin < last_tile;
-    if (early) issue(tile_begin, 0);
+    // every tile but the token's own last one was written by earlier steps: those among the first
+    // DECODE_STAGES - 1 are fetched before the wait for the previous kernel
+    int issued = 0;
+    while (issued < DECODE_STAGES - 1 && tile_begin + issued < tile_end && tile_begin + issued < last_tile) {
+        issue(tile_begin + issued, issued);
+        ++issued;
+    }
     fwb::pdl_wait();
 
     // rows 0..group-1 are the group's query heads; the rest are padding
@@ -362,15 +379,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         for (int j = 0; j < 4; ++j) o[n][j] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
-    if (tile_begin < tile_end && !early) issue(tile_begin, 0);
+    for (; issued < DECODE_STAGES - 1; ++issued) issue(tile_begin + issued, issued);
     for (int tile = tile_begin; tile < tile_end; ++tile) {
-        const int s = (tile - tile_begin) & 1;
-        if (tile + 1 < tile_end) {
-            issue(tile + 1, s ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int s = (tile - tile_begin) % DECODE_STAGES;
+        // the slot this tile's successor-but-two goes to was read in the iteration before this one
+        issue(tile + DECODE_STAGES - 1, (tile - tile_begin + DECODE_STAGES - 1) % DECODE_STAGES);
+        cp_async_wait<DECODE_STAGES - 1>();
         __syncthreads();
         if (pos - tile * KEYS + 1 < KEYS) {
             clear_v_rows<HD>(stage_v(s), pos - tile * KEYS + 1);
@@ -547,11 +561,15 @@ int launch_decode(const void* q, const void* k_pool, const void* v_pool, const i
                   float* part_ml, int T, int nh, int nkv, int splits, int tiles_per_split, int window,
                   float scale, bool in_cluster, cudaStream_t stream) {
     constexpr size_t merge_bytes = (size_t)(WARPS + 1) * 16 * HD * 4 + 16 * 2 * 4;
-    constexpr size_t bytes = Smem<HD>::BYTES > merge_bytes ? Smem<HD>::BYTES : merge_bytes;
+    // few CTAs (at most three per SM): the deep ring; else two stages and more CTAs per SM
+    const bool deep = (long)splits * nkv * T <= 3 * 148;
+    constexpr size_t shallow_bytes = Smem<HD>::BYTES > merge_bytes ? Smem<HD>::BYTES : merge_bytes;
+    constexpr size_t deep_bytes = Smem<HD>::DEEP_BYTES > merge_bytes ? Smem<HD>::DEEP_BYTES : merge_bytes;
+    const size_t bytes = deep ? deep_bytes : shallow_bytes;
     using bf = __nv_bfloat16;
     if (splits > 1 && in_cluster) {
         // the slices of a (token, KV head) as a cluster: merged through distributed shared memory
-        auto kernel = attention_decode_kernel<HD, true>;
+        auto kernel = deep ? attention_decode_kernel<HD, true, true> : attention_decode_kernel<HD, true, false>;
         int st = opt_in_smem(kernel, bytes);
         if (st != FWB_OK) return st;
         cudaLaunchConfig_t config = {};
@@ -574,7 +592,7 @@ int launch_decode(const void* q, const void* k_pool, const void* v_pool, const i
                                            tiles_per_split, window, scale * LOG2E);
         return e == cudaSuccess ? fwb_launch_status() : (int)e;
     }
-    auto kernel = attention_decode_kernel<HD, false>;
+    auto kernel = deep ? attention_decode_kernel<HD, false, true> : attention_decode_kernel<HD, false, false>;
     int st = opt_in_smem(kernel, bytes);
     if (st != FWB_OK) return st;
     fwb::pdl(kernel, dim3(splits, nkv, T), WARPS * 32, bytes, stream)(
