@@ -529,8 +529,9 @@ def run_kernel_times(args) -> int:
     """``--kernel-times decode|prefill|TOKENS``: one step of LFM2-1.2B launched kernel by kernel with
     a pair of CUDA events around every launch; prints {kernel, calls, us, share} by falling time,
     launches per step and the host time spent inside the launchers, as one JSON line.  The events
-    keep kernels from overlapping their neighbours, so the sum is above the step's real time
-    (printed beside it, from a second, unbracketed run of the same step)."""
+    keep kernels from overlapping their neighbours and every bracket includes the gap before its
+    kernel starts; ``net_us`` takes the bracket of an empty kernel off every launch, and the
+    step's real time (a second, unbracketed run) is printed beside the sums."""
     import torch
     from flyweight_b200.engine import ModelRunner
     from flyweight_b200.engine.runtime import Model
@@ -570,7 +571,26 @@ def run_kernel_times(args) -> int:
     kernel_lib.profile_start()
     step()
     report = kernel_lib.profile_stop()
-    report.update({"kernel_times": what, "tokens": tokens, "step_us_unbracketed": round(1e3 * start.elapsed_time(stop), 1)})
+    # what a pair of events costs around a kernel that does next to nothing (launched one by one,
+    # a kernel starts a few microseconds after the one before it ended): taken off every call
+    from flyweight_b200.kernels import ops
+    tiny_x = torch.zeros(8, device="cuda:0")
+    tiny_d = torch.zeros(8, device="cuda:0")
+    kernel_lib.profile_start()
+    for _ in range(50):
+        ops.add_(tiny_x, tiny_d)
+    gap = kernel_lib.profile_stop()["kernels"][0]
+    overhead = gap["us"] / gap["calls"]
+    net_total = 0.0
+    for entry in report["kernels"]:
+        entry["net_us"] = round(max(0.0, entry["us"] - overhead * entry["launches"]), 2)
+        net_total += entry["net_us"]
+    for entry in report["kernels"]:
+        entry["net_share"] = round(entry["net_us"] / (net_total or 1.0), 4)
+    report["kernels"].sort(key=lambda entry: -entry["net_us"])
+    report.update({"kernel_times": what, "tokens": tokens, "bracket_overhead_us": round(overhead, 2),
+                   "net_device_us": round(net_total, 1),
+                   "step_us_unbracketed": round(1e3 * start.elapsed_time(stop), 1)})
     print(json.dumps(report))
     return 0
 
