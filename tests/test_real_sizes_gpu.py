@@ -30,6 +30,14 @@ REAL = {
     "max_position_embeddings": 128000, "tie_embedding": True,
 }
 DTYPES = ("float32", "bfloat16")
+# The other two sizes of the family (their own feed-forward widths, head counts and groups), two
+# layers each: LFM2-350M has 16 query heads on 8 KV heads (two per group: 64-token attention
+# tiles) and a width of 4,608; LFM2-2.6B as the baseline states it has a width of 7,168.
+OTHERS = {
+    "lfm2-350m": dict(REAL, num_hidden_layers=2, layer_types=["full_attention", "conv"], hidden_size=1024,
+                      num_attention_heads=16, intermediate_size=6656),
+    "lfm2-2.6b": dict(REAL, num_hidden_layers=2, layer_types=["conv", "full_attention"], intermediate_size=10752),
+}
 
 
 @pytest.fixture(scope="module")
@@ -128,4 +136,28 @@ def test_mixed_batches_with_pages_that_come_back(dtype, runners, oracle):
         assert_close(got[rid], oracle(tokens[rid], rows[rid]), TOL_ORACLE[dtype],
                      f"real sizes {dtype}: mixed, request {rid}")
     assert runner.cache.stats()["groups"][0]["pages_in_use"] == 0
+    runner.check_health()
+
+
+@pytest.mark.parametrize("size", sorted(OTHERS))
+def test_the_other_sizes_of_the_family_in_bfloat16(size, tmp_path):
+    """Layer sizes of LFM2-350M and LFM2-2.6B (two layers each): whole, decoded and in portions
+    against the float64 oracle, in the precision that serves."""
+    from flyweight_b200.engine import ModelRunner, load_model
+    config = OTHERS[size]
+    folder = make_model_dir(tmp_path / size, config, seed=13, dtype=torch.bfloat16)
+    cfg, weights = PT.load_model_dir(folder, "cuda")
+    assert weights["model.layers.0.feed_forward.w1.weight"].shape[0] == {"lfm2-350m": 4608, "lfm2-2.6b": 7168}[size]
+    runner = ModelRunner(load_model(folder, "bfloat16"), num_pages=12, num_slots=2, max_model_len=1024,
+                         max_batched_tokens=1024)
+    tokens = _tokens(600, seed=22)
+    rows = sorted(set(range(0, 600, 11)) | set(range(560, 600)))
+    want = PT.forward(cfg, weights, tokens, rows=rows)
+    whole = _run(runner, "whole", tokens, [600], rows)
+    assert_close(whole, want, TOL_ORACLE["bfloat16"], f"{size}: whole request")
+    decoded = _run(runner, "decoded", tokens, [568, 1], rows)
+    assert_close(decoded, want, TOL_ORACLE["bfloat16"], f"{size}: 568 tokens, then 32 singly")
+    portions = _run(runner, "portions", tokens, [300, 2, 100, 64, 129, 5], rows)
+    assert_close(portions, want, TOL_ORACLE["bfloat16"], f"{size}: portions")
+    assert_close(portions, whole, TOL_CUTS["bfloat16"], f"{size}: portions against whole")
     runner.check_health()

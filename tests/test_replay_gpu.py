@@ -119,6 +119,35 @@ def test_long_decoding(name, dtype):
     assert_close(np.concatenate(parts), want, TOL_ORACLE[dtype], f"{name} {dtype} 327 decode steps")
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16")])
+def test_decoding_at_a_context_of_four_thousand_tokens(name, dtype):
+    """Sixty-two pages of context: a prompt of 3,900 tokens in portions of 1,000, then 60 tokens
+    one by one, the context cut into slices that a cluster merges, graphs of a wide block table;
+    another request decodes beside it at a short context (its rows of the table are mostly empty)."""
+    runner = new_runner(name, dtype, num_pages=70, num_slots=2, max_model_len=4000)
+    tokens = random_tokens(name, 3960, seed=31)
+    short = random_tokens(name, 80, seed=32)
+    want, want_short = plain_logits(name, dtype, tokens), plain_logits(name, dtype, short)
+    got = []
+    for start in range(0, 3900, 1000):
+        stop = min(start + 1000, 3900)
+        got.append(runner.step([("l", tokens[start:stop], [0, stop - start - 1])]).cpu().numpy())
+    assert_close(np.concatenate(got), want[[0, 999, 1000, 1999, 2000, 2999, 3000, 3899]], TOL_ORACLE[dtype],
+                 f"{name} {dtype} portions of a long prompt")
+    runner.step([("s", short[:20], [])])
+    got_long, got_short = [], []
+    for i in range(60):
+        out = runner.step([("l", [tokens[3900 + i]], [0]), ("s", [short[20 + i]], [0])]).cpu().numpy()
+        got_long.append(out[0])
+        got_short.append(out[1])
+    assert_close(np.stack(got_long), want[3900:], TOL_ORACLE[dtype], f"{name} {dtype} decoding at 3,900 tokens")
+    assert_close(np.stack(got_short), want_short[20:], TOL_ORACLE[dtype], f"{name} {dtype} its short neighbour")
+    runner.finish("l")
+    runner.finish("s")
+    runner.cache.check()
+    runner.check_health()
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_the_first_tokens_of_a_sequence(name, dtype):
     runner = new_runner(name, dtype)
