@@ -526,7 +526,8 @@ def run_mixed(args) -> int:
 
 
 def run_kernel_times(args) -> int:
-    """``--kernel-times decode|prefill|TOKENS``: one step of LFM2-1.2B launched kernel by kernel with
+    """``--kernel-times [MODEL:]decode|prefill|TOKENS``: one step (of LFM2-1.2B unless another of the
+    models is named, e.g. ``lfm2-350m:512``) launched kernel by kernel with
     a pair of CUDA events around every launch; prints {kernel, calls, us, share} by falling time,
     launches per step and the host time spent inside the launchers, as one JSON line.  The events
     keep kernels from overlapping their neighbours and every bracket includes the gap before its
@@ -537,10 +538,15 @@ def run_kernel_times(args) -> int:
     from flyweight_b200.engine.runtime import Model
     from flyweight_b200.kernels import lib as kernel_lib
     from flyweight_b200.sampling import sampler
-    model = Model.random(dict(LFM2_1P2B), seed=0, dtype="bfloat16", device="cuda:0").module
-    vocab = LFM2_1P2B["vocab_size"]
+    name, _, what = args.kernel_times.rpartition(":")
+    name = name or "lfm2-1.2b"
+    if name not in MODELS or not (what in ("decode", "prefill") or what.isdigit()):
+        print(json.dumps({"error": f"--kernel-times wants [MODEL:]decode|prefill|TOKENS with MODEL in {sorted(MODELS)}"}))
+        return 1
+    config = dict(MODELS[name])
+    model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
+    vocab = config["vocab_size"]
     rng = torch.Generator().manual_seed(0)
-    what = args.kernel_times
     if what == "decode":
         total = CONTEXT + 16
         runner = ModelRunner(model, num_pages=BATCH * (-(-total // 64)), num_slots=BATCH, max_model_len=total,
@@ -576,11 +582,14 @@ def run_kernel_times(args) -> int:
     from flyweight_b200.kernels import ops
     tiny_x = torch.zeros(8, device="cuda:0")
     tiny_d = torch.zeros(8, device="cuda:0")
-    kernel_lib.profile_start()
-    for _ in range(50):
-        ops.add_(tiny_x, tiny_d)
-    gap = kernel_lib.profile_stop()["kernels"][0]
-    overhead = gap["us"] / gap["calls"]
+    rounds = []
+    for _ in range(7):                   # the least of several rounds: a stall of the host inflates a round
+        kernel_lib.profile_start()
+        for _ in range(20):
+            ops.add_(tiny_x, tiny_d)
+        gap = kernel_lib.profile_stop()["kernels"][0]
+        rounds.append(gap["us"] / gap["calls"])
+    overhead = min(rounds)
     net_total = 0.0
     for entry in report["kernels"]:
         entry["net_us"] = round(max(0.0, entry["us"] - overhead * entry["launches"]), 2)
@@ -588,7 +597,7 @@ def run_kernel_times(args) -> int:
     for entry in report["kernels"]:
         entry["net_share"] = round(entry["net_us"] / (net_total or 1.0), 4)
     report["kernels"].sort(key=lambda entry: -entry["net_us"])
-    report.update({"kernel_times": what, "tokens": tokens, "bracket_overhead_us": round(overhead, 2),
+    report.update({"kernel_times": what, "model": name, "tokens": tokens, "bracket_overhead_us": round(overhead, 2),
                    "net_device_us": round(net_total, 1),
                    "step_us_unbracketed": round(1e3 * start.elapsed_time(stop), 1)})
     print(json.dumps(report))
@@ -625,7 +634,7 @@ def main() -> int:
     parser.add_argument("--mixed", default=None, metavar="MODEL",
                         help="64 requests, prompts of 128 to 8,192 tokens in portions of 512 beside decoding "
                              "requests, 256 new tokens each, through the public runtime (e.g. lfm2-350m)")
-    parser.add_argument("--kernel-times", default=None, metavar="decode|prefill|TOKENS",
+    parser.add_argument("--kernel-times", default=None, metavar="[MODEL:]decode|prefill|TOKENS",
                         help="one step with CUDA events around every launch: time per kernel as JSON")
     args = parser.parse_args()
     if args.gpus != 1:
