@@ -356,10 +356,13 @@ def run_sizes(args) -> int:
         timed = time_decode(model, batch, context, args.steps, args.warmup, config["vocab_size"])
         step_bytes = model.weight_bytes(with_embedding_rows=batch) + batch * context * kv_bytes_per_token(model)
         achieved = step_bytes / (timed["ms_per_step"] / 1e3) / 1e9
+        # the same point through the public runtime, host tokens in and out every step
+        e2e = time_e2e(model, batch, context, args.steps, args.warmup, config["vocab_size"])
         print(json.dumps({"sizes": True, "model": name, "parameters": model.parameter_count(),
                           "batch": batch, "context": context, "ms_per_step": timed["ms_per_step"],
                           "tokens_per_s": timed["tokens_per_s"], "bytes_per_step": step_bytes,
-                          "hbm_gbs": achieved, "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"]}),
+                          "hbm_gbs": achieved, "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"],
+                          "e2e_tokens_per_s": e2e["value"], "e2e_ms_per_step": e2e["ms_per_step"]}),
               flush=True)
     return 0
 
@@ -540,20 +543,26 @@ def run_kernel_times(args) -> int:
     from flyweight_b200.sampling import sampler
     name, _, what = args.kernel_times.rpartition(":")
     name = name or "lfm2-1.2b"
+    batch, context = BATCH, CONTEXT
+    if what.startswith("decode@"):                    # decode@BATCHxCONTEXT
+        shape = what[len("decode@"):].split("x")
+        if len(shape) == 2 and all(part.isdigit() for part in shape):
+            batch, context, what = int(shape[0]), int(shape[1]), "decode"
     if name not in MODELS or not (what in ("decode", "prefill") or what.isdigit()):
-        print(json.dumps({"error": f"--kernel-times wants [MODEL:]decode|prefill|TOKENS with MODEL in {sorted(MODELS)}"}))
+        print(json.dumps({"error": "--kernel-times wants [MODEL:]decode|decode@BATCHxCONTEXT|prefill|TOKENS "
+                                   f"with MODEL in {sorted(MODELS)}"}))
         return 1
     config = dict(MODELS[name])
     model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
     vocab = config["vocab_size"]
     rng = torch.Generator().manual_seed(0)
     if what == "decode":
-        total = CONTEXT + 16
-        runner = ModelRunner(model, num_pages=BATCH * (-(-total // 64)), num_slots=BATCH, max_model_len=total,
+        total = context + 16
+        runner = ModelRunner(model, num_pages=batch * (-(-total // 64)), num_slots=batch, max_model_len=total,
                              max_batched_tokens=2048, use_graphs=False, use_plan=False)
-        requests = [f"b{i}" for i in range(BATCH)]
-        fill_context(runner, requests, CONTEXT, vocab, rng)
-        tokens = BATCH
+        requests = [f"b{i}" for i in range(batch)]
+        fill_context(runner, requests, context, vocab, rng)
+        tokens = batch
 
         def step():
             sampler.argmax(runner.step([(r, [7], [0]) for r in requests]))
@@ -634,7 +643,7 @@ def main() -> int:
     parser.add_argument("--mixed", default=None, metavar="MODEL",
                         help="64 requests, prompts of 128 to 8,192 tokens in portions of 512 beside decoding "
                              "requests, 256 new tokens each, through the public runtime (e.g. lfm2-350m)")
-    parser.add_argument("--kernel-times", default=None, metavar="[MODEL:]decode|prefill|TOKENS",
+    parser.add_argument("--kernel-times", default=None, metavar="[MODEL:]decode[@BATCHxCONTEXT]|prefill|TOKENS",
                         help="one step with CUDA events around every launch: time per kernel as JSON")
     args = parser.parse_args()
     if args.gpus != 1:

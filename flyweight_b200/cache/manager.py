@@ -145,6 +145,7 @@ class CacheManager:
             elif spec is not None:
                 raise TypeError(f"schedule position {position}: unknown state spec {spec!r}")
             self.layer_caches.append(cache)
+        self._windowed = any(group.window for group in self.groups)
         self._rows: List[Dict[Hashable, tuple]] = [{} for _ in self.groups]   # block-table rows as arrays
         # All fixed-size states of one dtype lie side by side in one allocation, [num_slots][total],
         # and every execution sees its share as [num_slots][...]: admission clears one span per dtype.
@@ -253,6 +254,25 @@ class CacheManager:
             while len(table) * PAGE_SIZE < new_length:
                 table.append(group.pool.allocate())
         self._length[request] = new_length
+
+    def fits_last_page(self, request: Hashable) -> bool:
+        """Whether one more token of a live ``request`` needs no new page in any group and gives
+        none back: its next position lies inside its last mapped page, and no group has a window
+        (the short way for the hundreds of one-token entries of a decode step)."""
+        return not self._windowed and self._length[request] % PAGE_SIZE != 0
+
+    def grow(self, request: Hashable, count: int) -> Tuple[int, int]:
+        """``extend`` by ``count`` tokens for a caller that has checked the pages; returns the
+        request's state slot and its length before."""
+        length = self._length[request]
+        new_length = length + count
+        if count != 1 or length % PAGE_SIZE == 0:
+            for group in self.groups:
+                table = group.tables[request]
+                while len(table) * PAGE_SIZE < new_length:
+                    table.append(group.pool.allocate())
+        self._length[request] = new_length
+        return self._slot_of[request], length
 
     def bump(self, request: Hashable) -> None:
         """One more token of ``request`` inside its last mapped page (the caller has checked)."""

@@ -643,6 +643,19 @@ FWB_API int fwb_gemm_tcgen05_status() {
     return value;
 }
 
+// The two words a health check reads -- the status word above (not cleared here) and the
+// embedding's bad-token flag -- copied to pinned host memory behind the work queued on `stream`,
+// so that a caller who waits for that work anyway learns of a failure without a wait of its own.
+FWB_API int fwb_health_peek_async(int* pinned_host, const int* bad_token_flag, cudaStream_t stream) {
+    int* word = status_word();
+    if (!word || !pinned_host) return FWB_BAD_ARGUMENT;
+    pinned_host[1] = 0;
+    cudaError_t e = cudaMemcpyAsync(pinned_host, word, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess && bad_token_flag)
+        e = cudaMemcpyAsync(pinned_host + 1, bad_token_flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    return e == cudaSuccess ? FWB_OK : (int)e;
+}
+
 namespace {
 // One thread waits, with a short limit, on a barrier that nobody will ever arrive on: the wait
 // must give up, leave its code in the status word and let the kernel end normally.

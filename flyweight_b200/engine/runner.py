@@ -106,6 +106,8 @@ class StepPlanner:
         needs = [0] * len(cache.groups)
         for request, tokens, _ in entries:
             try:
+                if len(tokens) == 1 and cache.has(request) and cache.fits_last_page(request):
+                    continue                        # a decoding request inside its last page
                 have = 0
                 if cache.has(request):
                     cache.release_passed(request)
@@ -119,26 +121,50 @@ class StepPlanner:
         return sum(max(0, need - group.pool.n_free) for need, group in zip(needs, cache.groups))
 
     # ------------------------------------------------------------------ planning
-    def plan(self, entries: Sequence[Entry], pages_checked: bool = False) -> List[Segment]:
+    def plan(self, entries: Sequence[Entry], pages_checked: bool = False,
+             own_entries: bool = False) -> List[Segment]:
         """Check the entries, admit new requests, map their pages; all or nothing: if a
         slot or a page is lacking, nothing has changed when the error is raised.
         ``pages_checked``: the caller (the scheduler) has just asked ``pages_short`` for exactly
-        these entries and got 0."""
-        entries = [(r, _token_array(r, toks), [int(w) for w in want]) for r, toks, want in entries]
-        self._check_entries(entries)
-        new = [r for r, _, _ in entries if not self.cache.has(r)]
-        if len(new) > self.cache.free_slots:
-            raise OutOfSlots(f"{len(new)} new requests but {self.cache.free_slots} free state slots")
+        these entries and got 0.  ``own_entries``: the entries were built by the engine's own
+        scheduler from token ids that were checked when the request was submitted or that its
+        sampler drew (each request once, ids inside the vocabulary, lengths inside the limits), so
+        the checks of what a caller from outside may hand in are not repeated on every step."""
+        cache = self.cache
+        if own_entries:
+            vocab = self.vocab_size
+            checked, total = [], 0
+            for request, tokens, want in entries:
+                if len(tokens) == 1:
+                    low = high = tokens[0]
+                else:
+                    tokens = _token_array(request, tokens)
+                    low, high = int(tokens.min()), int(tokens.max())
+                if low < 0 or high >= vocab:        # a text damaged after it was submitted: that request alone
+                    raise StepError(f"a token id of request {request!r} is outside [0, {vocab})", request)
+                total += len(tokens)
+                checked.append((request, tokens, want))
+            entries = checked
+            if total > self.max_batched_tokens:
+                raise StepError(f"step of {total} tokens exceeds max_batched_tokens {self.max_batched_tokens}")
+        else:
+            entries = [(r, _token_array(r, toks), [int(w) for w in want]) for r, toks, want in entries]
+            self._check_entries(entries)
+        new = 0
+        for entry in entries:
+            if not cache.has(entry[0]):
+                new += 1
+        if new > cache.free_slots:
+            raise OutOfSlots(f"{new} new requests but {cache.free_slots} free state slots")
         short = 0 if pages_checked else self.pages_short(entries)
         if short:
             raise OutOfPages(f"this step needs {short} more cache pages than are free")
         segments: List[Segment] = []
         for request, tokens, want in entries:
-            if not self.cache.has(request):
-                self.cache.admit(request)
-            pos0 = self.cache.length(request)
-            self.cache.extend(request, pos0 + len(tokens), checked=True)
-            segments.append(Segment(request, self.cache.slot(request), pos0, tokens, want))
+            if new and not cache.has(request):
+                cache.admit(request)
+            slot, pos0 = cache.grow(request, len(tokens))
+            segments.append(Segment(request, slot, pos0, tokens, want))
         return segments
 
     def finish(self, request: Hashable) -> None:
@@ -180,13 +206,14 @@ class ModelRunner(StepPlanner):
         self.h2d_bytes = 0
 
     def step(self, entries: Sequence[Entry], pages_checked: bool = False,
-             patch_source: Optional[torch.Tensor] = None, patch: Optional[Sequence] = None) -> torch.Tensor:
-        """``patch``: (entry index, row of ``patch_source``) pairs.  The last token of those entries
+             patch_source: Optional[torch.Tensor] = None, patch: Optional[Sequence] = None,
+             own_entries: bool = False) -> torch.Tensor:
+        """``pages_checked``, ``own_entries``: see ``plan``.  ``patch``: (entry index, row of ``patch_source``) pairs.  The last token of those entries
         was sampled by the step before and has not been read by the host (the entry carries a
         placeholder id); its value is taken from ``patch_source`` (int32, on the device) there."""
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        segments = self.plan(entries, pages_checked)
+        segments = self.plan(entries, pages_checked, own_entries)
         requests = [seg.request for seg in segments]
         width = self.cache.max_table_len(requests)
         n_groups = len(self.cache.groups)

@@ -20,6 +20,7 @@ import torch
 
 from ..cache.manager import PAGE_SIZE
 from ..config.registry import load_config
+from ..kernels import lib as kernel_lib
 from ..sampling import sampler as device_sampler
 from ..sampling.config import GREEDY, SamplingConfig
 from .loading import load_model, parse_dtype, random_model
@@ -44,7 +45,8 @@ class EngineConfig:
     ``parallel_sequences``: most requests live at a time (flyweight's ``--parallel``);
     ``cache_tokens``: size of the KV pool in tokens (None: every live request at the context limit,
     plus the spare page the scheduler keeps per admission); ``max_batched_tokens``: token budget of
-    one step; ``use_graphs``: CUDA graphs for steps of single tokens; ``use_plan``: the native step
+    one step; ``max_queued``: most requests queued and running before ``task_submit`` refuses (raised to
+    ``parallel_sequences`` when that is larger); ``use_graphs``: CUDA graphs for steps of single tokens; ``use_plan``: the native step
     plan for the others; ``steady_decode`` / ``run_ahead``: the short ways of ``engine_step``."""
     context_limit: int = 4096
     parallel_sequences: int = 1
@@ -54,12 +56,19 @@ class EngineConfig:
     use_plan: bool = True
     steady_decode: bool = True
     run_ahead: bool = True
+    max_queued: int = 256          # flyweight's queue limit (native/src/v2_runtime.cpp:32588)
 
     def __post_init__(self):
         if self.context_limit <= 0 or self.parallel_sequences <= 0 or self.max_batched_tokens <= 0:
             raise ValueError("context_limit, parallel_sequences and max_batched_tokens must be positive")
         if self.cache_tokens is not None and self.cache_tokens < PAGE_SIZE:
             raise ValueError(f"cache_tokens must hold at least one page of {PAGE_SIZE} tokens")
+
+    @property
+    def queue_limit(self) -> int:
+        """Requests waiting and running together before a submit is refused: ``max_queued``, and
+        never fewer than can run side by side."""
+        return max(int(self.max_queued), self.parallel_sequences)
 
     @property
     def pool_tokens(self) -> int:
@@ -133,13 +142,15 @@ class Runtime:
                                   max_model_len=self.context_limit,
                                   max_batched_tokens=self.max_batched_tokens,
                                   use_graphs=self.config.use_graphs, use_plan=self.config.use_plan)
-        self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
+        self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit,
+                                   self.config.queue_limit)
 
     def reset(self) -> None:
         """Forget every request and give back everything the cache holds."""
         self._ahead = self._flight = None
         self.runner.cache.reset()
-        self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit)
+        self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit,
+                                   self.config.queue_limit)
 
     def close(self) -> None:
         runner, self.runner, self.scheduler = self.runner, None, None
@@ -228,7 +239,7 @@ class Runtime:
                 rows = {id(task): row for row, task in enumerate(after["tasks"])}
                 patch = [(index, rows[id(task)]) for index, task in enumerate(step.tasks) if task.in_flight]
             try:
-                logits = runner.step(step.entries, pages_checked=True,
+                logits = runner.step(step.entries, pages_checked=True, own_entries=True,
                                      patch_source=after["device"] if patch else None, patch=patch)
             except StepError as error:
                 # the step function refuses one request's entry before anything is launched or
@@ -239,9 +250,11 @@ class Runtime:
         if not step.entries:
             return None
         need = scheduler.advance(step)
-        for task in step.tasks:
-            if task not in need:
-                events.append((task.id, task.computed, EVENT_PROGRESS))
+        if len(need) != len(step.tasks):
+            sampled = {id(task) for task in need}
+            for task in step.tasks:
+                if id(task) not in sampled:
+                    events.append((task.id, task.computed, EVENT_PROGRESS))
         if not need:
             return None
         flight = self._sample_async(need, logits)
@@ -261,8 +274,8 @@ class Runtime:
             return False
         if (self.steady_decode and current.get("graph_step") and not scheduler.waiting
                 and len(current["tasks"]) == len(scheduler.running)
-                and not any(group.window for group in self.runner.cache.groups)):
-            return False
+                and self._same_requests_again() is not None):
+            return False                 # (with hundreds running, somebody needs a page every step: then not)
         return True
 
     def _sample_async(self, need, logits):
@@ -290,17 +303,14 @@ class Runtime:
         host = flight["host"].tolist()
         self._counters["d2h_bytes"] += 4 * len(host)
         self._counters["sampling_seconds"] += time.perf_counter() - sampled
+        if flight["health"][0] or flight["health"][1]:
+            self.runner.check_health()          # kernels fail loudly: raises, for the whole engine
         events: List[Tuple[int, int, int]] = []
-        finished = False
         for task, token in zip(flight["tasks"], host):
             if task.state == "finished":
                 task.in_flight = 0
                 continue
-            accepted = self._accept(task, token)
-            finished = finished or len(accepted) > 1
-            events.extend(accepted)
-        if finished:
-            self.runner.check_health()          # once per finished request: kernels fail loudly
+            events.extend(self._accept(task, token))
         return events
 
     def _sample_and_accept(self, need, logits, events) -> None:
@@ -393,12 +403,18 @@ class Runtime:
         turn = ring["turn"]
         ring["turn"] = turn ^ 1
         count = tokens.numel()
-        if ring["buffers"][turn].numel() < count:
-            ring["buffers"][turn] = torch.empty(2 * count, dtype=torch.int32).pin_memory()
-        view = ring["buffers"][turn][:count]
+        if ring["buffers"][turn].numel() < count + 2:
+            ring["buffers"][turn] = torch.empty(2 * count + 2, dtype=torch.int32).pin_memory()
+        buffer = ring["buffers"][turn]
+        view = buffer[:count]
         view.copy_(tokens, non_blocking=True)
+        # the two words of the health check ride along: a kernel that gave up, a token id outside
+        # the vocabulary -- known when the ids are read, without a wait of their own
+        kernel_lib.call("fwb_health_peek_async", buffer.data_ptr() + 4 * count,
+                        kernel_lib.ptr(self.runner.bad_token_flag), kernel_lib.stream())
         ring["events"][turn].record()
-        return {"tasks": list(tasks), "device": tokens, "host": view, "event": ring["events"][turn]}
+        return {"tasks": list(tasks), "device": tokens, "host": view, "health": buffer[count:count + 2],
+                "event": ring["events"][turn]}
 
     def _accept_async(self, step) -> List[Tuple[int, int, int]]:
         """Wait for the ids of a launched step and hand them to their requests.  A request that
@@ -409,21 +425,17 @@ class Runtime:
         host = step["host"].tolist()
         self._counters["d2h_bytes"] += 4 * len(host)
         self._counters["sampling_seconds"] += time.perf_counter() - sampled
+        if step["health"][0] or step["health"][1]:
+            self.runner.check_health()          # kernels fail loudly: raises, for the whole engine
         events: List[Tuple[int, int, int]] = []
-        finished = False
         for task in step["tasks"]:
             if task.cancelled and task.state == "running":     # cancelled while the step was in flight
                 self.scheduler._finish(task, "cancelled")
                 events.append((task.id, 0, EVENT_FINISHED))
-                finished = True
         for task, token in zip(step["tasks"], host):
             if task.state != "running":
                 continue
-            accepted = self._accept(task, token)
-            finished = finished or len(accepted) > 1
-            events.extend(accepted)
-        if finished:
-            self.runner.check_health()
+            events.extend(self._accept(task, token))
         return events
 
     def _same_requests_again(self):

@@ -101,10 +101,12 @@ class ScheduledStep:
 
 
 class Scheduler:
-    def __init__(self, planner, max_batched_tokens: int, max_model_len: int):
+    def __init__(self, planner, max_batched_tokens: int, max_model_len: int, max_queued: int = MAX_QUEUED):
         """``planner`` is a ``StepPlanner`` (the runner, or a device-free stand-in): the
-        scheduler asks it how many pages a step lacks and tells it when a request ends."""
+        scheduler asks it how many pages a step lacks and tells it when a request ends.
+        ``max_queued``: most requests waiting and running together before ``submit`` refuses."""
         self.planner = planner
+        self.max_queued = int(max_queued)
         self.cache = planner.cache
         self.max_batched_tokens = int(max_batched_tokens)
         self.max_model_len = int(max_model_len)
@@ -135,7 +137,7 @@ class Scheduler:
         for token in prompt:
             if not 0 <= token < vocab:
                 raise ValueError(f"token id {token} is outside [0, {vocab})")
-        if len(self.waiting) + len(self.running) >= MAX_QUEUED:
+        if len(self.waiting) + len(self.running) >= self.max_queued:
             raise QueueFull("the engine queue is full")
         sampling = sampling or SamplingConfig()
         task = Task(self._next_id, prompt, int(max_tokens), tuple(int(t) for t in stop_tokens),
@@ -235,21 +237,38 @@ class Scheduler:
         budget = self.max_batched_tokens
         chosen: List[Task] = []
         entries = []
-        for decoding in (True, False):
-            for task in list(self.running):
-                if (task.pending == 1) != decoding or budget <= 0 or task in chosen:
-                    continue
-                if task.in_flight and task.ends_with_the_token_in_flight(self.max_model_len):
+        # the running requests in two turns: those that decode (one token each) first, then the
+        # portions of prompts; a request's pending count is taken once (hundreds may be running)
+        decoding, reading = [], []
+        for task in self.running:
+            (decoding if task.pending == 1 else reading).append(task)
+        max_model_len = self.max_model_len
+        for task in decoding:
+            if budget <= 0:
+                break
+            if task.in_flight:
+                if task.ends_with_the_token_in_flight(max_model_len):
                     continue                        # it ends when that token is read: nothing more to run
-                try:
-                    entry = self._portion(task, budget)
-                except Exception as error:
-                    step.events.extend(self.fail(task, f"{type(error).__name__}: {error}"))
-                    step.failed.append(task.id)
-                    continue
-                budget -= len(entry[1])
-                chosen.append(task)
-                entries.append(entry)
+                token = IN_FLIGHT
+            else:
+                token = task.generated[-1] if task.generated else task.prompt[-1]
+            budget -= 1
+            chosen.append(task)
+            entries.append((task.id, [token], [0]))
+        for task in reading:
+            if budget <= 0:
+                break
+            if task.in_flight and task.ends_with_the_token_in_flight(max_model_len):
+                continue
+            try:
+                entry = self._portion(task, budget)
+            except Exception as error:
+                step.events.extend(self.fail(task, f"{type(error).__name__}: {error}"))
+                step.failed.append(task.id)
+                continue
+            budget -= len(entry[1])
+            chosen.append(task)
+            entries.append(entry)
         # make the step of the running requests fit, preempting the newest if it does not
         while entries and self._pages_short(entries, chosen, step):
             victim = max(self.running, key=lambda t: t.admitted_at)
@@ -265,8 +284,8 @@ class Scheduler:
                 budget += len(entries[index][1])
                 del chosen[index], entries[index]
         # admit waiting requests, first come first served
-        while self.waiting and budget > 0 and self.cache.free_slots > len(
-                [t for t in chosen if t.state == "waiting"]):
+        admitting = 0                                   # requests of this step that take a slot when it runs
+        while self.waiting and budget > 0 and self.cache.free_slots > admitting:
             task = self.waiting[0]
             if step.preempted and task.id in step.preempted:
                 break                                   # just evicted: not in the same step
@@ -290,6 +309,7 @@ class Scheduler:
             self.waiting.popleft()
             chosen.append(task)
             entries.append(entry)
+            admitting += 1
         for task in chosen:
             if task.state == "waiting":
                 task.state = "running"

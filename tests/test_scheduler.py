@@ -258,3 +258,24 @@ def test_the_default_pool_runs_two_requests_that_fill_the_context_side_by_side()
     assert all(len(sched.tasks[i].generated) == 56 for i in ids) and sched.stats["preemptions"] == 0
     with pytest.raises(ValueError):
         EngineConfig(context_limit=0)
+
+
+def test_the_queue_refuses_past_its_limit_and_the_limit_follows_the_parallel_sequences():
+    from flyweight_b200.engine.runtime import EngineConfig
+    from flyweight_b200.engine.scheduler import QueueFull
+    cache = CacheManager([PagedKV(1, 16), FixedState((4, 2))], 8, 4, device=None)
+    planner = StepPlanner(cache, VOCAB, 512, 32)
+    sched = Scheduler(planner, 32, 512, max_queued=3)
+    for _ in range(3):
+        sched.submit([1, 2, 3], 4)
+    with pytest.raises(QueueFull):
+        sched.submit([1, 2, 3], 4)
+    run_step(sched, planner)                      # nothing finished: still full
+    with pytest.raises(QueueFull):
+        sched.submit([1], 1)
+    while sched.has_work():
+        run_step(sched, planner)
+    sched.submit([1], 1)                          # room again
+    assert EngineConfig().queue_limit == 256      # native/src/v2_runtime.cpp:32588
+    assert EngineConfig(parallel_sequences=512).queue_limit == 512
+    assert EngineConfig(parallel_sequences=4, max_queued=16).queue_limit == 16
