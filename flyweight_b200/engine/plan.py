@@ -357,8 +357,23 @@ class StepPlan:
         seg_start = flat[o[3]:o[3] + S + 1]
         logit_rows = flat[o[6]:o[6] + R]
         seg_start[0] = 0
+        first_tokens = [seg.pos0 for seg in segments]
         base = row = 0
-        for index, (seg, n) in enumerate(zip(segments, lengths)):
+        if leading:
+            # the decoding requests at the head of the step (hundreds, in a large batch): whole
+            # columns at once instead of element by element
+            heads = segments[:leading]
+            ids[:leading] = [seg.tokens[0] for seg in heads]
+            positions[:leading] = first_tokens[:leading]
+            counting = np.arange(leading + 1, dtype=np.int32)
+            tok_seg[:leading] = counting[:leading]
+            seg_start[1:leading + 1] = counting[1:]
+            wanted = [index for index, seg in enumerate(heads) if seg.want]    # of one token: [] or [0]
+            row = len(wanted)
+            logit_rows[:row] = wanted
+            base = leading
+        for index in range(leading, S):
+            seg, n = segments[index], lengths[index]
             if n == 1:
                 ids[base] = seg.tokens[0]
                 positions[base] = seg.pos0
@@ -373,7 +388,7 @@ class StepPlan:
             base += n
             seg_start[index + 1] = base
         flat[o[4]:o[4] + S] = [seg.slot for seg in segments]
-        flat[o[5]:o[5] + S] = [seg.pos0 for seg in segments]
+        flat[o[5]:o[5] + S] = first_tokens
         for k, (seg_of, tok0) in enumerate(tiles):
             n = seg_of.size
             flat[o[7 + 2 * k]:o[7 + 2 * k] + n] = seg_of

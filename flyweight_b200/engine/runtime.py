@@ -269,8 +269,7 @@ class Runtime:
         if not self.run_ahead:
             return False
         scheduler = self.scheduler
-        if any(task.sampling.penalizes for task in scheduler.running) or \
-                any(task.sampling.penalizes for task in scheduler.waiting):
+        if scheduler.penalizing:
             return False
         if (self.steady_decode and current.get("graph_step") and not scheduler.waiting
                 and len(current["tasks"]) == len(scheduler.running)
@@ -283,10 +282,10 @@ class Runtime:
         nobody waits here.  The requests' tokens are in flight from now until ``_accept_flight``."""
         if self.logits_observer is not None:
             self.logits_observer(need, logits)
-        if all(task.sampling.greedy for task in need):
+        if all(task.greedy for task in need):
             tokens = device_sampler.argmax(logits)
         else:
-            uniforms = [0.0 if task.sampling.greedy else task.rng.uniform() for task in need]
+            uniforms = [0.0 if task.greedy else task.rng.uniform() for task in need]
             tokens = device_sampler.sample(logits, [task.sampling for task in need], uniforms,
                                            [task.generated for task in need])
         flight = self._queue_read(need, tokens)
@@ -317,10 +316,10 @@ class Runtime:
         sampled = time.perf_counter()
         if self.logits_observer is not None:
             self.logits_observer(need, logits)
-        if all(task.sampling.greedy for task in need):
+        if all(task.greedy for task in need):
             tokens = device_sampler.argmax(logits)
         else:
-            uniforms = [0.0 if task.sampling.greedy else task.rng.uniform() for task in need]
+            uniforms = [0.0 if task.greedy else task.rng.uniform() for task in need]
             tokens = device_sampler.sample(logits, [task.sampling for task in need], uniforms,
                                            [task.generated for task in need])
         host = self._read_tokens(tokens)              # the step's only device->host read
@@ -358,7 +357,7 @@ class Runtime:
                 return None
             logits = self.runner.step_same_requests([task.generated[-1] for task in need])
             self.scheduler.advance_decode(need)
-            if not (self.run_ahead and all(task.sampling.greedy for task in need)):
+            if not (self.run_ahead and all(task.greedy for task in need)):
                 events = []
                 self._sample_and_accept(need, logits, events)
                 return events

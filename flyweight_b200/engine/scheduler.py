@@ -58,6 +58,12 @@ class Task:
     preemptions: int = 0
     admitted_at: int = -1          # admission counter value (larger = admitted later)
     in_flight: int = 0             # 1: its next token is sampled on the device but not read yet
+    greedy: bool = field(init=False, default=True)       # of its sampling settings, read once: they
+    penalizes: bool = field(init=False, default=False)   # are asked of every running task on every step
+
+    def __post_init__(self):
+        self.greedy = bool(self.sampling.greedy)
+        self.penalizes = bool(self.sampling.penalizes)
 
     @property
     def text(self) -> List[int]:
@@ -117,6 +123,7 @@ class Scheduler:
         self._admissions = 0
         self.stats = {"preemptions": 0, "admitted": 0, "finished": 0, "failed": 0,
                       "prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
+        self.penalizing = 0         # live tasks (waiting or running) whose sampling has a penalty
 
     # ------------------------------------------------------------------ submit / cancel
     def submit(self, prompt: Sequence[int], max_tokens: int, stop_tokens: Sequence[int] = (),
@@ -145,6 +152,7 @@ class Scheduler:
         self._next_id += 1
         self.tasks[task.id] = task
         self.waiting.append(task)
+        self.penalizing += task.penalizes
         return task.id
 
     def cancel(self, task_id: int) -> None:
@@ -162,6 +170,8 @@ class Scheduler:
             self.planner.finish(task.id)
         elif task.state == "waiting" and task in self.waiting:
             self.waiting.remove(task)
+        if task.state != "finished":
+            self.penalizing -= task.penalizes
         task.state = "finished"
         task.finish_reason = reason
         task.error = error
@@ -180,6 +190,8 @@ class Scheduler:
                 self.running.remove(task)
             if task in self.waiting:
                 self.waiting.remove(task)
+            if task.state != "finished":
+                self.penalizing -= task.penalizes
             task.state, task.finish_reason = "finished", "error"
             task.error = f"{message}; while giving back what it held: {error}"
             self.stats["failed"] += 1
@@ -239,19 +251,22 @@ class Scheduler:
         entries = []
         # the running requests in two turns: those that decode (one token each) first, then the
         # portions of prompts; a request's pending count is taken once (hundreds may be running)
-        decoding, reading = [], []
-        for task in self.running:
-            (decoding if task.pending == 1 else reading).append(task)
+        reading = []
         max_model_len = self.max_model_len
-        for task in decoding:
+        for task in self.running:
+            generated = task.generated
+            known = len(task.prompt) + len(generated) + task.in_flight
+            if known - task.computed != 1:           # (its ``pending``, spelt out: this loop is the hot one)
+                reading.append(task)
+                continue
             if budget <= 0:
-                break
+                continue
             if task.in_flight:
-                if task.ends_with_the_token_in_flight(max_model_len):
+                if len(generated) + 1 >= task.max_tokens or known >= max_model_len:
                     continue                        # it ends when that token is read: nothing more to run
                 token = IN_FLIGHT
             else:
-                token = task.generated[-1] if task.generated else task.prompt[-1]
+                token = generated[-1] if generated else task.prompt[-1]
             budget -= 1
             chosen.append(task)
             entries.append((task.id, [token], [0]))
@@ -348,12 +363,13 @@ class Scheduler:
         """A sampled token for ``task``: emit it, then finish on a stop token, on
         ``max_tokens`` or at the context limit (emit-then-stop order of
         native/src/v2_runtime.cpp:33775-33780)."""
-        task.generated.append(int(token))
+        token = int(token)
+        task.generated.append(token)
         if task.in_flight:
             task.in_flight -= 1
-        events = [(task.id, int(token), EVENT_TOKEN)]
+        events = [(task.id, token, EVENT_TOKEN)]
         reason = None
-        if int(token) in task.stop_tokens:
+        if token in task.stop_tokens:
             reason = "stop"
         elif len(task.generated) >= task.max_tokens:
             reason = "length"
