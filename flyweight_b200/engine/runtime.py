@@ -127,6 +127,7 @@ class Runtime:
         self._ahead = None                 # a decode step already launched whose tokens were not read yet
         self._flight = None                # the same for a step of any kind (the pipelined way)
         self._token_ring = None            # pinned buffers for the sampled ids of two steps in flight
+        self._health_due, self._steps_unchecked = True, 0
         # tracing hook: called as observer(tasks, logits) with the fp32 logits [len(tasks)][vocab]
         # every time tokens are about to be sampled from them (the tensor is overwritten by the
         # next step: copy what is to be kept)
@@ -310,6 +311,8 @@ class Runtime:
                 task.in_flight = 0
                 continue
             events.extend(self._accept(task, token))
+        if len(events) != len(host):
+            self._health_due = True             # somebody ended (or had ended): look at the next step's words
         return events
 
     def _sample_and_accept(self, need, logits, events) -> None:
@@ -407,10 +410,16 @@ class Runtime:
         buffer = ring["buffers"][turn]
         view = buffer[:count]
         view.copy_(tokens, non_blocking=True)
-        # the two words of the health check ride along: a kernel that gave up, a token id outside
-        # the vocabulary -- known when the ids are read, without a wait of their own
-        kernel_lib.call("fwb_health_peek_async", buffer.data_ptr() + 4 * count,
-                        kernel_lib.ptr(self.runner.bad_token_flag), kernel_lib.stream())
+        # The two words of the health check (a kernel that gave up, a token id outside the
+        # vocabulary) ride along behind the ids, so that a failure is known when the ids are read,
+        # without a wait of its own: after every step in which a request ended, and every 32nd step
+        # (two small copies more would cost a decode step of eight requests 2 % of its time).
+        buffer[count] = buffer[count + 1] = 0
+        self._steps_unchecked += 1
+        if self._health_due or self._steps_unchecked >= 32:
+            self._health_due, self._steps_unchecked = False, 0
+            kernel_lib.call("fwb_health_peek_async", buffer.data_ptr() + 4 * count,
+                            kernel_lib.ptr(self.runner.bad_token_flag), kernel_lib.stream())
         ring["events"][turn].record()
         return {"tasks": list(tasks), "device": tokens, "host": view, "health": buffer[count:count + 2],
                 "event": ring["events"][turn]}
@@ -435,6 +444,8 @@ class Runtime:
             if task.state != "running":
                 continue
             events.extend(self._accept(task, token))
+        if len(events) != len(host):
+            self._health_due = True
         return events
 
     def _same_requests_again(self):
