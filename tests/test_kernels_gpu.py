@@ -223,6 +223,39 @@ def test_shortconv_prompt_sized_bfloat16(H, L, bias):
     assert torch.equal(torch.cat(parts), z) and torch.equal(sd2, sd)
 
 
+@pytest.mark.parametrize("n_requests,H,L,bias", [(300, 64, 3, True), (40, 72, 4, False), (257, 40, 2, True),
+                                                 (300, 48, 5, False)])
+def test_shortconv_of_hundreds_of_decoding_requests(n_requests, H, L, bias):
+    """A decode step of a large batch: every segment one token, every one with a slot of its own, in
+    an order that is not the slots' (all the work is at the segments' heads)."""
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(n_requests + H)
+    slots = torch.randperm(n_requests + 3, generator=g)[:n_requests].tolist()
+    segments = [(slot, 1) for slot in slots]
+    p = torch.randn(n_requests, 3 * H, generator=g).to(torch.bfloat16)
+    taps = torch.randn(H, L, generator=g)
+    b = torch.randn(H, generator=g) if bias else None
+    state = torch.randn(n_requests + 3, H, L - 1, generator=g)
+    seg_start = torch.arange(n_requests + 1, dtype=torch.int32)
+    seg_slot = torch.tensor(slots, dtype=torch.int32)
+    tok_seg = torch.arange(n_requests, dtype=torch.int32)
+    want_z, want_state = conv_reference(p, taps, b, state, segments)
+    sd = dev(state)
+    z = ops.shortconv(dev(p), dev(taps), None if b is None else dev(b), sd, dev(seg_start),
+                      dev(seg_slot), dev(tok_seg), n_requests, torch.bfloat16)
+    close(z, want_z, 2.0 ** -7, "conv output")
+    close(sd, want_state, 1e-6, "conv state")
+    # the same step in two halves (fewer than 256 tokens each: the other kernel) gives the same bits
+    sd2 = dev(state)
+    half = n_requests // 2
+    parts = []
+    for lo, hi in ((0, half), (half, n_requests)):
+        parts.append(ops.shortconv(dev(p[lo:hi]), dev(taps), None if b is None else dev(b), sd2,
+                                   dev(torch.arange(hi - lo + 1, dtype=torch.int32)), dev(seg_slot[lo:hi]),
+                                   dev(torch.arange(hi - lo, dtype=torch.int32)), hi - lo, torch.bfloat16))
+    assert torch.equal(torch.cat(parts), z) and torch.equal(sd2, sd)
+
+
 @pytest.mark.parametrize("T", [1, 2, 3])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_shortconv_of_one_two_and_three_tokens_stays_inside_its_buffers(T, dtype, guard_bands):
