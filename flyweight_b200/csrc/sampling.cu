@@ -226,7 +226,9 @@ __device__ int draw_sorted(const unsigned long long* keys, int n, const RowParam
 // whatever the order of addition: the draw is reproducible.  Against the sequential double sums
 // of the definition the kept prefix and the drawn token can differ only when a threshold falls
 // within ~2^-40 of the boundary between two candidates.
-constexpr int CLUSTER = 8;
+// CLUSTER (8, 4, 2 or 1) is chosen on the host by the number of rows: eight CTAs a row answer a
+// few rows soonest; with hundreds of rows the clusters would queue for the SMs in many rounds, each
+// bound by its barriers, and fewer CTAs a row keep every row in flight at once.
 constexpr int CTA_THREADS = 512;
 constexpr int CTA_WARPS = CTA_THREADS / 32;
 constexpr double MASS_ONE = 1099511627776.0;     // 2^40
@@ -271,7 +273,7 @@ struct Shared {
 };
 
 // Sum (or maximum) over the cluster of one value per thread.
-template <bool MAXIMUM>
+template <int CLUSTER, bool MAXIMUM>
 __device__ unsigned long long cluster_reduce(unsigned long long v, Shared& sh) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -309,7 +311,7 @@ __device__ unsigned long long cluster_reduce(unsigned long long v, Shared& sh) {
 
 // Calls f(logit, index, mass) for every element of the row this CTA owns: groups of four logits
 // (one 16-byte load, several loads in flight), dealt round robin to the CTAs of the cluster.
-template <bool WITH_MASS, typename F>
+template <int CLUSTER, bool WITH_MASS, typename F>
 __device__ __forceinline__ void sweep(const float* __restrict__ row, const unsigned long long* __restrict__ mass,
                                       int V, unsigned rank, F f) {
     const bool vectorised = (reinterpret_cast<uintptr_t>(row) & 15) == 0 &&
@@ -335,7 +337,7 @@ __device__ __forceinline__ void sweep(const float* __restrict__ row, const unsig
 // The largest key x among the row's members with weight{members > x} < target <= weight{members >= x}.
 // Members: keys >= low_cut whose mass is >= floor_mass; COUNT: every member weighs 1 (mass unused).
 // 1 <= target <= the members' weight.  Every CTA of the cluster returns the same key.
-template <bool COUNT>
+template <int CLUSTER, bool COUNT>
 __device__ unsigned long long descend(const float* __restrict__ row, int V, const unsigned long long* __restrict__ mass,
                                       unsigned long long low_cut, unsigned long long floor_mass,
                                       unsigned long long target, unsigned rank, Shared& sh) {
@@ -362,7 +364,7 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
         int held[4] = {-1, -1, -1, -1};
         unsigned long long sums[4] = {0ull, 0ull, 0ull, 0ull};
         int victim = 0;
-        sweep<!COUNT>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
+        sweep<CLUSTER, !COUNT>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
             const unsigned long long key = make_key(logit, i);
             if ((key & mask) != prefix || key < low_cut) return;
             if (COUNT) m = 1ull;
@@ -470,6 +472,7 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
 
 // Grid (CLUSTER, R), cluster (CLUSTER, 1, 1).  mass_all: [R][Vpad] 64-bit words of scratch, needed
 // by rows with more than SMALL_K candidates (null: such rows are refused on the host).
+template <int CLUSTER>
 __global__ void __launch_bounds__(CTA_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams* __restrict__ params,
               const double* __restrict__ uniform, const int* __restrict__ recent, int recent_stride,
@@ -493,11 +496,11 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
                            prm.frequency_penalty != 0.0f);
 
     unsigned long long best = 0ull;
-    sweep<false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+    sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
         const unsigned long long key = make_key(logit, i);
         best = key > best ? key : best;
     });
-    best = cluster_reduce<true>(best, sh);
+    best = cluster_reduce<CLUSTER, true>(best, sh);
     if ((!(prm.temperature > 0.0f) && !penalize) || k == 1) {
         if (rank == 0 && threadIdx.x == 0) out[r] = key_id(best);
         cluster_barrier();                          // no CTA leaves while a peer still reads its shared memory
@@ -506,14 +509,14 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
 
     if (k <= SMALL_K) {
         // the candidates are the k largest keys: find the k-th, gather them in rank 0, sort, draw
-        const unsigned long long kth = descend<true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k, rank, sh);
+        const unsigned long long kth = descend<CLUSTER, true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k, rank, sh);
         if (rank == 0) {
             for (int i = threadIdx.x; i < SMALL_K; i += CTA_THREADS) keys[i] = 0ull;
             if (threadIdx.x == 0) sh.count = 0u;
         }
         cluster_barrier();
         const unsigned keys_at_0 = peer_address(keys, 0), count_at_0 = peer_address(&sh.count, 0);
-        sweep<false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+        sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
             const unsigned long long key = make_key(logit, i);
             if (key < kth) return;                  // keys are distinct: exactly k keys pass
             unsigned at;
@@ -555,11 +558,11 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
     // more than SMALL_K candidates (the whole vocabulary among them): no sort at all
     unsigned long long* mass = mass_all + (size_t)r * Vpad;
     unsigned long long low_cut = 0ull;
-    if (k < V) low_cut = descend<true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k, rank, sh);
+    if (k < V) low_cut = descend<CLUSTER, true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k, rank, sh);
     const double t = (double)prm.temperature;
     const double maximum = (double)key_logit(best) / t;
     unsigned long long mine = 0ull;
-    sweep<false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+    sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
         unsigned long long m = 0ull;
         if (make_key(logit, i) >= low_cut) {
             const double scaled = (double)logit / t;
@@ -569,25 +572,25 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
         mass[i] = m;                                // read again only by this CTA, in the same order
         mine += m;
     });
-    const unsigned long long total = cluster_reduce<false>(mine, sh);     // >= 2^40: the first candidate weighs 1
+    const unsigned long long total = cluster_reduce<CLUSTER, false>(mine, sh);     // >= 2^40: the first candidate weighs 1
     if (prm.top_p < 1.0f) {
         // the shortest prefix whose mass reaches top_p of the total
         unsigned long long target = (unsigned long long)ceil((double)prm.top_p * (double)total);
         target = target < 1ull ? 1ull : (target > total ? total : target);
-        const unsigned long long cut = descend<false>(row, V, mass, low_cut, 0ull, target, rank, sh);
+        const unsigned long long cut = descend<CLUSTER, false>(row, V, mass, low_cut, 0ull, target, rank, sh);
         low_cut = cut > low_cut ? cut : low_cut;
     }
     // min_p: of that prefix, the candidates that weigh at least min_p of the first
     unsigned long long floor_mass = 0ull;
     if (prm.min_p > 0.0f) floor_mass = (unsigned long long)ceil((double)prm.min_p * MASS_ONE);
     unsigned long long kept_mine = 0ull;
-    sweep<true>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
+    sweep<CLUSTER, true>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
         if (make_key(logit, i) >= low_cut && m >= floor_mass) kept_mine += m;
     });
-    const unsigned long long kept = cluster_reduce<false>(kept_mine, sh);
+    const unsigned long long kept = cluster_reduce<CLUSTER, false>(kept_mine, sh);
     unsigned long long target = (unsigned long long)ceil(uniform[r] * (double)kept);
     target = target < 1ull ? 1ull : (target > kept ? kept : target);
-    const unsigned long long drawn = descend<false>(row, V, mass, low_cut, floor_mass, target, rank, sh);
+    const unsigned long long drawn = descend<CLUSTER, false>(row, V, mass, low_cut, floor_mass, target, rank, sh);
     if (rank == 0 && threadIdx.x == 0) out[r] = key_id(drawn);
     cluster_barrier();                              // no CTA leaves while a peer still reads its shared memory
 }
@@ -642,25 +645,16 @@ FWB_API int fwb_argmax(const float* logits, int R, int V, int* out, void* partia
     return fwb_launch_status();
 }
 
-// params: [R] records of 8 x 4 bytes {temperature f32, top_k i32, top_p f32, min_p f32,
-// repetition f32, presence f32, frequency f32, n_recent i32}; uniform: [R] doubles in [0,1);
-// recent: [R][recent_stride] token ids (only the first n_recent of a row are read).
-// keys_scratch: [R][Vpad] 64-bit words, needed only if some row keeps more than 1024 candidates
-// (`need_large`); probs_scratch is not used any more.
-FWB_API int fwb_sample(const float* logits, int R, int V, const void* params, const double* uniform,
-                       const int* recent, int recent_stride, int* out, void* keys_scratch,
-                       double* probs_scratch, int Vpad, int need_large, cudaStream_t stream) {
-    (void)probs_scratch;
-    if (R <= 0) return FWB_OK;
-    if (!logits || !out || !params || !uniform || V <= 0) return FWB_BAD_ARGUMENT;
-    if (recent_stride > MAX_RECENT || (recent_stride > 0 && !recent)) return FWB_BAD_ARGUMENT;
-    if (need_large && (!keys_scratch || Vpad < V)) return FWB_BAD_ARGUMENT;
-    if (V > (1 << 23)) return FWB_TOO_LARGE;      // the fixed-point masses of a row must fit 64 bits
-    if (R > 65535) return FWB_TOO_LARGE;
+namespace {
+int g_sample_cluster = 0;
+
+template <int CLUSTER>
+int launch_sample(const float* logits, int R, int V, int Vpad, const void* params, const double* uniform,
+                  const int* recent, int recent_stride, void* keys_scratch, int* out, cudaStream_t stream) {
+    auto kernel = sample_kernel<CLUSTER>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)sizeof(Shared));
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Shared));
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -678,9 +672,47 @@ FWB_API int fwb_sample(const float* logits, int R, int V, const void* params, co
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
     config.numAttrs = fwb::pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, sample_kernel, logits, V, Vpad, (const RowParams*)params, uniform,
+    cudaError_t e = cudaLaunchKernelEx(&config, kernel, logits, V, Vpad, (const RowParams*)params, uniform,
                                        recent, recent_stride, (unsigned long long*)keys_scratch, out);
     return e == cudaSuccess ? fwb_launch_status() : (int)e;
+}
+}  // namespace
+
+// params: [R] records of 8 x 4 bytes {temperature f32, top_k i32, top_p f32, min_p f32,
+// repetition f32, presence f32, frequency f32, n_recent i32}; uniform: [R] doubles in [0,1);
+// recent: [R][recent_stride] token ids (only the first n_recent of a row are read).
+// keys_scratch: [R][Vpad] 64-bit words, needed only if some row keeps more than 1024 candidates
+// (`need_large`); probs_scratch is not used any more.
+FWB_API int fwb_sample(const float* logits, int R, int V, const void* params, const double* uniform,
+                       const int* recent, int recent_stride, int* out, void* keys_scratch,
+                       double* probs_scratch, int Vpad, int need_large, cudaStream_t stream) {
+    (void)probs_scratch;
+    if (R <= 0) return FWB_OK;
+    if (!logits || !out || !params || !uniform || V <= 0) return FWB_BAD_ARGUMENT;
+    if (recent_stride > MAX_RECENT || (recent_stride > 0 && !recent)) return FWB_BAD_ARGUMENT;
+    if (need_large && (!keys_scratch || Vpad < V)) return FWB_BAD_ARGUMENT;
+    if (V > (1 << 23)) return FWB_TOO_LARGE;      // the fixed-point masses of a row must fit 64 bits
+    if (R > 65535) return FWB_TOO_LARGE;
+    // as many CTAs a row as keep all rows on the GPU at once (two CTAs fit an SM), eight at most
+    int cluster = g_sample_cluster;
+    if (cluster <= 0) {
+        cluster = 8;
+        while (cluster > 1 && (long long)R * cluster > 2 * 148) cluster >>= 1;
+    }
+    switch (cluster) {
+        case 8: return launch_sample<8>(logits, R, V, Vpad, params, uniform, recent, recent_stride, keys_scratch, out, stream);
+        case 4: return launch_sample<4>(logits, R, V, Vpad, params, uniform, recent, recent_stride, keys_scratch, out, stream);
+        case 2: return launch_sample<2>(logits, R, V, Vpad, params, uniform, recent, recent_stride, keys_scratch, out, stream);
+        default: return launch_sample<1>(logits, R, V, Vpad, params, uniform, recent, recent_stride, keys_scratch, out, stream);
+    }
+}
+
+// CTAs a row for the sampling kernel: 8, 4, 2 or 1 (0: chosen by the number of rows).  For tests
+// and measurements; every choice draws the same tokens.
+FWB_API int fwb_sample_set_cluster(int ctas) {
+    if (ctas != 0 && ctas != 1 && ctas != 2 && ctas != 4 && ctas != 8) return FWB_BAD_ARGUMENT;
+    g_sample_cluster = ctas;
+    return FWB_OK;
 }
 
 // In place on a copy of the logits that the caller owns: the penalties of every row that keeps

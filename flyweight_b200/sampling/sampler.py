@@ -70,6 +70,13 @@ def _argmax_scratch(device, n_partial: int, n_rows: int):
     return held
 
 
+def set_ctas_per_row(ctas: int) -> None:
+    """CTAs that share a row in the sampling kernel: 8, 4, 2 or 1; 0 (the default) lets the number of
+    rows decide -- eight for a few rows, fewer as rows fill the GPU by themselves.  Every choice
+    draws the same tokens (the masses are summed as integers)."""
+    lib.call("fwb_sample_set_cluster", int(ctas))
+
+
 def sample(logits: torch.Tensor, configs: Sequence[SamplingConfig], uniforms: Sequence[float],
            recents: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
     """int32 [R]: one token per row.  ``uniforms[r]`` is the number in [0, 1) row r draws

@@ -569,6 +569,35 @@ def test_sampling_equals_the_plain_sampler_draw_for_draw(V):
         assert got == want, (trial, got, want)
 
 
+@pytest.mark.parametrize("rows,V", [(3, 4099), (40, 5000), (150, 1000), (300, 65536)])
+def test_sampling_with_fewer_ctas_a_row_draws_the_same_tokens(rows, V):
+    """Eight CTAs share a row when there are few rows, four, two or one as rows fill the GPU by
+    themselves; the masses are integers, so every cut of a row gives the same sums and the same draw."""
+    from flyweight_b200.sampling import SamplingConfig, sampler
+    g = torch.Generator().manual_seed(rows + V)
+    kinds = [dict(temperature=0.8, top_k=40, top_p=0.95, min_p=0.05), dict(temperature=1.0, top_k=0, top_p=0.9, min_p=0.01),
+             dict(temperature=1.2, top_k=3000, top_p=0.8, min_p=0.0), dict(temperature=0.0, top_k=20, top_p=0.95, min_p=0.0),
+             dict(temperature=0.7, top_k=20, top_p=1.0, min_p=0.0, repetition_penalty=1.3)]
+    settings = [kinds[i % len(kinds)] for i in range(rows)]
+    logits = dev(torch.randn(rows, V, generator=g) * 3)
+    uniforms = [P.XorShift64Star(7 + i).uniform() for i in range(rows)]
+    recents = [[int(t) for t in torch.randint(0, V, (9,), generator=g)] for _ in range(rows)]
+    configs = [SamplingConfig(**s) for s in settings]
+    drawn = {}
+    try:
+        for ctas in (0, 8, 4, 2, 1):
+            sampler.set_ctas_per_row(ctas)
+            drawn[ctas] = sampler.sample(logits, configs, uniforms, recents).tolist()
+    finally:
+        sampler.set_ctas_per_row(0)
+    for ctas in (8, 4, 2, 1):
+        assert drawn[ctas] == drawn[0], f"{ctas} CTAs a row"
+    for i in range(min(rows, 12)):                        # and they are the plain sampler's
+        if "repetition_penalty" not in settings[i]:
+            want = P.sample(logits[i].cpu().numpy(), rng=P.XorShift64Star(7 + i), **settings[i])
+            assert drawn[0][i] == want, i
+
+
 def test_penalties_act_on_the_candidates():
     from flyweight_b200.sampling import SamplingConfig, sampler
     logits = torch.zeros(2, 50)
