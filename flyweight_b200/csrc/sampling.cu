@@ -230,6 +230,7 @@ __device__ int draw_sorted(const unsigned long long* keys, int n, const RowParam
 // few rows soonest; with hundreds of rows the clusters would queue for the SMs in many rounds, each
 // bound by its barriers, and fewer CTAs a row keep every row in flight at once.
 constexpr int CTA_THREADS = 512;
+constexpr int LIST_CAP = 2048;                   // shortlist entries a CTA keeps (16 KB)
 constexpr int CTA_WARPS = CTA_THREADS / 32;
 constexpr double MASS_ONE = 1099511627776.0;     // 2^40
 
@@ -270,6 +271,12 @@ struct Shared {
     unsigned long long keys[SMALL_K];              // the candidates of a top-k row (rank 0 sorts and draws)
     double probs[SMALL_K];
     unsigned count;
+    // top-k rows: once a pass has narrowed the k-th key down to a bucket with few members, this
+    // CTA's members of that bucket are kept here and the later passes walk them instead of the row
+    unsigned long long list[LIST_CAP];
+    unsigned list_count;
+    unsigned list_state;                           // 0: walking the row, 1: walking the lists, 2: a list overflowed (row again)
+    unsigned long long bucket_members;             // members of the bucket the last pass chose (cluster-wide)
 };
 
 // Sum (or maximum) over the cluster of one value per thread.
@@ -334,17 +341,51 @@ __device__ __forceinline__ void sweep(const float* __restrict__ row, const unsig
         f(row[i], i, WITH_MASS ? mass[i] : 0ull);
 }
 
+// The same walk with loops that all lanes of a warp run the same number of times: f(valid, logit,
+// index) is called by every lane in every turn (valid: the lane has an element), so f may use
+// warp-wide primitives with the full mask.
+template <int CLUSTER, typename F>
+__device__ __forceinline__ void sweep_together(const float* __restrict__ row, int V, unsigned rank, F f) {
+    const bool vectorised = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+    const int quads = vectorised ? V >> 2 : 0;
+#pragma unroll 2
+    for (int base = rank * CTA_THREADS; base < quads; base += CLUSTER * CTA_THREADS) {
+        const int qd = base + threadIdx.x;
+        const bool valid = qd < quads;
+        const float4 l4 = valid ? reinterpret_cast<const float4*>(row)[qd] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        f(valid, l4.x, 4 * qd);
+        f(valid, l4.y, 4 * qd + 1);
+        f(valid, l4.z, 4 * qd + 2);
+        f(valid, l4.w, 4 * qd + 3);
+    }
+    for (int base = 4 * quads + rank * CTA_THREADS; base < V; base += CLUSTER * CTA_THREADS) {
+        const int i = base + threadIdx.x;
+        const bool valid = i < V;
+        f(valid, valid ? row[i] : 0.0f, i);
+    }
+}
+
 // The largest key x among the row's members with weight{members > x} < target <= weight{members >= x}.
 // Members: keys >= low_cut whose mass is >= floor_mass; COUNT: every member weighs 1 (mass unused).
 // 1 <= target <= the members' weight.  Every CTA of the cluster returns the same key.
-template <int CLUSTER, bool COUNT>
+//
+// SHORTLIST (top-k rows, COUNT): as soon as the bucket a pass chose has few members (cluster-wide, at
+// most LIST_CAP / 2 a CTA on average), one more walk over the row puts every CTA's members of that
+// bucket on its list and sends the keys ABOVE the bucket -- fewer than `target` of them, candidates
+// for certain -- straight to rank 0's candidate array (keys_at_0 / count_at_0, which rank 0 has
+// emptied before); the remaining passes walk the lists.  sh.list_state says afterwards whether the
+// lists hold the bucket (1) or the row has to be walked for the candidates as before (0, 2).
+template <int CLUSTER, bool COUNT, bool SHORTLIST = false>
 __device__ unsigned long long descend(const float* __restrict__ row, int V, const unsigned long long* __restrict__ mass,
                                       unsigned long long low_cut, unsigned long long floor_mass,
-                                      unsigned long long target, unsigned rank, Shared& sh) {
+                                      unsigned long long target, unsigned rank, Shared& sh,
+                                      unsigned keys_at_0 = 0u, unsigned count_at_0 = 0u) {
     __syncthreads();
     if (threadIdx.x == 0) {
         sh.pick[0] = 0ull;
         sh.pick[1] = target;
+        sh.list_state = 0u;
+        sh.list_count = 0u;
     }
     unsigned long long* mine = sh.per_warp[threadIdx.x >> 5];
     for (int pass = 0; pass < 8; ++pass) {
@@ -358,43 +399,72 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
         __syncthreads();
         const unsigned long long prefix = sh.pick[0];
         const unsigned long long mask = pass == 0 ? 0ull : (~0ull << (shift + 8));
-        // in the first pass nearly all keys share two or three digits (the sign and the top of the
-        // exponent): a thread keeps four digits' sums in registers and touches the histogram only
-        // when a fifth digit turns up
-        int held[4] = {-1, -1, -1, -1};
-        unsigned long long sums[4] = {0ull, 0ull, 0ull, 0ull};
-        int victim = 0;
-        sweep<CLUSTER, !COUNT>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
-            const unsigned long long key = make_key(logit, i);
-            if ((key & mask) != prefix || key < low_cut) return;
-            if (COUNT) m = 1ull;
-            else if (m < floor_mass) return;
-            const int digit = (int)((key >> shift) & 0xffull);
-            if (pass == 3) {                         // few keys share 24 bits of a logit: no contention
-                atomicAdd(&sh.members[digit], 1u);
-                atomicMax(&sh.largest[digit], key);
-            }
-            bool hit = false;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (held[c] == digit) {
-                    sums[c] += m;
-                    hit = true;
+        if (COUNT) {
+            // Counting members (every weight 1): the lanes of a warp that hold the same digit are
+            // found with one match and their leader adds their number, so that thirty-two lanes never
+            // queue for one word of the histogram.  (In a first pass a few digits hold nearly every
+            // key: with one atomic a lane it took six times as long as a plain walk over the row.)
+            auto count_one = [&](bool valid, unsigned long long key) {
+                const bool member = valid && (key & mask) == prefix && key >= low_cut;
+                const int digit = member ? (int)((key >> shift) & 0xffull) : -1;
+                const unsigned same = __match_any_sync(0xffffffffu, digit);
+                if (!member) return;
+                const bool leader = (int)(__ffs(same) - 1) == (int)(threadIdx.x & 31);
+                if (pass == 3) {                     // few keys share 24 bits of a logit
+                    if (leader) atomicAdd(&sh.members[digit], (unsigned)__popc(same));
+                    atomicMax(&sh.largest[digit], key);
                 }
-            if (!hit) {
+                if (leader) atomicAdd(&mine[digit], (unsigned long long)__popc(same));
+            };
+            if (SHORTLIST && sh.list_state == 1u) {
+                const unsigned n_list = sh.list_count;
+                for (unsigned base = 0; base < n_list; base += CTA_THREADS) {
+                    const unsigned i = base + threadIdx.x;
+                    count_one(i < n_list, i < n_list ? sh.list[i] : 0ull);
+                }
+            } else {
+                sweep_together<CLUSTER>(row, V, rank, [&](bool valid, float logit, int i) {
+                    count_one(valid, make_key(logit, i));
+                });
+            }
+        } else {
+            // Masses: in the first pass nearly all keys share two or three digits (the sign and the
+            // top of the exponent): a thread keeps four digits' sums in registers and touches the
+            // histogram only when a fifth digit turns up.  (Adding the masses of equal digits inside
+            // the warp first, as the counts are, was slower: two integer reductions a key.)
+            int held[4] = {-1, -1, -1, -1};
+            unsigned long long sums[4] = {0ull, 0ull, 0ull, 0ull};
+            int victim = 0;
+            sweep<CLUSTER, true>(row, mass, V, rank, [&](float logit, int i, unsigned long long m) {
+                const unsigned long long key = make_key(logit, i);
+                if ((key & mask) != prefix || key < low_cut || m < floor_mass) return;
+                const int digit = (int)((key >> shift) & 0xffull);
+                if (pass == 3) {
+                    atomicAdd(&sh.members[digit], 1u);
+                    atomicMax(&sh.largest[digit], key);
+                }
+                bool hit = false;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
-                    if (c == victim) {
-                        if (held[c] >= 0) atomicAdd(&mine[held[c]], sums[c]);
-                        held[c] = digit;
-                        sums[c] = m;
+                    if (held[c] == digit) {
+                        sums[c] += m;
+                        hit = true;
                     }
-                victim = (victim + 1) & 3;
-            }
-        });
+                if (!hit) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-            if (held[c] >= 0) atomicAdd(&mine[held[c]], sums[c]);
+                    for (int c = 0; c < 4; ++c)
+                        if (c == victim) {
+                            if (held[c] >= 0) atomicAdd(&mine[held[c]], sums[c]);
+                            held[c] = digit;
+                            sums[c] = m;
+                        }
+                    victim = (victim + 1) & 3;
+                }
+            });
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (held[c] >= 0) atomicAdd(&mine[held[c]], sums[c]);
+        }
         __syncthreads();
         for (int d = threadIdx.x; d < 256; d += CTA_THREADS) {
             unsigned long long all = 0ull;
@@ -443,6 +513,7 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
                 sh.pick[0] = prefix | ((unsigned long long)digit << shift);
                 sh.pick[1] = rest;
                 sh.settled = 0u;
+                sh.bucket_members = sh.all[digit];
                 if (pass == 3) {
                     // the logit is settled.  If one key has it (nearly always), that is the answer
                     // and the four passes over the id bits are not needed.
@@ -464,6 +535,29 @@ __device__ unsigned long long descend(const float* __restrict__ row, int V, cons
         }
         __syncthreads();                            // pick is set
         if (pass == 3 && sh.settled) break;
+        if (SHORTLIST && sh.list_state == 0u && pass < 3 &&
+            sh.bucket_members <= (unsigned long long)(CLUSTER * (LIST_CAP / 2))) {
+            // few members left: every CTA lists its own, the keys above the bucket go to rank 0
+            const unsigned long long chosen = sh.pick[0];
+            const unsigned long long bucket_mask = ~0ull << shift;
+            unsigned over = 0u;
+            sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+                const unsigned long long key = make_key(logit, i);
+                if ((key & bucket_mask) == chosen) {
+                    const unsigned at = atomicAdd(&sh.list_count, 1u);
+                    if (at < (unsigned)LIST_CAP) sh.list[at] = key;
+                    else over = 1u;
+                } else if (key > chosen) {          // a digit above the chosen one: fewer than `target` such keys
+                    unsigned at;
+                    asm volatile("atom.shared::cluster.add.u32 %0, [%1], 1;" : "=r"(at) : "r"(count_at_0) : "memory");
+                    if (at < (unsigned)SMALL_K)
+                        asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(keys_at_0 + at * 8u), "l"(key) : "memory");
+                }
+            });
+            const unsigned long long any_over = cluster_reduce<CLUSTER, true>((unsigned long long)over, sh);
+            if (threadIdx.x == 0) sh.list_state = any_over ? 2u : 1u;
+            __syncthreads();
+        }
     }
     // the walk's last histogram may still be read by a peer: the next walk or reduction of this
     // kernel starts with writes to other words and passes a cluster barrier before it returns here
@@ -495,13 +589,16 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
                           (prm.repetition_penalty != 1.0f || prm.presence_penalty != 0.0f ||
                            prm.frequency_penalty != 0.0f);
 
+    const bool greedy_row = (!(prm.temperature > 0.0f) && !penalize) || k == 1;
     unsigned long long best = 0ull;
-    sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
-        const unsigned long long key = make_key(logit, i);
-        best = key > best ? key : best;
-    });
-    best = cluster_reduce<CLUSTER, true>(best, sh);
-    if ((!(prm.temperature > 0.0f) && !penalize) || k == 1) {
+    if (greedy_row || k > SMALL_K) {                // (a sorted candidate list knows its own maximum)
+        sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+            const unsigned long long key = make_key(logit, i);
+            best = key > best ? key : best;
+        });
+        best = cluster_reduce<CLUSTER, true>(best, sh);
+    }
+    if (greedy_row) {
         if (rank == 0 && threadIdx.x == 0) out[r] = key_id(best);
         cluster_barrier();                          // no CTA leaves while a peer still reads its shared memory
         return;
@@ -509,21 +606,35 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
 
     if (k <= SMALL_K) {
         // the candidates are the k largest keys: find the k-th, gather them in rank 0, sort, draw
-        const unsigned long long kth = descend<CLUSTER, true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k, rank, sh);
         if (rank == 0) {
             for (int i = threadIdx.x; i < SMALL_K; i += CTA_THREADS) keys[i] = 0ull;
             if (threadIdx.x == 0) sh.count = 0u;
         }
-        cluster_barrier();
+        cluster_barrier();                          // rank 0's array is empty before anybody sends to it
         const unsigned keys_at_0 = peer_address(keys, 0), count_at_0 = peer_address(&sh.count, 0);
-        sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
-            const unsigned long long key = make_key(logit, i);
-            if (key < kth) return;                  // keys are distinct: exactly k keys pass
+        const unsigned long long kth = descend<CLUSTER, true, true>(row, V, nullptr, 0ull, 0ull, (unsigned long long)k,
+                                                                    rank, sh, keys_at_0, count_at_0);
+        auto candidate = [&](unsigned long long key) {
+            if (key < kth) return;                  // keys are distinct: exactly k keys pass in all
             unsigned at;
             asm volatile("atom.shared::cluster.add.u32 %0, [%1], 1;" : "=r"(at) : "r"(count_at_0) : "memory");
             if (at < (unsigned)SMALL_K)
                 asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(keys_at_0 + at * 8u), "l"(key) : "memory");
-        });
+        };
+        if (sh.list_state == 1u) {
+            // the keys above the bucket are at rank 0 already; the rest of the candidates are on the lists
+            const unsigned n_list = sh.list_count;
+            for (unsigned i = threadIdx.x; i < n_list; i += CTA_THREADS) candidate(sh.list[i]);
+        } else {
+            if (sh.list_state == 2u) {              // a list overflowed: what was sent to rank 0 is sent again below
+                cluster_barrier();
+                if (rank == 0 && threadIdx.x == 0) sh.count = 0u;
+                cluster_barrier();
+            }
+            sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+                candidate(make_key(logit, i));
+            });
+        }
         cluster_barrier();
         if (rank != 0) return;
         int padded = 1;
