@@ -533,11 +533,12 @@ def test_kernels_refuse_what_they_cannot_take():
 
 
 # ------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("rows", [5, 70])            # few rows: cut into slices; many: one block a row
 @pytest.mark.parametrize("V", [100, 384, 65536, 50001])
-def test_argmax_takes_the_lowest_id_among_equals(V):
+def test_argmax_takes_the_lowest_id_among_equals(V, rows):
     from flyweight_b200.sampling import sampler
     g = torch.Generator().manual_seed(V)
-    logits = torch.randn(5, V, generator=g)
+    logits = torch.randn(rows, V, generator=g)
     logits[1, [7, V - 1]] = 50.0
     logits[2, :] = 0.0
     logits[3, V - 1] = 99.0
