@@ -175,7 +175,8 @@ class StepPlanner:
 
 class ModelRunner(StepPlanner):
     def __init__(self, model, num_pages: int, num_slots: int, max_model_len: int,
-                 max_batched_tokens: int = 8192, use_graphs: bool = True, use_plan: bool = True):
+                 max_batched_tokens: int = 8192, use_graphs: bool = True, use_plan: bool = True,
+                 graph_after: int = 0):
         require_cuda()
         self.model = model
         self.precision = model.precision
@@ -197,6 +198,11 @@ class ModelRunner(StepPlanner):
         # decode steps replay a CUDA graph per (batch size, block-table width)
         self.use_graphs = bool(use_graphs) and model.graph_safe
         self.max_graph_batch = 256
+        # A graph for a (batch size, table width) is recorded only once that many decode steps in a
+        # row have had this shape: recording costs 8 to 30 ms, ten to thirty steps, and pays only
+        # while the same requests go on decoding together.  0: at the first step of a shape.
+        self.graph_after = int(graph_after)
+        self._shape_run = (None, 0)         # the shape of the last decode steps and how many in a row
         self.max_graphs = 32                # graphs kept; the one unused for longest goes first
         self._graphs = {}
         self.last_decode_graph = None      # the graph the last step replayed (None: it ran eagerly)
@@ -221,7 +227,11 @@ class ModelRunner(StepPlanner):
                 and all(len(seg.tokens) == 1 and seg.want == [0] for seg in segments)):
             bucket = 16 * (-(-width // 16))         # a new graph every 1,024 tokens of context
             key = (len(segments), bucket)
+            seen = self._shape_run[1] + 1 if self._shape_run[0] == key else 1
+            self._shape_run = (key, seen)
             graph = self._graphs.pop(key, None)
+            if graph is None and seen <= self.graph_after:
+                return self._step_without_graph(segments, requests, width, n_groups, patch_source, patch)
             if graph is not None:
                 self._graphs[key] = graph              # most recently used: last in the dict
             if graph is None:
@@ -243,6 +253,10 @@ class ModelRunner(StepPlanner):
             self.tokens_run += len(segments)
             self.h2d_bytes += graph.batch.h2d_bytes
             return logits
+        self._shape_run = (None, 0)
+        return self._step_without_graph(segments, requests, width, n_groups, patch_source, patch)
+
+    def _step_without_graph(self, segments, requests, width, n_groups, patch_source, patch) -> torch.Tensor:
         self.last_decode_graph = None
         tables = [self.cache.block_table_array(g, requests, width) for g in range(n_groups)]
         if self.step_plan is not None and self.use_plan:

@@ -46,7 +46,9 @@ class EngineConfig:
     ``cache_tokens``: size of the KV pool in tokens (None: every live request at the context limit,
     plus the spare page the scheduler keeps per admission); ``max_batched_tokens``: token budget of
     one step; ``max_queued``: most requests queued and running before ``task_submit`` refuses (raised to
-    ``parallel_sequences`` when that is larger); ``use_graphs``: CUDA graphs for steps of single tokens; ``use_plan``: the native step
+    ``parallel_sequences`` when that is larger); ``graph_after``: how many decode steps in a row must have
+    the same batch size and table width before a graph is recorded for that shape (recording costs ten to
+    thirty steps' time; a batch whose size wanders never pays it back); ``use_graphs``: CUDA graphs for steps of single tokens; ``use_plan``: the native step
     plan for the others; ``steady_decode`` / ``run_ahead``: the short ways of ``engine_step``."""
     context_limit: int = 4096
     parallel_sequences: int = 1
@@ -57,6 +59,7 @@ class EngineConfig:
     steady_decode: bool = True
     run_ahead: bool = True
     max_queued: int = 256          # flyweight's queue limit (native/src/v2_runtime.cpp:32588)
+    graph_after: int = 16          # decode steps of one shape in a row before a CUDA graph is recorded for it
 
     def __post_init__(self):
         if self.context_limit <= 0 or self.parallel_sequences <= 0 or self.max_batched_tokens <= 0:
@@ -142,7 +145,8 @@ class Runtime:
                                   num_slots=self.parallel_sequences,
                                   max_model_len=self.context_limit,
                                   max_batched_tokens=self.max_batched_tokens,
-                                  use_graphs=self.config.use_graphs, use_plan=self.config.use_plan)
+                                  use_graphs=self.config.use_graphs, use_plan=self.config.use_plan,
+                                  graph_after=self.config.graph_after)
         self.scheduler = Scheduler(self.runner, self.max_batched_tokens, self.context_limit,
                                    self.config.queue_limit)
 

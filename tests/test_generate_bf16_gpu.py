@@ -138,7 +138,7 @@ def test_steady_decoding_and_the_step_launched_ahead_in_bfloat16():
     prompts = [random_tokens(name, n, seed=180 + n) for n in (30, 61, 64, 100)]
 
     def run(steady, ahead):
-        with open_runtime(name, context_limit=256, parallel_sequences=4) as runtime:
+        with open_runtime(name, context_limit=256, parallel_sequences=4, graph_after=0) as runtime:
             runtime.steady_decode = steady
             runtime.run_ahead = ahead
             ids = [runtime.task_submit(p, 40 + 17 * i) for i, p in enumerate(prompts)]

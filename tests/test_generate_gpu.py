@@ -141,7 +141,7 @@ def test_the_steady_decode_shortcut_changes_nothing():
     settings = dict(temperature=0.7, top_k=30, top_p=0.9, min_p=0.02)
 
     def run(steady):
-        with open_runtime(name, "float32", context_limit=256, parallel_sequences=4) as runtime:
+        with open_runtime(name, "float32", context_limit=256, parallel_sequences=4, graph_after=0) as runtime:
             runtime.steady_decode = steady
             ids = [runtime.task_submit(p, 40 + 17 * i, seed=3 + i, **(settings if i % 2 else {}))
                    for i, p in enumerate(prompts)]
@@ -164,7 +164,7 @@ def test_launching_the_next_step_before_reading_this_one_changes_nothing():
     prompts = [random_tokens(name, n, seed=90 + n) for n in (20, 50, 63, 90)]
 
     def run(ahead, stop):
-        with open_runtime(name, "float32", context_limit=256, parallel_sequences=4) as runtime:
+        with open_runtime(name, "float32", context_limit=256, parallel_sequences=4, graph_after=0) as runtime:
             runtime.run_ahead = ahead
             ids = [runtime.task_submit(p, 60 + 13 * i, stop) for i, p in enumerate(prompts)]
             log = []
@@ -334,3 +334,23 @@ def test_planning_the_next_step_before_this_one_is_read_changes_nothing(name):
             for i, prompt in enumerate(prompts):
                 if i % 3 and fast_reasons[i] == "length":
                     assert fast[i] == P.greedy_generate(cfg, w, prompt, len(fast[i]))
+
+
+def test_a_graph_is_recorded_only_for_a_batch_that_stays():
+    """Recording a CUDA graph costs ten to thirty decode steps, so the runtime records one for a
+    (batch size, table width) only after 16 decode steps in a row have had that shape; a batch whose
+    size changes every few steps runs through the native plan and records none.  Same tokens."""
+    name = "A"
+    cfg, w = plain_model(name, "float32")
+    prompts = [random_tokens(name, n, seed=300 + n) for n in (9, 14, 11)]
+    with open_runtime(name, "float32", context_limit=128, parallel_sequences=3) as runtime:
+        assert runtime.config.graph_after == 16
+        ids = [runtime.task_submit(p, n) for p, n in zip(prompts, (50, 12, 6))]    # 3, then 2, then 1 decoding
+        seen = []
+        while runtime.has_work():
+            runtime.engine_step()
+            seen.append(sorted(runtime.runner._graphs))
+        for i, p, n in zip(ids, prompts, (50, 12, 6)):
+            assert runtime.task(i).generated == P.greedy_generate(cfg, w, p, n)
+        assert seen[10] == [] and seen[-1] == [(1, 16)]       # three and two together never lasted 16 steps
+        assert runtime.info["steady_steps"] > 10
