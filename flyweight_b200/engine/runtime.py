@@ -352,9 +352,10 @@ class Runtime:
     # ------------------------------------------------------------------ steady decoding
     def _steady_step(self):
         """Steady decoding: nothing to schedule, no page to map, the captured graph replayed one
-        position further.  With greedy requests the step after this one is launched as well before
-        this one's tokens are read: its token ids go from the sampler's output to the embedding on
-        the device, so the device does not wait for the host between steps.  Returns the events
+        position further.  Unless a request has penalties (they need the ids on the host), the step
+        after this one is launched as well before this one's tokens are read: its token ids go from
+        the sampler's output to the embedding on the device, so the device does not wait for the
+        host between steps.  Returns the events
         of one step, or None when the next step is not a repeat of the last one."""
         current = self._ahead
         self._ahead = None
@@ -364,15 +365,15 @@ class Runtime:
                 return None
             logits = self.runner.step_same_requests([task.generated[-1] for task in need])
             self.scheduler.advance_decode(need)
-            if not (self.run_ahead and all(task.greedy for task in need)):
+            if not self.run_ahead or self.scheduler.penalizing:
                 events = []
                 self._sample_and_accept(need, logits, events)
                 return events
-            current = self._sample_greedy_async(need, logits)
+            current = self._sample_ahead(need, logits)
         if self.run_ahead and self.steady_decode and self._may_follow(current["tasks"]):
             logits = self.runner.step_same_requests(device_tokens=current["device"])
             self.scheduler.advance_decode(current["tasks"])
-            self._ahead = self._sample_greedy_async(current["tasks"], logits)
+            self._ahead = self._sample_ahead(current["tasks"], logits)
         return self._accept_async(current)
 
     def _may_follow(self, tasks) -> bool:
@@ -393,12 +394,19 @@ class Runtime:
                 return False
         return True
 
-    def _sample_greedy_async(self, tasks, logits):
-        """Arg-max on the device and the copy of the ids to pinned memory, both queued; nobody
-        waits here."""
+    def _sample_ahead(self, tasks, logits):
+        """Sampling on the device (arg-max, or draws with uniform numbers taken from the requests'
+        generators now: they do not depend on the tokens) and the copy of the ids to pinned memory,
+        both queued; nobody waits here.  Not for requests with penalties: those need the ids on
+        the host first."""
         if self.logits_observer is not None:
             self.logits_observer(tasks, logits)
-        return self._queue_read(tasks, device_sampler.argmax(logits))
+        if all(task.greedy for task in tasks):
+            tokens = device_sampler.argmax(logits)
+        else:
+            uniforms = [0.0 if task.greedy else task.rng.uniform() for task in tasks]
+            tokens = device_sampler.sample(logits, [task.sampling for task in tasks], uniforms)
+        return self._queue_read(tasks, tokens)
 
     def _queue_read(self, tasks, tokens):
         """The copy of sampled ids (int32 on the device) to one of two pinned buffers, queued."""
