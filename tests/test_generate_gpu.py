@@ -354,3 +354,28 @@ def test_a_graph_is_recorded_only_for_a_batch_that_stays():
             assert runtime.task(i).generated == P.greedy_generate(cfg, w, p, n)
         assert seen[10] == [] and seen[-1] == [(1, 16)]       # three and two together never lasted 16 steps
         assert runtime.info["steady_steps"] > 10
+
+
+def test_a_kernel_that_gave_up_is_noticed_while_requests_keep_running():
+    """The two words of the health check ride behind the sampled ids (after a step in which a request
+    ended, and every 32nd step), so a failure is raised without a wait of its own: here the status
+    word is set by the self-test kernel (a bounded wait on a barrier nobody arrives on) while two
+    requests decode, and the engine raises within the next 33 steps."""
+    from flyweight_b200.kernels import KernelError, lib, tensorcore
+    from flyweight_b200.kernels.lib import stream
+    name = "A"
+    prompts = [random_tokens(name, n, seed=400 + n) for n in (10, 12)]
+    runtime = open_runtime(name, "float32", context_limit=256, parallel_sequences=2)
+    try:
+        for p in prompts:
+            runtime.task_submit(p, 200)
+        for _ in range(40):
+            runtime.engine_step()
+        assert tensorcore.status() == 0
+        lib.call("fwb_selftest_bounded_wait", 91, stream())
+        with pytest.raises(KernelError, match="gave up"):
+            for _ in range(34):
+                runtime.engine_step()
+    finally:
+        assert tensorcore.status() == 0          # the check that raised has read and cleared the word
+        runtime.runner = None                    # (closing would run the health check once more)
