@@ -225,7 +225,7 @@ def time_e2e(model, batch, context, steps, warmup, vocab, seed=1):
     rng = torch.Generator().manual_seed(seed)
     # requests admitted first decode while the later ones still read their prompts, so every
     # request gets room for those extra tokens and none finishes inside the timed region
-    slack = 2 * batch * (-(-context // 2048)) + 8 + 24
+    slack = 2 * batch * (-(-context // 2048)) + 8 + 24 + SETTLE_STEPS
     total = context + warmup + steps + slack
     runtime = Model(_model=model).native_runtime(context_limit=total, parallel_sequences=batch,
                                                 max_batched_tokens=2048)
@@ -236,7 +236,7 @@ def time_e2e(model, batch, context, steps, warmup, vocab, seed=1):
         runtime.engine_step()                     # prompts in (untimed)
     # untimed: the steps after which the runtime records a CUDA graph for a batch that stays the same
     # (EngineConfig.graph_after), and the asked-for warm-up steps behind them
-    for _ in range(runtime.config.graph_after + 4 + warmup):
+    for _ in range(runtime.config.graph_after + 4 + SETTLE_STEPS + warmup):
         runtime.engine_step()
     torch.cuda.synchronize()
     h2d0, d2h0 = runtime.runner.h2d_bytes, runtime.info["d2h_bytes"]

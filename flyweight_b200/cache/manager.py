@@ -255,6 +255,21 @@ class CacheManager:
                 table.append(group.pool.allocate())
         self._length[request] = new_length
 
+    def room_for_one_more(self, requests: Sequence[Hashable], width: int) -> bool:
+        """Whether every one of these live requests can take one more token now: those at a page's
+        edge find a free page in every group (all of them together), and no block table grows past
+        ``width`` pages.  Nothing is changed."""
+        at_edge = 0
+        for request in requests:
+            length = self._length[request]
+            if length % PAGE_SIZE == 0:
+                at_edge += 1
+                if length // PAGE_SIZE + 1 > width:
+                    return False
+        if not at_edge:
+            return True
+        return not self._windowed and all(group.pool.n_free >= at_edge for group in self.groups)
+
     def fits_last_page(self, request: Hashable) -> bool:
         """Whether one more token of a live ``request`` needs no new page in any group and gives
         none back: its next position lies inside its last mapped page, and no group has a window

@@ -83,19 +83,8 @@ class DecodeBatch:
             pos0[index] = seg.pos0
         start = self._offsets["positions"][0]
         values[start:start + B] = pos0
-        for g, offset in enumerate(self._table_offsets):
-            group = cache.groups[g]
-            rows = self._table_rows[g]
-            stamps = self._stamps[g]
-            for index, seg in enumerate(segments):
-                table = group.tables[seg.request]
-                stamp = (cache.serial(seg.request), len(table),
-                         group.window and sum(1 for p in table if p < 0))
-                if stamps[index] != stamp:
-                    stamps[index] = stamp
-                    row = rows[index]
-                    row[:len(table)] = table
-                    row[len(table):] = -1
+        self.segments = segments
+        self.refresh_rows(cache, range(len(segments)))
         turn = self._turn
         self._turn = (turn + 1) % RING
         if self._events[turn] is not None:
@@ -110,6 +99,25 @@ class DecodeBatch:
         self.segments = segments
         self.max_context = int(pos0.max()) + 1
 
+
+    def refresh_rows(self, cache, indices) -> None:
+        """Bring the host copy of the block-table rows of these segments up to date (a row is
+        rewritten only if the request's table changed since it was last written here); the next
+        upload sends them."""
+        for g in range(len(self._table_offsets)):
+            group = cache.groups[g]
+            rows = self._table_rows[g]
+            stamps = self._stamps[g]
+            for index in indices:
+                request = self.segments[index].request
+                table = group.tables[request]
+                stamp = (cache.serial(request), len(table),
+                         group.window and sum(1 for p in table if p < 0))
+                if stamps[index] != stamp:
+                    stamps[index] = stamp
+                    row = rows[index]
+                    row[:len(table)] = table
+                    row[len(table):] = -1
 
     def upload_next(self, tokens: Optional[Sequence[int]]) -> None:
         """The same requests one position further (no page changes): only the token ids and the

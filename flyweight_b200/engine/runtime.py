@@ -387,12 +387,12 @@ class Runtime:
         for task, running in zip(tasks, scheduler.running):
             if task is not running or task.cancelled or len(task.generated) + 1 >= task.max_tokens:
                 return False
-            length = cache.length(task.id)
-            if length % PAGE_SIZE == 0 or length + 1 > runner.max_model_len:
+            if cache.length(task.id) + 1 > runner.max_model_len:
                 return False
             if len(task.prompt) + len(task.generated) + 1 >= self.scheduler.max_model_len:
                 return False
-        return True
+        graph = runner.last_decode_graph
+        return graph is not None and cache.room_for_one_more([task.id for task in tasks], graph.batch.width)
 
     def _sample_ahead(self, tasks, logits):
         """Sampling on the device (arg-max, or draws with uniform numbers taken from the requests'
@@ -478,9 +478,10 @@ class Runtime:
         for task, segment in zip(tasks, segments):
             if segment.request != task.id or task.cancelled or task.pending != 1:
                 return None
-            length = cache.length(task.id)
-            if length % PAGE_SIZE == 0 or length + 1 > runner.max_model_len:
+            if cache.length(task.id) + 1 > runner.max_model_len:
                 return None
+        if not cache.room_for_one_more([task.id for task in tasks], graph.batch.width):
+            return None                      # pages are short (the scheduler decides who waits) or the table outgrows the graph
         return list(tasks)
 
     def _read_tokens(self, tokens: torch.Tensor) -> List[int]:

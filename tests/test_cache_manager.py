@@ -176,3 +176,22 @@ def test_fixed_states_of_different_dtypes_get_pools_of_their_own_and_are_zeroed_
         assert all(float(state[other].float().min()) == 7.0 for other in range(3) if other != slot)
     states[0][slot].fill_(1)
     assert float(states[2][slot].sum()) == 0.0 and float(states[1][slot].float().sum()) == 0.0   # no overlap
+
+
+def test_room_for_one_more_token_counts_the_requests_at_a_page_edge():
+    from flyweight_b200.cache import PAGE_SIZE, CacheManager
+    from flyweight_b200.parts import PagedKV
+    cache = CacheManager([PagedKV(1, 16)], num_pages=5, num_slots=4, device=None)
+    for name, length in (("a", PAGE_SIZE), ("b", PAGE_SIZE), ("c", 10)):
+        cache.admit(name)
+        cache.extend(name, length)
+    assert cache.groups[0].pool.n_free == 2
+    assert cache.room_for_one_more(["a", "b", "c"], width=4)          # two at an edge, two pages free
+    assert not cache.room_for_one_more(["a", "b", "c"], width=1)      # a table of two pages is too wide
+    cache.admit("d")
+    cache.extend("d", 1)
+    assert not cache.room_for_one_more(["a", "b", "c"], width=4)      # one page free, two wanted
+    assert cache.room_for_one_more(["a", "c", "d"], width=4)
+    assert cache.grow("a", 1) == (cache.slot("a"), PAGE_SIZE) and cache.length("a") == PAGE_SIZE + 1
+    assert cache.groups[0].pool.n_free == 0 and not cache.room_for_one_more(["b"], width=4)
+    cache.check()
