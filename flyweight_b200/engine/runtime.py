@@ -378,8 +378,8 @@ class Runtime:
 
     def _may_follow(self, tasks) -> bool:
         """Whether the step after the one in flight may be launched now: the same requests go
-        on (nobody waits, is cancelled, or is known to end with the token in flight), and none
-        of them needs a new page or reaches the limit."""
+        on (nobody waits, is cancelled, or is known to end with the token in flight), none reaches
+        the limit, and those at a page's edge all find a page."""
         scheduler, runner = self.scheduler, self.runner
         if scheduler.waiting or len(scheduler.running) != len(tasks):
             return False
@@ -463,7 +463,7 @@ class Runtime:
     def _same_requests_again(self):
         """The running tasks, if the next step is the last one moved on by one token: nobody
         waits, everybody decodes, the last step replayed a graph for exactly these requests in
-        this order, and nobody needs a new page or reaches a limit.  Else None."""
+        this order, nobody reaches a limit, and those at a page's edge all find a page.  Else None."""
         scheduler, runner = self.scheduler, self.runner
         graph = runner.last_decode_graph
         tasks = scheduler.running
