@@ -599,6 +599,38 @@ def test_sampling_with_fewer_ctas_a_row_draws_the_same_tokens(rows, V):
             assert drawn[0][i] == want, i
 
 
+def test_sampling_rows_that_defeat_the_shortlist():
+    """Rows on which the top-k search cannot narrow its bucket early, or narrows it to nothing: all
+    logits equal, two values, thousands tied at the top, mostly -inf, one dominant value, a nearly flat
+    row, a huge range, all negative.  The kernel falls back to walking the row; draws as the plain sampler's."""
+    from flyweight_b200.sampling import SamplingConfig, sampler
+    V = 20000
+    g = torch.Generator().manual_seed(3)
+    rows = [torch.zeros(V)]
+    r = torch.zeros(V); r[::2] = 1.0; rows.append(r)
+    rows.append(torch.randn(V, generator=g) * 30)
+    r = torch.randn(V, generator=g); r[:18000] = -float("inf"); rows.append(r)
+    r = torch.full((V,), -1e30); r[5] = 0.0; r[9] = -1.0; rows.append(r)
+    rows.append(torch.randn(V, generator=g) * 1e-3)
+    r = torch.randn(V, generator=g); r[100:3000] = 7.25; rows.append(r)
+    rows.append(-torch.rand(V, generator=g) * 5 - 100)
+    logits = torch.stack(rows)
+    try:
+        for settings in (dict(temperature=0.8, top_k=20, top_p=0.95, min_p=0.0),
+                         dict(temperature=1.0, top_k=1000, top_p=0.9, min_p=0.01),
+                         dict(temperature=0.7, top_k=0, top_p=0.9, min_p=0.0)):
+            for ctas in (0, 1):
+                sampler.set_ctas_per_row(ctas)
+                for trial in range(2):
+                    uniforms = [P.XorShift64Star(50 + trial * 20 + i).uniform() for i in range(len(rows))]
+                    got = sampler.sample(dev(logits), [SamplingConfig(**settings)] * len(rows), uniforms).tolist()
+                    want = [P.sample(logits[i].numpy(), rng=P.XorShift64Star(50 + trial * 20 + i), **settings)
+                            for i in range(len(rows))]
+                    assert got == want, (settings, ctas, trial)
+    finally:
+        sampler.set_ctas_per_row(0)
+
+
 def test_penalties_act_on_the_candidates():
     from flyweight_b200.sampling import SamplingConfig, sampler
     logits = torch.zeros(2, 50)
