@@ -533,6 +533,7 @@ def run_mixed(args) -> int:
         "host_ms_per_step": round(1e3 * (info["step_seconds"] - waited) / steps, 4),
         "wait_ms_per_step": round(1e3 * waited / steps, 4),
         "steady_steps": info["steady_steps"], "preemptions": info["preemptions"],
+        "graphs_recorded": info["graphs_recorded"],
         "first_pass_seconds": round(results[0][0], 4), "clocks": clocks,
         "dtype": "bf16", "data": "synthetic: uniform-random token ids, seeded random weights"}))
     return 0

@@ -207,6 +207,7 @@ class ModelRunner(StepPlanner):
         self._graphs = {}
         self.last_decode_graph = None      # the graph the last step replayed (None: it ran eagerly)
         self.graph_replays = 0
+        self.graphs_recorded = 0
         self.steps = 0
         self.tokens_run = 0
         self.h2d_bytes = 0
@@ -245,6 +246,7 @@ class ModelRunner(StepPlanner):
                 graph = self._graphs[key] = DecodeGraph(
                     self.model, self.cache.layer_caches, self.precision, self.device,
                     self.bad_token_flag, len(segments), n_groups, bucket)
+                self.graphs_recorded += 1
             else:
                 self.graph_replays += 1
             logits = graph.run(segments, self.cache, patch_source, patch)

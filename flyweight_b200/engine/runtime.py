@@ -552,4 +552,7 @@ class Runtime:
         out["model_steps"] = self.runner.steps
         out["tokens_run"] = self.runner.tokens_run
         out["h2d_bytes"] = self.runner.h2d_bytes
+        out["graphs_recorded"] = self.runner.graphs_recorded
+        out["graph_replays"] = self.runner.graph_replays
+        out["graphs_held"] = len(self.runner._graphs)
         return out

@@ -353,7 +353,7 @@ def test_a_graph_is_recorded_only_for_a_batch_that_stays():
         for i, p, n in zip(ids, prompts, (50, 12, 6)):
             assert runtime.task(i).generated == P.greedy_generate(cfg, w, p, n)
         assert seen[10] == [] and seen[-1] == [(1, 16)]       # three and two together never lasted 16 steps
-        assert runtime.info["steady_steps"] > 10
+        assert runtime.info["steady_steps"] > 10 and runtime.info["graphs_recorded"] == 1
 
 
 def test_a_kernel_that_gave_up_is_noticed_while_requests_keep_running():
