@@ -222,19 +222,32 @@ class Runtime:
             current = self._launch_scheduled(events, None)
         if current is not None:
             if self._may_pipeline(current):
-                self._flight = self._launch_scheduled(events, current)
+                if self.scheduler.penalizing:
+                    # penalties want the ids of step k on the host before step k+1 is SAMPLED, not
+                    # before it is launched: launch its forward pass, read step k's ids while it
+                    # runs, then queue its sampling behind it
+                    launched = self._launch_scheduled(events, current, sample=False)
+                    events.extend(self._accept_flight(current))
+                    current = None
+                    if launched is not None:
+                        self._flight = self._sample_async(launched["need"], launched["logits"])
+                        self._flight["graph_step"] = launched["graph_step"]
+                else:
+                    self._flight = self._launch_scheduled(events, current)
                 if self._flight is not None:
                     self._counters["pipelined_steps"] += 1
-            events.extend(self._accept_flight(current))
+            if current is not None:
+                events.extend(self._accept_flight(current))
         self._counters["engine_steps"] += 1
         self._counters["step_seconds"] += time.perf_counter() - started
         return events
 
-    def _launch_scheduled(self, events, after):
+    def _launch_scheduled(self, events, after, sample=True):
         """Schedule a step, launch it and its sampling; nothing is waited for.  ``after``: the step
         launched before it whose tokens are not read yet (its requests' next ids are taken from its
         sampler's output on the device).  Returns the launched step's record, or None when the
-        step samples nothing (no tokens to read: nothing to wait for later either)."""
+        step samples nothing (no tokens to read: nothing to wait for later either).  ``sample``
+        False: the sampling is left to the caller, who gets the requests to sample and the logits."""
         scheduler, runner = self.scheduler, self.runner
         step = scheduler.schedule()
         logits = None
@@ -262,20 +275,20 @@ class Runtime:
                     events.append((task.id, task.computed, EVENT_PROGRESS))
         if not need:
             return None
+        if not sample:
+            return {"need": need, "logits": logits, "graph_step": runner.last_decode_graph is not None}
         flight = self._sample_async(need, logits)
         flight["graph_step"] = runner.last_decode_graph is not None
         return flight
 
     def _may_pipeline(self, current) -> bool:
         """Whether the step after ``current`` may be planned before ``current``'s tokens are read.
-        Not when a request's penalties need the token values on the host; and not when steady
-        decoding is about to take over (the same requests, everybody decoding, nobody waiting):
-        that way is shorter still and starts from a step whose tokens have been read."""
+        Not when steady decoding is about to take over (the same requests, everybody decoding,
+        nobody waiting): that way is shorter still and starts from a step whose tokens have been
+        read."""
         if not self.run_ahead:
             return False
         scheduler = self.scheduler
-        if scheduler.penalizing:
-            return False
         if (self.steady_decode and current.get("graph_step") and not scheduler.waiting
                 and len(current["tasks"]) == len(scheduler.running)
                 and self._same_requests_again() is not None):
@@ -352,10 +365,10 @@ class Runtime:
     # ------------------------------------------------------------------ steady decoding
     def _steady_step(self):
         """Steady decoding: nothing to schedule, no page to map, the captured graph replayed one
-        position further.  Unless a request has penalties (they need the ids on the host), the step
-        after this one is launched as well before this one's tokens are read: its token ids go from
-        the sampler's output to the embedding on the device, so the device does not wait for the
-        host between steps.  Returns the events
+        position further.  The step after this one is launched as well before this one's tokens
+        are read: its token ids go from the sampler's output to the embedding on the device, so the
+        device does not wait for the host between steps (with penalties in the batch the next
+        step's sampling, not its forward pass, waits until this step's ids have been read).  Returns the events
         of one step, or None when the next step is not a repeat of the last one."""
         current = self._ahead
         self._ahead = None
@@ -365,7 +378,7 @@ class Runtime:
                 return None
             logits = self.runner.step_same_requests([task.generated[-1] for task in need])
             self.scheduler.advance_decode(need)
-            if not self.run_ahead or self.scheduler.penalizing:
+            if not self.run_ahead:
                 events = []
                 self._sample_and_accept(need, logits, events)
                 return events
@@ -373,6 +386,12 @@ class Runtime:
         if self.run_ahead and self.steady_decode and self._may_follow(current["tasks"]):
             logits = self.runner.step_same_requests(device_tokens=current["device"])
             self.scheduler.advance_decode(current["tasks"])
+            if self.scheduler.penalizing:
+                # penalties want this step's ids on the host before the next step is SAMPLED: its
+                # forward pass is running, read the ids now, then queue its sampling behind it
+                events = self._accept_async(current)
+                self._ahead = self._sample_ahead(current["tasks"], logits)
+                return events
             self._ahead = self._sample_ahead(current["tasks"], logits)
         return self._accept_async(current)
 
@@ -397,15 +416,16 @@ class Runtime:
     def _sample_ahead(self, tasks, logits):
         """Sampling on the device (arg-max, or draws with uniform numbers taken from the requests'
         generators now: they do not depend on the tokens) and the copy of the ids to pinned memory,
-        both queued; nobody waits here.  Not for requests with penalties: those need the ids on
-        the host first."""
+        both queued; nobody waits here.  Requests with penalties are sampled with the tokens the
+        host knows at this moment: the caller has read the step before."""
         if self.logits_observer is not None:
             self.logits_observer(tasks, logits)
         if all(task.greedy for task in tasks):
             tokens = device_sampler.argmax(logits)
         else:
             uniforms = [0.0 if task.greedy else task.rng.uniform() for task in tasks]
-            tokens = device_sampler.sample(logits, [task.sampling for task in tasks], uniforms)
+            recents = [task.generated for task in tasks] if self.scheduler.penalizing else None
+            tokens = device_sampler.sample(logits, [task.sampling for task in tasks], uniforms, recents)
         return self._queue_read(tasks, tokens)
 
     def _queue_read(self, tasks, tokens):
