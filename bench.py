@@ -217,7 +217,15 @@ def decode_spread(model, batch, context, vocab, regions=5, steps=200, warmup=5):
             "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}
 
 
-def time_e2e(model, batch, context, steps, warmup, vocab, seed=1):
+SAMPLING_PRESETS = {
+    "greedy": dict(temperature=0.0),
+    "topk": dict(temperature=0.8, top_k=20, top_p=0.95),                 # the shape of flyweight's served default
+    "topp": dict(temperature=0.8, top_k=0, top_p=0.95),                  # the whole vocabulary, cut by mass only
+    "penalty": dict(temperature=0.8, top_k=20, top_p=0.95, repetition_penalty=1.2),
+}
+
+
+def time_e2e(model, batch, context, steps, warmup, vocab, seed=1, sampling="greedy"):
     """The same through the public entry point: tasks queued on a Runtime, ``engine_step``
     pumped; every step uploads its batch from pinned host memory and reads its tokens back."""
     import torch
@@ -229,9 +237,9 @@ def time_e2e(model, batch, context, steps, warmup, vocab, seed=1):
     total = context + warmup + steps + slack
     runtime = Model(_model=model).native_runtime(context_limit=total, parallel_sequences=batch,
                                                 max_batched_tokens=2048)
-    for _ in range(batch):
+    for index in range(batch):
         prompt = torch.randint(0, vocab, (context,), generator=rng).tolist()
-        runtime.task_submit(prompt, warmup + steps + slack - 2, temperature=0.0)
+        runtime.task_submit(prompt, warmup + steps + slack - 2, seed=index + 1, **SAMPLING_PRESETS[sampling])
     while runtime.scheduler.waiting or any(t.pending > 1 for t in runtime.scheduler.running):
         runtime.engine_step()                     # prompts in (untimed)
     # untimed: the steps after which the runtime records a CUDA graph for a batch that stays the same
@@ -367,12 +375,13 @@ def run_sizes(args) -> int:
         step_bytes = model.weight_bytes(with_embedding_rows=batch) + batch * context * kv_bytes_per_token(model)
         achieved = step_bytes / (timed["ms_per_step"] / 1e3) / 1e9
         # the same point through the public runtime, host tokens in and out every step
-        e2e = time_e2e(model, batch, context, args.steps, args.warmup, config["vocab_size"])
+        e2e = time_e2e(model, batch, context, args.steps, args.warmup, config["vocab_size"], sampling=args.sampling)
         print(json.dumps({"sizes": True, "model": name, "parameters": model.parameter_count(),
                           "batch": batch, "context": context, "ms_per_step": timed["ms_per_step"],
                           "tokens_per_s": timed["tokens_per_s"], "bytes_per_step": step_bytes,
                           "hbm_gbs": achieved, "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"],
-                          "e2e_tokens_per_s": e2e["value"], "e2e_ms_per_step": e2e["ms_per_step"]}),
+                          "e2e_tokens_per_s": e2e["value"], "e2e_ms_per_step": e2e["ms_per_step"],
+                          "e2e_sampling": args.sampling}),
               flush=True)
     return 0
 
@@ -645,6 +654,10 @@ def main() -> int:
                         help="run fewer layers than the configuration has (both counts are reported)")
     parser.add_argument("--sizes", default=None, metavar="MODEL:BxCTX[,BxCTX...]",
                         help="decode steps of lfm2-350m / lfm2-1.2b / lfm2-2.6b at other batches and contexts")
+    parser.add_argument("--sampling", choices=sorted(SAMPLING_PRESETS), default="greedy",
+                        help="with --sizes: how the requests of the runtime's column sample (greedy; topk: "
+                             "temperature 0.8, top-k 20, top-p 0.95; topp: the same over the whole vocabulary; "
+                             "penalty: topk with a repetition penalty)")
     parser.add_argument("--prefill-lengths", default=None, metavar="N[,N...]",
                         help="time one prompt of each length through one step (lfm2-1.2b)")
     parser.add_argument("--chunked-prefill", default=None, metavar="MODEL:CONTEXTxPORTION",
