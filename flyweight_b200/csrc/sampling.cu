@@ -154,6 +154,46 @@ __device__ void bitonic_sort_desc(unsigned long long* keys, int n) {
     __syncthreads();
 }
 
+// Inclusive prefix sums of a[0 .. 2 * blockDim.x) in place (every thread owns two neighbours);
+// `warp_totals` holds one word per warp.  All threads call it.
+__device__ void block_prefix_sums(unsigned long long* a, unsigned long long* warp_totals) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, warps = blockDim.x >> 5;
+    const unsigned long long x0 = a[2 * t], x1 = a[2 * t + 1];
+    unsigned long long s = x0 + x1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long v = __shfl_up_sync(0xffffffffu, s, o);
+        if (lane >= o) s += v;
+    }
+    if (lane == 31) warp_totals[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long v = lane < warps ? warp_totals[lane] : 0ull;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long w = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += w;
+        }
+        if (lane < warps) warp_totals[lane] = v;
+    }
+    __syncthreads();
+    const unsigned long long before = (warp ? warp_totals[warp - 1] : 0ull) + (s - (x0 + x1));
+    a[2 * t] = before + x0;
+    a[2 * t + 1] = before + x0 + x1;
+    __syncthreads();
+}
+
+// The first index of the non-decreasing a[0 .. n) with a[index] >= target (n if there is none).
+__device__ int first_reaching(const unsigned long long* a, int n, unsigned long long target) {
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (a[mid] >= target) hi = mid;
+        else lo = mid + 1;
+    }
+    return lo;
+}
+
 struct RowParams {
     float temperature;
     int top_k;
@@ -277,6 +317,7 @@ struct Shared {
     unsigned list_count;
     unsigned list_state;                           // 0: walking the row, 1: walking the lists, 2: a list overflowed (row again)
     unsigned long long bucket_members;             // members of the bucket the last pass chose (cluster-wide)
+    unsigned done;                                 // rank 0: the row's token has been drawn from the sorted candidates
 };
 
 // Sum (or maximum) over the cluster of one value per thread.
@@ -684,6 +725,81 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
         mine += m;
     });
     const unsigned long long total = cluster_reduce<CLUSTER, false>(mine, sh);     // >= 2^40: the first candidate weighs 1
+    if (prm.top_p < 1.0f && CTA_THREADS * 2 == SMALL_K) {
+        // The prefix that top_p keeps is, for any row that is not nearly flat, far shorter than
+        // 1,024 candidates.  So: gather the 1,024 largest keys (two or three walks with the
+        // shortlist), sort them, give them the same fixed-point masses, add those up in order --
+        // if they reach top_p of the row's total, the cut, the min_p floor and the draw are all
+        // inside them and the row is done after five walks instead of a dozen.  The same integers
+        // in the same comparisons as below, so the same token.  If they do not reach it, go on below.
+        if (rank == 0) {
+            for (int i = threadIdx.x; i < SMALL_K; i += CTA_THREADS) keys[i] = 0ull;
+            if (threadIdx.x == 0) {
+                sh.count = 0u;
+                sh.done = 0u;
+            }
+        }
+        cluster_barrier();
+        const unsigned keys_at_0 = peer_address(keys, 0), count_at_0 = peer_address(&sh.count, 0);
+        const unsigned long long last = descend<CLUSTER, true, true>(row, V, nullptr, low_cut, 0ull,
+                                                                     (unsigned long long)SMALL_K, rank, sh,
+                                                                     keys_at_0, count_at_0);
+        auto candidate = [&](unsigned long long key) {
+            if (key < last) return;
+            unsigned at;
+            asm volatile("atom.shared::cluster.add.u32 %0, [%1], 1;" : "=r"(at) : "r"(count_at_0) : "memory");
+            if (at < (unsigned)SMALL_K)
+                asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(keys_at_0 + at * 8u), "l"(key) : "memory");
+        };
+        if (sh.list_state == 1u) {
+            const unsigned n_list = sh.list_count;
+            for (unsigned i = threadIdx.x; i < n_list; i += CTA_THREADS) candidate(sh.list[i]);
+        } else {
+            if (sh.list_state == 2u) {
+                cluster_barrier();
+                if (rank == 0 && threadIdx.x == 0) sh.count = 0u;
+                cluster_barrier();
+            }
+            sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
+                candidate(make_key(logit, i));
+            });
+        }
+        cluster_barrier();
+        if (rank == 0) {
+            bitonic_sort_desc(keys, SMALL_K);
+            unsigned long long* sums = reinterpret_cast<unsigned long long*>(probs);
+            for (int i = threadIdx.x; i < SMALL_K; i += CTA_THREADS) {
+                const double scaled = (double)key_logit(keys[i]) / t;
+                const double p = isfinite(scaled) ? exp(scaled - maximum) : 0.0;
+                sums[i] = (unsigned long long)llrint(p * MASS_ONE);
+            }
+            __syncthreads();
+            block_prefix_sums(sums, sh.scratch);
+            if (threadIdx.x == 0) {
+                unsigned long long target = (unsigned long long)ceil((double)prm.top_p * (double)total);
+                target = target < 1ull ? 1ull : (target > total ? total : target);
+                if (sums[SMALL_K - 1] >= target) {
+                    int keep = first_reaching(sums, SMALL_K, target) + 1;
+                    if (prm.min_p > 0.0f) {
+                        const unsigned long long floor_mass = (unsigned long long)ceil((double)prm.min_p * MASS_ONE);
+                        int kept = 1;                  // the first candidate weighs 2^40: it stays
+                        while (kept < keep && sums[kept] - sums[kept - 1] >= floor_mass) ++kept;
+                        keep = kept;
+                    }
+                    const unsigned long long kept_mass = sums[keep - 1];
+                    unsigned long long draw = (unsigned long long)ceil(uniform[r] * (double)kept_mass);
+                    draw = draw < 1ull ? 1ull : (draw > kept_mass ? kept_mass : draw);
+                    out[r] = key_id(keys[first_reaching(sums, keep, draw)]);
+                    sh.done = 1u;
+                }
+            }
+        }
+        cluster_barrier();                          // rank 0 has decided
+        unsigned done;
+        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(done) : "r"(peer_address(&sh.done, 0)));
+        cluster_barrier();                          // no CTA leaves while a peer still reads its shared memory
+        if (done) return;
+    }
     if (prm.top_p < 1.0f) {
         // the shortest prefix whose mass reaches top_p of the total
         unsigned long long target = (unsigned long long)ceil((double)prm.top_p * (double)total);

@@ -165,7 +165,9 @@ def run_sample(args) -> dict:
     rows, vocab = args.rows, args.vocab
     # enough copies of the logits that the timed reads come from HBM
     copies = max(2, min(16, int(160e6 // (rows * vocab * 4)) + 1))
-    logits = [torch.randn(rows, vocab, device="cuda") * 3.0 for _ in range(copies)]
+    # Gaussian logits of the given spread: at temperature 0.8 and top-p 0.95 a spread of 3 keeps about
+    # 1,200 candidates of 65,536 (a flat row), a spread of 4 about 200 (a peaked one, like a model's)
+    logits = [torch.randn(rows, vocab, device="cuda") * args.logit_scale for _ in range(copies)]
     config = SamplingConfig(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=0.0, seed=1)
     uniforms = [((i * 37) % 97) / 97.0 for i in range(rows)]
     turn = [0]
@@ -176,9 +178,31 @@ def run_sample(args) -> dict:
             return sampler.argmax(logits[turn[0]])
         return sampler.sample(logits[turn[0]], [config] * rows, uniforms)
 
+    if args.kernel_only and args.temperature > 0.0:
+        # the launches alone: the rows' settings are staged once, not by every call's Python
+        import struct
+        from . import lib
+        from .lib import ptr, stream
+        k = min(args.top_k, vocab) if args.top_k > 0 else vocab
+        large = k > sampler.SMALL_K
+        record = struct.pack("<fifffffi", args.temperature, args.top_k, args.top_p, 0.0, 1.0, 0.0, 0.0, 0)
+        params = torch.frombuffer(bytearray(record * rows), dtype=torch.uint8).cuda()
+        uni = torch.tensor(uniforms, dtype=torch.float64, device="cuda")
+        out = torch.empty(rows, dtype=torch.int32, device="cuda")
+        vpad = 1
+        while vpad < vocab:
+            vpad <<= 1
+        keys = torch.empty((rows, vpad), dtype=torch.int64, device="cuda") if large else None
+
+        def step():
+            turn[0] = (turn[0] + 1) % copies
+            lib.call("fwb_sample", ptr(logits[turn[0]]), rows, vocab, ptr(params), ptr(uni), None, 0, ptr(out),
+                     ptr(keys), None, vpad if large else 0, 1 if large else 0, stream())
+
     us = _time(step, args.repeat)
     return {"kernel": "argmax" if args.temperature <= 0.0 else "sample_kernel", "rows": rows, "vocab": vocab,
-            "top_k": args.top_k, "top_p": args.top_p, "us": us, "gb_s": rows * vocab * 4 / us / 1e3}
+            "top_k": args.top_k, "top_p": args.top_p, "logit_scale": args.logit_scale,
+            "kernel_only": bool(args.kernel_only), "us": us, "gb_s": rows * vocab * 4 / us / 1e3}
 
 
 def main(argv=None) -> int:
@@ -222,6 +246,8 @@ def main(argv=None) -> int:
     smp.add_argument("--temperature", type=float, default=0.8, help="0: arg-max")
     smp.add_argument("--top-k", type=int, default=40, help="0: the whole vocabulary")
     smp.add_argument("--top-p", type=float, default=0.95)
+    smp.add_argument("--logit-scale", type=float, default=3.0, help="spread of the Gaussian logits")
+    smp.add_argument("--kernel-only", action="store_true", help="time the launches without the Python call around them")
     for p in sub.choices.values():
         p.add_argument("--repeat", type=int, default=20)
     args = parser.parse_args(argv)
