@@ -273,6 +273,7 @@ constexpr int CTA_THREADS = 512;
 constexpr int LIST_CAP = 2048;                   // shortlist entries a CTA keeps (16 KB)
 constexpr int CTA_WARPS = CTA_THREADS / 32;
 constexpr double MASS_ONE = 1099511627776.0;     // 2^40
+constexpr int LEVELS = 7;                        // mass levels 2^38, 2^36 ... 2^26 (a quarter ... 2^-14 of the first candidate's)
 
 __device__ __forceinline__ unsigned cluster_cta_rank() {
     unsigned r;
@@ -318,6 +319,9 @@ struct Shared {
     unsigned list_state;                           // 0: walking the row, 1: walking the lists, 2: a list overflowed (row again)
     unsigned long long bucket_members;             // members of the bucket the last pass chose (cluster-wide)
     unsigned done;                                 // rank 0: the row's token has been drawn from the sorted candidates
+    unsigned attempt;                              // the 1,024 largest candidates may hold the top-p prefix
+    unsigned long long level_all[2 * LEVELS + 2];  // `level` summed over the cluster
+    unsigned long long level[2 * LEVELS + 2];      // of a sample of this CTA's candidates: how many weigh at least each mass level and their mass; the sample's size and mass
 };
 
 // Sum (or maximum) over the cluster of one value per thread.
@@ -714,6 +718,10 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
     const double t = (double)prm.temperature;
     const double maximum = (double)key_logit(best) / t;
     unsigned long long mine = 0ull;
+    constexpr int LEVEL_WORDS = 2 * LEVELS + 2;
+    if (threadIdx.x < LEVEL_WORDS) sh.level[threadIdx.x] = 0ull;
+    __syncthreads();
+    const bool estimate = prm.top_p < 1.0f;
     sweep<CLUSTER, false>(row, nullptr, V, rank, [&](float logit, int i, unsigned long long) {
         unsigned long long m = 0ull;
         if (make_key(logit, i) >= low_cut) {
@@ -724,8 +732,94 @@ sample_kernel(const float* __restrict__ logits, int V, int Vpad, const RowParams
         mass[i] = m;                                // read again only by this CTA, in the same order
         mine += m;
     });
+    if (estimate && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // Of every eighth group of 128 masses this CTA has just written (each thread reads its own
+        // back): how many weigh at least 2^38, 2^36 ... 2^26 and what those weigh together -- an
+        // estimate, enough to tell further down a row whose top-p prefix will not lie inside its
+        // 1,024 largest candidates.  (A walk of its own: kept beside the masses above, these sums
+        // cost the registers that let two CTAs share an SM.)
+        unsigned level_count[LEVELS];
+        unsigned long long level_mass[LEVELS];
+#pragma unroll
+        for (int j = 0; j < LEVELS; ++j) {
+            level_count[j] = 0u;
+            level_mass[j] = 0ull;
+        }
+        unsigned seen = 0u;
+        unsigned long long seen_mass = 0ull;
+        const int quads = V >> 2;
+        int turn = threadIdx.x >> 5;
+        for (int qd = rank * CTA_THREADS + threadIdx.x; qd < quads; qd += CLUSTER * CTA_THREADS, ++turn) {
+            if (turn & 7) continue;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const unsigned long long m = mass[4 * qd + e];
+                ++seen;
+                seen_mass += m;
+                const unsigned top = (unsigned)(m >> 26);   // m <= 2^40
+#pragma unroll
+                for (int j = 0; j < LEVELS; ++j)
+                    if (top >= (1u << (12 - 2 * j))) {
+                        ++level_count[j];
+                        level_mass[j] += m;
+                    }
+            }
+        }
+        if (__any_sync(0xffffffffu, seen != 0u)) {
+            auto add_up = [&](unsigned long long v, int word) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if ((threadIdx.x & 31) == 0 && v) atomicAdd(&sh.level[word], v);
+            };
+#pragma unroll
+            for (int j = 0; j < LEVELS; ++j) {
+                add_up(level_count[j], 2 * j);
+                add_up(level_mass[j], 2 * j + 1);
+            }
+            add_up(seen, 2 * LEVELS);
+            add_up(seen_mass, 2 * LEVELS + 1);
+        }
+    }
+    // (the barriers inside the reduction put these sums before the peers' reads below)
     const unsigned long long total = cluster_reduce<CLUSTER, false>(mine, sh);     // >= 2^40: the first candidate weighs 1
-    if (prm.top_p < 1.0f && CTA_THREADS * 2 == SMALL_K) {
+    // Can the 1,024 largest candidates reach top_p of the total?  None weighs more than the first
+    // one's 2^40, so not if that asks for more than 1,024 * 2^40.  And with n candidates at or above
+    // a level L, the candidates outside the 1,024 largest weigh at least (mass below L) + (n - 1024) L
+    // (for n < 1,024: the 1,024 largest take fewer than 1,024 - n from below L); if that, as estimated
+    // from the sample, is more than top_p leaves over, the row goes straight to the walks further down.
+    // Either way the same token is drawn: this only chooses the shorter way.
+    bool prefix_may_be_short = false;
+    if (estimate) {
+        const double wanted = ceil((double)prm.top_p * (double)total);
+        prefix_may_be_short = wanted <= (double)SMALL_K * MASS_ONE;
+        // one thread a word fetches the peers' sums; thread 0 decides for the CTA (every CTA of the
+        // cluster adds the same integers and decides alike)
+        if (threadIdx.x < LEVEL_WORDS) {
+            unsigned long long sum = 0ull;
+#pragma unroll
+            for (unsigned c = 0; c < CLUSTER; ++c) sum += peer_load_u64(&sh.level[threadIdx.x], c);
+            sh.level_all[threadIdx.x] = sum;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned long long* word = sh.level_all;
+            unsigned may = prefix_may_be_short ? 1u : 0u;
+            if (word[2 * LEVELS] > 0ull) {
+                const double scale = (double)V / (double)word[2 * LEVELS];
+                const double left_over = (double)total - wanted;
+                for (int j = 0; j < LEVELS; ++j) {
+                    const double level = (double)(1ull << (38 - 2 * j));
+                    const double n = scale * (double)word[2 * j];
+                    const double below = scale * (double)(word[2 * LEVELS + 1] - word[2 * j + 1]);
+                    if (below + (n - (double)SMALL_K) * level > left_over) may = 0u;
+                }
+            }
+            sh.attempt = may;
+        }
+        __syncthreads();
+        prefix_may_be_short = sh.attempt != 0u;
+    }
+    if (prm.top_p < 1.0f && prefix_may_be_short && CTA_THREADS * 2 == SMALL_K) {
         // The prefix that top_p keeps is, for any row that is not nearly flat, far shorter than
         // 1,024 candidates.  So: gather the 1,024 largest keys (two or three walks with the
         // shortlist), sort them, give them the same fixed-point masses, add those up in order --

@@ -631,6 +631,26 @@ def test_sampling_rows_that_defeat_the_shortlist():
         sampler.set_ctas_per_row(0)
 
 
+@pytest.mark.parametrize("V", [65536, 50001, 3000])     # 50001: odd rows do not start on 16 bytes (no estimate)
+def test_sampling_whole_vocabulary_rows_from_flat_to_peaked(V):
+    """A row that keeps more than 1,024 candidates looks for its top-p prefix among its 1,024 largest
+    first, unless an estimate says it cannot be there: flat rows (the prefix is most of the row), rows at
+    the edge (a prefix of about 1,024) and peaked rows (a handful) all draw the plain sampler's token."""
+    from flyweight_b200.sampling import SamplingConfig, sampler
+    g = torch.Generator().manual_seed(V + 5)
+    spreads = [0.01, 0.5, 1.0, 2.0, 2.6, 2.8, 3.0, 3.2, 3.5, 4.0, 6.0, 12.0]
+    logits = torch.stack([torch.randn(V, generator=g) * s for s in spreads])
+    for settings in (dict(temperature=0.8, top_k=0, top_p=0.95, min_p=0.0),
+                     dict(temperature=1.0, top_k=0, top_p=0.5, min_p=0.02),
+                     dict(temperature=0.6, top_k=2000, top_p=0.99, min_p=0.0)):
+        for trial in range(3):
+            uniforms = [P.XorShift64Star(900 + trial * 20 + i).uniform() for i in range(len(spreads))]
+            got = sampler.sample(dev(logits), [SamplingConfig(**settings)] * len(spreads), uniforms).tolist()
+            want = [P.sample(logits[i].numpy(), rng=P.XorShift64Star(900 + trial * 20 + i), **settings)
+                    for i in range(len(spreads))]
+            assert got == want, (settings, trial)
+
+
 def test_penalties_act_on_the_candidates():
     from flyweight_b200.sampling import SamplingConfig, sampler
     logits = torch.zeros(2, 50)
