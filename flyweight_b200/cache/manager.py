@@ -266,9 +266,8 @@ class CacheManager:
                 at_edge += 1
                 if length // PAGE_SIZE + 1 > width:
                     return False
-        if not at_edge:
-            return True
-        return not self._windowed and all(group.pool.n_free >= at_edge for group in self.groups)
+        # (pages that a window passes with this token are not counted as free: on the safe side)
+        return not at_edge or all(group.pool.n_free >= at_edge for group in self.groups)
 
     def fits_last_page(self, request: Hashable) -> bool:
         """Whether one more token of a live ``request`` needs no new page in any group and gives
@@ -288,6 +287,19 @@ class CacheManager:
                     table.append(group.pool.allocate())
         self._length[request] = new_length
         return self._slot_of[request], length
+
+    def advance_one(self, request: Hashable) -> bool:
+        """One more token of a live ``request`` whose caller has asked ``room_for_one_more``: the
+        pages a window has passed are given back, a request at a page's edge gets its next page in
+        every group.  True if one of its block tables changed."""
+        changed = self._windowed and self.release_passed(request) > 0
+        length = self._length[request]
+        if length % PAGE_SIZE == 0:
+            for group in self.groups:
+                group.tables[request].append(group.pool.allocate())
+            changed = True
+        self._length[request] = length + 1
+        return changed
 
     def bump(self, request: Hashable) -> None:
         """One more token of ``request`` inside its last mapped page (the caller has checked)."""

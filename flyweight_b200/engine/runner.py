@@ -295,20 +295,15 @@ class ModelRunner(StepPlanner):
     def step_same_requests(self, tokens: Optional[Sequence[int]] = None,
                            device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The decode step that follows the last one for exactly the same requests: lengths grow by
-        one (a request at a page's edge gets its next page: the caller has asked
-        ``cache.room_for_one_more``), the captured graph is replayed.  The tokens are given by the
+        one (a request at a page's edge gets its next page, pages that a window has passed go back:
+        the caller has asked ``cache.room_for_one_more``), the captured graph is replayed.  The tokens are given by the
         host, or on the device (int32, one per request, in the batch's order)."""
         graph = self.last_decode_graph
         cache = self.cache
-        grown = []
-        for index, seg in enumerate(graph.batch.segments):
-            if cache.length(seg.request) % PAGE_SIZE:
-                cache.bump(seg.request)
-            else:
-                cache.grow(seg.request, 1)
-                grown.append(index)
-        if grown:
-            graph.batch.refresh_rows(cache, grown)
+        advance = cache.advance_one
+        changed = [index for index, seg in enumerate(graph.batch.segments) if advance(seg.request)]
+        if changed:
+            graph.batch.refresh_rows(cache, changed)
         logits = graph.run_next(tokens, device_tokens)
         self.graph_replays += 1
         self.steps += 1

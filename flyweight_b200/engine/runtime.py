@@ -493,8 +493,6 @@ class Runtime:
         if len(segments) != len(tasks):
             return None
         cache = runner.cache
-        if any(group.window for group in cache.groups):
-            return None                      # a window may hand pages back between steps
         for task, segment in zip(tasks, segments):
             if segment.request != task.id or task.cancelled or task.pending != 1:
                 return None

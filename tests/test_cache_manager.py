@@ -195,3 +195,30 @@ def test_room_for_one_more_token_counts_the_requests_at_a_page_edge():
     assert cache.grow("a", 1) == (cache.slot("a"), PAGE_SIZE) and cache.length("a") == PAGE_SIZE + 1
     assert cache.groups[0].pool.n_free == 0 and not cache.room_for_one_more(["b"], width=4)
     cache.check()
+
+
+def test_advancing_token_by_token_keeps_the_tables_of_the_general_way():
+    """``advance_one`` (the short way of a decode step that follows its predecessor) against
+    ``pages_short`` + ``extend`` (what a planned step does): the same tables in a group with a window
+    and in one without, pages passed by the window given back at the same token."""
+    from flyweight_b200.cache import PAGE_SIZE
+    short, general = manager(num_pages=12, window=70), manager(num_pages=12, window=70)
+    for m in (short, general):
+        for name, length in (("a", 3), ("b", PAGE_SIZE)):
+            m.admit(name)
+            m.extend(name, length)
+    for step in range(5 * PAGE_SIZE):
+        assert short.room_for_one_more(["a", "b"], width=8)
+        changed = {name: short.advance_one(name) for name in ("a", "b")}
+        for name in ("a", "b"):
+            before = [list(group.tables[name]) for group in general.groups]
+            assert general.pages_short(name, general.length(name) + 1) == 0
+            general.extend(name, general.length(name) + 1, checked=True)
+            assert changed[name] == (before != [group.tables[name] for group in general.groups])
+        for mine, theirs in zip(short.groups, general.groups):
+            for name in ("a", "b"):
+                assert [p >= 0 for p in mine.tables[name]] == [p >= 0 for p in theirs.tables[name]]
+            assert mine.pool.n_used == theirs.pool.n_used
+        short.check()
+    assert short.groups[1].pool.n_used < short.groups[0].pool.n_used      # the window gave pages back
+    assert not short.room_for_one_more(["a", "b"], width=5)              # a table of six pages is too wide

@@ -379,3 +379,80 @@ def test_a_kernel_that_gave_up_is_noticed_while_requests_keep_running():
     finally:
         assert tensorcore.status() == 0          # the check that raised has read and cleared the word
         runtime.runner = None                    # (closing would run the health check once more)
+
+
+def windowed_toy_architecture():
+    """Defined only here, from the framework's own parts (so its decode steps are recorded as graphs):
+    two attention layers, the first with a sliding window of 70 keys and so with pages of its own."""
+    from flyweight_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from flyweight_b200.parts.model import DecoderModel
+
+    class WindowConfig:
+        architectures = ("ToyWindowForCausalLM",)
+
+        def __init__(self, raw):
+            self.raw = dict(raw)
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw)
+
+        def to_dict(self):
+            return dict(self.raw)
+
+        def model_spec(self):
+            H, V = self.raw["hidden_size"], self.raw["vocab_size"]
+            norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": name})
+            attn = lambda i, window: PartSpec("gqa_attention", {
+                "hidden_size": H, "num_heads": 2, "num_kv_heads": 1, "head_dim": H // 2, "qk_norm_eps": 1e-5,
+                "window": window, "position": PartSpec("rope_half_split", {"theta": 100.0, "rotary_dim": H // 2})},
+                {k: f"l{i}.attn.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")})
+            ffn = lambda i: PartSpec("swiglu", {"hidden_size": H, "ffn_dim": 2 * H},
+                                     {"gate": f"l{i}.gate", "up": f"l{i}.up", "down": f"l{i}.down"})
+            layers = tuple(LayerSpec("prenorm_residual", norm(f"l{i}.n1"), attn(i, window), norm(f"l{i}.n2"), ffn(i))
+                           for i, window in enumerate((self.raw["window"], 0)))
+            return ModelSpec("ToyWindowForCausalLM", H, V, 512, "embed", norm("final"), None, layers,
+                             (ScheduleEntry(0), ScheduleEntry(1)))
+
+    class ToyWindowForCausalLM(DecoderModel):
+        def __init__(self, config, precision, device):
+            self.config = config
+            super().__init__(config.model_spec(), precision, device)
+
+    register_architecture("ToyWindowForCausalLM", WindowConfig, ToyWindowForCausalLM)
+    return {"architectures": ["ToyWindowForCausalLM"], "hidden_size": 32, "vocab_size": 50, "window": 70}
+
+
+def test_steady_decoding_with_a_sliding_window(tmp_path):
+    """A model with a window group goes the short ways too: the graph is replayed for the same requests
+    while the window hands pages back and page edges bring new ones.  Same tokens as the long way, and
+    the window's group holds fewer pages than the group that keeps every key."""
+    from flyweight_b200 import Model
+    from tiny_configs import make_model_dir
+    folder = make_model_dir(tmp_path / "toy_window", windowed_toy_architecture(), seed=4, dtype=torch.float32)
+    rng = np.random.default_rng(5)
+    prompts = [[int(t) for t in rng.integers(0, 50, size=n)] for n in (30, 100, 130)]
+    settings = dict(temperature=0.9, top_k=0, top_p=0.95)
+
+    def run(steady):
+        with Model(folder, dtype="float32").native_runtime(context_limit=512, parallel_sequences=3,
+                                                           graph_after=0) as runtime:
+            assert runtime.runner.model.graph_safe
+            runtime.steady_decode = steady
+            ids = [runtime.task_submit(p, 200 + 10 * i, seed=11 + i, **(settings if i else {}))
+                   for i, p in enumerate(prompts)]
+            groups = runtime.runner.cache.groups
+            assert [g.window for g in groups] == [70, 0]
+            windowed = kept = 0
+            while runtime.has_work():
+                runtime.engine_step()
+                windowed, kept = max(windowed, groups[0].pool.n_used), max(kept, groups[1].pool.n_used)
+                runtime.runner.cache.check()
+            assert groups[0].pool.n_used == 0 and groups[1].pool.n_used == 0
+            return [runtime.task(i).generated for i in ids], runtime.info["steady_steps"], windowed, kept
+
+    fast, steady_steps, windowed, kept = run(True)
+    slow, none, windowed_slow, kept_slow = run(False)
+    assert fast == slow and [len(g) for g in fast] == [200, 210, 220]
+    assert steady_steps > 150 and none == 0
+    assert windowed <= 9 < kept == kept_slow              # three requests, at most three pages of a window each
