@@ -12,10 +12,14 @@
 //   decode kernel:  one CTA = one token, one KV head, one slice of the context ("split");
 //       the group's heads are the (padded) 16 rows, the 4 warps take 16 keys each of every
 //       64-key tile; warps and then splits are merged with the usual (max, sum, acc) rule --
-//       splits through a small fp32 scratch buffer and a second kernel.
+//       splits through a small fp32 scratch buffer and a second kernel, or inside the kernel as a
+//       cluster.  At head sizes 64 and 128 the K and V tiles come by TMA: a (page, KV head) tile of
+//       the pool is one box of a tensor map (two at head size 128), one thread asks for it and an
+//       mbarrier says when it has landed; the 128-byte swizzle the copy leaves is what the
+//       ldmatrix addresses undo.  Other head sizes are copied by cp.async into padded rows.
 //
 // Key tiles start at multiples of 64 and are visited in ascending order, whatever the cut.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 using namespace fwb;
 
@@ -27,6 +31,7 @@ constexpr int WARPS = 4;
 // operations (fp32, relative error 2^-22); running maxima and the partial results of context
 // slices live in the same domain.
 constexpr float LOG2E = 1.4426950408889634f;
+int g_decode_tma = 1;               // test switch: 0 sends head sizes 64 and 128 down the cp.async way too
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -71,8 +76,16 @@ struct Smem {
     static constexpr int ROW = HD + 8;                     // bf16 elements; +16 bytes: no bank conflicts
     static constexpr int TILE = KEYS * ROW;                // one K or V tile
     static constexpr int BYTES = 2 * 2 * TILE * 2;         // 2 stages x (K, V) x bf16
-    static constexpr int DEEP_BYTES = decode_stages<HD>() * 2 * TILE * 2;
 };
+
+// Where 8 channels (one 16-byte chunk) of a key lie in a tile.  Padded rows (cp.async), or what a
+// TMA box of [64 keys][64 channels] with the 128-byte swizzle leaves: rows of 128 bytes whose chunks
+// are XOR-ed with the row number mod 8; a head of 128 channels is two such boxes, one after the other.
+template <int HD, bool SWZ>
+__device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* tile, int key, int chunk) {
+    if (!SWZ) return tile + key * Smem<HD>::ROW + chunk * 8;
+    return tile + (chunk >> 3) * (KEYS * 64) + key * 64 + (((chunk & 7) ^ (key & 7)) << 3);
+}
 
 // Copy one (page, kv head) tile of K and of V into shared memory (whole CTA).
 template <int HD>
@@ -90,17 +103,17 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
 // Rows of a V tile past the last key anybody may see hold whatever the page held before
 // (or nothing yet); their probabilities are exactly 0, but 0 * garbage must stay 0, so the
 // rows are cleared.  Called by the whole CTA between two barriers.
-template <int HD>
+template <int HD, bool SWZ = false>
 __device__ __forceinline__ void clear_v_rows(__nv_bfloat16* vs, int first_row) {
     constexpr int CHUNKS = HD / 8;
     for (int i = threadIdx.x; i < (KEYS - first_row) * CHUNKS; i += WARPS * 32) {
         const int r = first_row + i / CHUNKS, c = i % CHUNKS;
-        *reinterpret_cast<uint4*>(vs + r * Smem<HD>::ROW + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(tile_at<HD, SWZ>(vs, r, c))) = make_uint4(0u, 0u, 0u, 0u);
     }
 }
 
 // One warp: S[16 x NK*8] += Q[16 x HD] * K[keys][HD]^T for the keys that start at `key0`.
-template <int HD, int NT>
+template <int HD, int NT, bool SWZ = false>
 __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qf)[HD / 16][4],
                                         const __nv_bfloat16* ks, int key0, int lane) {
 #pragma unroll
@@ -115,7 +128,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qf)[
 #pragma unroll
         for (int n = 0; n < NT; n += 2) {
             uint32_t b[4];
-            ldmatrix_x4(b, ks + (key0 + n * 8 + key_off) * Smem<HD>::ROW + k * 16 + d_off);
+            ldmatrix_x4(b, tile_at<HD, SWZ>(ks, key0 + n * 8 + key_off, 2 * k + (d_off >> 3)));
             mma_bf16(s[n], qf[k], b[0], b[1]);
             mma_bf16(s[n + 1], qf[k], b[2], b[3]);
         }
@@ -123,7 +136,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qf)[
 }
 
 // One warp: O[16 x HD] += P[16 x NT*8] * V[keys][HD], P taken from the score registers.
-template <int HD, int NT>
+template <int HD, int NT, bool SWZ = false>
 __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&p)[NT][4],
                                         const __nv_bfloat16* vs, int key0, int lane) {
     // ldmatrix.x4.trans: matrices (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
@@ -139,7 +152,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&p)[
 #pragma unroll
         for (int n = 0; n < HD / 8; n += 2) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, vs + (key0 + kk * 16 + key_off) * Smem<HD>::ROW + n * 8 + d_off);
+            ldmatrix_x4_trans(b, tile_at<HD, SWZ>(vs, key0 + kk * 16 + key_off, n + (d_off >> 3)));
             mma_bf16(o[n], a, b[0], b[1]);
             mma_bf16(o[n + 1], a, b[2], b[3]);
         }
@@ -316,18 +329,29 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 // grid (splits, nkv, T).  A split covers `tiles_per_split` key tiles; with splits == 1 the
 // result goes straight to `out`, else (acc, max, sum) go to the scratch buffers:
 //   part_o[t][kvh][split][group][HD] fp32 (not normalised), part_ml[t][kvh][split][group][2].
-template <int HD, bool CLUSTER, bool DEEP>
+//
+// TMA: the tiles are boxes of the tensor maps `map_k` / `map_v` over the pools seen as
+// [pages * nkv * 64 keys][HD] (head sizes 64 and 128; the maps are not read otherwise).  Thread 0
+// asks for a tile's boxes and arms the stage's mbarrier with their bytes; every thread waits on that
+// barrier itself (bounded: after the limit the library's status word is raised and nobody waits again).
+template <int HD, bool CLUSTER, bool DEEP, bool TMA>
 __global__ void __launch_bounds__(WARPS * 32)
-attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
                         const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                         int max_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int group, int tiles_per_split,
-                        int window, float scale) {
+                        int window, float scale, int* status) {
     fwb::pdl_launch_dependents();
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(16) uint8_t smem_dynamic[];
+    // the swizzle of a TMA box counts rows from a 1024-byte boundary
+    uint8_t* smem_raw = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dynamic) + 1023) & ~uintptr_t(1023))
+                            : smem_dynamic;
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __shared__ float merge_ml[WARPS][16][2];
+    __shared__ uint64_t full_bar[4];
+    __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, tok = blockIdx.z;
@@ -344,11 +368,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     if (tile_end > last_tile + 1) tile_end = last_tile + 1;
 
     constexpr int DECODE_STAGES = DEEP ? decode_stages<HD>() : 2;
+    constexpr int TILE = TMA ? KEYS * HD : Smem<HD>::TILE;  // elements of one K or V tile in shared memory
     // A ring of DECODE_STAGES key/value tiles: a slice of eight tiles has half of its bytes in
     // flight from the start (two stages left the memory pipe waiting on every tile's round trip).
-    auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
-    auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
+    auto stage_k = [&](int s) { return smem + s * 2 * TILE; };
+    auto stage_v = [&](int s) { return smem + s * 2 * TILE + TILE; };
+    if (TMA) {
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < DECODE_STAGES; ++s) tc5::mbar_init(&full_bar[s], 1);
+            abort_flag = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+    }
     auto issue = [&](int tile, int s) {
+        if (TMA) {
+            if (threadIdx.x == 0 && tile < tile_end) {
+                // the stage was read (and, in a token's last tile, cleared) through ordinary loads and stores
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc5::mbar_expect_tx(&full_bar[s], 2 * TILE * 2);
+                const int row = (table[tile] * nkv + kvh) * KEYS;
+#pragma unroll
+                for (int x = 0; x < HD / 64; ++x) {
+                    tc5::tma_load_2d(stage_k(s) + x * KEYS * 64, &map_k, &full_bar[s], x * 64, row);
+                    tc5::tma_load_2d(stage_v(s) + x * KEYS * 64, &map_v, &full_bar[s], x * 64, row);
+                }
+            }
+            return;
+        }
         if (tile < tile_end) {
             const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
             load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
@@ -384,16 +431,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const int s = (tile - tile_begin) % DECODE_STAGES;
         // the slot this tile's successor-but-two goes to was read in the iteration before this one
         issue(tile + DECODE_STAGES - 1, (tile - tile_begin + DECODE_STAGES - 1) % DECODE_STAGES);
-        cp_async_wait<DECODE_STAGES - 1>();
-        __syncthreads();
+        if (TMA) {
+            // the tile's bytes have landed when its barrier's phase completes; a thread that has
+            // seen that may read them
+            tc5::mbar_wait(&full_bar[s], (uint32_t)((tile - tile_begin) / DECODE_STAGES) & 1u, &abort_flag, 21, status);
+        } else {
+            cp_async_wait<DECODE_STAGES - 1>();
+            __syncthreads();
+        }
         if (pos - tile * KEYS + 1 < KEYS) {
-            clear_v_rows<HD>(stage_v(s), pos - tile * KEYS + 1);
+            clear_v_rows<HD, TMA>(stage_v(s), pos - tile * KEYS + 1);
             __syncthreads();
         }
         float sc[2][4];                                     // this warp's 16 keys of the tile
-        qk_tile<HD, 2>(sc, qf, stage_k(s), warp * 16, lane);
+        qk_tile<HD, 2, TMA>(sc, qf, stage_k(s), warp * 16, lane);
         softmax_update<HD, 2>(sc, o, m, l, tile * KEYS + warp * 16, lo, hi, scale, lane);
-        pv_tile<HD, 2>(o, sc, stage_v(s), warp * 16, lane);
+        pv_tile<HD, 2, TMA>(o, sc, stage_v(s), warp * 16, lane);
         __syncthreads();
     }
 
@@ -555,21 +608,26 @@ int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const 
     return fwb_launch_status();
 }
 
-template <int HD>
-int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* positions,
-                  const int* tok_seg, const int* block_table, int max_pages, void* out, float* part_o,
-                  float* part_ml, int T, int nh, int nkv, int splits, int tiles_per_split, int window,
-                  float scale, bool in_cluster, cudaStream_t stream) {
+template <int HD, bool TMA>
+int launch_decode_as(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* q, const void* k_pool,
+                     const void* v_pool, const int* positions, const int* tok_seg, const int* block_table,
+                     int max_pages, void* out, float* part_o, float* part_ml, int T, int nh, int nkv, int splits,
+                     int tiles_per_split, int window, float scale, bool in_cluster, cudaStream_t stream) {
     constexpr size_t merge_bytes = (size_t)(WARPS + 1) * 16 * HD * 4 + 16 * 2 * 4;
     // few CTAs (at most three per SM): the deep ring; else two stages and more CTAs per SM
     const bool deep = (long)splits * nkv * T <= 3 * 148;
-    constexpr size_t shallow_bytes = Smem<HD>::BYTES > merge_bytes ? Smem<HD>::BYTES : merge_bytes;
-    constexpr size_t deep_bytes = Smem<HD>::DEEP_BYTES > merge_bytes ? Smem<HD>::DEEP_BYTES : merge_bytes;
+    // TMA tiles are not padded, but start on a 1024-byte boundary
+    constexpr size_t tile_bytes = TMA ? (size_t)KEYS * HD * 2 : (size_t)Smem<HD>::TILE * 2;
+    constexpr size_t slack = TMA ? 1024 : 0;
+    constexpr size_t shallow_ring = 2 * 2 * tile_bytes, deep_ring = decode_stages<HD>() * 2 * tile_bytes;
+    constexpr size_t shallow_bytes = (shallow_ring > merge_bytes ? shallow_ring : merge_bytes) + slack;
+    constexpr size_t deep_bytes = (deep_ring > merge_bytes ? deep_ring : merge_bytes) + slack;
     const size_t bytes = deep ? deep_bytes : shallow_bytes;
+    int* status = tc5::status_word();
     using bf = __nv_bfloat16;
     if (splits > 1 && in_cluster) {
         // the slices of a (token, KV head) as a cluster: merged through distributed shared memory
-        auto kernel = deep ? attention_decode_kernel<HD, true, true> : attention_decode_kernel<HD, true, false>;
+        auto kernel = deep ? attention_decode_kernel<HD, true, true, TMA> : attention_decode_kernel<HD, true, false, TMA>;
         int st = opt_in_smem(kernel, bytes);
         if (st != FWB_OK) return st;
         cudaLaunchConfig_t config = {};
@@ -586,23 +644,46 @@ int launch_decode(const void* q, const void* k_pool, const void* v_pool, const i
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         config.attrs = attr;
         config.numAttrs = pdl_enabled() ? 2 : 1;
-        cudaError_t e = cudaLaunchKernelEx(&config, kernel, (const bf*)q, (const bf*)k_pool, (const bf*)v_pool,
-                                           positions, tok_seg, block_table, max_pages, (bf*)out,
+        cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_k, map_v, (const bf*)q, (const bf*)k_pool,
+                                           (const bf*)v_pool, positions, tok_seg, block_table, max_pages, (bf*)out,
                                            (float*)nullptr, (float*)nullptr, nh, nkv, nh / nkv,
-                                           tiles_per_split, window, scale * LOG2E);
+                                           tiles_per_split, window, scale * LOG2E, status);
         return e == cudaSuccess ? fwb_launch_status() : (int)e;
     }
-    auto kernel = deep ? attention_decode_kernel<HD, false, true> : attention_decode_kernel<HD, false, false>;
+    auto kernel = deep ? attention_decode_kernel<HD, false, true, TMA> : attention_decode_kernel<HD, false, false, TMA>;
     int st = opt_in_smem(kernel, bytes);
     if (st != FWB_OK) return st;
     fwb::pdl(kernel, dim3(splits, nkv, T), WARPS * 32, bytes, stream)(
-        (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
-        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E);
+        map_k, map_v, (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
+        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E, status);
     st = fwb_launch_status();
     if (st != FWB_OK || splits == 1) return st;
     fwb::pdl(attention_merge_kernel, dim3(nkv, T), 128, 0, stream)(part_o, part_ml, (bf*)out, nh, nkv, nh / nkv, HD,
                                                              splits);
     return fwb_launch_status();
+}
+
+// `num_pages` > 0 (the pools' first extent) lets head sizes 64 and 128 take their tiles by TMA.
+template <int HD>
+int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* positions,
+                  const int* tok_seg, const int* block_table, int max_pages, int num_pages, void* out,
+                  float* part_o, float* part_ml, int T, int nh, int nkv, int splits, int tiles_per_split,
+                  int window, float scale, bool in_cluster, cudaStream_t stream) {
+    CUtensorMap map_k, map_v;
+    memset(&map_k, 0, sizeof(map_k));
+    memset(&map_v, 0, sizeof(map_v));
+    if constexpr (HD == 64 || HD == 128) {
+        const long pool_rows = (long)num_pages * nkv * KEYS;
+        const bool aligned = ((((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15) == 0;
+        if (g_decode_tma && num_pages > 0 && aligned && pool_rows <= 2147483647L &&
+            tc5::make_map(&map_k, k_pool, pool_rows, HD, KEYS) && tc5::make_map(&map_v, v_pool, pool_rows, HD, KEYS))
+            return launch_decode_as<HD, true>(map_k, map_v, q, k_pool, v_pool, positions, tok_seg, block_table,
+                                              max_pages, out, part_o, part_ml, T, nh, nkv, splits, tiles_per_split,
+                                              window, scale, in_cluster, stream);
+    }
+    return launch_decode_as<HD, false>(map_k, map_v, q, k_pool, v_pool, positions, tok_seg, block_table, max_pages,
+                                       out, part_o, part_ml, T, nh, nkv, splits, tiles_per_split, window, scale,
+                                       in_cluster, stream);
 }
 
 bool shape_ok(int nh, int nkv, int hd, int page_size) {
@@ -648,20 +729,29 @@ FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const v
 // Decode tokens: one query token each.  The slices of the context are merged either inside the
 // kernel (`merge_in_cluster` != 0, splits <= 8: the slices form a thread-block cluster; best
 // while the launch has few CTAs) or by a second kernel through scratch: part_o needs
-// T*nkv*splits*group*hd floats and part_ml T*nkv*splits*group*2 floats.
+// T*nkv*splits*group*hd floats and part_ml T*nkv*splits*group*2 floats.  num_pages: the pools'
+// first extent (0: unknown, no TMA).
 FWB_API int fwb_attention_decode_mma(const void* q, const void* k_pool, const void* v_pool,
                                      const int* positions, const int* tok_seg, const int* block_table,
-                                     int max_pages, int page_size, void* out, float* part_o, float* part_ml,
-                                     int T, int nh, int nkv, int hd, int splits, int tiles_per_split,
-                                     int window, float scale, int merge_in_cluster, cudaStream_t stream) {
+                                     int max_pages, int page_size, int num_pages, void* out, float* part_o,
+                                     float* part_ml, int T, int nh, int nkv, int hd, int splits,
+                                     int tiles_per_split, int window, float scale, int merge_in_cluster,
+                                     cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!q || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out) return FWB_BAD_ARGUMENT;
     if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
     const bool in_cluster = merge_in_cluster != 0 && splits <= 8;
     if (splits < 1 || tiles_per_split < 1 || (splits > 1 && !in_cluster && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
 #define CALL(HD)                                                                                          \
-    launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, out, part_o, part_ml, T, \
-                      nh, nkv, splits, tiles_per_split, window, scale, in_cluster, stream)
+    launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, num_pages, out, part_o,  \
+                      part_ml, T, nh, nkv, splits, tiles_per_split, window, scale, in_cluster, stream)
     FWB_HD_SWITCH(hd, CALL)
 #undef CALL
+}
+
+// Test switch: whether head sizes 64 and 128 take their key and value tiles by TMA (the default) or by
+// cp.async like the other head sizes.  Both give the same bits: the arithmetic does not change.
+FWB_API int fwb_attention_decode_set_tma(int on) {
+    g_decode_tma = on ? 1 : 0;
+    return FWB_OK;
 }

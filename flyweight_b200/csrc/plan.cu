@@ -50,7 +50,7 @@ int fwb_attention_prefill_tcgen05(const void*, const void*, const void*, const i
                                   const int*, const int*, int, int, int, void*, int, int, int, int, int, int,
                                   float, cudaStream_t);
 int fwb_attention_decode_mma(const void*, const void*, const void*, const int*, const int*, const int*, int,
-                             int, void*, float*, float*, int, int, int, int, int, int, int, float, int,
+                             int, int, void*, float*, float*, int, int, int, int, int, int, int, float, int,
                              cudaStream_t);
 }
 
@@ -448,7 +448,7 @@ void run_decode_attention(Launches& L, const Op& op, const FwbStep& step, const 
     const bool merged_in_kernel = in_cluster && splits > 1 && splits <= 8;
     const bool scratch = splits > 1 && !merged_in_kernel;
     L.add(fwb_attention_decode_mma(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS), meta(step, META_TOK_SEG),
-                                   table, width, op.page_size, op.out, scratch ? op.part_o : nullptr,
+                                   table, width, op.page_size, op.num_pages, op.out, scratch ? op.part_o : nullptr,
                                    scratch ? op.part_ml : nullptr, n_tokens, op.nh, op.nkv, op.hd, splits,
                                    tiles_per_split, op.window, op.scale, merged_in_kernel ? 1 : 0, stream),
           scratch ? 2 : 1);

@@ -96,11 +96,15 @@ def run_attention_decode(args) -> dict:
     if args.splits:
         splits, per, in_cluster = args.splits, -(-width // args.splits), args.cluster_merge
     scale = 1.0 / math.sqrt(args.head_dim)
+    ops.set_decode_attention_tma(not args.cp_async)
     us = _time(lambda: ops.attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, table,
                                                 args.heads, 0, scale, splits, per, in_cluster), args.repeat)
+    ops.set_decode_attention_tma(True)
     kv_bytes = B * ctx * args.kv_heads * args.head_dim * 2 * 2
+    from . import tensorcore
     return {"kernel": "attention_decode_mma", "batch": B, "context": ctx, "splits": splits,
-            "us": us, "kv_gb_s": kv_bytes / us / 1e3}
+            "tiles_by": "cp.async" if args.cp_async or args.head_dim not in (64, 128) else "tma",
+            "us": us, "kv_gb_s": kv_bytes / us / 1e3, "status": tensorcore.status()}
 
 
 def run_attention_prefill(args) -> dict:
@@ -231,6 +235,7 @@ def main(argv=None) -> int:
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--mma-sync", action="store_true", help="the mma.sync prompt kernel")
         p.add_argument("--cluster-merge", action="store_true", help="with --splits <= 8: merge inside the kernel")
+        p.add_argument("--cp-async", action="store_true", help="decode: key and value tiles by cp.async, not TMA")
     conv = sub.add_parser("shortconv")
     conv.add_argument("--tokens", type=int, default=2048)
     conv.add_argument("--hidden", type=int, default=2048)

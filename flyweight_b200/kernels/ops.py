@@ -335,6 +335,12 @@ def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg,
     return out
 
 
+def set_decode_attention_tma(on: bool) -> None:
+    """Test switch: whether the decode attention kernel takes its key and value tiles by TMA at head
+    sizes 64 and 128 (the default) or by cp.async, as at the other head sizes.  The same bits."""
+    lib.call("fwb_attention_decode_set_tma", 1 if on else 0)
+
+
 def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_heads, window, scale,
                          splits: int, tiles_per_split: int, merge_in_cluster: bool = False,
                          out=None, n_tokens=None) -> torch.Tensor:
@@ -366,7 +372,7 @@ def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_h
         part_o = torch.empty((T, n_kv, splits, group, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((T, n_kv, splits, group, 2), dtype=torch.float32, device=q.device)
     lib.call("fwb_attention_decode_mma", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
-             ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size, ptr(out), ptr(part_o),
+             ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size, k_pool.shape[0], ptr(out), ptr(part_o),
              ptr(part_ml), T, n_heads, n_kv, head_dim, splits, tiles_per_split, window,
              c_float(scale), 1 if in_cluster else 0, stream(),
              launches=2 if (splits > 1 and not in_cluster) else 1)

@@ -902,6 +902,22 @@ def test_decode_attention_over_split_contexts(nh, nkv, hd, window):
         got = ops.attention_decode_mma(qd, cache.k_pool, cache.v_pool, ctx.batch.positions, ctx.batch.tok_seg,
                                        table_dev, nh, window, scale, splits, per, merge_in_cluster=True)
         close(got.reshape(-1, nh, hd), want, 2.0 ** -7, f"{splits} splits in a cluster")
+    if hd in (64, 128):
+        # at these head sizes the tiles come by TMA (swizzled boxes, an mbarrier a stage); by cp.async
+        # into padded rows the same numbers go through the same arithmetic: the same bits
+        for splits, per, cluster in ((1, 24, False), (5, 5, False), (24, 1, False), (3, 8, True), (8, 3, True)):
+            run = lambda: ops.attention_decode_mma(qd, cache.k_pool, cache.v_pool, ctx.batch.positions,
+                                                   ctx.batch.tok_seg, table_dev, nh, window, scale, splits, per,
+                                                   merge_in_cluster=cluster)
+            by_tma = run()
+            try:
+                ops.set_decode_attention_tma(False)
+                by_cp_async = run()
+            finally:
+                ops.set_decode_attention_tma(True)
+            assert torch.equal(by_tma, by_cp_async), (splits, per, cluster)
+    from flyweight_b200.kernels import tensorcore
+    assert tensorcore.status() == 0
 
 
 def test_tensor_core_attention_finds_a_far_key_and_the_window_edge():
