@@ -32,6 +32,8 @@ constexpr int WARPS = 4;
 // slices live in the same domain.
 constexpr float LOG2E = 1.4426950408889634f;
 int g_decode_tma = 1;               // test switch: 0 sends head sizes 64 and 128 down the cp.async way too
+int g_decode_tma_stages = 0;        // test switch: ring depth of the TMA way (0: chosen by the launcher)
+constexpr int MAX_TMA_STAGES = 8;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -342,7 +344,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                         int max_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int group, int tiles_per_split,
-                        int window, float scale, int* status) {
+                        int window, float scale, int* status, int tma_stages) {
     fwb::pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t smem_dynamic[];
     // the swizzle of a TMA box counts rows from a 1024-byte boundary
@@ -350,7 +352,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                             : smem_dynamic;
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __shared__ float merge_ml[WARPS][16][2];
-    __shared__ uint64_t full_bar[4];
+    __shared__ uint64_t full_bar[MAX_TMA_STAGES];
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -367,7 +369,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     int tile_end = tile_begin + tiles_per_split;
     if (tile_end > last_tile + 1) tile_end = last_tile + 1;
 
-    constexpr int DECODE_STAGES = DEEP ? decode_stages<HD>() : 2;
+    // cp.async: two stages, or the deep ring; TMA: as many as the launcher found room for
+    const int DECODE_STAGES = TMA ? tma_stages : (DEEP ? decode_stages<HD>() : 2);
     constexpr int TILE = TMA ? KEYS * HD : Smem<HD>::TILE;  // elements of one K or V tile in shared memory
     // A ring of DECODE_STAGES key/value tiles: a slice of eight tiles has half of its bytes in
     // flight from the start (two stages left the memory pipe waiting on every tile's round trip).
@@ -436,7 +439,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             // seen that may read them
             tc5::mbar_wait(&full_bar[s], (uint32_t)((tile - tile_begin) / DECODE_STAGES) & 1u, &abort_flag, 21, status);
         } else {
-            cp_async_wait<DECODE_STAGES - 1>();
+            cp_async_wait<(DEEP ? decode_stages<HD>() : 2) - 1>();
             __syncthreads();
         }
         if (pos - tile * KEYS + 1 < KEYS) {
@@ -622,7 +625,26 @@ int launch_decode_as(const CUtensorMap& map_k, const CUtensorMap& map_v, const v
     constexpr size_t shallow_ring = 2 * 2 * tile_bytes, deep_ring = decode_stages<HD>() * 2 * tile_bytes;
     constexpr size_t shallow_bytes = (shallow_ring > merge_bytes ? shallow_ring : merge_bytes) + slack;
     constexpr size_t deep_bytes = (deep_ring > merge_bytes ? deep_ring : merge_bytes) + slack;
-    const size_t bytes = deep ? deep_bytes : shallow_bytes;
+    size_t bytes = deep ? deep_bytes : shallow_bytes;
+    int stages = 0;
+    if (TMA) {
+        // as deep a ring as lets the CTAs that share an SM all fit (registers allow five at head size
+        // 64, three at 128), and no deeper than a slice is long: a CTA more on an SM is worth more
+        // than a stage more in the ring (8 x 4,096 keys: 15.4 us with three stages, 21.7 with four).
+        // (Six CTAs an SM, with the registers capped at 80, were slower: 64 x 4,096 keys 90 -> 94 us.)
+        const long ctas = (long)splits * nkv * T;
+        const long most = HD <= 64 ? 5 : 3;
+        long resident = (ctas + 147) / 148;
+        resident = resident < 1 ? 1 : (resident > most ? most : resident);
+        const size_t room = (size_t)(220 * 1024) / (size_t)resident - slack;
+        stages = (int)(room / (2 * tile_bytes));
+        stages = stages > MAX_TMA_STAGES ? MAX_TMA_STAGES : stages;
+        stages = stages > tiles_per_split ? tiles_per_split : stages;
+        stages = stages < 2 ? 2 : stages;
+        if (g_decode_tma_stages >= 2 && g_decode_tma_stages <= MAX_TMA_STAGES) stages = g_decode_tma_stages;
+        const size_t ring = (size_t)stages * 2 * tile_bytes;
+        bytes = (ring > merge_bytes ? ring : merge_bytes) + slack;
+    }
     int* status = tc5::status_word();
     using bf = __nv_bfloat16;
     if (splits > 1 && in_cluster) {
@@ -647,7 +669,7 @@ int launch_decode_as(const CUtensorMap& map_k, const CUtensorMap& map_v, const v
         cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_k, map_v, (const bf*)q, (const bf*)k_pool,
                                            (const bf*)v_pool, positions, tok_seg, block_table, max_pages, (bf*)out,
                                            (float*)nullptr, (float*)nullptr, nh, nkv, nh / nkv,
-                                           tiles_per_split, window, scale * LOG2E, status);
+                                           tiles_per_split, window, scale * LOG2E, status, stages);
         return e == cudaSuccess ? fwb_launch_status() : (int)e;
     }
     auto kernel = deep ? attention_decode_kernel<HD, false, true, TMA> : attention_decode_kernel<HD, false, false, TMA>;
@@ -655,7 +677,7 @@ int launch_decode_as(const CUtensorMap& map_k, const CUtensorMap& map_v, const v
     if (st != FWB_OK) return st;
     fwb::pdl(kernel, dim3(splits, nkv, T), WARPS * 32, bytes, stream)(
         map_k, map_v, (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
-        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E, status);
+        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E, status, stages);
     st = fwb_launch_status();
     if (st != FWB_OK || splits == 1) return st;
     fwb::pdl(attention_merge_kernel, dim3(nkv, T), 128, 0, stream)(part_o, part_ml, (bf*)out, nh, nkv, nh / nkv, HD,
@@ -750,8 +772,10 @@ FWB_API int fwb_attention_decode_mma(const void* q, const void* k_pool, const vo
 }
 
 // Test switch: whether head sizes 64 and 128 take their key and value tiles by TMA (the default) or by
-// cp.async like the other head sizes.  Both give the same bits: the arithmetic does not change.
-FWB_API int fwb_attention_decode_set_tma(int on) {
+// cp.async like the other head sizes, and how deep the TMA way's ring is (0: the launcher's choice).
+// All give the same bits: the arithmetic does not change.
+FWB_API int fwb_attention_decode_set_tma(int on, int stages) {
     g_decode_tma = on ? 1 : 0;
+    g_decode_tma_stages = stages;
     return FWB_OK;
 }

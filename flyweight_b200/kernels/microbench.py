@@ -96,7 +96,7 @@ def run_attention_decode(args) -> dict:
     if args.splits:
         splits, per, in_cluster = args.splits, -(-width // args.splits), args.cluster_merge
     scale = 1.0 / math.sqrt(args.head_dim)
-    ops.set_decode_attention_tma(not args.cp_async)
+    ops.set_decode_attention_tma(not args.cp_async, args.stages)
     us = _time(lambda: ops.attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, table,
                                                 args.heads, 0, scale, splits, per, in_cluster), args.repeat)
     ops.set_decode_attention_tma(True)
@@ -236,6 +236,7 @@ def main(argv=None) -> int:
         p.add_argument("--mma-sync", action="store_true", help="the mma.sync prompt kernel")
         p.add_argument("--cluster-merge", action="store_true", help="with --splits <= 8: merge inside the kernel")
         p.add_argument("--cp-async", action="store_true", help="decode: key and value tiles by cp.async, not TMA")
+        p.add_argument("--stages", type=int, default=0, help="decode by TMA: ring depth, 2 to 8 (0: the launcher's choice)")
     conv = sub.add_parser("shortconv")
     conv.add_argument("--tokens", type=int, default=2048)
     conv.add_argument("--hidden", type=int, default=2048)

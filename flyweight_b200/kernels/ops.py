@@ -335,10 +335,11 @@ def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg,
     return out
 
 
-def set_decode_attention_tma(on: bool) -> None:
+def set_decode_attention_tma(on: bool, stages: int = 0) -> None:
     """Test switch: whether the decode attention kernel takes its key and value tiles by TMA at head
-    sizes 64 and 128 (the default) or by cp.async, as at the other head sizes.  The same bits."""
-    lib.call("fwb_attention_decode_set_tma", 1 if on else 0)
+    sizes 64 and 128 (the default) or by cp.async, as at the other head sizes; and the depth of the TMA
+    way's ring (2 to 8; 0: the launcher's choice).  The same bits."""
+    lib.call("fwb_attention_decode_set_tma", 1 if on else 0, int(stages))
 
 
 def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_heads, window, scale,
