@@ -427,7 +427,24 @@ void run_linear_residual(Launches& L, const Op& op, const FwbStep& step, bool& p
     pending = true;
 }
 
-void decode_splits(int n_tokens, int n_kv, int max_tiles, int& splits, int& tiles_per_split, bool& in_cluster) {
+void decode_splits(int n_tokens, int n_kv, int max_tiles, int head_dim, int& splits, int& tiles_per_split,
+                   bool& in_cluster) {
+    // (the same rule as kernels/attention.py: decode_splits)
+    const long pairs = (long)n_tokens * n_kv;
+    if (pairs >= 3 * SM_COUNT) {
+        const long resident = (long)SM_COUNT * (head_dim <= 64 ? 5 : 3);
+        for (int s = 1; s <= 16; s *= 2) {
+            if (s * 64 < max_tiles || (s > 1 && max_tiles < 4 * s)) continue;
+            const long ctas = pairs * s;
+            const long rounds = (ctas + resident - 1) / resident;
+            if (ctas <= resident || (double)ctas >= 0.85 * (double)(rounds * resident)) {
+                tiles_per_split = ceil_div(max_tiles, s);
+                splits = ceil_div(max_tiles, tiles_per_split);
+                in_cluster = false;
+                return;
+            }
+        }
+    }
     int most = ceil_div(4 * SM_COUNT, n_tokens * n_kv > 1 ? n_tokens * n_kv : 1);
     most = most > 64 ? 64 : most;
     most = most < 16 ? 16 : most;
@@ -444,7 +461,7 @@ void run_decode_attention(Launches& L, const Op& op, const FwbStep& step, const 
                           int n_tokens, cudaStream_t stream) {
     int splits, tiles_per_split;
     bool in_cluster;
-    decode_splits(n_tokens, op.nkv, width, splits, tiles_per_split, in_cluster);
+    decode_splits(n_tokens, op.nkv, width, op.hd, splits, tiles_per_split, in_cluster);
     const bool merged_in_kernel = in_cluster && splits > 1 && splits <= 8;
     const bool scratch = splits > 1 && !merged_in_kernel;
     L.add(fwb_attention_decode_mma(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS), meta(step, META_TOK_SEG),

@@ -65,9 +65,25 @@ def force_tiled(flag: bool) -> None:
     lib.set_option("force_tiled", _force_tiled)
 
 
-def decode_splits(n_tokens: int, n_kv: int, max_tiles: int):
+def decode_splits(n_tokens: int, n_kv: int, max_tiles: int, head_dim: int = 64):
     """How many slices of the context run as separate CTAs.  Depends only on static sizes of the step
     (tokens, KV heads, block-table width), so a captured graph stays valid."""
+    pairs = n_tokens * n_kv
+    if pairs >= 3 * SM_COUNT:
+        # Many (token, KV head) pairs fill the GPU by themselves: slices only add their fixed costs and
+        # a merge kernel (64 x 4,096 keys: 83.7 us in one piece, 91.8 in eight slices; 256 x 512: 46.9
+        # against 59.6).  Cut only (a) so that no CTA walks more than 64 tiles -- the grid is laid out
+        # for the longest request of the step, and one long request among short ones must not walk its
+        # context alone -- and (b) when the CTAs would fill a last round of the SMs badly (128 x 4,096
+        # in one piece is 1.4 rounds: 182 us; in two slices 163 us).
+        resident = SM_COUNT * (5 if head_dim <= 64 else 3)
+        for splits in (1, 2, 4, 8, 16):
+            if splits * 64 < max_tiles or (splits > 1 and max_tiles < 4 * splits):
+                continue
+            ctas = pairs * splits
+            if ctas <= resident or ctas >= 0.85 * (-(-ctas // resident) * resident):
+                tiles_per_split = -(-max_tiles // splits)
+                return -(-max_tiles // tiles_per_split), tiles_per_split, False
     # measured on B200 (hd 64, 8 KV heads, batch 1..64, 4k..32k context): about eight 64-key tiles
     # per slice, at most 16 slices.  While the launch has few CTAs (small batches), up to 8 slices
     # that merge inside the kernel as a cluster beat more slices with a merge kernel; with many
@@ -93,7 +109,7 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
             and out_dtype == torch.bfloat16
             and ops.attention_mma_shape_ok(n_heads, n_kv, head_dim, page_size)):
         if batch.max_segment == 1 and not _force_tiled:
-            splits, tiles_per_split, in_cluster = decode_splits(batch.n_tokens, n_kv, block_table.shape[1])
+            splits, tiles_per_split, in_cluster = decode_splits(batch.n_tokens, n_kv, block_table.shape[1], head_dim)
             return ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg,
                                             block_table, n_heads, window, scale, splits,
                                             tiles_per_split, in_cluster)
@@ -106,7 +122,7 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
             # portions of prompts behind them the tiled kernels; both write their rows of `out`
             first = batch.leading_singles
             out = torch.empty_like(q)
-            splits, tiles_per_split, in_cluster = decode_splits(first, n_kv, block_table.shape[1])
+            splits, tiles_per_split, in_cluster = decode_splits(first, n_kv, block_table.shape[1], head_dim)
             ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg, block_table,
                                      n_heads, window, scale, splits, tiles_per_split, in_cluster,
                                      out=out, n_tokens=first)

@@ -92,7 +92,7 @@ def run_attention_decode(args) -> dict:
     q, k_pool, v_pool, table, width = _paged_inputs(B, ctx, 1, args.heads, args.kv_heads, args.head_dim)
     positions = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
     tok_seg = torch.arange(B, dtype=torch.int32, device="cuda")
-    splits, per, in_cluster = attention.decode_splits(B, args.kv_heads, width)
+    splits, per, in_cluster = attention.decode_splits(B, args.kv_heads, width, args.head_dim)
     if args.splits:
         splits, per, in_cluster = args.splits, -(-width // args.splits), args.cluster_merge
     scale = 1.0 / math.sqrt(args.head_dim)
