@@ -429,32 +429,28 @@ void run_linear_residual(Launches& L, const Op& op, const FwbStep& step, bool& p
 
 void decode_splits(int n_tokens, int n_kv, int max_tiles, int head_dim, int& splits, int& tiles_per_split,
                    bool& in_cluster) {
-    // (the same rule as kernels/attention.py: decode_splits)
-    const long pairs = (long)n_tokens * n_kv;
-    if (pairs >= 3 * SM_COUNT) {
-        const long resident = (long)SM_COUNT * (head_dim <= 64 ? 5 : 3);
-        for (int s = 1; s <= 16; s *= 2) {
-            if (s * 64 < max_tiles || (s > 1 && max_tiles < 4 * s)) continue;
+    // the same rule as kernels/attention.py: decode_splits (the measurements are quoted there): as many
+    // slices as keep every CTA resident at once, of 8 to 64 tiles; else the fewest that fill the SMs'
+    // last round to 85 %
+    const long pairs = (long)n_tokens * n_kv > 1 ? (long)n_tokens * n_kv : 1;
+    const long resident = (long)SM_COUNT * (head_dim <= 64 ? 5 : 3);
+    int least = 1;
+    while (least * 64 < max_tiles && least < 64) least *= 2;
+    int choice = 0;
+    for (int s = least; s <= 64 && pairs * s <= resident && (s == least || s * 8 <= max_tiles); s *= 2) choice = s;
+    if (!choice)
+        for (int s = least; s <= 64; s *= 2) {
             const long ctas = pairs * s;
             const long rounds = (ctas + resident - 1) / resident;
-            if (ctas <= resident || (double)ctas >= 0.85 * (double)(rounds * resident)) {
-                tiles_per_split = ceil_div(max_tiles, s);
-                splits = ceil_div(max_tiles, tiles_per_split);
-                in_cluster = false;
-                return;
+            if ((double)ctas >= 0.85 * (double)(rounds * resident)) {
+                choice = s;
+                break;
             }
         }
-    }
-    int most = ceil_div(4 * SM_COUNT, n_tokens * n_kv > 1 ? n_tokens * n_kv : 1);
-    most = most > 64 ? 64 : most;
-    most = most < 16 ? 16 : most;
-    splits = ceil_div(max_tiles, 8);
-    splits = splits > most ? most : splits;
-    splits = splits < 1 ? 1 : splits;
-    in_cluster = n_tokens * n_kv * (splits < 8 ? splits : 8) <= CLUSTER_MERGE_CTAS && splits <= 16;
-    if (in_cluster && splits > 8) splits = 8;
-    tiles_per_split = ceil_div(max_tiles, splits);
+    if (!choice) choice = least;
+    tiles_per_split = ceil_div(max_tiles, choice);
     splits = ceil_div(max_tiles, tiles_per_split);
+    in_cluster = splits > 1 && splits <= 8 && pairs * splits <= CLUSTER_MERGE_CTAS;
 }
 
 void run_decode_attention(Launches& L, const Op& op, const FwbStep& step, const int* table, int width,

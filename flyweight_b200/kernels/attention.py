@@ -66,37 +66,41 @@ def force_tiled(flag: bool) -> None:
 
 
 def decode_splits(n_tokens: int, n_kv: int, max_tiles: int, head_dim: int = 64):
-    """How many slices of the context run as separate CTAs.  Depends only on static sizes of the step
-    (tokens, KV heads, block-table width), so a captured graph stays valid."""
-    pairs = n_tokens * n_kv
-    if pairs >= 3 * SM_COUNT:
-        # Many (token, KV head) pairs fill the GPU by themselves: slices only add their fixed costs and
-        # a merge kernel (64 x 4,096 keys: 83.7 us in one piece, 91.8 in eight slices; 256 x 512: 46.9
-        # against 59.6).  Cut only (a) so that no CTA walks more than 64 tiles -- the grid is laid out
-        # for the longest request of the step, and one long request among short ones must not walk its
-        # context alone -- and (b) when the CTAs would fill a last round of the SMs badly (128 x 4,096
-        # in one piece is 1.4 rounds: 182 us; in two slices 163 us).
-        resident = SM_COUNT * (5 if head_dim <= 64 else 3)
-        for splits in (1, 2, 4, 8, 16):
-            if splits * 64 < max_tiles or (splits > 1 and max_tiles < 4 * splits):
-                continue
+    """How many slices of the context run as separate CTAs: (slices, tiles per slice, merged inside the
+    kernel by a cluster).  Depends only on static sizes of the step (tokens, KV heads, block-table
+    width), so a captured graph stays valid."""
+    # Measured on B200 (hd 64, 8 KV heads, batch 1 to 256, 512 to 127k keys), tiles by TMA: the kernel
+    # is fastest when all its CTAs are resident at once -- five an SM -- and there are as many of
+    # them as that allows: 8 x 4,096 keys in 8 slices (512 CTAs) 15.5 us, 16 x 4,096 in 4 slices 25.4 us
+    # (in 8: 32.7), 32 x 4,096 in 2 slices 45.9 us (in 8: 52.9), 64 x 4,096 in one piece 83.7 us (in 8:
+    # 91.8).  A slice has at least 8 tiles, and at most 64: the grid is laid out for the longest request
+    # of the step, and one long request among short ones must not walk its context alone.  Where the
+    # CTAs cannot all be resident, the fewest slices that fill the last round of the SMs to 85 % (128 x
+    # 4,096 in one piece is 1.4 rounds: 182 us; in two slices 163 us).  Up to 8 slices merge inside the
+    # kernel as a cluster while the launch is small; more, or many CTAs, go through a merge kernel.
+    pairs = max(1, n_tokens * n_kv)
+    resident = SM_COUNT * (5 if head_dim <= 64 else 3)
+    least = 1
+    while least * 64 < max_tiles and least < 64:
+        least *= 2
+    choice = 0
+    splits = least
+    while splits <= 64 and pairs * splits <= resident and (splits == least or splits * 8 <= max_tiles):
+        choice = splits
+        splits *= 2
+    if not choice:
+        splits = least
+        while splits <= 64:
             ctas = pairs * splits
-            if ctas <= resident or ctas >= 0.85 * (-(-ctas // resident) * resident):
-                tiles_per_split = -(-max_tiles // splits)
-                return -(-max_tiles // tiles_per_split), tiles_per_split, False
-    # measured on B200 (hd 64, 8 KV heads, batch 1..64, 4k..32k context): about eight 64-key tiles
-    # per slice, at most 16 slices.  While the launch has few CTAs (small batches), up to 8 slices
-    # that merge inside the kernel as a cluster beat more slices with a merge kernel; with many
-    # CTAs the clusters' placement costs more than the second launch.
-    # a step with few (token, KV head) pairs and a very long context may cut it finer, up to 64 slices
-    # of at least four tiles, until the launch has about four CTAs per SM
-    most = max(16, min(64, -(-4 * SM_COUNT // max(1, n_tokens * n_kv))))
-    splits = max(1, min(most, -(-max_tiles // 8)))
-    in_cluster = n_tokens * n_kv * min(splits, 8) <= CLUSTER_MERGE_CTAS and splits <= 16
-    if in_cluster:
-        splits = min(8, splits)
-    tiles_per_split = -(-max_tiles // splits)
+            if ctas >= 0.85 * (-(-ctas // resident) * resident):
+                choice = splits
+                break
+            splits *= 2
+    if not choice:
+        choice = least
+    tiles_per_split = -(-max_tiles // choice)
     splits = -(-max_tiles // tiles_per_split)
+    in_cluster = 1 < splits <= 8 and pairs * splits <= CLUSTER_MERGE_CTAS
     return splits, tiles_per_split, in_cluster
 
 

@@ -149,24 +149,33 @@ def test_real_tile_shapes_step_for_step(tmp_path):
         r.check_health()
 
 
-def test_many_decoding_requests_whose_slices_a_second_kernel_merges(tmp_path):
-    """36 requests of 3,700 cached tokens decode together: too many CTAs for the in-cluster merge, so
-    the slices go through scratch memory (the plan's own, inside its arena) and a merge kernel."""
+def test_decoding_requests_whose_slices_a_second_kernel_merges(tmp_path):
+    """Two requests of 8,300 cached tokens decode together: few CTAs and a long context, so it is cut into
+    more slices than a cluster merges, and the slices go through scratch memory (the plan's own, inside
+    its arena) and a merge kernel.  And 36 requests of 1,900 tokens: slices that a cluster merges."""
     from flyweight_b200.engine import load_model
     from flyweight_b200.kernels import attention
-    folder = make_model_dir(tmp_path / "medium", dict(MEDIUM, num_hidden_layers=2, layer_types=["full_attention", "conv"]),
+    folder = make_model_dir(tmp_path / "medium", dict(MEDIUM, num_hidden_layers=2, layer_types=["full_attention", "conv"],
+                                                      max_position_embeddings=16384),
                             seed=9, dtype=torch.bfloat16)
     model = load_model(folder, "bfloat16")
-    runners = pair_of_runners(model, num_pages=2200, num_slots=40, max_model_len=4096, max_batched_tokens=4096)
-    splits, _, in_cluster = attention.decode_splits(36, 4, 58)
-    assert splits > 1 and not in_cluster
+    n_kv, head_dim = MEDIUM["num_key_value_heads"], MEDIUM["hidden_size"] // MEDIUM["num_attention_heads"]
     rng = np.random.default_rng(5)
     draw = lambda n: [int(t) for t in rng.integers(0, MEDIUM["vocab_size"], size=n)]
-    steps = [{"entries": [{"id": f"d{i}", "tokens": draw(3700), "want": []}], "end": []} for i in range(36)]
-    for _ in range(3):
-        steps.append({"entries": [{"id": f"d{i}", "tokens": draw(1), "want": [0]} for i in range(36)], "end": []})
-    steps[-1]["end"] = [f"d{i}" for i in range(36)]
-    same_steps(runners, steps, "36 decoding requests")
+    for count, length, merged_by_cluster in ((2, 8300, False), (36, 1900, True)):
+        splits, _, in_cluster = attention.decode_splits(count, n_kv, -(-(length + 3) // 64), head_dim)
+        assert splits > 1 and in_cluster == merged_by_cluster, (count, length, splits, in_cluster)
+        runners = pair_of_runners(model, num_pages=count * (length // 64 + 2), num_slots=40, max_model_len=8400,
+                                  max_batched_tokens=4096)
+        steps = []
+        for i in range(count):
+            prompt = draw(length)
+            for start in range(0, length, 4096):
+                steps.append({"entries": [{"id": f"d{i}", "tokens": prompt[start:start + 4096], "want": []}], "end": []})
+        for _ in range(3):
+            steps.append({"entries": [{"id": f"d{i}", "tokens": draw(1), "want": [0]} for i in range(count)], "end": []})
+        steps[-1]["end"] = [f"d{i}" for i in range(count)]
+        same_steps(runners, steps, f"{count} decoding requests of {length} tokens")
 
 
 def test_a_model_with_a_part_defined_elsewhere_keeps_the_python_path():
