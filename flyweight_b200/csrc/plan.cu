@@ -430,12 +430,12 @@ void run_linear_residual(Launches& L, const Op& op, const FwbStep& step, bool& p
 void decode_splits(int n_tokens, int n_kv, int max_tiles, int head_dim, int& splits, int& tiles_per_split,
                    bool& in_cluster) {
     // the same rule as kernels/attention.py: decode_splits (the measurements are quoted there): as many
-    // slices as keep every CTA resident at once, of 8 to 64 tiles; else the fewest that fill the SMs'
+    // slices as keep every CTA resident at once, of 8 to 128 tiles; else the fewest that fill the SMs'
     // last round to 85 %
     const long pairs = (long)n_tokens * n_kv > 1 ? (long)n_tokens * n_kv : 1;
     const long resident = (long)SM_COUNT * (head_dim <= 64 ? 5 : 3);
     int least = 1;
-    while (least * 64 < max_tiles && least < 64) least *= 2;
+    while (least * 128 < max_tiles && least < 64) least *= 2;
     int choice = 0;
     for (int s = least; s <= 64 && pairs * s <= resident && (s == least || s * 8 <= max_tiles); s *= 2) choice = s;
     if (!choice)

@@ -73,7 +73,7 @@ def decode_splits(n_tokens: int, n_kv: int, max_tiles: int, head_dim: int = 64):
     # is fastest when all its CTAs are resident at once -- five an SM -- and there are as many of
     # them as that allows: 8 x 4,096 keys in 8 slices (512 CTAs) 15.5 us, 16 x 4,096 in 4 slices 25.4 us
     # (in 8: 32.7), 32 x 4,096 in 2 slices 45.9 us (in 8: 52.9), 64 x 4,096 in one piece 83.7 us (in 8:
-    # 91.8).  A slice has at least 8 tiles, and at most 64: the grid is laid out for the longest request
+    # 91.8).  A slice has at least 8 tiles, and at most 128: the grid is laid out for the longest request
     # of the step, and one long request among short ones must not walk its context alone.  Where the
     # CTAs cannot all be resident, the fewest slices that fill the last round of the SMs to 85 % (128 x
     # 4,096 in one piece is 1.4 rounds: 182 us; in two slices 163 us).  Up to 8 slices merge inside the
@@ -81,7 +81,7 @@ def decode_splits(n_tokens: int, n_kv: int, max_tiles: int, head_dim: int = 64):
     pairs = max(1, n_tokens * n_kv)
     resident = SM_COUNT * (5 if head_dim <= 64 else 3)
     least = 1
-    while least * 64 < max_tiles and least < 64:
+    while least * 128 < max_tiles and least < 64:
         least *= 2
     choice = 0
     splits = least
