@@ -19,6 +19,7 @@
 //       ldmatrix addresses undo.  Other head sizes are copied by cp.async into padded rows.
 //
 // Key tiles start at multiples of 64 and are visited in ascending order, whatever the cut.
+#include "qk_head.cuh"
 #include "tcgen05.cuh"
 
 using namespace fwb;
@@ -328,6 +329,59 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 }
 
 // ------------------------------------------------------------------ decode
+// The decode kernel may do the step's q/k norm, rotation and page write itself (a step of single
+// tokens only): it then reads the rows of the fused q|k|v projection instead of finished queries.
+struct FusedQkv {
+    const __nv_bfloat16* qkv;    // [T][(nh + 2 nkv_in) HD]; null: `q` holds finished queries
+    const float* wq;             // [HD] head-norm weights (unused when !use_norm)
+    const float* wk;
+    const float2* table;         // [positions][rot / 2] (cos, sin)
+    __nv_bfloat16* k_pool;       // where the token's key and value go (nkv_in > 0)
+    __nv_bfloat16* v_pool;
+    int nkv_in;                  // KV heads in the qkv row (0: this layer reads another layer's cache)
+    int rot, pairing, use_norm;
+    float eps;
+};
+
+// The fused form's prologue (not inlined: its registers are not the main loop's): norm and turn the
+// queries of this KV head's group into `own_q` [group][HD]; in the slice that holds the token's own
+// position also its key and value, into `own_kv` [2][HD] and into the pools at `cache_at` (for the
+// steps to come).  hd/8 adjacent lanes own a head, as in the kernel that does this for whole steps.
+template <int HD>
+__device__ __noinline__ void fused_heads(const FusedQkv& fused, int tok, int pos, int kvh, int nh, int nkv, int group,
+                                         bool owns_token, size_t cache_at, __nv_bfloat16* own_q,
+                                         __nv_bfloat16* own_kv) {
+    constexpr int G = HD / 8, PER_WARP = 32 / G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / G, gl = lane - sub * G;
+    const int heads_in = nh + 2 * fused.nkv_in;
+    const __nv_bfloat16* row = fused.qkv + (size_t)tok * heads_in * HD;
+    const float2* cs = fused.table + (size_t)pos * (fused.rot / 2);
+    const int n_slots = group + (owns_token ? 2 : 0);
+    for (int slot0 = warp * PER_WARP; slot0 < n_slots; slot0 += WARPS * PER_WARP) {
+        const int slot = slot0 + sub;
+        const bool valid = sub < PER_WARP && slot < n_slots;
+        const int kind = slot < group ? 0 : (slot == group ? 1 : 2);
+        const int h = kind == 0 ? kvh * group + slot : (kind == 1 ? nh + kvh : nh + fused.nkv_in + kvh);
+        float v[8];
+        if (valid) {
+            load8(row + (size_t)h * HD + gl * 8, v);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        }
+        head_norm_rope8(v, valid, kind, sub, gl, G, HD, fused.rot, fused.pairing, fused.use_norm, fused.eps,
+                        fused.wq, fused.wk, cs);
+        if (!valid) continue;
+        if (kind == 0) {
+            store8(own_q + slot * HD + gl * 8, v);
+        } else {
+            store8(own_kv + (kind - 1) * HD + gl * 8, v);
+            store8((kind == 1 ? fused.k_pool : fused.v_pool) + cache_at + gl * 8, v);
+        }
+    }
+}
+
 // grid (splits, nkv, T).  A split covers `tiles_per_split` key tiles; with splits == 1 the
 // result goes straight to `out`, else (acc, max, sum) go to the scratch buffers:
 //   part_o[t][kvh][split][group][HD] fp32 (not normalised), part_ml[t][kvh][split][group][2].
@@ -336,15 +390,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 // [pages * nkv * 64 keys][HD] (head sizes 64 and 128; the maps are not read otherwise).  Thread 0
 // asks for a tile's boxes and arms the stage's mbarrier with their bytes; every thread waits on that
 // barrier itself (bounded: after the limit the library's status word is raised and nobody waits again).
-template <int HD, bool CLUSTER, bool DEEP, bool TMA>
-__global__ void __launch_bounds__(WARPS * 32)
+// FUSED: the form that norms, turns and stores its own token's heads (an instantiation of its own: the
+// plain form carries none of its registers, shared memory or branches).
+template <int HD, bool CLUSTER, bool DEEP, bool TMA, bool FUSED>
+__global__ void __launch_bounds__(WARPS * 32, (TMA && HD <= 64) ? 5 : 1)   // five CTAs an SM: what the slicing rule counts on
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
                         const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                         int max_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int group, int tiles_per_split,
-                        int window, float scale, int* status, int tma_stages) {
+                        int window, float scale, int* status, int tma_stages, const FusedQkv fused) {
     fwb::pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t smem_dynamic[];
     // the swizzle of a TMA box counts rows from a 1024-byte boundary
@@ -354,6 +410,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     __shared__ float merge_ml[WARPS][16][2];
     __shared__ uint64_t full_bar[MAX_TMA_STAGES];
     __shared__ int abort_flag;
+    __shared__ __align__(16) __nv_bfloat16 own_q[FUSED ? 16 * HD : 8];    // fused form: the group's queries, normed and turned
+    __shared__ __align__(16) __nv_bfloat16 own_kv[FUSED ? 2 * HD : 8];    // ... and the token's own key and value
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, tok = blockIdx.z;
@@ -414,9 +472,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
     fwb::pdl_wait();
 
+    constexpr bool fuse = FUSED;
+    // the slice that holds the token's own position also norms, turns and stores its key and value
+    const bool owns_token = fuse && fused.nkv_in > 0 && last_tile >= tile_begin && last_tile < tile_end;
+    if constexpr (fuse) {
+        fused_heads<HD>(fused, tok, pos, kvh, nh, nkv, group, owns_token,
+                        owns_token ? (((size_t)table[last_tile] * nkv + kvh) * KEYS + (size_t)(pos % KEYS)) * HD : 0,
+                        own_q, own_kv);
+        __syncthreads();
+    }
     // rows 0..group-1 are the group's query heads; the rest are padding
-    const __nv_bfloat16* qrow0 = g < group ? q + ((size_t)tok * nh + kvh * group + g) * HD : nullptr;
-    const __nv_bfloat16* qrow1 = g + 8 < group ? q + ((size_t)tok * nh + kvh * group + g + 8) * HD : nullptr;
+    const __nv_bfloat16* q_rows = fuse ? own_q : q + ((size_t)tok * nh + kvh * group) * HD;
+    const __nv_bfloat16* qrow0 = g < group ? q_rows + (size_t)g * HD : nullptr;
+    const __nv_bfloat16* qrow1 = g + 8 < group ? q_rows + (size_t)(g + 8) * HD : nullptr;
     uint32_t qf[HD / 16][4];
     load_q<HD>(qf, qrow0, qrow1, lane);
     const int lo[2] = {lo_key, lo_key};
@@ -442,8 +510,16 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             cp_async_wait<(DEEP ? decode_stages<HD>() : 2) - 1>();
             __syncthreads();
         }
-        if (pos - tile * KEYS + 1 < KEYS) {
-            clear_v_rows<HD, TMA>(stage_v(s), pos - tile * KEYS + 1);
+        if (tile == last_tile && (owns_token || pos - tile * KEYS + 1 < KEYS)) {
+            if (owns_token && threadIdx.x < 2 * (HD / 8)) {
+                // the page row of the token itself: what this CTA has just computed (the copy in the
+                // pool may or may not have been seen by the tile's load)
+                const int which = threadIdx.x / (HD / 8), c = threadIdx.x % (HD / 8);
+                __nv_bfloat16* tile_base = which ? stage_v(s) : stage_k(s);
+                *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(tile_at<HD, TMA>(tile_base, pos % KEYS, c))) =
+                    *reinterpret_cast<const uint4*>(own_kv + which * HD + c * 8);
+            }
+            if (pos - tile * KEYS + 1 < KEYS) clear_v_rows<HD, TMA>(stage_v(s), pos - tile * KEYS + 1);
             __syncthreads();
         }
         float sc[2][4];                                     // this warp's 16 keys of the tile
@@ -615,7 +691,8 @@ template <int HD, bool TMA>
 int launch_decode_as(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* q, const void* k_pool,
                      const void* v_pool, const int* positions, const int* tok_seg, const int* block_table,
                      int max_pages, void* out, float* part_o, float* part_ml, int T, int nh, int nkv, int splits,
-                     int tiles_per_split, int window, float scale, bool in_cluster, cudaStream_t stream) {
+                     int tiles_per_split, int window, float scale, bool in_cluster, const FusedQkv& fused,
+                     cudaStream_t stream) {
     constexpr size_t merge_bytes = (size_t)(WARPS + 1) * 16 * HD * 4 + 16 * 2 * 4;
     // few CTAs (at most three per SM): the deep ring; else two stages and more CTAs per SM
     const bool deep = (long)splits * nkv * T <= 3 * 148;
@@ -649,7 +726,9 @@ int launch_decode_as(const CUtensorMap& map_k, const CUtensorMap& map_v, const v
     using bf = __nv_bfloat16;
     if (splits > 1 && in_cluster) {
         // the slices of a (token, KV head) as a cluster: merged through distributed shared memory
-        auto kernel = deep ? attention_decode_kernel<HD, true, true, TMA> : attention_decode_kernel<HD, true, false, TMA>;
+        const bool fuse = fused.qkv != nullptr;
+        auto kernel = fuse ? (deep ? attention_decode_kernel<HD, true, true, TMA, true> : attention_decode_kernel<HD, true, false, TMA, true>)
+                           : (deep ? attention_decode_kernel<HD, true, true, TMA, false> : attention_decode_kernel<HD, true, false, TMA, false>);
         int st = opt_in_smem(kernel, bytes);
         if (st != FWB_OK) return st;
         cudaLaunchConfig_t config = {};
@@ -669,15 +748,17 @@ int launch_decode_as(const CUtensorMap& map_k, const CUtensorMap& map_v, const v
         cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_k, map_v, (const bf*)q, (const bf*)k_pool,
                                            (const bf*)v_pool, positions, tok_seg, block_table, max_pages, (bf*)out,
                                            (float*)nullptr, (float*)nullptr, nh, nkv, nh / nkv,
-                                           tiles_per_split, window, scale * LOG2E, status, stages);
+                                           tiles_per_split, window, scale * LOG2E, status, stages, fused);
         return e == cudaSuccess ? fwb_launch_status() : (int)e;
     }
-    auto kernel = deep ? attention_decode_kernel<HD, false, true, TMA> : attention_decode_kernel<HD, false, false, TMA>;
+    const bool fuse = fused.qkv != nullptr;
+    auto kernel = fuse ? (deep ? attention_decode_kernel<HD, false, true, TMA, true> : attention_decode_kernel<HD, false, false, TMA, true>)
+                       : (deep ? attention_decode_kernel<HD, false, true, TMA, false> : attention_decode_kernel<HD, false, false, TMA, false>);
     int st = opt_in_smem(kernel, bytes);
     if (st != FWB_OK) return st;
     fwb::pdl(kernel, dim3(splits, nkv, T), WARPS * 32, bytes, stream)(
         map_k, map_v, (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, tok_seg, block_table, max_pages,
-        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E, status, stages);
+        (bf*)out, part_o, part_ml, nh, nkv, nh / nkv, tiles_per_split, window, scale * LOG2E, status, stages, fused);
     st = fwb_launch_status();
     if (st != FWB_OK || splits == 1) return st;
     fwb::pdl(attention_merge_kernel, dim3(nkv, T), 128, 0, stream)(part_o, part_ml, (bf*)out, nh, nkv, nh / nkv, HD,
@@ -690,7 +771,7 @@ template <int HD>
 int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                   const int* tok_seg, const int* block_table, int max_pages, int num_pages, void* out,
                   float* part_o, float* part_ml, int T, int nh, int nkv, int splits, int tiles_per_split,
-                  int window, float scale, bool in_cluster, cudaStream_t stream) {
+                  int window, float scale, bool in_cluster, const FusedQkv& fused, cudaStream_t stream) {
     CUtensorMap map_k, map_v;
     memset(&map_k, 0, sizeof(map_k));
     memset(&map_v, 0, sizeof(map_v));
@@ -701,11 +782,11 @@ int launch_decode(const void* q, const void* k_pool, const void* v_pool, const i
             tc5::make_map(&map_k, k_pool, pool_rows, HD, KEYS) && tc5::make_map(&map_v, v_pool, pool_rows, HD, KEYS))
             return launch_decode_as<HD, true>(map_k, map_v, q, k_pool, v_pool, positions, tok_seg, block_table,
                                               max_pages, out, part_o, part_ml, T, nh, nkv, splits, tiles_per_split,
-                                              window, scale, in_cluster, stream);
+                                              window, scale, in_cluster, fused, stream);
     }
     return launch_decode_as<HD, false>(map_k, map_v, q, k_pool, v_pool, positions, tok_seg, block_table, max_pages,
                                        out, part_o, part_ml, T, nh, nkv, splits, tiles_per_split, window, scale,
-                                       in_cluster, stream);
+                                       in_cluster, fused, stream);
 }
 
 bool shape_ok(int nh, int nkv, int hd, int page_size) {
@@ -764,9 +845,54 @@ FWB_API int fwb_attention_decode_mma(const void* q, const void* k_pool, const vo
     if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
     const bool in_cluster = merge_in_cluster != 0 && splits <= 8;
     if (splits < 1 || tiles_per_split < 1 || (splits > 1 && !in_cluster && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
+    FusedQkv fused;
+    memset(&fused, 0, sizeof(fused));
 #define CALL(HD)                                                                                          \
     launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, num_pages, out, part_o,  \
-                      part_ml, T, nh, nkv, splits, tiles_per_split, window, scale, in_cluster, stream)
+                      part_ml, T, nh, nkv, splits, tiles_per_split, window, scale, in_cluster, fused, stream)
+    FWB_HD_SWITCH(hd, CALL)
+#undef CALL
+}
+
+// The same for a step of single tokens only, with the q/k head norm, the rotation and the page write
+// done by the attention kernel itself: qkv [T][(nh + 2 nkv_in) hd] bf16 is the fused projection
+// (nkv_in = nkv, or 0 for a layer that reads another layer's cache and writes none), wq / wk [hd] fp32
+// the head-norm weights (use_norm), table [positions][rot / 2] (cos, sin) pairs, pairing 0 half-split /
+// 1 interleaved.  Each CTA norms and turns the queries of its KV head's group; the slice that holds a
+// token's own position does the same to its key, copies its value, stores both into the pools for the
+// steps to come and into its own tile of shared memory.  The arithmetic is that of fwb_qk_norm_rope's
+// bfloat16 form (one function): the same bits.  Needs rot % 16 == 0 and 16-byte aligned rows.
+FWB_API int fwb_attention_decode_fused(const void* qkv, int nkv_in, const float* wq, const float* wk,
+                                       const void* table, int rot, float eps, int use_norm, int pairing,
+                                       void* k_pool, void* v_pool, const int* positions, const int* tok_seg,
+                                       const int* block_table, int max_pages, int page_size, int num_pages,
+                                       void* out, float* part_o, float* part_ml, int T, int nh, int nkv, int hd,
+                                       int splits, int tiles_per_split, int window, float scale,
+                                       int merge_in_cluster, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!qkv || !table || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out) return FWB_BAD_ARGUMENT;
+    if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
+    if (nkv_in != 0 && nkv_in != nkv) return FWB_BAD_ARGUMENT;
+    if (use_norm && (!wq || (nkv_in > 0 && !wk))) return FWB_BAD_ARGUMENT;
+    if (rot < 0 || rot > hd || (rot & 15) || (pairing != 0 && pairing != 1)) return FWB_UNSUPPORTED;
+    if ((((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) != 0) return FWB_UNSUPPORTED;
+    const bool in_cluster = merge_in_cluster != 0 && splits <= 8;
+    if (splits < 1 || tiles_per_split < 1 || (splits > 1 && !in_cluster && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
+    FusedQkv fused;
+    fused.qkv = static_cast<const __nv_bfloat16*>(qkv);
+    fused.wq = wq;
+    fused.wk = wk;
+    fused.table = static_cast<const float2*>(table);
+    fused.k_pool = static_cast<__nv_bfloat16*>(k_pool);
+    fused.v_pool = static_cast<__nv_bfloat16*>(v_pool);
+    fused.nkv_in = nkv_in;
+    fused.rot = rot;
+    fused.pairing = pairing;
+    fused.use_norm = use_norm;
+    fused.eps = eps;
+#define CALL(HD)                                                                                                \
+    launch_decode<HD>(nullptr, k_pool, v_pool, positions, tok_seg, block_table, max_pages, num_pages, out, part_o, \
+                      part_ml, T, nh, nkv, splits, tiles_per_split, window, scale, in_cluster, fused, stream)
     FWB_HD_SWITCH(hd, CALL)
 #undef CALL
 }

@@ -12,6 +12,7 @@
 // With nkv_in == 0 the launch handles queries only (a layer that reads another
 // layer's cache writes none of its own).
 #include "common.cuh"
+#include "qk_head.cuh"
 
 using namespace fwb;
 
@@ -96,25 +97,6 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
 // load and store per lane), so a warp works on 32/(hd/8) heads at a time.  The sum of squares
 // goes over the lanes of a head in lane order; the rotation partner (i +- rot/2) sits
 // rot/16 lanes away and is fetched with shuffles.  Needs hd % 8 == 0, hd <= 256, rot % 16 == 0.
-__device__ __forceinline__ void load8(const __nv_bfloat16* src, float (&f)[8]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(src);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 t = __bfloat1622float2(h[i]);
-        f[2 * i] = t.x;
-        f[2 * i + 1] = t.y;
-    }
-}
-
-__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&f)[8]) {
-    uint4 out;
-    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    *reinterpret_cast<uint4*>(dst) = out;
-}
-
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ wq,
                            const float* __restrict__ wk, const float2* __restrict__ table,
@@ -137,8 +119,6 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
         const int page = block_table[(size_t)tok_seg[t] * max_pages + pos / page_size];
         cache_base = ((size_t)page * nkv) * page_size * hd + (size_t)(pos % page_size) * hd;
     }
-    const int half_lanes = rot >> 4, rot_lanes = rot >> 3;
-    const int partner = gl < half_lanes ? lane + half_lanes : (gl < rot_lanes ? lane - half_lanes : lane);
     const int block_warps = blockDim.x >> 5;
     for (int h0 = (blockIdx.y * block_warps + warp) * per_warp; h0 < heads; h0 += gridDim.y * block_warps * per_warp) {
         const int h = h0 + sub;
@@ -151,42 +131,8 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
             for (int i = 0; i < 8; ++i) v[i] = 0.0f;
         }
         const bool is_v = h >= nh + nkv, is_q = h < nh;
-        float ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
-        float total = 0.0f;
-        for (int j = 0; j < G; ++j) total += __shfl_sync(0xffffffffu, ss, (sub * G + j) & 31);
-        if (use_norm && !is_v) {
-            const float inv = rsqrtf(total / (float)hd + eps);
-            const float* w = (is_q ? wq : wk) + gl * 8;
-            if (valid) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = (v[i] * inv) * w[i];
-            }
-        }
-        float other[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, v[i], partner);
+        head_norm_rope8(v, valid, is_q ? 0 : (is_v ? 2 : 1), sub, gl, G, hd, rot, pairing, use_norm, eps, wq, wk, cs);
         if (!valid) continue;
-        if (!is_v && gl < rot_lanes && pairing) {
-            // interleaved pairs lie side by side in this lane's eight channels
-            const float2* c = cs + gl * 4;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 a = c[j];
-                const float x0 = v[2 * j], x1 = v[2 * j + 1];
-                v[2 * j] = x0 * a.x - x1 * a.y;
-                v[2 * j + 1] = x1 * a.x + x0 * a.y;
-            }
-        } else if (!is_v && gl < rot_lanes) {
-            const bool low = gl < half_lanes;
-            const float2* c = cs + (low ? gl : gl - half_lanes) * 8;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float2 a = c[i];
-                v[i] = low ? v[i] * a.x - other[i] * a.y : v[i] * a.x + other[i] * a.y;
-            }
-        }
         __nv_bfloat16* dst;
         if (is_q) dst = q_out + ((size_t)t * nh + h) * hd;
         else if (!is_v) dst = k_pool + cache_base + (size_t)(h - nh) * page_size * hd;

@@ -104,6 +104,48 @@ def decode_splits(n_tokens: int, n_kv: int, max_tiles: int, head_dim: int = 64):
     return splits, tiles_per_split, in_cluster
 
 
+_fuse_rope = True
+
+
+def set_rope_fusion(flag: bool) -> None:
+    """Whether a step of single tokens does its q/k norm, rotation and page write inside the decode
+    attention kernel (the default) or in the kernel of its own that every other step uses."""
+    global _fuse_rope
+    _fuse_rope = bool(flag)
+
+
+FUSE_ROPE_CLUSTER_CTAS = 256
+
+
+def decode_fusable(ctx, qkv, cache, block_table, n_heads: int, rotary_dim: int) -> bool:
+    """Whether ``fused_decode_attention`` takes this step: single tokens only, everything bfloat16, a
+    shape the tensor-core decode kernel has, a rotary width the 16-byte lanes can pair up -- and a
+    launch that gains by it.  Measured in the decode step of LFM2-1.2B: batch 1 (64 CTAs in clusters)
+    0.783 -> 0.775 ms, batch 64 (512 CTAs, no clusters) 1.56 -> 1.53 ms, but batch 8 (512 CTAs in clusters
+    of 8) 0.867 -> 0.881 ms: the kernel of its own was the window in which that many clusters found
+    their SMs and fetched their first tiles, so such launches keep it."""
+    k_pool = cache.k_pool
+    if not (_fuse_rope and _use_mma and not _force_tiled and ctx.batch.max_segment == 1
+            and qkv.dtype == torch.bfloat16 and k_pool is not None and k_pool.dtype == torch.bfloat16
+            and ctx.precision.act_dtype == torch.bfloat16 and rotary_dim % 16 == 0
+            and ops.attention_mma_shape_ok(n_heads, k_pool.shape[1], k_pool.shape[3], k_pool.shape[2])):
+        return False
+    n_kv, head_dim = k_pool.shape[1], k_pool.shape[3]
+    splits, _, in_cluster = decode_splits(ctx.batch.n_tokens, n_kv, block_table.shape[1], head_dim)
+    return not (in_cluster and ctx.batch.n_tokens * n_kv * splits >= FUSE_ROPE_CLUSTER_CTAS)
+
+
+def fused_decode_attention(ctx, qkv, cache, block_table, n_heads, n_kv_in, window, scale, q_norm, k_norm, eps,
+                           table, rotary_dim, pairing):
+    """A step of single tokens: head norms, rotation, page write and attention in one kernel."""
+    batch = ctx.batch
+    _, n_kv, _, head_dim = cache.k_pool.shape
+    splits, tiles_per_split, in_cluster = decode_splits(batch.n_tokens, n_kv, block_table.shape[1], head_dim)
+    return ops.attention_decode_fused(qkv, q_norm, k_norm, table, rotary_dim, float(eps or 0.0), pairing, n_kv_in,
+                                      cache.k_pool, cache.v_pool, batch.positions, batch.tok_seg, block_table,
+                                      n_heads, window, scale, splits, tiles_per_split, in_cluster)
+
+
 def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype):
     """Causal GQA of every token of the step over its request's pages."""
     batch = ctx.batch

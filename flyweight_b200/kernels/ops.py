@@ -335,6 +335,49 @@ def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg,
     return out
 
 
+def attention_decode_fused(qkv, q_norm, k_norm, table, rotary_dim: int, eps: float, pairing: str, n_kv_in: int,
+                           k_pool, v_pool, positions, tok_seg, block_table, n_heads: int, window: int,
+                           scale: float, splits: int, tiles_per_split: int, merge_in_cluster: bool = False
+                           ) -> torch.Tensor:
+    """``qk_norm_rope`` and ``attention_decode_mma`` of a step of single tokens in one kernel: every
+    CTA of the attention norms and turns the queries of its KV head's group itself, and the slice that
+    holds a token's own position its key (and copies its value) into the pages.  ``qkv`` is the fused
+    projection [T][(n_heads + 2 n_kv_in) head_dim] in bfloat16; the other arguments are those of the two
+    functions.  The same bits as the two kernels (one device function does the arithmetic of both)."""
+    pairing_code = ROPE_PAIRINGS[pairing]
+    check_tensor("qkv", qkv, torch.bfloat16)
+    check_tensor("k pool", k_pool, torch.bfloat16)
+    check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
+    check_tensor("rope table", table, torch.float32)
+    T = qkv.shape[0]
+    num_pages, n_kv, page_size, head_dim = k_pool.shape
+    if qkv.shape[1] != (n_heads + 2 * n_kv_in) * head_dim:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(n_heads + 2 * n_kv_in) * head_dim}")
+    if table.dim() != 3 or table.shape[1] != max(1, rotary_dim // 2) or table.shape[2] != 2:
+        raise KernelError("rope table must be [positions][rotary_dim/2][2]")
+    use_norm = 1 if q_norm is not None else 0
+    if use_norm:
+        check_tensor("q norm weight", q_norm, torch.float32, (head_dim,))
+        if n_kv_in:
+            check_tensor("k norm weight", k_norm, torch.float32, (head_dim,))
+    _i32("positions", positions, T)
+    _i32("tok_seg", tok_seg, T)
+    _i32("block table", block_table)
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    part_o = part_ml = None
+    in_cluster = merge_in_cluster and 1 < splits <= 8
+    if splits > 1 and not in_cluster:
+        group = n_heads // n_kv
+        part_o = torch.empty((T, n_kv, splits, group, head_dim), dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty((T, n_kv, splits, group, 2), dtype=torch.float32, device=qkv.device)
+    lib.call("fwb_attention_decode_fused", ptr(qkv), n_kv_in, ptr(q_norm), ptr(k_norm), ptr(table), rotary_dim,
+             c_float(eps), use_norm, pairing_code, ptr(k_pool), ptr(v_pool), ptr(positions), ptr(tok_seg),
+             ptr(block_table), block_table.shape[1], page_size, num_pages, ptr(out), ptr(part_o), ptr(part_ml),
+             T, n_heads, n_kv, head_dim, splits, tiles_per_split, window, c_float(scale),
+             1 if in_cluster else 0, stream(), launches=2 if (splits > 1 and not in_cluster) else 1)
+    return out
+
+
 def set_decode_attention_tma(on: bool, stages: int = 0) -> None:
     """Test switch: whether the decode attention kernel takes its key and value tiles by TMA at head
     sizes 64 and 128 (the default) or by cp.async, as at the other head sizes; and the depth of the TMA

@@ -101,11 +101,20 @@ class GQAttention(Mixer):
         # q|k|v in the activation dtype; the head norm and the rotation widen it to fp32
         qkv = ops.linear(h, self.w_qkv, act)
         block_table = ctx.batch.block_tables[cache.group]
+        from ..kernels import attention as attention_kernels
+        rotation = self.position.rotation()
+        if rotation is not None and attention_kernels.decode_fusable(ctx, qkv, cache, block_table, self.n_heads, rotation[1]):
+            # a step of single tokens whose position part is a plain rotation: the decode attention
+            # kernel norms, turns and stores its own token's heads (one kernel and one pass less)
+            table, rotary_dim, pairing = rotation
+            out = attention_kernels.fused_decode_attention(
+                ctx, qkv, cache, block_table, self.n_heads, self._kv_in, self.window, self.scale,
+                self.q_norm, self.k_norm, self.eps, table, rotary_dim, pairing)
+            return ops.linear_into_residual(out, self.w_o, residual)
         # positions are the position part's business: it norms, encodes and writes the pages
         q = self.position.encode(ctx, qkv, n_heads=self.n_heads, n_kv_in=self._kv_in,
                                  head_dim=self.head_dim, q_norm=self.q_norm, k_norm=self.k_norm,
                                  eps=self.eps, cache=cache, block_table=block_table)
-        from ..kernels import attention as attention_kernels
         out = attention_kernels.paged_attention(ctx, q, cache, block_table, self.n_heads,
                                                 self.window, self.scale, act)
         return ops.linear_into_residual(out, self.w_o, residual)

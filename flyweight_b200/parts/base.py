@@ -191,6 +191,14 @@ class PositionEncoding(Part):
             cache.v_pool if n_kv_in else None, n_heads, n_kv_in, head_dim, self.rotary_dim,
             float(eps or 0.0), ctx.precision.act_dtype, pairing=self.pairing)
 
+    def rotation(self):
+        """(table, rotary_dim, pairing) for a mixer that can do the default ``encode`` inside a kernel
+        of its own (the decode attention does, for steps of single tokens); None from an encoding that
+        encodes in its own way, which is then always asked to ``encode``."""
+        if type(self).encode is not PositionEncoding.encode:
+            return None
+        return self._table, self.rotary_dim, self.pairing
+
     def plan(self, builder, qkv, q_out, *, n_heads: int, n_kv_in: int, head_dim: int, q_norm, k_norm,
              eps, cache) -> None:
         """``encode`` for the native step plan.  Only an encoding that keeps the default ``encode``

@@ -920,6 +920,50 @@ def test_decode_attention_over_split_contexts(nh, nkv, hd, window):
     assert tensorcore.status() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot,pairing,normed,shares", [
+    (32, 8, 64, 64, "half_split", True, False), (16, 1, 128, 64, "interleaved", True, False),
+    (6, 2, 80, 32, "half_split", False, False), (4, 2, 16, 16, "half_split", True, False),
+    (12, 4, 64, 0, "half_split", True, False), (8, 2, 64, 32, "interleaved", True, True)])
+def test_decode_attention_that_norms_turns_and_stores_its_own_token(nh, nkv, hd, rot, pairing, normed, shares):
+    """A step of single tokens: the decode attention kernel does the q/k head norm, the rotation and
+    the page write of its own token itself.  Against the two kernels that every other step uses (the
+    norm-and-rotate kernel, then the attention): the same output bits and the same pools, at page edges
+    (positions 0, 63, 64), with the context in one piece, in slices, in a cluster; with partial and no
+    rotation, both pairings, no norm, and a layer that reads another layer's cache and writes none."""
+    from flyweight_b200.kernels import ops
+    g = torch.Generator().manual_seed(nh * 5 + hd + rot)
+    lens = [1, 64, 65, 700, 1500, 257, 128]
+    n_kv_in = 0 if shares else nkv
+    k_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    v_seqs = [bf16_round(torch.randn(n, nkv, hd, generator=g).double()) for n in lens]
+    k_pool, v_pool, table = build_paged(k_seqs, v_seqs, 48, torch.bfloat16, shuffle_seed=hd + 2, fill=0.0)
+    ctx, cache, table_dev = make_ctx(lens, [1] * len(lens), table, k_pool, v_pool)
+    qkv = dev((torch.randn(len(lens), (nh + 2 * n_kv_in) * hd, generator=g) * 2).to(torch.bfloat16))
+    q_norm = dev(torch.rand(hd, generator=g) + 0.5) if normed else None
+    k_norm = dev(torch.rand(hd, generator=g) + 0.5) if normed else None
+    half = max(1, rot // 2)
+    angle = torch.arange(1600, dtype=torch.float64)[:, None] * torch.rand(half, generator=g).double()[None]
+    rope = dev(torch.stack([angle.cos(), angle.sin()], -1).float().contiguous())
+    scale = 1.0 / math.sqrt(hd)
+    pos, seg = ctx.batch.positions, ctx.batch.tok_seg
+    for splits, per, cluster in ((1, 24, False), (3, 8, True), (8, 3, True), (5, 5, False), (24, 1, False)):
+        two = [cache.k_pool.clone(), cache.v_pool.clone()]
+        q = ops.qk_norm_rope(qkv, q_norm, k_norm, rope, pos, seg, table_dev if n_kv_in else None,
+                             two[0] if n_kv_in else None, two[1] if n_kv_in else None, nh, n_kv_in, hd, rot, 1e-5,
+                             torch.bfloat16, pairing=pairing)
+        want = ops.attention_decode_mma(q, two[0], two[1], pos, seg, table_dev, nh, 0, scale, splits, per,
+                                        merge_in_cluster=cluster)
+        one = [cache.k_pool.clone(), cache.v_pool.clone()]
+        got = ops.attention_decode_fused(qkv, q_norm, k_norm, rope, rot, 1e-5, pairing, n_kv_in, one[0], one[1], pos,
+                                         seg, table_dev, nh, 0, scale, splits, per, merge_in_cluster=cluster)
+        assert torch.equal(got, want), (splits, per, cluster)
+        assert torch.equal(one[0], two[0]) and torch.equal(one[1], two[1]), "pools"
+        if n_kv_in:
+            assert not torch.equal(one[0], cache.k_pool)         # the keys of this step were written
+    from flyweight_b200.kernels import tensorcore
+    assert tensorcore.status() == 0
+
+
 def test_tensor_core_attention_finds_a_far_key_and_the_window_edge():
     from flyweight_b200.kernels import attention as attention_kernels
     g = torch.Generator().manual_seed(12)
