@@ -117,7 +117,7 @@ def set_rope_fusion(flag: bool) -> None:
 FUSE_ROPE_CLUSTER_CTAS = 256
 
 
-def decode_fusable(ctx, qkv, cache, block_table, n_heads: int, rotary_dim: int) -> bool:
+def decode_fusable(ctx, qkv, cache, block_table, n_heads: int, rotary_dim: int, window: int = 0) -> bool:
     """Whether ``fused_decode_attention`` takes this step: single tokens only, everything bfloat16, a
     shape the tensor-core decode kernel has, a rotary width the 16-byte lanes can pair up -- and a
     launch that gains by it.  Measured in the decode step of LFM2-1.2B: batch 1 (64 CTAs in clusters)
@@ -125,6 +125,8 @@ def decode_fusable(ctx, qkv, cache, block_table, n_heads: int, rotary_dim: int) 
     of 8) 0.867 -> 0.881 ms: the kernel of its own was the window in which that many clusters found
     their SMs and fetched their first tiles, so such launches keep it."""
     k_pool = cache.k_pool
+    if window:
+        return False                 # (layers with a sliding window keep the two kernels: not measured, not tested)
     if not (_fuse_rope and _use_mma and not _force_tiled and ctx.batch.max_segment == 1
             and qkv.dtype == torch.bfloat16 and k_pool is not None and k_pool.dtype == torch.bfloat16
             and ctx.precision.act_dtype == torch.bfloat16 and rotary_dim % 16 == 0

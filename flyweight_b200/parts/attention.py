@@ -103,7 +103,7 @@ class GQAttention(Mixer):
         block_table = ctx.batch.block_tables[cache.group]
         from ..kernels import attention as attention_kernels
         rotation = self.position.rotation()
-        if rotation is not None and attention_kernels.decode_fusable(ctx, qkv, cache, block_table, self.n_heads, rotation[1]):
+        if rotation is not None and attention_kernels.decode_fusable(ctx, qkv, cache, block_table, self.n_heads, rotation[1], self.window):
             # a step of single tokens whose position part is a plain rotation: the decode attention
             # kernel norms, turns and stores its own token's heads (one kernel and one pass less)
             table, rotary_dim, pairing = rotation
