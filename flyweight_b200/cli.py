@@ -210,7 +210,15 @@ def _make_random(args) -> int:
 
 
 def main(argv=None) -> int:
-    args = _parser().parse_args(argv)
+    from .engine.loading import NoGpu
+    try:
+        return _run(_parser().parse_args(argv))
+    except NoGpu as error:
+        print(f"flyweight_b200: {error}", file=sys.stderr)
+        return 3
+
+
+def _run(args) -> int:
     if args.command == "generate":
         return _generate(args)
     if args.command == "benchmark":

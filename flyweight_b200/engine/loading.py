@@ -26,8 +26,21 @@ def parse_dtype(dtype) -> Precision:
         raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}") from None
 
 
+class NoGpu(RuntimeError):
+    """The engine was asked for a CUDA device where there is none: it has no other path."""
+
+
+def require_gpu(device) -> None:
+    """One clear error instead of whatever the first CUDA call would say.  (A model may still be
+    put together on ``cpu`` -- the random-weights mode and the tests do -- but nothing runs there.)"""
+    if torch.device(device).type == "cuda" and not torch.cuda.is_available():
+        raise NoGpu("flyweight_b200 runs on an NVIDIA GPU (B200, sm_100a) only and found no CUDA device; "
+                    "there is no CPU path")
+
+
 def load_model(model_dir, dtype="bfloat16", device="cuda:0"):
     """The model that ``config.json`` names, with ``model.safetensors`` bound by name."""
+    require_gpu(device)
     arch, config = load_config(model_dir)
     reconcile = getattr(config, "reconciled_with", None)
     if reconcile is not None:
@@ -48,6 +61,7 @@ def random_model(config: Any, seed: int, dtype="bfloat16", device="cuda:0",
     else:
         arch = lookup(config.architectures[0])
     precision = parse_dtype(dtype)
+    require_gpu(device)
     device = torch.device(device)
     model = arch.model_class(config, precision, device)
     if stored_dtype is None:

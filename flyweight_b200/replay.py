@@ -31,12 +31,16 @@ def build_parser() -> argparse.ArgumentParser:
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     from .cache.manager import PAGE_SIZE
-    from .engine.loading import load_model
+    from .engine.loading import NoGpu, load_model
     from .engine.runner import ModelRunner
 
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
-    model = load_model(args.model, args.dtype, args.device)
+    try:
+        model = load_model(args.model, args.dtype, args.device)
+    except NoGpu as error:
+        print(f"trace_run: {error}", file=sys.stderr)
+        return 3
     num_pages = max(1, args.max_tokens // PAGE_SIZE)
     max_len = min(model.spec.max_positions, num_pages * PAGE_SIZE)
     runner = ModelRunner(model, num_pages=num_pages, num_slots=max(1, args.max_live),

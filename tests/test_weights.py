@@ -111,3 +111,26 @@ def test_baseline_preset_scales():
     assert abs(t["model.layers.1.conv.in_proj.weight"].std().item() - 0.02) < 0.002
     assert abs(t["model.embed_tokens.weight"].std().item() - 0.02) < 0.002
     assert abs(t["model.embedding_norm.weight"].mean().item() - 1.0) < 0.05
+
+
+def test_without_a_gpu_the_entry_points_say_so_in_one_line(tmp_path):
+    """No CPU path: where there is no CUDA device, opening a model says that (and the command line and
+    the trace replay exit with 3) instead of failing somewhere inside the first CUDA call."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from flyweight_b200.engine.loading import NoGpu, load_model, random_model
+    folder = make_model_dir(tmp_path / "m", TINY_A, seed=1)
+    with pytest.raises(NoGpu, match="no CPU path"):
+        load_model(folder, "float32")
+    with pytest.raises(NoGpu, match="no CPU path"):
+        random_model(TINY_A, seed=1)
+    root = Path(__file__).resolve().parent.parent
+    for command in ([sys.executable, "-m", "flyweight_b200", "generate", str(folder), "--prompt", "1,2", "--max-tokens", "2"],
+                    [sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
+                     "--out", str(tmp_path / "out"), "--max-tokens", "64"]):
+        done = subprocess.run(command, cwd=root, capture_output=True, text=True, input="", timeout=120)
+        assert done.returncode == 3, done.stderr[-500:]
+        assert "no CPU path" in done.stderr and "Traceback" not in done.stderr
